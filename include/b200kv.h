@@ -1,0 +1,255 @@
+/*
+ * b200kv.h -- C ABI of the B200-native quantized KV-cache path.
+ *
+ * This is the boundary a MIInfer maintainer binds in place of the HIP operator
+ * layer for the KV path.  The reference has no FFI: its boundary is a set of
+ * C++ free functions with C-compatible arguments
+ * (include/miinfer/qwen3_gpu_primitives.hpp) plus one POD view struct
+ * (include/miinfer/prefill_v2/kv_cache.hpp:24-46).  Every entry point below
+ * names the reference interface it replaces (paths relative to the MIInfer
+ * source tree).
+ *
+ * Conventions
+ *   - Plain pointers and sizes only.  Device pointers unless stated otherwise.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *   - Every function returns a b200kv_status (0 = ok, negative = error); nothing
+ *     aborts the process, reads the environment or allocates device memory in a
+ *     launch call (the reference launchers abort on a bad argument,
+ *     include/miinfer/hip_check.hpp:11-24, and allocate nothing).
+ *   - All launches are asynchronous on `stream`; the caller owns every buffer.
+ *   - There is no CPU fallback: without a usable sm_100 device every launch
+ *     returns B200KV_ERR_DEVICE.
+ */
+#ifndef B200KV_H
+#define B200KV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200KV_VERSION 100 /* 0.1.0 */
+
+#if defined(__GNUC__)
+#define B200KV_API __attribute__((visibility("default")))
+#else
+#define B200KV_API
+#endif
+
+/* OR into `num_splits` to run the generic stage-1 kernel even where a
+ * specialised one exists (testing and A/B measurement). */
+#define B200KV_SPLITS_FORCE_GENERIC 0x80000000u
+
+typedef enum b200kv_status {
+    B200KV_OK = 0,
+    B200KV_ERR_INVALID = -1,     /* null/mismatched argument (reference: hipErrorInvalidValue + abort) */
+    B200KV_ERR_UNSUPPORTED = -2, /* shape or mode this build has no kernel for */
+    B200KV_ERR_CUDA = -3,        /* a CUDA runtime call failed; see b200kv_last_cuda_error */
+    B200KV_ERR_DEVICE = -4,      /* no sm_100 device */
+    B200KV_ERR_WORKSPACE = -5,   /* workspace too small */
+    B200KV_ERR_RANGE = -6,       /* positions beyond the cache capacity */
+    B200KV_ERR_FORMAT = -7,      /* session file: bad magic/version/geometry/checksum */
+    B200KV_ERR_IO = -8,          /* session file: open/read/write failed */
+    B200KV_ERR_MISMATCH = -9     /* session file does not match the requested prefix */
+} b200kv_status;
+
+/* KvCacheQuantMode, include/miinfer/prefill_v2/kv_cache.hpp:16-21 (same values). */
+typedef enum b200kv_quant_mode {
+    B200KV_F16_F16 = 0,
+    B200KV_Q8_F16 = 1, /* int8 K, fp16 V */
+    B200KV_F16_Q8 = 2,
+    B200KV_Q8_Q8 = 3
+} b200kv_quant_mode;
+
+typedef enum b200kv_dtype { B200KV_F16 = 0, B200KV_F32 = 1 } b200kv_dtype;
+
+/* RoPE applied to K inside the append kernel.
+ * NEOX_FULL: pairs (i, i+d/2), frequency powf(theta, -2i/d) -- qwen3_rope_kernel,
+ *   gfx906/kernels/qwen3_primitives.hip:1850-1870.
+ * SECTIONED64: pairs (i, i+32) on dims [0,64), angle position * s^i by successive
+ *   fp32 multiplies with s = powf(theta, -2/64) -- compute_qwen35_rope_pair, .hip:622-659. */
+typedef enum b200kv_rope_mode { B200KV_ROPE_NONE = 0, B200KV_ROPE_NEOX_FULL = 1, B200KV_ROPE_SECTIONED64 = 2 } b200kv_rope_mode;
+
+/*
+ * Non-owning view of one attention layer's KV cache in device memory.
+ * Replaces AttentionKvCacheView (include/miinfer/prefill_v2/kv_cache.hpp:24-46):
+ * same planar pointers, plus `qblock`.  Layout (head-major, as the reference):
+ *   key_f16/value_f16    [kv_heads][capacity][head_dim]            fp16
+ *   key_q8/value_q8      [kv_heads][capacity][head_dim]            int8
+ *   key/value_scales     [kv_heads][capacity][head_dim / qblock]   fp16
+ * qblock == 32 is the q8_0 format (32 int8 + one fp16 scale: 136 B per 128-wide
+ * head row); qblock == head_dim is the reference's one-scale-per-row format.
+ * All plane base pointers must be 16-byte aligned.
+ */
+typedef struct b200kv_view {
+    void* key_f16;
+    void* value_f16;
+    int8_t* key_q8;
+    void* key_scales;
+    int8_t* value_q8;
+    void* value_scales;
+    uint64_t capacity;  /* positions per head */
+    uint32_t kv_heads;
+    uint32_t head_dim;  /* 128 or 256 */
+    uint32_t qblock;    /* 32 or head_dim */
+    uint32_t quant_mode; /* b200kv_quant_mode */
+} b200kv_view;
+
+/* Device-resident step state so a captured graph replays with new positions.
+ * Same layout as DeviceDecodeState / DevicePrefillState,
+ * include/miinfer/qwen3_gpu_primitives.hpp:30-45 (64-byte aligned, 64 bytes). */
+typedef struct b200kv_decode_state {
+    uint32_t current_token, position, generated, stop, max_generated;
+    uint32_t pad_[11];
+} b200kv_decode_state;
+typedef struct b200kv_prefill_state {
+    uint32_t base_position, token_count, total_length, kv_capacity;
+    uint32_t pad_[12];
+} b200kv_prefill_state;
+
+/* ---- library / device ------------------------------------------------------ */
+
+B200KV_API int b200kv_version(void);
+B200KV_API const char* b200kv_status_string(int status);
+/* Text of the last CUDA error seen by this thread's calls (empty if none). */
+B200KV_API const char* b200kv_last_cuda_error(void);
+/* sm_100 guard; replaces validate_device (src/device_validation.cpp:60-95), which accepts gfx906 only. */
+B200KV_API int b200kv_device_check(int device);
+
+/* ---- cache storage ---------------------------------------------------------
+ * Replaces class AttentionLayerKvCacheStorage (kv_cache.hpp:49-122,
+ * src/prefill_v2/kv_cache.cpp:10-130): owns the 2-4 device planes of one layer. */
+typedef struct b200kv_cache b200kv_cache;
+
+/* key_bytes()+value_bytes() for a geometry, kv_cache.hpp:88-106 (scale bytes generalised to 2*head_dim/qblock per row). */
+B200KV_API size_t b200kv_cache_bytes(uint64_t capacity, uint32_t kv_heads, uint32_t head_dim, uint32_t qblock, uint32_t quant_mode);
+/* ctor, kv_cache.cpp:10-39: allocates on the current device and zero-fills.  capacity 0 -> B200KV_ERR_INVALID (the ctor throws). */
+B200KV_API int b200kv_cache_create(b200kv_cache** out, uint64_t capacity, uint32_t kv_heads, uint32_t head_dim,
+                        uint32_t qblock, uint32_t quant_mode);
+/* dtor, kv_cache.cpp:41-67. */
+B200KV_API int b200kv_cache_destroy(b200kv_cache* cache);
+/* reset(stream), kv_cache.cpp:99-130: zero every plane, asynchronously on `stream`. */
+B200KV_API int b200kv_cache_reset(b200kv_cache* cache, void* stream);
+/* view(), kv_cache.hpp:68-81. */
+B200KV_API int b200kv_cache_view(const b200kv_cache* cache, b200kv_view* out);
+
+/* ---- append ----------------------------------------------------------------
+ * Replaces launch_qwen35_decoupled_k_norm_rope_kv_store_batch_quant
+ * (include/miinfer/qwen3_gpu_primitives.hpp:695-716; kernel
+ * gfx906/kernels/qwen3_primitives.hip:7213-7326).
+ * key/value: [token][kv_heads*head_dim] of `dtype`.  k_norm_weight (fp32
+ * [head_dim]) may be NULL = no K RMSNorm (the reference requires it).  Token t
+ * goes to position base_position + t; a non-NULL prefill_state (base_position,
+ * token_count, kv_capacity>0 overrides capacity) or decode_state (position,
+ * one token) is read ON THE DEVICE instead, exactly as the reference kernel does
+ * (.hip:7235-7242) -- in that case `token_count` is the launch bound (rows beyond
+ * the device-side count are skipped).  Quantizer: per qblock scale = amax/127
+ * (1 if amax==0), inv = 1/scale, q = clamp(rint_half_even(x*inv), -128, 127),
+ * scale stored as fp16 round-to-nearest (.hip:7285-7300). */
+B200KV_API int b200kv_append(const b200kv_view* view, const void* key, const void* value, int dtype,
+                  const float* k_norm_weight, int rope_mode, float theta, float epsilon,
+                  uint32_t token_count, uint32_t base_position,
+                  const b200kv_prefill_state* prefill_state, const b200kv_decode_state* decode_state,
+                  void* stream);
+
+/* ---- decode attention ------------------------------------------------------- */
+
+/* Workspace bytes for the split-K partials of one decode launch over
+ * `sessions` sessions.  The reference keeps these in file-scope __device__
+ * arrays sized for 24 heads (.hip:2104-2113); here the caller owns them. */
+B200KV_API size_t b200kv_decode_workspace_bytes(uint32_t query_heads, uint32_t head_dim, uint32_t sessions);
+
+/* Replaces launch_qwen35_tiled_online_attention_quant_dynamic
+ * (qwen3_gpu_primitives.hpp:719-739; kernels .hip:7371-7485 and 2295-2352).
+ * One query token per session: q [query_heads][head_dim] of q_dtype; attends
+ * positions [0, cache_length), or [0, decode_state->position + 1) read on the
+ * device when decode_state != NULL (.hip:7394-7395).  output (ungated) and
+ * gated_output (= output * sigmoid(gate), gate fp32 [query_heads][head_dim]) are
+ * fp32 [query_heads][head_dim]; at least one must be non-NULL; gate may be NULL
+ * (then gated_output == output).  num_splits 0 = choose for the device.
+ * The reference's gated_output_q8 (Q8_1 re-quantised output) is not provided. */
+B200KV_API int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
+                       float* output, float* gated_output, uint32_t query_heads, float scale,
+                       uint32_t cache_length, const b200kv_decode_state* decode_state,
+                       void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream);
+
+/* Batched decode over `sessions` independent caches of one geometry (no
+ * counterpart in the reference, which keeps one session resident,
+ * tools/miinfer_cli.cpp:5663-5676).  views: HOST array of `sessions` views
+ * (same head_dim, kv_heads, qblock, quant_mode; capacities may differ);
+ * lengths: DEVICE array of `sessions` uint32 cache lengths; max_length: host
+ * upper bound of those lengths (sizes the launch).  q/gate/output/gated_output:
+ * [sessions][query_heads][head_dim].  view_table: DEVICE scratch of
+ * sessions*sizeof(b200kv_view) bytes that this call fills (it may be reused
+ * across calls with the same views by passing views == NULL). */
+B200KV_API int b200kv_decode_attn_batched(const b200kv_view* views, void* view_table, const uint32_t* lengths,
+                               uint32_t sessions, uint32_t max_length, const void* q, int q_dtype,
+                               const float* gate, float* output, float* gated_output,
+                               uint32_t query_heads, float scale, void* workspace, size_t workspace_bytes,
+                               uint32_t num_splits, void* stream);
+
+/* Sequence-sharded decode, stage 1 only: online-softmax partials of this
+ * shard's positions [range_begin, range_end) reduced over the local splits to
+ * ONE (m, l, acc) per query head: part_m/part_l fp32 [query_heads], part_acc
+ * fp32 [query_heads][head_dim] (acc unnormalised, relative to m).  The stage-1
+ * arithmetic of .hip:7371-7485 restricted to a position range. */
+B200KV_API int b200kv_decode_partials(const b200kv_view* view, const void* q, int q_dtype, uint32_t query_heads,
+                           float scale, uint32_t range_begin, uint32_t range_end,
+                           float* part_m, float* part_l, float* part_acc,
+                           void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream);
+
+/* Log-sum-exp combine of `num_parts` partials laid out [part][query_heads]
+ * (m, l) and [part][query_heads][head_dim] (acc).  Replaces
+ * qwen3_splitk_stage2_kernel (.hip:2295-2352); with one part per GPU it is the
+ * cross-GPU merge of sequence-sharded decode.  Empty parts (l <= 0 or
+ * non-finite m) are skipped as in .hip:6681,6701. */
+B200KV_API int b200kv_merge_partials(const float* part_m, const float* part_l, const float* part_acc,
+                          uint32_t num_parts, uint32_t query_heads, uint32_t head_dim,
+                          const float* gate, float* output, float* gated_output, void* stream);
+
+/* ---- suffix / prefill attention -------------------------------------------- */
+
+B200KV_API size_t b200kv_prefill_workspace_bytes(uint32_t token_count, uint32_t query_heads, uint32_t head_dim);
+
+/* Replaces launch_qwen35_splitk_suffix_attention_quant
+ * (qwen3_gpu_primitives.hpp:670-692; kernels .hip:6788-7119 and 6637-6725).
+ * q, gate, gated_output: [token][query_heads][head_dim] (q of q_dtype, the
+ * others fp32; gate may be NULL).  Query token t attends cache positions
+ * [0, base_position + t + 1): the chunk must already have been appended.  A
+ * non-NULL prefill_state overrides base_position/token_count on the device
+ * (.hip:6810-6814).  Tokens whose causal length exceeds the capacity get a
+ * zero row (the reference leaves them unwritten, .hip:6830). */
+B200KV_API int b200kv_prefill_attn(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
+                        float* gated_output, uint32_t token_count, uint32_t base_position,
+                        uint32_t query_heads, float scale, const b200kv_prefill_state* prefill_state,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- prefix snapshot / restore ---------------------------------------------
+ * Raw compact layout of AttentionLayerKvCacheStorage::download_raw/upload_raw
+ * (src/prefill_v2/kv_cache.cpp:214-369): K first -- per kv head the int8 slice
+ * of `tokens` rows followed by its scale slice (or the fp16 slice) -- then V the
+ * same way; capacity-strided rows are compacted to `tokens`. */
+B200KV_API size_t b200kv_snapshot_bytes(const b200kv_view* view, uint64_t tokens);
+/* dst/src may be device memory or (pinned or pageable) host memory; the copies
+ * are issued on `stream` and, like the reference with a non-null stream
+ * (src/prefill_v2/persistent_session.cpp:112-114), NOT synchronised. */
+B200KV_API int b200kv_snapshot_save(const b200kv_view* view, uint64_t tokens, void* dst, void* stream);
+B200KV_API int b200kv_snapshot_restore(const b200kv_view* view, uint64_t tokens, const void* src, void* stream);
+/* Device-to-device copy of the first `tokens` positions of src into dst (both
+ * caches of one geometry; capacities may differ): one kernel launch.  The
+ * in-VRAM counterpart of copy_session_checkpoint/restore_session_checkpoint,
+ * tools/miinfer_cli.cpp:1248-1317. */
+B200KV_API int b200kv_snapshot_clone(const b200kv_view* dst, const b200kv_view* src, uint64_t tokens, void* stream);
+
+/* ---- prefix identity and the on-disk session (host side) -------------------- */
+
+/* 64-bit FNV-1a-style hash, one xor+multiply round per token id (not per byte):
+ * compute_token_sequence_hash, include/miinfer/prefill_v2/reusable_context.hpp:38-45. */
+B200KV_API uint64_t b200kv_token_sequence_hash(const uint32_t* tokens, size_t count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200KV_H */

@@ -1,0 +1,83 @@
+"""ctypes binding of libb200kv.so (the C ABI declared in include/b200kv.h).
+
+The library is the product; this module only loads it.  There is no fallback:
+if the shared object is missing or a symbol is absent, importing fails.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libb200kv.so"
+
+
+class View(C.Structure):
+    """b200kv_view (include/b200kv.h); mirrors MIInfer's AttentionKvCacheView,
+    include/miinfer/prefill_v2/kv_cache.hpp:24-46."""
+
+    _fields_ = [
+        ("key_f16", C.c_void_p), ("value_f16", C.c_void_p),
+        ("key_q8", C.c_void_p), ("key_scales", C.c_void_p),
+        ("value_q8", C.c_void_p), ("value_scales", C.c_void_p),
+        ("capacity", C.c_uint64), ("kv_heads", C.c_uint32), ("head_dim", C.c_uint32),
+        ("qblock", C.c_uint32), ("quant_mode", C.c_uint32),
+    ]
+
+
+u32, u64, sz, vp, fl, i32 = C.c_uint32, C.c_uint64, C.c_size_t, C.c_void_p, C.c_float, C.c_int
+VP = C.POINTER(View)
+
+# name -> (restype, argtypes); one entry per declaration in include/b200kv.h
+SIGNATURES = {
+    "b200kv_version": (i32, []),
+    "b200kv_status_string": (C.c_char_p, [i32]),
+    "b200kv_last_cuda_error": (C.c_char_p, []),
+    "b200kv_device_check": (i32, [i32]),
+    "b200kv_cache_bytes": (sz, [u64, u32, u32, u32, u32]),
+    "b200kv_cache_create": (i32, [C.POINTER(vp), u64, u32, u32, u32, u32]),
+    "b200kv_cache_destroy": (i32, [vp]),
+    "b200kv_cache_reset": (i32, [vp, vp]),
+    "b200kv_cache_view": (i32, [vp, VP]),
+    "b200kv_append": (i32, [VP, vp, vp, i32, vp, i32, fl, fl, u32, u32, vp, vp, vp]),
+    "b200kv_decode_workspace_bytes": (sz, [u32, u32, u32]),
+    "b200kv_decode_attn": (i32, [VP, vp, i32, vp, vp, vp, u32, fl, u32, vp, vp, sz, u32, vp]),
+    "b200kv_decode_attn_batched": (i32, [VP, vp, vp, u32, u32, vp, i32, vp, vp, vp, u32, fl, vp, sz, u32, vp]),
+    "b200kv_decode_partials": (i32, [VP, vp, i32, u32, fl, u32, u32, vp, vp, vp, vp, sz, u32, vp]),
+    "b200kv_merge_partials": (i32, [vp, vp, vp, u32, u32, u32, vp, vp, vp, vp]),
+    "b200kv_prefill_workspace_bytes": (sz, [u32, u32, u32]),
+    "b200kv_prefill_attn": (i32, [VP, vp, i32, vp, vp, u32, u32, u32, fl, vp, vp, sz, vp]),
+    "b200kv_snapshot_bytes": (sz, [VP, u64]),
+    "b200kv_snapshot_save": (i32, [VP, u64, vp, vp]),
+    "b200kv_snapshot_restore": (i32, [VP, u64, vp, vp]),
+    "b200kv_snapshot_clone": (i32, [VP, VP, u64, vp]),
+    "b200kv_token_sequence_hash": (u64, [C.POINTER(u32), sz]),
+}
+
+
+def load() -> C.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m miinfer_b200.build` "
+            "(there is no CPU or PyTorch fallback for the KV path)")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+lib = load()
+
+
+class B200KvError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        text = lib.b200kv_status_string(status).decode()
+        detail = lib.b200kv_last_cuda_error().decode() if status == -3 else ""
+        super().__init__(f"{where}: {text} ({status}){' — ' + detail if detail else ''}")
+
+
+def check(status: int, where: str) -> None:
+    if status != 0:
+        raise B200KvError(status, where)

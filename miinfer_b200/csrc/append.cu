@@ -1,0 +1,233 @@
+// Fused KV append: (optional K RMSNorm) -> RoPE on K -> int8 quantization with
+// fp16 block scales (or fp16 passthrough) -> cache write, for K and V of every
+// (token, kv_head) row in one launch.
+//
+// Behaviour follows MIInfer's store kernel
+// (gfx906/kernels/qwen3_primitives.hip:7213-7326): same operation order, same
+// quantizer, positions optionally read from device-resident state.  The mapping
+// is new: one warp owns one row, lane L holds elements L, L+32, L+64, ... so
+//   - a q8_0 block (32 consecutive dims) is one register index across the warp
+//     and its amax is a single warp reduction;
+//   - both RoPE pairings (i, i+d/2) and (i, i+32) pair two registers of the SAME
+//     lane, so the rotation needs no exchange;
+//   - the reference's shared-memory binary tree for the sum of squares (stride
+//     d/2 .. 1) becomes register adds followed by a shuffle-down tree that adds
+//     exactly the same pairs in the same order (bit-identical sum).
+// Rows are staged through shared memory so the cache is written with one 4- or
+// 8-byte store per lane (a full 128/256-byte line per row).
+#include "kv_common.cuh"
+
+#include <cmath>
+
+namespace b200kv {
+
+struct AppendParams {
+    b200kv_view view;
+    const void* key;
+    const void* value;
+    const float* k_norm_weight;
+    const b200kv_prefill_state* prefill_state;
+    const b200kv_decode_state* decode_state;
+    uint32_t token_count;
+    uint32_t base_position;
+    int rope_mode;
+    float epsilon;
+    float sectioned_step;    // powf(theta, -2/64)
+    float inv_freq[128];     // NeoX: powf(theta, -2i/d), i < d/2
+};
+
+constexpr int kAppendWarps = 4;
+
+template <int NJ>
+__device__ __forceinline__ void quantize_and_stage(const float (&x)[NJ], uint32_t qblock_is_row, int lane,
+                                                   int8_t* stage, __half* scale_dst) {
+    float scale[NJ];
+    if (qblock_is_row) {
+        float amax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) amax = fmaxf(amax, fabsf(x[j]));
+        amax = warp_max(amax);
+        const float s = (amax > 0.0f) ? __fdiv_rn(amax, 127.0f) : 1.0f;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) scale[j] = s;
+        if (lane == 0) scale_dst[0] = __float2half_rn(s);
+    } else {
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+            const float amax = warp_max(fabsf(x[j]));
+            scale[j] = (amax > 0.0f) ? __fdiv_rn(amax, 127.0f) : 1.0f;
+        }
+        // lane j stores the scale of block j (NJ <= 8 lanes take part)
+#pragma unroll
+        for (int j = 0; j < NJ; ++j)
+            if (lane == j) scale_dst[j] = __float2half_rn(scale[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        const float inv = (scale[j] > 0.0f) ? __fdiv_rn(1.0f, scale[j]) : 1.0f;
+        int q = __float2int_rn(__fmul_rn(x[j], inv));
+        q = max(-128, min(127, q));
+        stage[lane + 32 * j] = static_cast<int8_t>(q);
+    }
+}
+
+template <int D, bool IN_F16>
+__global__ void __launch_bounds__(kAppendWarps * 32)
+append_kernel(const __grid_constant__ AppendParams p) {
+    constexpr int NJ = D / 32;
+    __shared__ __align__(16) int8_t stage[kAppendWarps][2][D];
+
+    uint32_t base_position = p.base_position;
+    uint32_t token_count = p.token_count;
+    uint64_t capacity = p.view.capacity;
+    if (p.prefill_state != nullptr) {
+        base_position = p.prefill_state->base_position;
+        token_count = min(token_count, p.prefill_state->token_count);
+        if (p.prefill_state->kv_capacity > 0) capacity = p.prefill_state->kv_capacity;
+    } else if (p.decode_state != nullptr) {
+        base_position = p.decode_state->position;
+        token_count = min(token_count, 1u);
+    }
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t H = p.view.kv_heads;
+    const uint64_t row = static_cast<uint64_t>(blockIdx.x) * kAppendWarps + warp;
+    if (row >= static_cast<uint64_t>(token_count) * H) return;
+    const uint32_t token = static_cast<uint32_t>(row / H), head = static_cast<uint32_t>(row % H);
+    const uint64_t position = static_cast<uint64_t>(base_position) + token;
+    if (position >= capacity) return;  // never write outside the cache
+
+    const size_t in_base = (static_cast<size_t>(token) * H + head) * D;
+    float k[NJ], v[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        if (IN_F16) {
+            k[j] = __half2float(static_cast<const __half*>(p.key)[in_base + lane + 32 * j]);
+            v[j] = __half2float(static_cast<const __half*>(p.value)[in_base + lane + 32 * j]);
+        } else {
+            k[j] = static_cast<const float*>(p.key)[in_base + lane + 32 * j];
+            v[j] = static_cast<const float*>(p.value)[in_base + lane + 32 * j];
+        }
+    }
+
+    if (p.k_norm_weight != nullptr) {
+        float sq[NJ];
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) sq[j] = __fmul_rn(k[j], k[j]);
+#pragma unroll
+        for (int half = NJ / 2; half >= 1; half >>= 1)
+#pragma unroll
+            for (int j = 0; j < half; ++j) sq[j] = __fadd_rn(sq[j], sq[j + half]);
+        float ss = sq[0];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, o));
+        ss = __shfl_sync(0xffffffffu, ss, 0);
+        const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(D)), p.epsilon)));
+#pragma unroll
+        for (int j = 0; j < NJ; ++j)
+            k[j] = __fmul_rn(__fmul_rn(k[j], r), p.k_norm_weight[lane + 32 * j]);
+    }
+
+    if (p.rope_mode == B200KV_ROPE_NEOX_FULL) {
+#pragma unroll
+        for (int j = 0; j < NJ / 2; ++j) {
+            const float angle = __fmul_rn(static_cast<float>(static_cast<uint32_t>(position)), p.inv_freq[lane + 32 * j]);
+            float s, c;
+            sincos_pinned(angle, &s, &c);
+            const float x0 = k[j], x1 = k[j + NJ / 2];
+            k[j] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+            k[j + NJ / 2] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+        }
+    } else if (p.rope_mode == B200KV_ROPE_SECTIONED64) {
+        float angle = static_cast<float>(static_cast<uint32_t>(position));
+        for (int i = 0; i < lane; ++i) angle = __fmul_rn(angle, p.sectioned_step);
+        float s, c;
+        sincos_pinned(angle, &s, &c);
+        const float x0 = k[0], x1 = k[1];
+        k[0] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+        k[1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+    }
+
+    const uint32_t mode = p.view.quant_mode;
+    const bool k_q8 = (mode == B200KV_Q8_F16 || mode == B200KV_Q8_Q8);
+    const bool v_q8 = (mode == B200KV_F16_Q8 || mode == B200KV_Q8_Q8);
+    const uint32_t nblk = D / p.view.qblock;
+    const size_t row_index = static_cast<size_t>(head) * capacity + position;
+
+    if (k_q8) quantize_and_stage<NJ>(k, nblk == 1, lane, stage[warp][0],
+                                     static_cast<__half*>(p.view.key_scales) + row_index * nblk);
+    if (v_q8) quantize_and_stage<NJ>(v, nblk == 1, lane, stage[warp][1],
+                                     static_cast<__half*>(p.view.value_scales) + row_index * nblk);
+    __syncwarp();
+    using word_t = typename std::conditional<D == 128, uint32_t, uint2>::type;
+    if (k_q8) {
+        reinterpret_cast<word_t*>(p.view.key_q8 + row_index * D)[lane] = reinterpret_cast<const word_t*>(stage[warp][0])[lane];
+    } else {
+        __half* dst = static_cast<__half*>(p.view.key_f16) + row_index * D;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) dst[lane + 32 * j] = __float2half_rn(k[j]);
+    }
+    if (v_q8) {
+        reinterpret_cast<word_t*>(p.view.value_q8 + row_index * D)[lane] = reinterpret_cast<const word_t*>(stage[warp][1])[lane];
+    } else {
+        __half* dst = static_cast<__half*>(p.view.value_f16) + row_index * D;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) dst[lane + 32 * j] = __float2half_rn(v[j]);
+    }
+}
+
+}  // namespace b200kv
+
+using namespace b200kv;
+
+extern "C" int b200kv_append(const b200kv_view* view, const void* key, const void* value, int dtype,
+                             const float* k_norm_weight, int rope_mode, float theta, float epsilon,
+                             uint32_t token_count, uint32_t base_position,
+                             const b200kv_prefill_state* prefill_state, const b200kv_decode_state* decode_state,
+                             void* stream) {
+    int rc = validate_view(view);
+    if (rc != B200KV_OK) return rc;
+    if (key == nullptr || value == nullptr || (dtype != B200KV_F16 && dtype != B200KV_F32)) return B200KV_ERR_INVALID;
+    if (rope_mode < B200KV_ROPE_NONE || rope_mode > B200KV_ROPE_SECTIONED64) return B200KV_ERR_INVALID;
+    if (!std::isfinite(theta) || !std::isfinite(epsilon)) return B200KV_ERR_INVALID;
+    if (rope_mode != B200KV_ROPE_NONE && !(theta > 0.0f)) return B200KV_ERR_INVALID;
+    if (token_count == 0) return B200KV_OK;
+    if (prefill_state == nullptr && decode_state == nullptr &&
+        static_cast<uint64_t>(base_position) + token_count > view->capacity)
+        return B200KV_ERR_RANGE;
+    rc = ensure_device();
+    if (rc != B200KV_OK) return rc;
+
+    AppendParams p{};
+    p.view = *view;
+    p.key = key;
+    p.value = value;
+    p.k_norm_weight = k_norm_weight;
+    p.prefill_state = prefill_state;
+    p.decode_state = decode_state;
+    p.token_count = token_count;
+    p.base_position = base_position;
+    p.rope_mode = rope_mode;
+    p.epsilon = epsilon;
+    if (rope_mode == B200KV_ROPE_NEOX_FULL) {
+        const uint32_t d = view->head_dim;
+        for (uint32_t i = 0; i < d / 2; ++i)
+            p.inv_freq[i] = std::pow(theta, -static_cast<float>(2 * i) / static_cast<float>(d));
+    } else if (rope_mode == B200KV_ROPE_SECTIONED64) {
+        p.sectioned_step = std::pow(theta, -2.0f / 64.0f);
+    }
+
+    const uint64_t rows = static_cast<uint64_t>(token_count) * view->kv_heads;
+    const unsigned grid = static_cast<unsigned>((rows + kAppendWarps - 1) / kAppendWarps);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool f16 = (dtype == B200KV_F16);
+    if (view->head_dim == 128) {
+        if (f16) append_kernel<128, true><<<grid, kAppendWarps * 32, 0, s>>>(p);
+        else append_kernel<128, false><<<grid, kAppendWarps * 32, 0, s>>>(p);
+    } else {
+        if (f16) append_kernel<256, true><<<grid, kAppendWarps * 32, 0, s>>>(p);
+        else append_kernel<256, false><<<grid, kAppendWarps * 32, 0, s>>>(p);
+    }
+    B200KV_CUDA_TRY(cudaGetLastError());
+    return B200KV_OK;
+}

@@ -1,0 +1,381 @@
+// Split-K GQA decode attention: entry points, the log-sum-exp merge kernel and
+// the generic stage-1 kernel that covers every cache mode (fp16 or int8 K/V,
+// block or row scales).  The specialised int8 streaming kernel lives in
+// decode_q8.cu and is preferred whenever it supports the geometry.
+//
+// Stage-1 arithmetic follows MIInfer's decode kernel
+// (gfx906/kernels/qwen3_primitives.hip:7371-7485) with the per-row scale
+// generalised to per-block scales; the merge follows its stage 2
+// (.hip:2295-2352).  Unlike the reference the partials live in a caller-owned
+// workspace, not in file-scope device arrays (.hip:2111-2113), so launches on
+// different streams do not interfere.
+#include "decode_common.cuh"
+
+#include <cmath>
+
+namespace b200kv {
+
+// ---------------------------------------------------------------------------
+// Generic stage 1: one warp per (query head, split, session); lane L owns the
+// D/32 consecutive dims starting at L*D/32.
+// ---------------------------------------------------------------------------
+template <int D, bool K_Q8, bool V_Q8>
+__global__ void __launch_bounds__(32) decode_generic_kernel(const __grid_constant__ DecodeParams p) {
+    constexpr int E = D / 32;
+    const uint32_t head = blockIdx.x, split = blockIdx.y, session = blockIdx.z;
+    const int lane = threadIdx.x;
+    const b200kv_view& view = session_view(p, session);
+    uint32_t begin, end;
+    resolve_range(p, session, view, &begin, &end);
+    const uint32_t per = (end - begin + p.num_splits - 1) / p.num_splits;
+    const uint32_t pos0 = begin + split * per;
+    const uint32_t pos1 = min(pos0 + per, end);
+    const uint32_t kv_head = head / (p.query_heads / view.kv_heads);
+    const uint32_t nblk = D / view.qblock;
+    const uint32_t blk = (nblk == 1) ? 0u : static_cast<uint32_t>(lane * E) / 32u;
+
+    float q[E];
+    const size_t q_base = (static_cast<size_t>(session) * p.query_heads + head) * D + lane * E;
+#pragma unroll
+    for (int i = 0; i < E; ++i)
+        q[i] = p.q_is_f16 ? __half2float(static_cast<const __half*>(p.q)[q_base + i])
+                          : static_cast<const float*>(p.q)[q_base + i];
+
+    float acc[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) acc[i] = 0.0f;
+    float m = -INFINITY, l = 0.0f;
+
+    const size_t head_row0 = static_cast<size_t>(kv_head) * view.capacity;
+    for (uint32_t pos = pos0; pos < pos1; ++pos) {
+        const size_t row = head_row0 + pos;
+        float kf[E], vf[E];
+        float ks = 1.0f, vs = 1.0f;
+        if (K_Q8) {
+            const int8_t* src = view.key_q8 + row * D + lane * E;
+#pragma unroll
+            for (int w = 0; w < E / 4; ++w) {
+                const uint32_t raw = reinterpret_cast<const uint32_t*>(src)[w];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) kf[w * 4 + b] = static_cast<float>(static_cast<int8_t>(raw >> (8 * b)));
+            }
+            ks = __half2float(static_cast<const __half*>(view.key_scales)[row * nblk + blk]);
+        } else {
+            const __half* src = static_cast<const __half*>(view.key_f16) + row * D + lane * E;
+#pragma unroll
+            for (int i = 0; i < E; ++i) kf[i] = __half2float(src[i]);
+        }
+        float prod = 0.0f;
+#pragma unroll
+        for (int i = 0; i < E; ++i) prod = fmaf(q[i], kf[i], prod);
+        const float dot = warp_sum(prod * ks) * p.scale;
+
+        const float m_new = fmaxf(m, dot);
+        const float alpha = __expf(m - m_new);  // m == -inf on the first position: exp(-inf) = 0
+        const float weight = __expf(dot - m_new);
+        l = l * alpha + weight;
+        m = m_new;
+
+        if (V_Q8) {
+            const int8_t* src = view.value_q8 + row * D + lane * E;
+#pragma unroll
+            for (int w = 0; w < E / 4; ++w) {
+                const uint32_t raw = reinterpret_cast<const uint32_t*>(src)[w];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) vf[w * 4 + b] = static_cast<float>(static_cast<int8_t>(raw >> (8 * b)));
+            }
+            vs = __half2float(static_cast<const __half*>(view.value_scales)[row * nblk + blk]);
+        } else {
+            const __half* src = static_cast<const __half*>(view.value_f16) + row * D + lane * E;
+#pragma unroll
+            for (int i = 0; i < E; ++i) vf[i] = __half2float(src[i]);
+        }
+        const float ew = weight * vs;
+#pragma unroll
+        for (int i = 0; i < E; ++i) acc[i] = fmaf(acc[i], alpha, ew * vf[i]);
+    }
+
+    const size_t slot = (static_cast<size_t>(session) * p.num_splits + split) * p.query_heads + head;
+#pragma unroll
+    for (int i = 0; i < E; ++i) p.ws_acc[slot * D + lane * E + i] = acc[i];
+    if (lane == 0) {
+        p.ws_m[slot] = m;
+        p.ws_l[slot] = l;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Merge (stage 2): one block per (head, group), one thread per dim.
+// ---------------------------------------------------------------------------
+__global__ void merge_kernel(const __grid_constant__ MergeParams p) {
+    const uint32_t head = blockIdx.x, group = blockIdx.y, dim = threadIdx.x;
+    const uint32_t H = p.query_heads, D = p.head_dim;
+    const size_t base = static_cast<size_t>(group) * p.num_parts * H + head;
+    float gmax = -INFINITY;
+    for (uint32_t s = 0; s < p.num_parts; ++s) {
+        const float m = p.part_m[base + static_cast<size_t>(s) * H];
+        const float l = p.part_l[base + static_cast<size_t>(s) * H];
+        if (l > 0.0f && isfinite(m)) gmax = fmaxf(gmax, m);
+    }
+    float gsum = 0.0f, total = 0.0f;
+    for (uint32_t s = 0; s < p.num_parts; ++s) {
+        const size_t idx = base + static_cast<size_t>(s) * H;
+        const float m = p.part_m[idx], l = p.part_l[idx];
+        if (l > 0.0f && isfinite(m)) {
+            const float a = __expf(m - gmax);
+            gsum = fmaf(l, a, gsum);
+            total = fmaf(p.part_acc[idx * D + dim], a, total);
+        }
+    }
+    const size_t out_idx = (static_cast<size_t>(group) * H + head) * D + dim;
+    if (p.out_m != nullptr) {
+        p.out_acc[out_idx] = total;
+        if (dim == 0) {
+            p.out_m[static_cast<size_t>(group) * H + head] = gmax;
+            p.out_l[static_cast<size_t>(group) * H + head] = gsum;
+        }
+        return;
+    }
+    const float o = gsum > 0.0f ? total / gsum : 0.0f;
+    if (p.output != nullptr) p.output[out_idx] = o;
+    if (p.gated_output != nullptr) {
+        float g = o;
+        if (p.gate != nullptr) g = o * (1.0f / (1.0f + __expf(-p.gate[out_idx])));
+        p.gated_output[out_idx] = g;
+    }
+}
+
+int launch_merge(const MergeParams& p, uint32_t groups, cudaStream_t stream) {
+    merge_kernel<<<dim3(p.query_heads, groups), p.head_dim, 0, stream>>>(p);
+    B200KV_CUDA_TRY(cudaGetLastError());
+    return B200KV_OK;
+}
+
+static uint32_t pick_splits_generic(uint32_t query_heads, uint32_t sessions, uint32_t max_length) {
+    // one warp per (head, split, session): aim at ~16 warps per SM on 148 SMs
+    uint32_t want = (148u * 16u + query_heads * sessions - 1) / (query_heads * sessions);
+    uint32_t by_length = (max_length + 63) / 64;  // at least 64 positions per split
+    uint32_t s = want < by_length ? want : by_length;
+    const uint32_t cap = max_splits_per_session(sessions);
+    if (s > cap) s = cap;
+    return s ? s : 1;
+}
+
+template <int D>
+static void launch_generic(const DecodeParams& p, uint32_t mode, dim3 grid, cudaStream_t s) {
+    switch (mode) {
+        case B200KV_F16_F16: decode_generic_kernel<D, false, false><<<grid, 32, 0, s>>>(p); break;
+        case B200KV_Q8_F16: decode_generic_kernel<D, true, false><<<grid, 32, 0, s>>>(p); break;
+        case B200KV_F16_Q8: decode_generic_kernel<D, false, true><<<grid, 32, 0, s>>>(p); break;
+        default: decode_generic_kernel<D, true, true><<<grid, 32, 0, s>>>(p); break;
+    }
+}
+
+// Runs stage 1 (fast kernel if available, else generic) into the workspace.
+// `force_generic` is a debugging/testing switch carried in the top bit of num_splits.
+int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, void* workspace,
+                      size_t workspace_bytes, uint32_t num_splits_arg, cudaStream_t stream) {
+    const bool force_generic = (num_splits_arg & 0x80000000u) != 0;
+    uint32_t num_splits = num_splits_arg & 0x7fffffffu;
+    const uint32_t cap = max_splits_per_session(p.sessions);
+    const bool q8q8 = geometry.quant_mode == B200KV_Q8_Q8;
+    bool use_fast = q8q8 && !force_generic;
+    if (num_splits == 0) {
+        uint32_t fast = use_fast ? pick_splits_q8(geometry, p.query_heads, p.sessions, max_length) : 0;
+        if (fast == 0) use_fast = false;
+        num_splits = use_fast ? fast : pick_splits_generic(p.query_heads, p.sessions, max_length);
+    }
+    if (num_splits > cap) num_splits = cap;
+    const size_t slots = static_cast<size_t>(p.sessions) * num_splits * p.query_heads;
+    const size_t need = slots * (geometry.head_dim + 2u) * sizeof(float);
+    if (workspace == nullptr || workspace_bytes < need) return B200KV_ERR_WORKSPACE;
+    p.num_splits = num_splits;
+    p.ws_m = static_cast<float*>(workspace);
+    p.ws_l = p.ws_m + slots;
+    p.ws_acc = p.ws_l + slots;
+    if (use_fast) {
+        int rc = launch_decode_q8(p, geometry, max_length, stream);
+        if (rc != B200KV_ERR_UNSUPPORTED) return rc;
+    }
+    dim3 grid(p.query_heads, num_splits, p.sessions);
+    if (geometry.head_dim == 128) launch_generic<128>(p, geometry.quant_mode, grid, stream);
+    else launch_generic<256>(p, geometry.quant_mode, grid, stream);
+    B200KV_CUDA_TRY(cudaGetLastError());
+    return B200KV_OK;
+}
+
+static int check_heads(const b200kv_view* view, uint32_t query_heads, float scale) {
+    if (query_heads == 0 || query_heads % view->kv_heads != 0 || !std::isfinite(scale)) return B200KV_ERR_INVALID;
+    if (query_heads / view->kv_heads > 8) return B200KV_ERR_UNSUPPORTED;
+    return B200KV_OK;
+}
+
+}  // namespace b200kv
+
+using namespace b200kv;
+
+extern "C" {
+
+size_t b200kv_decode_workspace_bytes(uint32_t query_heads, uint32_t head_dim, uint32_t sessions) {
+    if (sessions == 0) sessions = 1;
+    const size_t slots = static_cast<size_t>(sessions) * max_splits_per_session(sessions) * query_heads;
+    return slots * (head_dim + 2u) * sizeof(float);
+}
+
+int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
+                       float* output, float* gated_output, uint32_t query_heads, float scale,
+                       uint32_t cache_length, const b200kv_decode_state* decode_state,
+                       void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream) {
+    int rc = validate_view(view);
+    if (rc != B200KV_OK) return rc;
+    if (q == nullptr || (output == nullptr && gated_output == nullptr)) return B200KV_ERR_INVALID;
+    if (q_dtype != B200KV_F16 && q_dtype != B200KV_F32) return B200KV_ERR_INVALID;
+    if ((rc = check_heads(view, query_heads, scale)) != B200KV_OK) return rc;
+    if (decode_state == nullptr && cache_length > view->capacity) return B200KV_ERR_RANGE;
+    if ((rc = ensure_device()) != B200KV_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    DecodeParams p{};
+    p.view = *view;
+    p.decode_state = decode_state;
+    p.cache_length = cache_length;
+    p.sessions = 1;
+    p.q = q;
+    p.q_is_f16 = (q_dtype == B200KV_F16);
+    p.query_heads = query_heads;
+    p.scale = scale;
+    // with a device-side length the launch is sized for the whole cache
+    const uint32_t max_length = decode_state ? static_cast<uint32_t>(view->capacity) : cache_length;
+    rc = run_decode_stage1(p, *view, max_length, workspace, workspace_bytes, num_splits, s);
+    if (rc != B200KV_OK) return rc;
+
+    MergeParams mp{};
+    mp.part_m = p.ws_m;
+    mp.part_l = p.ws_l;
+    mp.part_acc = p.ws_acc;
+    mp.num_parts = p.num_splits;
+    mp.query_heads = query_heads;
+    mp.head_dim = view->head_dim;
+    mp.gate = gate;
+    mp.output = output;
+    mp.gated_output = gated_output;
+    return launch_merge(mp, 1, s);
+}
+
+int b200kv_decode_attn_batched(const b200kv_view* views, void* view_table, const uint32_t* lengths,
+                               uint32_t sessions, uint32_t max_length, const void* q, int q_dtype,
+                               const float* gate, float* output, float* gated_output,
+                               uint32_t query_heads, float scale, void* workspace, size_t workspace_bytes,
+                               uint32_t num_splits, void* stream) {
+    if (sessions == 0) return B200KV_OK;
+    if (view_table == nullptr || lengths == nullptr || q == nullptr || (output == nullptr && gated_output == nullptr))
+        return B200KV_ERR_INVALID;
+    if (q_dtype != B200KV_F16 && q_dtype != B200KV_F32) return B200KV_ERR_INVALID;
+    if (sessions > 65535) return B200KV_ERR_UNSUPPORTED;
+    int rc;
+    if ((rc = ensure_device()) != B200KV_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    b200kv_view geometry;
+    if (views != nullptr) {
+        for (uint32_t i = 0; i < sessions; ++i) {
+            if ((rc = validate_view(&views[i])) != B200KV_OK) return rc;
+            if (views[i].head_dim != views[0].head_dim || views[i].kv_heads != views[0].kv_heads ||
+                views[i].qblock != views[0].qblock || views[i].quant_mode != views[0].quant_mode)
+                return B200KV_ERR_INVALID;
+        }
+        geometry = views[0];
+        B200KV_CUDA_TRY(cudaMemcpyAsync(view_table, views, sizeof(b200kv_view) * sessions, cudaMemcpyHostToDevice, s));
+    } else {
+        // the table already holds the views of an earlier call: fetch the geometry of entry 0
+        B200KV_CUDA_TRY(cudaMemcpyAsync(&geometry, view_table, sizeof geometry, cudaMemcpyDeviceToHost, s));
+        B200KV_CUDA_TRY(cudaStreamSynchronize(s));
+        if ((rc = validate_view(&geometry)) != B200KV_OK) return rc;
+    }
+    if ((rc = check_heads(&geometry, query_heads, scale)) != B200KV_OK) return rc;
+
+    DecodeParams p{};
+    p.view = geometry;
+    p.views = static_cast<const b200kv_view*>(view_table);
+    p.lengths = lengths;
+    p.sessions = sessions;
+    p.q = q;
+    p.q_is_f16 = (q_dtype == B200KV_F16);
+    p.query_heads = query_heads;
+    p.scale = scale;
+    rc = run_decode_stage1(p, geometry, max_length, workspace, workspace_bytes, num_splits, s);
+    if (rc != B200KV_OK) return rc;
+
+    MergeParams mp{};
+    mp.part_m = p.ws_m;
+    mp.part_l = p.ws_l;
+    mp.part_acc = p.ws_acc;
+    mp.num_parts = p.num_splits;
+    mp.query_heads = query_heads;
+    mp.head_dim = geometry.head_dim;
+    mp.gate = gate;
+    mp.output = output;
+    mp.gated_output = gated_output;
+    return launch_merge(mp, sessions, s);
+}
+
+int b200kv_decode_partials(const b200kv_view* view, const void* q, int q_dtype, uint32_t query_heads,
+                           float scale, uint32_t range_begin, uint32_t range_end,
+                           float* part_m, float* part_l, float* part_acc,
+                           void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream) {
+    int rc = validate_view(view);
+    if (rc != B200KV_OK) return rc;
+    if (q == nullptr || part_m == nullptr || part_l == nullptr || part_acc == nullptr) return B200KV_ERR_INVALID;
+    if (q_dtype != B200KV_F16 && q_dtype != B200KV_F32) return B200KV_ERR_INVALID;
+    if ((rc = check_heads(view, query_heads, scale)) != B200KV_OK) return rc;
+    if (range_end > view->capacity || range_begin > range_end) return B200KV_ERR_RANGE;
+    if ((rc = ensure_device()) != B200KV_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    DecodeParams p{};
+    p.view = *view;
+    p.cache_length = range_end;
+    p.range_begin = range_begin;
+    p.sessions = 1;
+    p.q = q;
+    p.q_is_f16 = (q_dtype == B200KV_F16);
+    p.query_heads = query_heads;
+    p.scale = scale;
+    rc = run_decode_stage1(p, *view, range_end - range_begin, workspace, workspace_bytes, num_splits, s);
+    if (rc != B200KV_OK) return rc;
+
+    MergeParams mp{};
+    mp.part_m = p.ws_m;
+    mp.part_l = p.ws_l;
+    mp.part_acc = p.ws_acc;
+    mp.num_parts = p.num_splits;
+    mp.query_heads = query_heads;
+    mp.head_dim = view->head_dim;
+    mp.out_m = part_m;
+    mp.out_l = part_l;
+    mp.out_acc = part_acc;
+    return launch_merge(mp, 1, s);
+}
+
+int b200kv_merge_partials(const float* part_m, const float* part_l, const float* part_acc,
+                          uint32_t num_parts, uint32_t query_heads, uint32_t head_dim,
+                          const float* gate, float* output, float* gated_output, void* stream) {
+    if (part_m == nullptr || part_l == nullptr || part_acc == nullptr || num_parts == 0 || query_heads == 0)
+        return B200KV_ERR_INVALID;
+    if (output == nullptr && gated_output == nullptr) return B200KV_ERR_INVALID;
+    if (head_dim == 0 || head_dim > 1024) return B200KV_ERR_UNSUPPORTED;
+    int rc;
+    if ((rc = ensure_device()) != B200KV_OK) return rc;
+    MergeParams mp{};
+    mp.part_m = part_m;
+    mp.part_l = part_l;
+    mp.part_acc = part_acc;
+    mp.num_parts = num_parts;
+    mp.query_heads = query_heads;
+    mp.head_dim = head_dim;
+    mp.gate = gate;
+    mp.output = output;
+    mp.gated_output = gated_output;
+    return launch_merge(mp, 1, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

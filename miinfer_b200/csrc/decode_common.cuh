@@ -1,0 +1,93 @@
+// Parameter block and split bookkeeping shared by the decode-attention kernels.
+#pragma once
+
+#include "kv_common.cuh"
+
+namespace b200kv {
+
+// Upper bound on split slots per launch: slots = sessions * splits_per_session.
+constexpr uint32_t kMaxSplitsPerSession = 128;
+constexpr uint32_t kSplitSlotBudget = 1024;
+
+inline uint32_t max_splits_per_session(uint32_t sessions) {
+    uint32_t s = kSplitSlotBudget / (sessions ? sessions : 1);
+    if (s > kMaxSplitsPerSession) s = kMaxSplitsPerSession;
+    return s ? s : 1;
+}
+
+struct DecodeParams {
+    b200kv_view view;                        // single-session launch
+    const b200kv_view* views;                // device table [sessions], or null
+    const uint32_t* lengths;                 // device [sessions], or null
+    const b200kv_decode_state* decode_state; // device, or null
+    uint32_t cache_length;                   // used when neither of the above is given
+    uint32_t range_begin;                    // first position scanned (sequence shard), normally 0
+    // Suffix/prefill use: "session" t is query token t of ONE cache and attends
+    // [0, causal_base + t + 1); prefill_state (device) overrides base and count.
+    int causal;
+    uint32_t causal_base;
+    const b200kv_prefill_state* prefill_state;
+    uint32_t sessions;
+    const void* q;                           // [sessions][query_heads][d]
+    int q_is_f16;
+    uint32_t query_heads;
+    float scale;
+    uint32_t num_splits;                     // per session
+    float* ws_m;                             // [sessions][num_splits][query_heads]
+    float* ws_l;
+    float* ws_acc;                           // [sessions][num_splits][query_heads][d]
+};
+
+// The scanned range [begin, end) of one session, resolved on the device the way
+// the reference resolves its DeviceDecodeState (position + 1 entries,
+// gfx906/kernels/qwen3_primitives.hip:7394-7395).
+__device__ __forceinline__ void resolve_range(const DecodeParams& p, uint32_t session, const b200kv_view& view,
+                                              uint32_t* begin, uint32_t* end) {
+    uint32_t length = p.cache_length;
+    if (p.causal) {
+        uint32_t base = p.causal_base, count = p.sessions;
+        if (p.prefill_state != nullptr) {
+            base = p.prefill_state->base_position;
+            count = p.prefill_state->token_count;
+        }
+        // tokens past the device-side count, or whose causal range leaves the cache, scan nothing
+        length = (session < count && static_cast<uint64_t>(base) + session + 1u <= view.capacity) ? base + session + 1u : 0u;
+    } else if (p.lengths != nullptr) length = p.lengths[session];
+    else if (p.decode_state != nullptr) length = p.decode_state->position + 1u;
+    if (length > view.capacity) length = static_cast<uint32_t>(view.capacity);
+    *end = length;
+    *begin = p.range_begin < length ? p.range_begin : length;
+}
+
+__device__ __forceinline__ const b200kv_view& session_view(const DecodeParams& p, uint32_t session) {
+    return p.views != nullptr ? p.views[session] : p.view;
+}
+
+struct MergeParams {
+    const float* part_m;   // [groups][num_parts][query_heads]
+    const float* part_l;
+    const float* part_acc; // [groups][num_parts][query_heads][d]
+    uint32_t num_parts;
+    uint32_t query_heads;
+    uint32_t head_dim;
+    const float* gate;     // [groups][query_heads][d] or null
+    float* output;         // normalised, or null
+    float* gated_output;   // normalised * sigmoid(gate), or null
+    float* out_m;          // when non-null: emit ONE merged partial per (group, head) instead
+    float* out_l;
+    float* out_acc;
+};
+
+int launch_merge(const MergeParams& p, uint32_t groups, cudaStream_t stream);
+
+// Stage 1 into `workspace` (fills p.num_splits and p.ws_*).  num_splits_arg: 0 =
+// choose; top bit set = use the generic kernel even where a fast one exists.
+int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, void* workspace,
+                      size_t workspace_bytes, uint32_t num_splits_arg, cudaStream_t stream);
+
+// Fast path for int8 K and V (decode_q8.cu).  Returns B200KV_ERR_UNSUPPORTED when
+// the geometry has no specialised kernel, so the caller can use the generic one.
+int launch_decode_q8(const DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, cudaStream_t stream);
+uint32_t pick_splits_q8(const b200kv_view& geometry, uint32_t query_heads, uint32_t sessions, uint32_t max_length);
+
+}  // namespace b200kv

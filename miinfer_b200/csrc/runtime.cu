@@ -1,0 +1,202 @@
+// Library plumbing: status strings, device guard, view validation and the
+// owning cache storage object (the counterpart of MIInfer's
+// AttentionLayerKvCacheStorage, src/prefill_v2/kv_cache.cpp:10-130).
+#include "kv_common.cuh"
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+namespace b200kv {
+
+static thread_local char g_last_error[256] = "";
+
+void set_last_cuda_error(cudaError_t err, const char* where) {
+    std::snprintf(g_last_error, sizeof g_last_error, "%s: %s (%s)", cudaGetErrorName(err),
+                  cudaGetErrorString(err), where);
+    (void)cudaGetLastError();  // clear the sticky-less error so later calls report their own
+}
+
+int ensure_device() {
+    static thread_local int checked_device = -1;
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return B200KV_ERR_DEVICE;
+    }
+    if (device == checked_device) return B200KV_OK;
+    int rc = b200kv_device_check(device);
+    if (rc == B200KV_OK) checked_device = device;
+    return rc;
+}
+
+int validate_view(const b200kv_view* v) {
+    if (v == nullptr) return B200KV_ERR_INVALID;
+    if (v->capacity == 0 || v->kv_heads == 0 || v->quant_mode > B200KV_Q8_Q8) return B200KV_ERR_INVALID;
+    if (v->head_dim != 128 && v->head_dim != 256) return B200KV_ERR_UNSUPPORTED;
+    if (v->qblock != 32 && v->qblock != v->head_dim) return B200KV_ERR_UNSUPPORTED;
+    if (v->capacity > 0x7fffffffull) return B200KV_ERR_UNSUPPORTED;  // positions are 32-bit in the device state
+    auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    if (is_k_q8(v->quant_mode)) {
+        if (!v->key_q8 || !v->key_scales || !aligned(v->key_q8) || !aligned(v->key_scales)) return B200KV_ERR_INVALID;
+    } else if (!v->key_f16 || !aligned(v->key_f16)) {
+        return B200KV_ERR_INVALID;
+    }
+    if (is_v_q8(v->quant_mode)) {
+        if (!v->value_q8 || !v->value_scales || !aligned(v->value_q8) || !aligned(v->value_scales)) return B200KV_ERR_INVALID;
+    } else if (!v->value_f16 || !aligned(v->value_f16)) {
+        return B200KV_ERR_INVALID;
+    }
+    return B200KV_OK;
+}
+
+}  // namespace b200kv
+
+using namespace b200kv;
+
+struct b200kv_cache {
+    b200kv_view view;
+    int device;
+};
+
+extern "C" {
+
+int b200kv_version(void) { return B200KV_VERSION; }
+
+const char* b200kv_status_string(int status) {
+    switch (status) {
+        case B200KV_OK: return "ok";
+        case B200KV_ERR_INVALID: return "invalid argument";
+        case B200KV_ERR_UNSUPPORTED: return "unsupported shape or mode";
+        case B200KV_ERR_CUDA: return "CUDA error";
+        case B200KV_ERR_DEVICE: return "no sm_100 device";
+        case B200KV_ERR_WORKSPACE: return "workspace too small";
+        case B200KV_ERR_RANGE: return "position beyond cache capacity";
+        case B200KV_ERR_FORMAT: return "bad session file";
+        case B200KV_ERR_IO: return "session file I/O failed";
+        case B200KV_ERR_MISMATCH: return "session does not match";
+        default: return "unknown status";
+    }
+}
+
+const char* b200kv_last_cuda_error(void) { return g_last_error; }
+
+int b200kv_device_check(int device) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+        (void)cudaGetLastError();
+        return B200KV_ERR_DEVICE;
+    }
+    int major = 0, minor = 0;
+    B200KV_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+    B200KV_CUDA_TRY(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device));
+    return (major == 10) ? B200KV_OK : B200KV_ERR_DEVICE;
+}
+
+static size_t side_bytes(uint64_t capacity, uint32_t kv_heads, uint32_t head_dim, uint32_t qblock, bool q8) {
+    const size_t rows = static_cast<size_t>(capacity) * kv_heads;
+    return q8 ? rows * (head_dim + 2u * (head_dim / qblock)) : rows * head_dim * 2u;
+}
+
+size_t b200kv_cache_bytes(uint64_t capacity, uint32_t kv_heads, uint32_t head_dim, uint32_t qblock, uint32_t quant_mode) {
+    if (qblock == 0 || head_dim % qblock != 0) return 0;
+    return side_bytes(capacity, kv_heads, head_dim, qblock, is_k_q8(quant_mode)) +
+           side_bytes(capacity, kv_heads, head_dim, qblock, is_v_q8(quant_mode));
+}
+
+int b200kv_cache_destroy(b200kv_cache* cache) {
+    if (cache == nullptr) return B200KV_OK;
+    b200kv_view& v = cache->view;
+    void* planes[6] = {v.key_f16, v.value_f16, v.key_q8, v.key_scales, v.value_q8, v.value_scales};
+    for (void* p : planes)
+        if (p != nullptr) (void)cudaFree(p);
+    delete cache;
+    return B200KV_OK;
+}
+
+int b200kv_cache_create(b200kv_cache** out, uint64_t capacity, uint32_t kv_heads, uint32_t head_dim,
+                        uint32_t qblock, uint32_t quant_mode) {
+    if (out == nullptr) return B200KV_ERR_INVALID;
+    *out = nullptr;
+    if (capacity == 0 || kv_heads == 0 || quant_mode > B200KV_Q8_Q8) return B200KV_ERR_INVALID;
+    if (head_dim != 128 && head_dim != 256) return B200KV_ERR_UNSUPPORTED;
+    if (qblock != 32 && qblock != head_dim) return B200KV_ERR_UNSUPPORTED;
+    if (capacity > 0x7fffffffull) return B200KV_ERR_UNSUPPORTED;
+    int rc = ensure_device();
+    if (rc != B200KV_OK) return rc;
+    b200kv_cache* cache = new (std::nothrow) b200kv_cache();
+    if (cache == nullptr) return B200KV_ERR_INVALID;
+    std::memset(&cache->view, 0, sizeof cache->view);
+    (void)cudaGetDevice(&cache->device);
+    b200kv_view& v = cache->view;
+    v.capacity = capacity;
+    v.kv_heads = kv_heads;
+    v.head_dim = head_dim;
+    v.qblock = qblock;
+    v.quant_mode = quant_mode;
+    const size_t rows = static_cast<size_t>(capacity) * kv_heads;
+    const size_t q8_bytes = rows * head_dim, scale_bytes = rows * (head_dim / qblock) * 2u, f16_bytes = rows * head_dim * 2u;
+    cudaError_t err = cudaSuccess;
+    if (is_k_q8(quant_mode)) {
+        err = cudaMalloc(reinterpret_cast<void**>(&v.key_q8), q8_bytes);
+        if (err == cudaSuccess) err = cudaMalloc(&v.key_scales, scale_bytes);
+    } else {
+        err = cudaMalloc(&v.key_f16, f16_bytes);
+    }
+    if (err == cudaSuccess) {
+        if (is_v_q8(quant_mode)) {
+            err = cudaMalloc(reinterpret_cast<void**>(&v.value_q8), q8_bytes);
+            if (err == cudaSuccess) err = cudaMalloc(&v.value_scales, scale_bytes);
+        } else {
+            err = cudaMalloc(&v.value_f16, f16_bytes);
+        }
+    }
+    if (err != cudaSuccess) {
+        set_last_cuda_error(err, "cudaMalloc(cache plane)");
+        b200kv_cache_destroy(cache);
+        return B200KV_ERR_CUDA;
+    }
+    rc = b200kv_cache_reset(cache, nullptr);
+    if (rc == B200KV_OK) {
+        cudaError_t sync = cudaStreamSynchronize(nullptr);
+        if (sync != cudaSuccess) { set_last_cuda_error(sync, "cudaStreamSynchronize"); rc = B200KV_ERR_CUDA; }
+    }
+    if (rc != B200KV_OK) {
+        b200kv_cache_destroy(cache);
+        return rc;
+    }
+    *out = cache;
+    return B200KV_OK;
+}
+
+int b200kv_cache_reset(b200kv_cache* cache, void* stream) {
+    if (cache == nullptr) return B200KV_ERR_INVALID;
+    const b200kv_view& v = cache->view;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t rows = static_cast<size_t>(v.capacity) * v.kv_heads;
+    const size_t q8_bytes = rows * v.head_dim, scale_bytes = rows * (v.head_dim / v.qblock) * 2u, f16_bytes = rows * v.head_dim * 2u;
+    if (v.key_f16) B200KV_CUDA_TRY(cudaMemsetAsync(v.key_f16, 0, f16_bytes, s));
+    if (v.value_f16) B200KV_CUDA_TRY(cudaMemsetAsync(v.value_f16, 0, f16_bytes, s));
+    if (v.key_q8) B200KV_CUDA_TRY(cudaMemsetAsync(v.key_q8, 0, q8_bytes, s));
+    if (v.key_scales) B200KV_CUDA_TRY(cudaMemsetAsync(v.key_scales, 0, scale_bytes, s));
+    if (v.value_q8) B200KV_CUDA_TRY(cudaMemsetAsync(v.value_q8, 0, q8_bytes, s));
+    if (v.value_scales) B200KV_CUDA_TRY(cudaMemsetAsync(v.value_scales, 0, scale_bytes, s));
+    return B200KV_OK;
+}
+
+int b200kv_cache_view(const b200kv_cache* cache, b200kv_view* out) {
+    if (cache == nullptr || out == nullptr) return B200KV_ERR_INVALID;
+    *out = cache->view;
+    return B200KV_OK;
+}
+
+uint64_t b200kv_token_sequence_hash(const uint32_t* tokens, size_t count) {
+    uint64_t hash = 0xcbf29ce484222325ull;
+    for (size_t i = 0; i < count; ++i) {
+        hash ^= static_cast<uint64_t>(tokens[i]);
+        hash *= 0x100000001b3ull;
+    }
+    return hash;
+}
+
+}  // extern "C"

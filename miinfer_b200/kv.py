@@ -1,0 +1,247 @@
+"""Python mirror of MIInfer's KV-cache operator interface over the B200 library.
+
+Names and argument meaning follow the reference's C++ interface so call sites
+read the same: KvCacheQuantMode / AttentionKvCacheView /
+AttentionLayerKvCacheStorage (include/miinfer/prefill_v2/kv_cache.hpp) and the
+three launchers of include/miinfer/qwen3_gpu_primitives.hpp:670-739.  Tensors are
+torch CUDA tensors used only as device buffers; all arithmetic runs in
+libb200kv.so.  Argument errors raise B200KvError (the reference aborts).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from typing import Optional
+
+import torch
+
+from ._lib import B200KvError, View, check, lib
+
+__all__ = [
+    "KvCacheQuantMode", "RopeMode", "AttentionKvCacheView", "AttentionLayerKvCacheStorage",
+    "launch_kv_store_quant", "launch_decode_attention_quant", "launch_decode_attention_batched",
+    "launch_decode_partials", "launch_merge_partials", "launch_suffix_attention_quant",
+    "decode_workspace", "prefill_workspace", "make_decode_state", "make_prefill_state",
+    "token_sequence_hash", "B200KvError", "FORCE_GENERIC",
+]
+
+FORCE_GENERIC = 0x80000000
+
+
+class KvCacheQuantMode(enum.IntEnum):
+    """kv_cache.hpp:16-21."""
+    kFp16Fp16 = 0
+    kQ8Fp16 = 1
+    kFp16Q8 = 2
+    kQ8Q8 = 3
+
+
+class RopeMode(enum.IntEnum):
+    NONE = 0
+    NEOX_FULL = 1
+    SECTIONED64 = 2
+
+
+AttentionKvCacheView = View
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda or not t.is_contiguous():
+        raise ValueError("expected a contiguous CUDA tensor")
+    return t.data_ptr()
+
+
+def _dtype(t: torch.Tensor) -> int:
+    if t.dtype == torch.float16:
+        return 0
+    if t.dtype == torch.float32:
+        return 1
+    raise ValueError(f"unsupported dtype {t.dtype}: fp16 or fp32 expected")
+
+
+def _stream(stream: Optional[torch.cuda.Stream]) -> int:
+    return (stream or torch.cuda.current_stream()).cuda_stream
+
+
+class AttentionLayerKvCacheStorage:
+    """Owns one layer's planes (kv_cache.hpp:49-122, src/prefill_v2/kv_cache.cpp).
+
+    The reference fixes kv_heads=4, head_dim=256 and one scale per row; here
+    they are constructor arguments and `qblock=32` selects the q8_0 format.
+    """
+
+    def __init__(self, capacity: int, quant_mode: KvCacheQuantMode = KvCacheQuantMode.kFp16Fp16, *,
+                 kv_heads: int = 4, head_dim: int = 256, qblock: Optional[int] = None,
+                 device: Optional[torch.device] = None):
+        if capacity <= 0:
+            raise RuntimeError("AttentionLayerKvCacheStorage: capacity must be > 0")  # kv_cache.cpp:12-14
+        self.capacity, self.kv_heads, self.head_dim = int(capacity), int(kv_heads), int(head_dim)
+        self.qblock = int(qblock if qblock is not None else head_dim)
+        self.quant_mode = KvCacheQuantMode(quant_mode)
+        if self.head_dim % self.qblock:
+            raise ValueError("qblock must divide head_dim")
+        dev = device or torch.device("cuda", torch.cuda.current_device())
+        rows = self.kv_heads * self.capacity
+        nblk = self.head_dim // self.qblock
+        k_q8 = self.quant_mode in (KvCacheQuantMode.kQ8Fp16, KvCacheQuantMode.kQ8Q8)
+        v_q8 = self.quant_mode in (KvCacheQuantMode.kFp16Q8, KvCacheQuantMode.kQ8Q8)
+        z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=dev)
+        shape = (self.kv_heads, self.capacity, self.head_dim)
+        sshape = (self.kv_heads, self.capacity, nblk)
+        self.key_cache = None if k_q8 else z(shape, torch.float16)
+        self.value_cache = None if v_q8 else z(shape, torch.float16)
+        self.key_cache_q8 = z(shape, torch.int8) if k_q8 else None
+        self.key_scales = z(sshape, torch.float16) if k_q8 else None
+        self.value_cache_q8 = z(shape, torch.int8) if v_q8 else None
+        self.value_scales = z(sshape, torch.float16) if v_q8 else None
+        del rows
+
+    def planes(self):
+        return [t for t in (self.key_cache, self.value_cache, self.key_cache_q8, self.key_scales,
+                            self.value_cache_q8, self.value_scales) if t is not None]
+
+    def reset(self, stream: Optional[torch.cuda.Stream] = None) -> None:
+        with torch.cuda.stream(stream or torch.cuda.current_stream()):
+            for t in self.planes():
+                t.zero_()
+
+    def view(self) -> View:
+        return View(_ptr(self.key_cache), _ptr(self.value_cache), _ptr(self.key_cache_q8), _ptr(self.key_scales),
+                    _ptr(self.value_cache_q8), _ptr(self.value_scales), self.capacity, self.kv_heads,
+                    self.head_dim, self.qblock, int(self.quant_mode))
+
+    def total_bytes(self) -> int:
+        return int(lib.b200kv_cache_bytes(self.capacity, self.kv_heads, self.head_dim, self.qblock, int(self.quant_mode)))
+
+    def raw_tokens_bytes(self, tokens: int) -> int:
+        """kv_cache.cpp:214-225."""
+        v = self.view()
+        return int(lib.b200kv_snapshot_bytes(C.byref(v), tokens))
+
+    def download_raw(self, dst: torch.Tensor, tokens: int, stream: Optional[torch.cuda.Stream] = None) -> None:
+        """kv_cache.cpp:227-297.  dst: uint8 tensor (CUDA, or CPU -- pinned for an async copy)."""
+        if tokens > self.capacity:
+            raise RuntimeError("AttentionLayerKvCacheStorage::download_raw: tokens exceeds capacity")
+        if dst.numel() * dst.element_size() < self.raw_tokens_bytes(tokens):
+            raise ValueError("snapshot buffer too small")
+        v = self.view()
+        check(lib.b200kv_snapshot_save(C.byref(v), tokens, dst.data_ptr(), _stream(stream)), "b200kv_snapshot_save")
+
+    def upload_raw(self, src: torch.Tensor, tokens: int, stream: Optional[torch.cuda.Stream] = None) -> None:
+        """kv_cache.cpp:299-369."""
+        if tokens > self.capacity:
+            raise RuntimeError("AttentionLayerKvCacheStorage::upload_raw: tokens exceeds capacity")
+        if src.numel() * src.element_size() < self.raw_tokens_bytes(tokens):
+            raise ValueError("snapshot buffer too small")
+        v = self.view()
+        check(lib.b200kv_snapshot_restore(C.byref(v), tokens, src.data_ptr(), _stream(stream)), "b200kv_snapshot_restore")
+
+    def clone_prefix_from(self, other: "AttentionLayerKvCacheStorage", tokens: int,
+                          stream: Optional[torch.cuda.Stream] = None) -> None:
+        """Device-to-device copy of the first `tokens` positions (tools/miinfer_cli.cpp:1248-1317)."""
+        d, s = self.view(), other.view()
+        check(lib.b200kv_snapshot_clone(C.byref(d), C.byref(s), tokens, _stream(stream)), "b200kv_snapshot_clone")
+
+
+def make_decode_state(position: int, device=None) -> torch.Tensor:
+    """A DeviceDecodeState (qwen3_gpu_primitives.hpp:30-37) as a 16-word uint32 tensor."""
+    t = torch.zeros(16, dtype=torch.int32, device=device or "cuda")
+    t[1] = position
+    return t
+
+
+def make_prefill_state(base_position: int, token_count: int, kv_capacity: int = 0, device=None) -> torch.Tensor:
+    """A DevicePrefillState (qwen3_gpu_primitives.hpp:39-45)."""
+    t = torch.zeros(16, dtype=torch.int32, device=device or "cuda")
+    t[0], t[1], t[2], t[3] = base_position, token_count, base_position + token_count, kv_capacity
+    return t
+
+
+def decode_workspace(query_heads: int, head_dim: int, sessions: int = 1, device=None) -> torch.Tensor:
+    n = int(lib.b200kv_decode_workspace_bytes(query_heads, head_dim, sessions))
+    return torch.empty(n, dtype=torch.uint8, device=device or "cuda")
+
+
+def prefill_workspace(token_count: int, query_heads: int, head_dim: int, device=None) -> torch.Tensor:
+    n = int(lib.b200kv_prefill_workspace_bytes(token_count, query_heads, head_dim))
+    return torch.empty(n, dtype=torch.uint8, device=device or "cuda")
+
+
+def launch_kv_store_quant(view: View, key: torch.Tensor, value: torch.Tensor, k_norm_weight: Optional[torch.Tensor],
+                          token_count: int, base_position: int, *, rope_mode: RopeMode = RopeMode.SECTIONED64,
+                          theta: float = 1.0e6, epsilon: float = 1.0e-6,
+                          prefill_state: Optional[torch.Tensor] = None, decode_state: Optional[torch.Tensor] = None,
+                          stream: Optional[torch.cuda.Stream] = None) -> None:
+    """launch_qwen35_decoupled_k_norm_rope_kv_store_batch_quant (qwen3_gpu_primitives.hpp:695-716).
+
+    key/value: [token][kv_heads*head_dim] fp16 or fp32; the cache planes and
+    quant mode travel in `view`."""
+    if key.dtype != value.dtype:
+        raise ValueError("key and value must share a dtype")
+    check(lib.b200kv_append(C.byref(view), _ptr(key), _ptr(value), _dtype(key), _ptr(k_norm_weight), int(rope_mode),
+                            theta, epsilon, token_count, base_position, _ptr(prefill_state), _ptr(decode_state),
+                            _stream(stream)), "b200kv_append")
+
+
+def launch_decode_attention_quant(view: View, q: torch.Tensor, *, query_heads: int, scale: float,
+                                  cache_length: int = 0, decode_state: Optional[torch.Tensor] = None,
+                                  output: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                                  gated_output: Optional[torch.Tensor] = None, workspace: torch.Tensor,
+                                  num_splits: int = 0, stream: Optional[torch.cuda.Stream] = None) -> None:
+    """launch_qwen35_tiled_online_attention_quant_dynamic (qwen3_gpu_primitives.hpp:719-739)."""
+    check(lib.b200kv_decode_attn(C.byref(view), _ptr(q), _dtype(q), _ptr(gate), _ptr(output), _ptr(gated_output),
+                                 query_heads, scale, cache_length, _ptr(decode_state), _ptr(workspace),
+                                 workspace.numel(), num_splits, _stream(stream)), "b200kv_decode_attn")
+
+
+def launch_decode_attention_batched(views, view_table: torch.Tensor, lengths: torch.Tensor, max_length: int,
+                                    q: torch.Tensor, *, query_heads: int, scale: float,
+                                    output: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                                    gated_output: Optional[torch.Tensor] = None, workspace: torch.Tensor,
+                                    num_splits: int = 0, stream: Optional[torch.cuda.Stream] = None) -> None:
+    """One decode step for many sessions in one launch (b200kv_decode_attn_batched).
+
+    views: sequence of View, or None to reuse the table filled by an earlier call."""
+    sessions = int(lengths.numel())
+    arr = None
+    if views is not None:
+        arr = (View * sessions)(*views)
+    check(lib.b200kv_decode_attn_batched(arr, _ptr(view_table), _ptr(lengths), sessions, max_length, _ptr(q), _dtype(q),
+                                         _ptr(gate), _ptr(output), _ptr(gated_output), query_heads, scale,
+                                         _ptr(workspace), workspace.numel(), num_splits, _stream(stream)),
+          "b200kv_decode_attn_batched")
+
+
+def launch_decode_partials(view: View, q: torch.Tensor, *, query_heads: int, scale: float, range_begin: int,
+                           range_end: int, part_m: torch.Tensor, part_l: torch.Tensor, part_acc: torch.Tensor,
+                           workspace: torch.Tensor, num_splits: int = 0,
+                           stream: Optional[torch.cuda.Stream] = None) -> None:
+    check(lib.b200kv_decode_partials(C.byref(view), _ptr(q), _dtype(q), query_heads, scale, range_begin, range_end,
+                                     _ptr(part_m), _ptr(part_l), _ptr(part_acc), _ptr(workspace), workspace.numel(),
+                                     num_splits, _stream(stream)), "b200kv_decode_partials")
+
+
+def launch_merge_partials(part_m: torch.Tensor, part_l: torch.Tensor, part_acc: torch.Tensor, *, num_parts: int,
+                          query_heads: int, head_dim: int, output: Optional[torch.Tensor] = None,
+                          gate: Optional[torch.Tensor] = None, gated_output: Optional[torch.Tensor] = None,
+                          stream: Optional[torch.cuda.Stream] = None) -> None:
+    check(lib.b200kv_merge_partials(_ptr(part_m), _ptr(part_l), _ptr(part_acc), num_parts, query_heads, head_dim,
+                                    _ptr(gate), _ptr(output), _ptr(gated_output), _stream(stream)),
+          "b200kv_merge_partials")
+
+
+def launch_suffix_attention_quant(view: View, q: torch.Tensor, gate: Optional[torch.Tensor], gated_output: torch.Tensor,
+                                  workspace: torch.Tensor, token_count: int, base_position: int, *, query_heads: int,
+                                  scale: float, prefill_state: Optional[torch.Tensor] = None,
+                                  stream: Optional[torch.cuda.Stream] = None) -> None:
+    """launch_qwen35_splitk_suffix_attention_quant (qwen3_gpu_primitives.hpp:670-692)."""
+    check(lib.b200kv_prefill_attn(C.byref(view), _ptr(q), _dtype(q), _ptr(gate), _ptr(gated_output), token_count,
+                                  base_position, query_heads, scale, _ptr(prefill_state), _ptr(workspace),
+                                  workspace.numel(), _stream(stream)), "b200kv_prefill_attn")
+
+
+def token_sequence_hash(tokens) -> int:
+    arr = (C.c_uint32 * len(tokens))(*tokens)
+    return int(lib.b200kv_token_sequence_hash(arr, len(tokens)))

@@ -1,0 +1,205 @@
+"""GPU parity: split-K GQA decode attention against the oracle's fp32-accumulated
+two-pass reference, max-abs <= 2e-3 (the tolerance BASELINE.json states),
+through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import kvoracle as ko
+from gpu_util import to_dev, upload
+from miinfer_b200 import kv
+
+pytestmark = pytest.mark.gpu
+TOL = 2.0e-3
+
+
+def filled(rng, L, H, d, qb, mode, cap=None, std=1.0):
+    host = ko.HostCache(cap or L, H, d, qb, mode)
+    host.append(ko.normal_f16(rng, (L, H * d), std).astype(np.float32), ko.normal_f16(rng, (L, H * d), std).astype(np.float32),
+                None, 0, rope_mode=0)
+    return host
+
+
+def gpu_decode(st, q, Hq, scale, length, *, gate=None, num_splits=0, decode_state=None):
+    d = st.head_dim
+    out = torch.full((Hq, d), float("nan"), device="cuda")
+    gated = torch.full((Hq, d), float("nan"), device="cuda")
+    ws = kv.decode_workspace(Hq, d, 1)
+    kv.launch_decode_attention_quant(st.view(), q, query_heads=Hq, scale=scale, cache_length=length,
+                                     decode_state=decode_state, output=out, gate=gate, gated_output=gated,
+                                     workspace=ws, num_splits=num_splits)
+    torch.cuda.synchronize()
+    return out.cpu().numpy(), gated.cpu().numpy()
+
+
+# (d, H, Hq, qblock, mode, L)
+SHAPES = [
+    (128, 8, 32, 32, 3, 4097),     # BASELINE config 1
+    (128, 8, 32, 32, 3, 1),
+    (128, 8, 32, 32, 3, 31),
+    (128, 8, 32, 32, 3, 1025),
+    (256, 4, 24, 32, 3, 777),      # hybrid-model shape, q8_0 blocks
+    (256, 4, 24, 256, 3, 2049),    # the reference's row-scale format
+    (256, 4, 24, 256, 1, 300),
+    (256, 4, 24, 256, 2, 300),
+    (256, 4, 24, 256, 0, 300),
+    (128, 2, 2, 32, 3, 100),       # no GQA sharing
+    (128, 1, 8, 128, 3, 515),      # group of 8
+]
+
+
+@pytest.mark.parametrize("d,H,Hq,qb,mode,L", SHAPES)
+@pytest.mark.parametrize("path", ["auto", "generic"])
+def test_decode_matches_two_pass_reference(cuda, d, H, Hq, qb, mode, L, path):
+    rng = np.random.default_rng(d + L + mode)
+    host = filled(rng, L, H, d, qb, mode, cap=L + 5)
+    st = upload(host)
+    q16 = ko.normal_f16(rng, (Hq, d))
+    gate = rng.standard_normal((Hq, d)).astype(np.float32)
+    ref, ref_g = host.decode_ref(q16.astype(np.float32), d ** -0.5, L, gate)
+    flag = kv.FORCE_GENERIC if path == "generic" else 0
+    for q_dev in (to_dev(q16), to_dev(q16.astype(np.float32))):       # fp16 and fp32 queries
+        out, gated = gpu_decode(st, q_dev, Hq, d ** -0.5, L, gate=to_dev(gate), num_splits=flag)
+        assert np.max(np.abs(out - ref)) <= TOL, np.max(np.abs(out - ref))
+        assert np.max(np.abs(gated - ref_g)) <= TOL
+
+
+def test_decode_split_count_invariance_and_determinism(cuda):
+    rng = np.random.default_rng(77)
+    host = filled(rng, 3000, 8, 128, 32, 3)
+    st = upload(host)
+    q = to_dev(ko.normal_f16(rng, (32, 128)))
+    ref, _ = host.decode_ref(q.float().cpu().numpy(), 128 ** -0.5, 3000)
+    outs = []
+    for splits in (1, 2, 5, 16, 37, 64, 128):
+        for flag in (0, kv.FORCE_GENERIC):
+            out, _ = gpu_decode(st, q, 32, 128 ** -0.5, 3000, num_splits=splits | flag)
+            assert np.max(np.abs(out - ref)) <= TOL, (splits, flag)
+            outs.append(out)
+    assert max(np.max(np.abs(o - outs[0])) for o in outs) <= 2e-5   # invariance up to rounding, not bit equality
+    a, _ = gpu_decode(st, q, 32, 128 ** -0.5, 3000)
+    for _ in range(8):
+        b, _ = gpu_decode(st, q, 32, 128 ** -0.5, 3000)
+        assert np.array_equal(a, b)   # replay is bit-identical
+
+
+def test_decode_peaked_softmax_and_large_magnitudes(cuda):
+    # one key aligned with the query dominates the softmax; values have a large range
+    rng = np.random.default_rng(5)
+    L, H, Hq, d = 2000, 8, 32, 128
+    kf = ko.normal_f16(rng, (L, H * d)).astype(np.float32)
+    vf = (ko.normal_f16(rng, (L, H * d)).astype(np.float32) * 8).astype(np.float16).astype(np.float32)
+    q16 = ko.normal_f16(rng, (Hq, d), 2.0)
+    for h in range(H):
+        kf[1234, h * d:(h + 1) * d] = q16[h * 4].astype(np.float32) * 1.5
+    host = ko.HostCache(L, H, d, 32, 3)
+    host.append(kf, vf, None, 0, rope_mode=0)
+    st = upload(host)
+    ref, _ = host.decode_ref(q16.astype(np.float32), d ** -0.5, L)
+    for flag in (0, kv.FORCE_GENERIC):
+        out, _ = gpu_decode(st, to_dev(q16), Hq, d ** -0.5, L, num_splits=flag)
+        assert np.max(np.abs(out - ref)) <= TOL * max(1.0, np.abs(ref).max() / 4)
+
+
+def test_decode_length_from_device_state_and_quirk_free_length(cuda):
+    # L = position + 1: entries 0..position, including the just-appended token
+    rng = np.random.default_rng(6)
+    host = filled(rng, 600, 8, 128, 32, 3, cap=1024)
+    st = upload(host)
+    q = to_dev(ko.normal_f16(rng, (32, 128)))
+    ref, _ = host.decode_ref(q.float().cpu().numpy(), 128 ** -0.5, 600)
+    state = kv.make_decode_state(599)
+    for flag in (0, kv.FORCE_GENERIC):
+        out, _ = gpu_decode(st, q, 32, 128 ** -0.5, 0, decode_state=state, num_splits=flag)
+        assert np.max(np.abs(out - ref)) <= TOL
+    # attending one slot too many (the reference's non-graph path quirk) or too few is visible
+    wrong, _ = host.decode_ref(q.float().cpu().numpy(), 128 ** -0.5, 599)
+    assert np.max(np.abs(wrong - ref)) > 1e-4
+
+
+def test_decode_after_gpu_append_end_to_end(cuda):
+    # build the whole cache through the append kernel (RoPE at true positions), then attend: config 1 shape
+    rng = np.random.default_rng(8)
+    L, H, Hq, d = 257, 8, 32, 128
+    k16, v16 = ko.normal_f16(rng, (L, H * d)), ko.normal_f16(rng, (L, H * d))
+    host = ko.HostCache(L, H, d, 32, 3)
+    host.append(k16.astype(np.float32), v16.astype(np.float32), None, 0, rope_mode=1)
+    st = kv.AttentionLayerKvCacheStorage(L, kv.KvCacheQuantMode.kQ8Q8, kv_heads=H, head_dim=d, qblock=32)
+    kv.launch_kv_store_quant(st.view(), to_dev(k16[:L - 1]), to_dev(v16[:L - 1]), None, L - 1, 0, rope_mode=kv.RopeMode.NEOX_FULL)
+    kv.launch_kv_store_quant(st.view(), to_dev(k16[L - 1:]), to_dev(v16[L - 1:]), None, 1, L - 1, rope_mode=kv.RopeMode.NEOX_FULL)
+    q16 = ko.normal_f16(rng, (Hq, d))
+    ref, _ = host.decode_ref(q16.astype(np.float32), d ** -0.5, L)
+    out, _ = gpu_decode(st, to_dev(q16), Hq, d ** -0.5, L)
+    assert np.max(np.abs(out - ref)) <= TOL
+
+
+def test_decode_batched_variable_lengths(cuda):
+    rng = np.random.default_rng(9)
+    H, Hq, d = 8, 32, 128
+    lengths = [1, 37, 512, 1300, 64, 2049]
+    hosts = [filled(rng, L, H, d, 32, 3, cap=L + 7) for L in lengths]
+    sts = [upload(h) for h in hosts]
+    q16 = ko.normal_f16(rng, (len(lengths), Hq, d))
+    table = torch.empty(len(lengths) * 80, dtype=torch.uint8, device="cuda")
+    lens = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    ws = kv.decode_workspace(Hq, d, len(lengths))
+    for flag in (0, kv.FORCE_GENERIC):
+        out = torch.full((len(lengths), Hq, d), float("nan"), device="cuda")
+        kv.launch_decode_attention_batched([s.view() for s in sts], table, lens, max(lengths), to_dev(q16),
+                                           query_heads=Hq, scale=d ** -0.5, output=out, workspace=ws, num_splits=flag)
+        torch.cuda.synchronize()
+        for i, h in enumerate(hosts):
+            ref, _ = h.decode_ref(q16[i].astype(np.float32), d ** -0.5, lengths[i])
+            assert np.max(np.abs(out[i].cpu().numpy() - ref)) <= TOL, (i, flag)
+    # second call reusing the device view table
+    out2 = torch.zeros_like(out)
+    kv.launch_decode_attention_batched(None, table, lens, max(lengths), to_dev(q16), query_heads=Hq, scale=d ** -0.5,
+                                       output=out2, workspace=ws)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2) or np.max(np.abs((out - out2).cpu().numpy())) <= 2e-5
+
+
+def test_sequence_shard_partials_merge_to_full_attention(cuda):
+    rng = np.random.default_rng(10)
+    L, H, Hq, d = 4096, 8, 32, 128
+    host = filled(rng, L, H, d, 32, 3)
+    st = upload(host)
+    q16 = ko.normal_f16(rng, (Hq, d))
+    ref, _ = host.decode_ref(q16.astype(np.float32), d ** -0.5, L)
+    ws = kv.decode_workspace(Hq, d, 1)
+    for shards in (2, 4, 8):
+        pm = torch.empty(shards, Hq, device="cuda"); pl = torch.empty(shards, Hq, device="cuda")
+        pa = torch.empty(shards, Hq, d, device="cuda")
+        per = L // shards
+        for r in range(shards):
+            kv.launch_decode_partials(st.view(), to_dev(q16), query_heads=Hq, scale=d ** -0.5, range_begin=r * per,
+                                      range_end=(r + 1) * per, part_m=pm[r], part_l=pl[r], part_acc=pa[r], workspace=ws)
+        # device partial of shard 0 agrees with the oracle's kernel-order partial reduced the same way
+        om, ol, oa = host.decode_partials(q16.astype(np.float32), d ** -0.5, 0, per, 1)
+        scale_fix = np.exp(om[0] - pm[0].cpu().numpy())
+        np.testing.assert_allclose(pl[0].cpu().numpy(), ol[0] * scale_fix, rtol=2e-4)
+        out = torch.empty(Hq, d, device="cuda")
+        kv.launch_merge_partials(pm, pl, pa, num_parts=shards, query_heads=Hq, head_dim=d, output=out)
+        torch.cuda.synchronize()
+        assert np.max(np.abs(out.cpu().numpy() - ref)) <= TOL
+    # merge kernel alone == oracle merge on the same partials, including an empty part
+    pm2 = torch.cat([pm, torch.full((1, Hq), float("-inf"), device="cuda")])
+    pl2 = torch.cat([pl, torch.zeros(1, Hq, device="cuda")])
+    pa2 = torch.cat([pa, torch.zeros(1, Hq, d, device="cuda")])
+    out2 = torch.empty(Hq, d, device="cuda")
+    kv.launch_merge_partials(pm2, pl2, pa2, num_parts=shards + 1, query_heads=Hq, head_dim=d, output=out2)
+    o_ref, _ = ko.merge_partials(pm2.cpu().numpy(), pl2.cpu().numpy(), pa2.cpu().numpy())
+    assert np.max(np.abs(out2.cpu().numpy() - o_ref)) <= 1e-5
+
+
+def test_decode_workspace_too_small_and_bad_heads(cuda):
+    st = kv.AttentionLayerKvCacheStorage(64, kv.KvCacheQuantMode.kQ8Q8, kv_heads=8, head_dim=128, qblock=32)
+    q = torch.zeros(32, 128, device="cuda", dtype=torch.float16)
+    out = torch.zeros(32, 128, device="cuda")
+    with pytest.raises(kv.B200KvError) as e:
+        kv.launch_decode_attention_quant(st.view(), q, query_heads=32, scale=0.1, cache_length=64, output=out,
+                                         workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
+    assert e.value.status == -5
+    with pytest.raises(kv.B200KvError):
+        kv.launch_decode_attention_quant(st.view(), q, query_heads=30, scale=0.1, cache_length=64, output=out,
+                                         workspace=kv.decode_workspace(32, 128))

@@ -1,0 +1,148 @@
+"""GPU parity: suffix/prefill attention over a quantized prefix, and prefix
+snapshot/restore, against the oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import kvoracle as ko
+from gpu_util import assert_planes_equal, device_storage_like, to_dev, upload
+from miinfer_b200 import kv
+
+pytestmark = pytest.mark.gpu
+TOL = 2.0e-3
+
+
+def filled(rng, L, H, d, qb, mode, cap=None, std=1.0):
+    host = ko.HostCache(cap or L, H, d, qb, mode)
+    host.append(ko.normal_f16(rng, (L, H * d), std).astype(np.float32), ko.normal_f16(rng, (L, H * d), std).astype(np.float32),
+                None, 0, rope_mode=0)
+    return host
+
+
+# (prefix, suffix, d, H, Hq, qb, mode)
+SUFFIX = [
+    (64, 16, 256, 4, 24, 256, 3),     # the reference's own test ladder, tests/qwen3_quant_kv_attention_test.cpp:82-87
+    (512, 64, 256, 4, 24, 256, 3),
+    (512, 64, 256, 4, 24, 32, 3),     # same with q8_0 blocks (BASELINE config 3 format)
+    (100, 33, 256, 4, 24, 256, 1),
+    (100, 33, 256, 4, 24, 256, 2),
+    (0, 40, 256, 4, 24, 32, 3),       # cold prefill: no prefix at all
+    (300, 17, 128, 8, 32, 32, 3),
+]
+
+
+@pytest.mark.parametrize("P,T,d,H,Hq,qb,mode", SUFFIX)
+def test_suffix_attention_matches_reference(cuda, P, T, d, H, Hq, qb, mode):
+    rng = np.random.default_rng(P + T + mode)
+    host = filled(rng, P + T, H, d, qb, mode, cap=P + T + 128, std=0.5)   # N(0, 0.5) as the reference's test
+    st = upload(host)
+    q = (rng.standard_normal((T, Hq, d)) * 0.5).astype(np.float32)
+    gate = (rng.standard_normal((T, Hq, d)) * 0.5).astype(np.float32)
+    ref = host.suffix_ref(q, gate, P, d ** -0.5)
+    out = torch.full((T, Hq, d), float("nan"), device="cuda")
+    ws = kv.prefill_workspace(T, Hq, d)
+    kv.launch_suffix_attention_quant(st.view(), to_dev(q), to_dev(gate), out, ws, T, P, query_heads=Hq, scale=d ** -0.5)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    assert np.max(np.abs(got - ref)) <= TOL
+    # the reference's own gate for this path: cosine >= 0.999, MAE <= 0.05 (test :278)
+    cos = float((got * ref).sum() / (np.linalg.norm(got) * np.linalg.norm(ref) + 1e-12))
+    assert cos >= 0.999 and np.mean(np.abs(got - ref)) <= 0.05
+    # ungated + fp16 queries + device-side prefill state
+    q16 = q.astype(np.float16)
+    ref2 = host.suffix_ref(q16.astype(np.float32), None, P, d ** -0.5)
+    out2 = torch.empty((T, Hq, d), device="cuda")
+    kv.launch_suffix_attention_quant(st.view(), to_dev(q16), None, out2, ws, T, 0, query_heads=Hq, scale=d ** -0.5,
+                                     prefill_state=kv.make_prefill_state(P, T))
+    torch.cuda.synchronize()
+    assert np.max(np.abs(out2.cpu().numpy() - ref2)) <= TOL
+
+
+def test_suffix_is_causal_inside_the_chunk(cuda):
+    # changing a later chunk position must not change an earlier token's output
+    rng = np.random.default_rng(3)
+    P, T, d, H, Hq = 50, 12, 256, 4, 24
+    host = filled(rng, P + T, H, d, 32, 3)
+    st = upload(host)
+    q = to_dev(ko.normal_f16(rng, (T, Hq, d)))
+    ws = kv.prefill_workspace(T, Hq, d)
+    a = torch.empty((T, Hq, d), device="cuda")
+    kv.launch_suffix_attention_quant(st.view(), q, None, a, ws, T, P, query_heads=Hq, scale=d ** -0.5)
+    st.value_cache_q8[:, P + 6:] = 77
+    b = torch.empty((T, Hq, d), device="cuda")
+    kv.launch_suffix_attention_quant(st.view(), q, None, b, ws, T, P, query_heads=Hq, scale=d ** -0.5)
+    torch.cuda.synchronize()
+    assert torch.equal(a[:6], b[:6]) and not torch.equal(a[6:], b[6:])
+
+
+@pytest.mark.parametrize("mode,qb,d,H", [(3, 32, 128, 8), (3, 256, 256, 4), (1, 256, 256, 4), (2, 32, 256, 4), (0, 128, 128, 8)])
+def test_snapshot_save_restore_matches_reference_layout(cuda, mode, qb, d, H):
+    rng = np.random.default_rng(17 + mode)
+    cap, tokens = 97, 41
+    host = filled(rng, cap, H, d, qb, mode)
+    st = upload(host)
+    blob_ref = host.download_raw(tokens)
+    assert st.raw_tokens_bytes(tokens) == blob_ref.size
+    # save to pageable host, pinned host and device memory: identical bytes, identical to the oracle's layout
+    for dst in (torch.zeros(blob_ref.size, dtype=torch.uint8), torch.zeros(blob_ref.size, dtype=torch.uint8).pin_memory(),
+                torch.zeros(blob_ref.size, dtype=torch.uint8, device="cuda")):
+        st.download_raw(dst, tokens)
+        torch.cuda.synchronize()
+        assert np.array_equal(dst.cpu().numpy(), blob_ref)
+    # restore into a cache of another capacity: first `tokens` rows equal, the rest untouched (zero)
+    other_host = ko.HostCache(cap + 30, H, d, qb, mode)
+    other_host.upload_raw(blob_ref, tokens)
+    other = device_storage_like(other_host)
+    other.upload_raw(torch.from_numpy(blob_ref).pin_memory(), tokens)
+    torch.cuda.synchronize()
+    assert_planes_equal(other, other_host, "restore")
+    # device-to-device clone gives the same planes
+    third = device_storage_like(other_host)
+    third.clone_prefix_from(st, tokens)
+    torch.cuda.synchronize()
+    assert_planes_equal(third, other_host, "clone")
+    with pytest.raises(RuntimeError):
+        st.download_raw(torch.zeros(10, dtype=torch.uint8), cap + 1)     # the reference throws (kv_cache.cpp:228-230)
+
+
+def test_restored_session_decodes_like_the_original(cuda):
+    # cold vs restored outputs must be identical (the reference's persistent-session gate)
+    rng = np.random.default_rng(23)
+    H, Hq, d, P = 8, 32, 128, 4096
+    host = filled(rng, P, H, d, 32, 3, cap=P + 8)
+    st = upload(host)
+    blob = torch.zeros(st.raw_tokens_bytes(P), dtype=torch.uint8, device="cuda")
+    st.download_raw(blob, P)
+    restored = device_storage_like(host)
+    restored.upload_raw(blob, P)
+    q = to_dev(ko.normal_f16(rng, (Hq, d)))
+    ws = kv.decode_workspace(Hq, d)
+    outs = []
+    for s in (st, restored):
+        o = torch.empty(Hq, d, device="cuda")
+        kv.launch_decode_attention_quant(s.view(), q, query_heads=Hq, scale=d ** -0.5, cache_length=P, output=o, workspace=ws)
+        outs.append(o)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_native_cache_object_lifecycle(cuda):
+    import ctypes as C
+    from miinfer_b200._lib import View, lib
+
+    handle = C.c_void_p()
+    assert lib.b200kv_cache_create(C.byref(handle), 33, 8, 128, 32, 3) == 0
+    v = View()
+    assert lib.b200kv_cache_view(handle, C.byref(v)) == 0
+    assert v.capacity == 33 and v.key_q8 and v.key_scales and not v.key_f16
+    x = torch.randn(3, 1024, device="cuda", dtype=torch.float16)
+    assert lib.b200kv_append(C.byref(v), x.data_ptr(), x.data_ptr(), 0, None, 1, 1e6, 1e-6, 3, 4, None, None, None) == 0
+    blob = torch.zeros(lib.b200kv_snapshot_bytes(C.byref(v), 8), dtype=torch.uint8, device="cuda")
+    assert lib.b200kv_snapshot_save(C.byref(v), 8, blob.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    assert blob.count_nonzero().item() > 0
+    assert lib.b200kv_cache_reset(handle, None) == 0
+    assert lib.b200kv_snapshot_save(C.byref(v), 8, blob.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    assert blob.count_nonzero().item() == 0
+    assert lib.b200kv_cache_destroy(handle) == 0

@@ -1,0 +1,369 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-KV decode path (BASELINE.json metric).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload `decode32k`: a 36-layer Qwen3-8B-shaped KV decode sweep at 32K
+context (32 Q / 8 KV heads, d=128, q8_0 K/V, batch 1): per layer one fused
+append (fp16 K/V, NeoX RoPE) and one split-K GQA decode attention.  One "step"
+is one decode step over all 36 layers; `value` is decode tokens/s with the
+caches resident in HBM.  With N GPUs every rank decodes its own session (weak
+scaling, no data-path collective).  Other workloads (for tables in DESIGN.md):
+`seqshard` (one 128K-token session sharded by sequence over the ranks, NCCL
+all-gather of the per-rank partials + merge), `batched` (64 sessions of mixed
+length), `prefill` (512-token suffix over an 8K prefix, d=256).
+
+The `--impl reference` arm times the CPU restatement of the reference path
+(oracle/) on the host cores; the reference itself has no CPU implementation of
+the quantized path and its GPU code is HIP for gfx906 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for p in (str(ROOT), str(ROOT / "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+LAYERS, HQ, HKV, D, QB = 36, 32, 8, 128, 32
+ROW = D + 2 * (D // QB)  # 136 bytes per head-row
+THETA = 1.0e6
+
+# dram bytes per decode-attention launch measured by ncu (profiles/), scaled to a
+# 32K-context launch; None until a capture exists for the current kernel.
+NCU_TRAFFIC_BYTES_32K = None
+
+
+def measured_peak_gbs() -> tuple[float, str]:
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi during the timed region."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        out, _ = self.proc.communicate(timeout=5)
+        sm, mx, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = max(mx, float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle port on host cores
+# ---------------------------------------------------------------------------------
+
+def cpu_decode_sample(context: int, sample_layers: int, threads: int, repeats: int = 1) -> dict:
+    """Times `sample_layers` layers of one decode step (append + split-K attention) of the
+    oracle on `threads` host threads; returns tokens/s scaled to LAYERS layers."""
+    import numpy as np
+
+    import kvoracle as ko
+
+    ko.set_threads(threads)
+    rng = np.random.default_rng(42)
+    host = ko.HostCache(context + 8, HKV, D, QB, 3)
+    chunk = 4096
+    for base in range(0, context - 1, chunk):
+        n = min(chunk, context - 1 - base)
+        host.append(ko.normal_f16(rng, (n, HKV * D)).astype(np.float32), ko.normal_f16(rng, (n, HKV * D)).astype(np.float32),
+                    None, base, rope_mode=0)
+    q = ko.normal_f16(rng, (HQ, D)).astype(np.float32)
+    k_new = ko.normal_f16(rng, (1, HKV * D)).astype(np.float32)
+    v_new = ko.normal_f16(rng, (1, HKV * D)).astype(np.float32)
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        for _layer in range(sample_layers):   # the same cache stands in for each sampled layer (32K x 2176 B = 71 MB >> host L2)
+            host.append(k_new, v_new, None, context - 1, rope_mode=1, theta=THETA)
+            host.decode_splitk(q, D ** -0.5, context, 0)
+        best = min(best, time.perf_counter() - t0)
+    per_token = best * LAYERS / sample_layers
+    return {"value": 1.0 / per_token, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"{sample_layers} of {LAYERS} layers of one decode step at {context} context "
+                      f"(append + split-K attention, oracle/kv_oracle.c), scaled x{LAYERS}/{sample_layers}",
+            "seconds": best}
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    ctx = 32768
+    times = []
+    for _ in range(args.warmup):
+        cpu_decode_sample(ctx, 1, threads)
+    t_all = time.perf_counter()
+    res = None
+    for _ in range(args.steps):
+        res = cpu_decode_sample(ctx, 2, threads)
+        times.append(res["seconds"] * LAYERS / 2)
+    ms = 1000.0 * sum(times) / len(times)
+    value = 1000.0 / ms
+    line = {
+        "impl": "reference", "metric": "q8_0_kv_decode_tokens_per_s_32k_ctx", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 KV / fp32 accumulate", "data": "synthetic",
+        "config": workload_config("decode32k", ctx, 1),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": res["sample"]},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU restatement of the reference's HIP kernels (oracle/); the reference has no CPU implementation of "
+                "the quantized path and its GPU code is gfx906-only HIP",
+        "wall_s": time.perf_counter() - t_all,
+    }
+    print(json.dumps(line))
+
+
+def workload_config(name: str, context: int, n_gpus: int) -> dict:
+    return {"workload": f"{name}: {LAYERS}-layer Qwen3-8B-shaped KV decode step (BASELINE configs[1] at 32K context): "
+                        f"per layer fused append + split-K GQA attention, {HQ} Q / {HKV} KV heads, d={D}, q8_0 K/V "
+                        f"(32 int8 + fp16 scale), batch 1 per GPU",
+            "context": context, "layers": LAYERS, "sessions_per_gpu": 1, "parallelism": f"session-parallel x{n_gpus}",
+            "l2": "inputs larger than L2: 2.57 GB of KV per step vs 126 MB L2"}
+
+
+# ---------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------
+
+def fill_cache(kv, torch, storage, tokens: int, seed: int) -> None:
+    """Existing context: fp16 N(0,1) source rows quantised by the append kernel (no RoPE on filler rows)."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    chunk = 8192
+    width = storage.kv_heads * storage.head_dim
+    for base in range(0, tokens, chunk):
+        n = min(chunk, tokens - base)
+        k = torch.randn(n, width, generator=g, device="cuda", dtype=torch.float32).half()
+        v = torch.randn(n, width, generator=g, device="cuda", dtype=torch.float32).half()
+        kv.launch_kv_store_quant(storage.view(), k, v, None, n, base, rope_mode=kv.RopeMode.NONE)
+
+
+def run_decode32k(args, torch, dist, rank, world, local_rank):
+    from miinfer_b200 import kv
+
+    ctx = args.context
+    cap = ctx + args.warmup + 2 * args.steps + 128
+    dev = torch.device("cuda", local_rank)
+    caches = [kv.AttentionLayerKvCacheStorage(cap, kv.KvCacheQuantMode.kQ8Q8, kv_heads=HKV, head_dim=D, qblock=QB, device=dev)
+              for _ in range(LAYERS)]
+    for i, c in enumerate(caches):
+        fill_cache(kv, torch, c, ctx - 1, seed=1000 * rank + i)
+    views = [c.view() for c in caches]
+    g = torch.Generator(device="cuda")
+    g.manual_seed(4242 + rank)
+    q = torch.randn(LAYERS, HQ, D, generator=g, device=dev).half()
+    k_new = torch.randn(LAYERS, 1, HKV * D, generator=g, device=dev).half()
+    v_new = torch.randn(LAYERS, 1, HKV * D, generator=g, device=dev).half()
+    out = torch.zeros(LAYERS, HQ, D, device=dev)
+    ws = kv.decode_workspace(HQ, D, 1, device=dev)
+    state = kv.make_decode_state(ctx - 1, device=dev)   # position of the token being appended; length = position + 1
+    scale = D ** -0.5
+
+    def layer_pass():
+        for l in range(LAYERS):
+            kv.launch_kv_store_quant(views[l], k_new[l], v_new[l], None, 1, 0, rope_mode=kv.RopeMode.NEOX_FULL,
+                                     theta=THETA, decode_state=state)
+            kv.launch_decode_attention_quant(views[l], q[l], query_heads=HQ, scale=scale, decode_state=state,
+                                             output=out[l], workspace=ws)
+
+    def attention_only_pass():
+        for l in range(LAYERS):
+            kv.launch_decode_attention_quant(views[l], q[l], query_heads=HQ, scale=scale, decode_state=state,
+                                             output=out[l], workspace=ws)
+
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        layer_pass()                       # eager once (loads modules) before capture
+        stream.synchronize()
+        state[1] = ctx - 1
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            layer_pass()
+            state[1] += 1                  # device-side advance so the replay appends at the next position
+        attn_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(attn_graph, stream=stream):
+            attention_only_pass()
+    torch.cuda.synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput -------------------------------------------------
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            graph.replay()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+
+    # ---- dominant kernel: decode attention alone (stage 1 + merge launches), for the roofline -----
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            attn_graph.replay()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record(stream)
+        for _ in range(args.steps):
+            attn_graph.replay()
+        a1.record(stream)
+    torch.cuda.synchronize()
+    length_now = int(state[1].item())   # context length the attention-only replays scanned
+    attn_us = 1000.0 * a0.elapsed_time(a1) / (args.steps * LAYERS)
+    attn_bytes = length_now * HKV * ROW * 2 + HQ * D * 2 + HQ * D * 4
+
+    # ---- end to end through the public API with host buffers --------------------------------
+    h_q = torch.randn(LAYERS, HQ, D).half().pin_memory()
+    h_k = torch.randn(LAYERS, 1, HKV * D).half().pin_memory()
+    h_v = torch.randn(LAYERS, 1, HKV * D).half().pin_memory()
+    h_out = torch.empty(LAYERS, HQ, D).pin_memory()
+    e2e_steps = max(3, min(args.steps, 50))
+    with torch.cuda.stream(stream):
+        for i in range(3 + e2e_steps):
+            if i == 3:
+                stream.synchronize()
+                t0 = torch.cuda.Event(enable_timing=True)
+                t1 = torch.cuda.Event(enable_timing=True)
+                t0.record(stream)
+            q.copy_(h_q, non_blocking=True)
+            k_new.copy_(h_k, non_blocking=True)
+            v_new.copy_(h_v, non_blocking=True)
+            graph.replay()
+            h_out.copy_(out, non_blocking=True)
+            stream.synchronize()           # the caller needs the step's result before the next token
+        t1.record(stream)
+    barrier()
+    e2e_ms = t0.elapsed_time(t1) / e2e_steps
+
+    ms = torch.tensor([ms_total / args.steps, e2e_ms, attn_us], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_step, e2e_ms, attn_us = (float(x) for x in ms.tolist())
+    if rank != 0:
+        return None
+    peak, peak_kind = measured_peak_gbs()
+    achieved = attn_bytes / (attn_us * 1e-6) / 1e9
+    step_bytes = LAYERS * (attn_bytes + HKV * D * 2 * 2 + HKV * ROW * 2)
+    line = {
+        "metric": "q8_0_kv_decode_tokens_per_s_32k_ctx", "value": world * 1000.0 / ms_step, "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 KV / fp32 accumulate", "data": "synthetic",
+        "config": workload_config("decode32k", ctx, world),
+        "hbm_gbs_whole_step": step_bytes / (ms_step * 1e-3) / 1e9,
+        "hbm_frac_whole_step": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES_32K, "peak_kind": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs, burst copy)",
+                     "kernel": "decode attention launch (split-K stage 1 + merge)", "us_per_launch": attn_us,
+                     "algorithmic_bytes_per_launch": attn_bytes, "frac_of_nominal_8TBs": achieved / 8000.0},
+        "e2e": {"value": world * 1000.0 / e2e_ms, "unit": "tokens/s",
+                "h2d_bytes_per_step": int(h_q.numel() * 2 + h_k.numel() * 2 + h_v.numel() * 2),
+                "d2h_bytes_per_step": int(h_out.numel() * 4), "ms_per_step": e2e_ms},
+        "gpu_launches": args.steps * LAYERS * 3,
+        "clocks": clocks,
+    }
+    return line
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode32k")
+    ap.add_argument("--context", type=int, default=32768)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the KV path has no CPU fallback")
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+
+    if args.workload == "decode32k":
+        line = run_decode32k(args, torch, dist, rank, world, local_rank)
+    else:
+        from miinfer_b200 import workloads
+
+        line = workloads.run(args, torch, dist, rank, world, local_rank)
+    if rank == 0 and line is not None:
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            cpu = cpu_decode_sample(args.context, 2, threads)
+            cpu.pop("seconds", None)
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -183,7 +183,7 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
     from miinfer_b200 import kv
 
     ctx = args.context
-    cap = ctx + args.warmup + 2 * args.steps + 128
+    cap = (ctx + args.warmup + 2 * args.steps + 128 + 63) // 64 * 64
     dev = torch.device("cuda", local_rank)
     caches = [kv.AttentionLayerKvCacheStorage(cap, kv.KvCacheQuantMode.kQ8Q8, kv_heads=HKV, head_dim=D, qblock=QB, device=dev)
               for _ in range(LAYERS)]
@@ -323,9 +323,12 @@ def main() -> None:
     ap.add_argument("--workload", default="decode32k")
     ap.add_argument("--context", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=36, help="layers per step (36 = the benchmark; fewer only for ncu captures)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
+    global LAYERS
+    LAYERS = args.layers
 
     if args.impl == "reference":
         run_reference_arm(args)

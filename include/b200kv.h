@@ -175,6 +175,12 @@ B200KV_API int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_
                        uint32_t cache_length, const b200kv_decode_state* decode_state,
                        void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream);
 
+/* Which stage-1 kernel b200kv_decode_attn picks for this view: 1 = the streaming
+ * int8 kernel (int8 K and V, head_dim 128, 1/2/4 query heads per kv head,
+ * capacity a multiple of 8), 0 = the generic kernel (every other mode and shape).
+ * No counterpart in the reference. */
+B200KV_API int b200kv_decode_kernel_kind(const b200kv_view* view, uint32_t query_heads);
+
 /* Batched decode over `sessions` independent caches of one geometry (no
  * counterpart in the reference, which keeps one session resident,
  * tools/miinfer_cli.cpp:5663-5676).  views: HOST array of `sessions` views
@@ -182,8 +188,11 @@ B200KV_API int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_
  * lengths: DEVICE array of `sessions` uint32 cache lengths; max_length: host
  * upper bound of those lengths (sizes the launch).  q/gate/output/gated_output:
  * [sessions][query_heads][head_dim].  view_table: DEVICE scratch of
- * sessions*sizeof(b200kv_view) bytes that this call fills (it may be reused
- * across calls with the same views by passing views == NULL). */
+ * b200kv_view_table_bytes(sessions) bytes, 128-byte aligned, that this call
+ * fills with the views and their TMA descriptors (one blocking copy); pass
+ * views == NULL to reuse the table of an earlier call with the same sessions,
+ * e.g. on every decode step after the first. */
+B200KV_API size_t b200kv_view_table_bytes(uint32_t sessions);
 B200KV_API int b200kv_decode_attn_batched(const b200kv_view* views, void* view_table, const uint32_t* lengths,
                                uint32_t sessions, uint32_t max_length, const void* q, int q_dtype,
                                const float* gate, float* output, float* gated_output,

@@ -12,6 +12,8 @@
 #include "decode_common.cuh"
 
 #include <cmath>
+#include <cstring>
+#include <vector>
 
 namespace b200kv {
 
@@ -178,8 +180,7 @@ int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max
     const bool force_generic = (num_splits_arg & 0x80000000u) != 0;
     uint32_t num_splits = num_splits_arg & 0x7fffffffu;
     const uint32_t cap = max_splits_per_session(p.sessions);
-    const bool q8q8 = geometry.quant_mode == B200KV_Q8_Q8;
-    bool use_fast = q8q8 && !force_generic;
+    bool use_fast = !force_generic && q8_fast_path_ok(geometry, p.query_heads);
     if (num_splits == 0) {
         uint32_t fast = use_fast ? pick_splits_q8(geometry, p.query_heads, p.sessions, max_length) : 0;
         if (fast == 0) use_fast = false;
@@ -215,6 +216,13 @@ static int check_heads(const b200kv_view* view, uint32_t query_heads, float scal
 using namespace b200kv;
 
 extern "C" {
+
+int b200kv_decode_kernel_kind(const b200kv_view* view, uint32_t query_heads) {
+    if (validate_view(view) != B200KV_OK) return 0;
+    return q8_fast_path_ok(*view, query_heads) ? 1 : 0;
+}
+
+size_t b200kv_view_table_bytes(uint32_t sessions) { return sizeof(SessionEntry) * static_cast<size_t>(sessions ? sessions : 1); }
 
 size_t b200kv_decode_workspace_bytes(uint32_t query_heads, uint32_t head_dim, uint32_t sessions) {
     if (sessions == 0) sessions = 1;
@@ -273,6 +281,7 @@ int b200kv_decode_attn_batched(const b200kv_view* views, void* view_table, const
     if (q_dtype != B200KV_F16 && q_dtype != B200KV_F32) return B200KV_ERR_INVALID;
     if (sessions > 65535) return B200KV_ERR_UNSUPPORTED;
     int rc;
+    bool geometry_fast = false;
     if ((rc = ensure_device()) != B200KV_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     b200kv_view geometry;
@@ -284,24 +293,44 @@ int b200kv_decode_attn_batched(const b200kv_view* views, void* view_table, const
                 return B200KV_ERR_INVALID;
         }
         geometry = views[0];
-        B200KV_CUDA_TRY(cudaMemcpyAsync(view_table, views, sizeof(b200kv_view) * sessions, cudaMemcpyHostToDevice, s));
-    } else {
-        // the table already holds the views of an earlier call: fetch the geometry of entry 0
-        B200KV_CUDA_TRY(cudaMemcpyAsync(&geometry, view_table, sizeof geometry, cudaMemcpyDeviceToHost, s));
+        // Entries are staged in host memory and copied once; the copy from pageable memory completes
+        // (as far as the host buffer is concerned) before cudaMemcpyAsync returns.
+        std::vector<SessionEntry> staged(sessions);
+        bool fast_ok = true;
+        for (uint32_t i = 0; i < sessions; ++i) {
+            std::memset(&staged[i], 0, sizeof(SessionEntry));
+            staged[i].view = views[i];
+            if (!q8_fast_path_ok(views[i], query_heads) || encode_k_map(views[i], &staged[i].kmap) != B200KV_OK) fast_ok = false;
+        }
+        if (!fast_ok)
+            for (uint32_t i = 0; i < sessions; ++i) std::memset(&staged[i].kmap, 0, sizeof(CUtensorMap));
+        geometry_fast = fast_ok;
+        B200KV_CUDA_TRY(cudaMemcpyAsync(view_table, staged.data(), sizeof(SessionEntry) * sessions, cudaMemcpyHostToDevice, s));
         B200KV_CUDA_TRY(cudaStreamSynchronize(s));
+    } else {
+        // the table already holds the entries of an earlier call: fetch the geometry of entry 0
+        SessionEntry first;
+        B200KV_CUDA_TRY(cudaMemcpyAsync(&first, view_table, sizeof first, cudaMemcpyDeviceToHost, s));
+        B200KV_CUDA_TRY(cudaStreamSynchronize(s));
+        geometry = first.view;
         if ((rc = validate_view(&geometry)) != B200KV_OK) return rc;
+        // an all-zero descriptor marks a table whose sessions cannot take the streaming kernel
+        const uint64_t* words = reinterpret_cast<const uint64_t*>(&first.kmap);
+        geometry_fast = false;
+        for (int w = 0; w < 16; ++w) geometry_fast = geometry_fast || words[w] != 0;
     }
     if ((rc = check_heads(&geometry, query_heads, scale)) != B200KV_OK) return rc;
 
     DecodeParams p{};
     p.view = geometry;
-    p.views = static_cast<const b200kv_view*>(view_table);
+    p.views = static_cast<const SessionEntry*>(view_table);
     p.lengths = lengths;
     p.sessions = sessions;
     p.q = q;
     p.q_is_f16 = (q_dtype == B200KV_F16);
     p.query_heads = query_heads;
     p.scale = scale;
+    if (!geometry_fast) num_splits |= B200KV_SPLITS_FORCE_GENERIC;
     rc = run_decode_stage1(p, geometry, max_length, workspace, workspace_bytes, num_splits, s);
     if (rc != B200KV_OK) return rc;
 

@@ -3,7 +3,18 @@
 
 #include "kv_common.cuh"
 
+#include <cuda.h>  // CUtensorMap and its enums only; the encoder is fetched at run time, libcuda is not linked
+
 namespace b200kv {
+
+// One session of a batched launch as it sits in the device-side view table: the
+// TMA descriptor of its int8 K plane followed by its view.
+struct alignas(128) SessionEntry {
+    CUtensorMap kmap;
+    b200kv_view view;
+    uint8_t pad[128 - sizeof(b200kv_view)];
+};
+static_assert(sizeof(SessionEntry) == 256, "table entry layout");
 
 // Upper bound on split slots per launch: slots = sessions * splits_per_session.
 constexpr uint32_t kMaxSplitsPerSession = 128;
@@ -17,7 +28,7 @@ inline uint32_t max_splits_per_session(uint32_t sessions) {
 
 struct DecodeParams {
     b200kv_view view;                        // single-session launch
-    const b200kv_view* views;                // device table [sessions], or null
+    const SessionEntry* views;               // device table [sessions], or null
     const uint32_t* lengths;                 // device [sessions], or null
     const b200kv_decode_state* decode_state; // device, or null
     uint32_t cache_length;                   // used when neither of the above is given
@@ -60,7 +71,7 @@ __device__ __forceinline__ void resolve_range(const DecodeParams& p, uint32_t se
 }
 
 __device__ __forceinline__ const b200kv_view& session_view(const DecodeParams& p, uint32_t session) {
-    return p.views != nullptr ? p.views[session] : p.view;
+    return p.views != nullptr ? p.views[session].view : p.view;
 }
 
 struct MergeParams {
@@ -89,5 +100,9 @@ int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max
 // the geometry has no specialised kernel, so the caller can use the generic one.
 int launch_decode_q8(const DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, cudaStream_t stream);
 uint32_t pick_splits_q8(const b200kv_view& geometry, uint32_t query_heads, uint32_t sessions, uint32_t max_length);
+// TMA descriptor of a view's int8 K plane (rows of head_dim bytes, 128-byte swizzle).  B200KV_ERR_UNSUPPORTED
+// when the view cannot take the streaming kernel (then `out` is zeroed and the generic kernel is used).
+int encode_k_map(const b200kv_view& view, CUtensorMap* out);
+bool q8_fast_path_ok(const b200kv_view& view, uint32_t query_heads);
 
 }  // namespace b200kv

@@ -21,8 +21,8 @@ __all__ = [
     "KvCacheQuantMode", "RopeMode", "AttentionKvCacheView", "AttentionLayerKvCacheStorage",
     "launch_kv_store_quant", "launch_decode_attention_quant", "launch_decode_attention_batched",
     "launch_decode_partials", "launch_merge_partials", "launch_suffix_attention_quant",
-    "decode_workspace", "prefill_workspace", "make_decode_state", "make_prefill_state",
-    "token_sequence_hash", "B200KvError", "FORCE_GENERIC",
+    "decode_workspace", "prefill_workspace", "view_table", "make_decode_state", "make_prefill_state",
+    "token_sequence_hash", "decode_kernel_kind", "B200KvError", "FORCE_GENERIC",
 ]
 
 FORCE_GENERIC = 0x80000000
@@ -164,6 +164,11 @@ def decode_workspace(query_heads: int, head_dim: int, sessions: int = 1, device=
     return torch.empty(n, dtype=torch.uint8, device=device or "cuda")
 
 
+def view_table(sessions: int, device=None) -> torch.Tensor:
+    """Device scratch for launch_decode_attention_batched (views + TMA descriptors per session)."""
+    return torch.zeros(int(lib.b200kv_view_table_bytes(sessions)), dtype=torch.uint8, device=device or "cuda")
+
+
 def prefill_workspace(token_count: int, query_heads: int, head_dim: int, device=None) -> torch.Tensor:
     n = int(lib.b200kv_prefill_workspace_bytes(token_count, query_heads, head_dim))
     return torch.empty(n, dtype=torch.uint8, device=device or "cuda")
@@ -240,6 +245,11 @@ def launch_suffix_attention_quant(view: View, q: torch.Tensor, gate: Optional[to
     check(lib.b200kv_prefill_attn(C.byref(view), _ptr(q), _dtype(q), _ptr(gate), _ptr(gated_output), token_count,
                                   base_position, query_heads, scale, _ptr(prefill_state), _ptr(workspace),
                                   workspace.numel(), _stream(stream)), "b200kv_prefill_attn")
+
+
+def decode_kernel_kind(view: View, query_heads: int) -> int:
+    """1 if decode attention on this view runs the streaming int8 kernel, 0 for the generic one."""
+    return int(lib.b200kv_decode_kernel_kind(C.byref(view), query_heads))
 
 
 def token_sequence_hash(tokens) -> int:

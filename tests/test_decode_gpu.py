@@ -52,8 +52,11 @@ SHAPES = [
 @pytest.mark.parametrize("path", ["auto", "generic"])
 def test_decode_matches_two_pass_reference(cuda, d, H, Hq, qb, mode, L, path):
     rng = np.random.default_rng(d + L + mode)
-    host = filled(rng, L, H, d, qb, mode, cap=L + 5)
+    host = filled(rng, L, H, d, qb, mode, cap=(L + 5 + 7) // 8 * 8)
     st = upload(host)
+    v = st.view()
+    streaming = mode == 3 and d == 128 and Hq // H in (1, 2, 4)
+    assert kv.decode_kernel_kind(v, Hq) == (1 if streaming else 0)
     q16 = ko.normal_f16(rng, (Hq, d))
     gate = rng.standard_normal((Hq, d)).astype(np.float32)
     ref, ref_g = host.decode_ref(q16.astype(np.float32), d ** -0.5, L, gate)
@@ -62,6 +65,17 @@ def test_decode_matches_two_pass_reference(cuda, d, H, Hq, qb, mode, L, path):
         out, gated = gpu_decode(st, q_dev, Hq, d ** -0.5, L, gate=to_dev(gate), num_splits=flag)
         assert np.max(np.abs(out - ref)) <= TOL, np.max(np.abs(out - ref))
         assert np.max(np.abs(gated - ref_g)) <= TOL
+
+
+def test_decode_odd_capacity_uses_generic_kernel_and_still_matches(cuda):
+    rng = np.random.default_rng(12)
+    host = filled(rng, 700, 8, 128, 32, 3, cap=701)     # scale-plane tiles would not be 16-byte aligned
+    st = upload(host)
+    assert kv.decode_kernel_kind(st.view(), 32) == 0
+    q16 = ko.normal_f16(rng, (32, 128))
+    ref, _ = host.decode_ref(q16.astype(np.float32), 128 ** -0.5, 700)
+    out, _ = gpu_decode(st, to_dev(q16), 32, 128 ** -0.5, 700)
+    assert np.max(np.abs(out - ref)) <= TOL
 
 
 def test_decode_split_count_invariance_and_determinism(cuda):
@@ -137,10 +151,10 @@ def test_decode_batched_variable_lengths(cuda):
     rng = np.random.default_rng(9)
     H, Hq, d = 8, 32, 128
     lengths = [1, 37, 512, 1300, 64, 2049]
-    hosts = [filled(rng, L, H, d, 32, 3, cap=L + 7) for L in lengths]
+    hosts = [filled(rng, L, H, d, 32, 3, cap=(L + 7 + 7) // 8 * 8) for L in lengths]
     sts = [upload(h) for h in hosts]
     q16 = ko.normal_f16(rng, (len(lengths), Hq, d))
-    table = torch.empty(len(lengths) * 80, dtype=torch.uint8, device="cuda")
+    table = kv.view_table(len(lengths))
     lens = torch.tensor(lengths, dtype=torch.int32, device="cuda")
     ws = kv.decode_workspace(Hq, d, len(lengths))
     for flag in (0, kv.FORCE_GENERIC):
@@ -156,7 +170,9 @@ def test_decode_batched_variable_lengths(cuda):
     kv.launch_decode_attention_batched(None, table, lens, max(lengths), to_dev(q16), query_heads=Hq, scale=d ** -0.5,
                                        output=out2, workspace=ws)
     torch.cuda.synchronize()
-    assert torch.equal(out, out2) or np.max(np.abs((out - out2).cpu().numpy())) <= 2e-5
+    for i, h in enumerate(hosts):
+        ref, _ = h.decode_ref(q16[i].astype(np.float32), d ** -0.5, lengths[i])
+        assert np.max(np.abs(out2[i].cpu().numpy() - ref)) <= TOL, i
 
 
 def test_sequence_shard_partials_merge_to_full_attention(cuda):

@@ -212,6 +212,9 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
             kv.launch_decode_attention_quant(views[l], q[l], query_heads=HQ, scale=scale, decode_state=state,
                                              output=out[l], workspace=ws)
 
+    # consecutive layers' kernels may overlap their ramp-up and tail (programmatic dependent launch);
+    # one trailing cache row -- the token appended by the preceding kernel -- is guarded
+    kv.set_launch_overlap(0 if args.no_overlap else 1)
     stream = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):
         layer_pass()                       # eager once (loads modules) before capture
@@ -323,6 +326,7 @@ def main() -> None:
     ap.add_argument("--workload", default="decode32k")
     ap.add_argument("--context", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true", help="launch every kernel fully serialised (A/B of launch overlap)")
     ap.add_argument("--layers", type=int, default=36, help="layers per step (36 = the benchmark; fewer only for ncu captures)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

@@ -118,6 +118,23 @@ B200KV_API const char* b200kv_last_cuda_error(void);
 /* sm_100 guard; replaces validate_device (src/device_validation.cpp:60-95), which accepts gfx906 only. */
 B200KV_API int b200kv_device_check(int device);
 
+/* Launch overlap (off by default; process-wide; no counterpart in the reference,
+ * which replays a HIP graph of fully serialised kernels, src/prefill_v2/model.cpp:1136-1197).
+ * With tail_positions > 0 the append and streaming decode kernels are launched
+ * with programmatic stream serialization: a kernel may become resident and
+ * start streaming OLD cache rows while the previous kernel of the stream is
+ * still finishing -- this hides launch ramp and tail between the layers of a
+ * decode step.  The kernels order themselves: everything a preceding kernel may
+ * produce -- Q, gate, the workspace, outputs, and the last `tail_positions`
+ * rows of the scanned cache range -- is only touched after that kernel has
+ * completed (griddepcontrol.wait).  Set tail_positions >= the number of rows
+ * the preceding kernel can append (1 in a decode loop).  Device-side state
+ * (decode_state, lengths) is read early, so it must not be written by a kernel
+ * that itself triggers dependents early; kernels of this library never do, and
+ * an ordinary kernel between two launches acts as a full barrier.  0 turns the
+ * overlap off again. */
+B200KV_API int b200kv_set_launch_overlap(uint32_t tail_positions);
+
 /* ---- cache storage ---------------------------------------------------------
  * Replaces class AttentionLayerKvCacheStorage (kv_cache.hpp:49-122,
  * src/prefill_v2/kv_cache.cpp:10-130): owns the 2-4 device planes of one layer. */
@@ -158,7 +175,11 @@ B200KV_API int b200kv_append(const b200kv_view* view, const void* key, const voi
 
 /* Workspace bytes for the split-K partials of one decode launch over
  * `sessions` sessions.  The reference keeps these in file-scope __device__
- * arrays sized for 24 heads (.hip:2104-2113); here the caller owns them. */
+ * arrays sized for 24 heads (.hip:2104-2113); here the caller owns them.
+ * The workspace must be 16-byte aligned and ZERO-FILLED ONCE before its first
+ * use (cudaMemset): its head holds the arrival counters of the fused merge,
+ * which every launch leaves at zero again.  One workspace serves one launch at
+ * a time (launches that overlap on the GPU need separate workspaces). */
 B200KV_API size_t b200kv_decode_workspace_bytes(uint32_t query_heads, uint32_t head_dim, uint32_t sessions);
 
 /* Replaces launch_qwen35_tiled_online_attention_quant_dynamic

@@ -6,9 +6,11 @@ if the shared object is missing or a symbol is absent, importing fails.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "lib" / "libb200kv.so"
+# B200KV_LIBRARY points the binding at another build of the same library (A/B measurements).
+LIB_PATH = Path(os.environ.get("B200KV_LIBRARY") or Path(__file__).resolve().parent / "lib" / "libb200kv.so")
 
 
 class View(C.Structure):
@@ -33,6 +35,7 @@ SIGNATURES = {
     "b200kv_status_string": (C.c_char_p, [i32]),
     "b200kv_last_cuda_error": (C.c_char_p, []),
     "b200kv_device_check": (i32, [i32]),
+    "b200kv_set_launch_overlap": (i32, [u32]),
     "b200kv_cache_bytes": (sz, [u64, u32, u32, u32, u32]),
     "b200kv_cache_create": (i32, [C.POINTER(vp), u64, u32, u32, u32, u32]),
     "b200kv_cache_destroy": (i32, [vp]),

@@ -18,6 +18,7 @@
 #include "kv_common.cuh"
 
 #include <cmath>
+#include <type_traits>
 
 namespace b200kv {
 
@@ -76,6 +77,10 @@ __global__ void __launch_bounds__(kAppendWarps * 32)
 append_kernel(const __grid_constant__ AppendParams p) {
     constexpr int NJ = D / 32;
     __shared__ __align__(16) int8_t stage[kAppendWarps][2][D];
+    // Let the next kernel of the stream become resident now (it orders itself against this one), then wait
+    // for everything before us: K/V inputs and the device-side position come from preceding kernels.
+    pdl_launch_dependents();
+    pdl_wait();
 
     uint32_t base_position = p.base_position;
     uint32_t token_count = p.token_count;
@@ -221,13 +226,15 @@ extern "C" int b200kv_append(const b200kv_view* view, const void* key, const voi
     const unsigned grid = static_cast<unsigned>((rows + kAppendWarps - 1) / kAppendWarps);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool f16 = (dtype == B200KV_F16);
+    const dim3 block(kAppendWarps * 32);
+    cudaError_t err;
     if (view->head_dim == 128) {
-        if (f16) append_kernel<128, true><<<grid, kAppendWarps * 32, 0, s>>>(p);
-        else append_kernel<128, false><<<grid, kAppendWarps * 32, 0, s>>>(p);
+        err = f16 ? launch_kernel(append_kernel<128, true>, grid, block, 0, s, true, p)
+                  : launch_kernel(append_kernel<128, false>, grid, block, 0, s, true, p);
     } else {
-        if (f16) append_kernel<256, true><<<grid, kAppendWarps * 32, 0, s>>>(p);
-        else append_kernel<256, false><<<grid, kAppendWarps * 32, 0, s>>>(p);
+        err = f16 ? launch_kernel(append_kernel<256, true>, grid, block, 0, s, true, p)
+                  : launch_kernel(append_kernel<256, false>, grid, block, 0, s, true, p);
     }
-    B200KV_CUDA_TRY(cudaGetLastError());
+    B200KV_CUDA_TRY(err);
     return B200KV_OK;
 }

@@ -107,28 +107,50 @@ __global__ void __launch_bounds__(32) decode_generic_kernel(const __grid_constan
 }
 
 // ---------------------------------------------------------------------------
-// Merge (stage 2): one block per (head, group), one thread per dim.
+// Merge (stage 2): one block per (head, group), one thread per dim.  The (m, l)
+// of all parts are staged in shared memory first so the accumulation is a run
+// of independent loads.  A part with l <= 0 or m == -inf is empty and skipped
+// (gfx906/kernels/qwen3_primitives.hip:6681,6701); a NaN part propagates.
 // ---------------------------------------------------------------------------
 __global__ void merge_kernel(const __grid_constant__ MergeParams p) {
+    extern __shared__ float sh[];   // a[num_parts], then gmax, gsum
     const uint32_t head = blockIdx.x, group = blockIdx.y, dim = threadIdx.x;
-    const uint32_t H = p.query_heads, D = p.head_dim;
-    const size_t base = static_cast<size_t>(group) * p.num_parts * H + head;
-    float gmax = -INFINITY;
-    for (uint32_t s = 0; s < p.num_parts; ++s) {
-        const float m = p.part_m[base + static_cast<size_t>(s) * H];
-        const float l = p.part_l[base + static_cast<size_t>(s) * H];
-        if (l > 0.0f && isfinite(m)) gmax = fmaxf(gmax, m);
+    const uint32_t H = p.query_heads, D = p.head_dim, S = p.num_parts;
+    const size_t base = static_cast<size_t>(group) * S * H + head;
+    float* sa = sh;
+    float* sl = sh + S;
+    for (uint32_t s = dim; s < S; s += blockDim.x) {
+        sa[s] = p.part_m[base + static_cast<size_t>(s) * H];
+        sl[s] = p.part_l[base + static_cast<size_t>(s) * H];
     }
-    float gsum = 0.0f, total = 0.0f;
-    for (uint32_t s = 0; s < p.num_parts; ++s) {
-        const size_t idx = base + static_cast<size_t>(s) * H;
-        const float m = p.part_m[idx], l = p.part_l[idx];
-        if (l > 0.0f && isfinite(m)) {
-            const float a = __expf(m - gmax);
-            gsum = fmaf(l, a, gsum);
-            total = fmaf(p.part_acc[idx * D + dim], a, total);
+    __syncthreads();
+    if (dim < 32) {
+        float gmax = -INFINITY;
+        for (uint32_t s = dim; s < S; s += 32)
+            if (!(sl[s] <= 0.0f) && sa[s] != -INFINITY) gmax = fmaxf(gmax, sa[s]);
+        gmax = warp_max(gmax);
+        float gsum = 0.0f;
+        for (uint32_t s = dim; s < S; s += 32) {
+            const float a = (!(sl[s] <= 0.0f) && sa[s] != -INFINITY) ? __expf(sa[s] - gmax) : 0.0f;
+            gsum = fmaf(sl[s], a, gsum);
+            sa[s] = a;
         }
+        gsum = warp_sum(gsum);
+        if (dim == 0) { sh[2 * S] = gmax; sh[2 * S + 1] = gsum; }
     }
+    __syncthreads();
+    const float gmax = sh[2 * S], gsum = sh[2 * S + 1];
+    const float* accp = p.part_acc + base * D + dim;
+    const size_t stride = static_cast<size_t>(H) * D;
+    float t0 = 0.0f, t1 = 0.0f, t2 = 0.0f, t3 = 0.0f;
+    uint32_t s = 0;
+    for (; s + 4 <= S; s += 4) {
+        const float a0 = accp[(s + 0) * stride], a1 = accp[(s + 1) * stride];
+        const float a2 = accp[(s + 2) * stride], a3 = accp[(s + 3) * stride];
+        t0 = fmaf(a0, sa[s], t0); t1 = fmaf(a1, sa[s + 1], t1); t2 = fmaf(a2, sa[s + 2], t2); t3 = fmaf(a3, sa[s + 3], t3);
+    }
+    for (; s < S; ++s) t0 = fmaf(accp[s * stride], sa[s], t0);
+    const float total = (t0 + t1) + (t2 + t3);
     const size_t out_idx = (static_cast<size_t>(group) * H + head) * D + dim;
     if (p.out_m != nullptr) {
         p.out_acc[out_idx] = total;
@@ -138,7 +160,7 @@ __global__ void merge_kernel(const __grid_constant__ MergeParams p) {
         }
         return;
     }
-    const float o = gsum > 0.0f ? total / gsum : 0.0f;
+    const float o = gsum > 0.0f ? total / gsum : (gsum == gsum ? 0.0f : gsum);
     if (p.output != nullptr) p.output[out_idx] = o;
     if (p.gated_output != nullptr) {
         float g = o;
@@ -148,7 +170,8 @@ __global__ void merge_kernel(const __grid_constant__ MergeParams p) {
 }
 
 int launch_merge(const MergeParams& p, uint32_t groups, cudaStream_t stream) {
-    merge_kernel<<<dim3(p.query_heads, groups), p.head_dim, 0, stream>>>(p);
+    if (p.num_parts > 4096) return B200KV_ERR_UNSUPPORTED;
+    merge_kernel<<<dim3(p.query_heads, groups), p.head_dim, (2 * p.num_parts + 2) * sizeof(float), stream>>>(p);
     B200KV_CUDA_TRY(cudaGetLastError());
     return B200KV_OK;
 }
@@ -173,12 +196,20 @@ static void launch_generic(const DecodeParams& p, uint32_t mode, dim3 grid, cuda
     }
 }
 
-// Runs stage 1 (fast kernel if available, else generic) into the workspace.
-// `force_generic` is a debugging/testing switch carried in the top bit of num_splits.
+size_t decode_counter_bytes(uint32_t query_heads, uint32_t sessions) {
+    // one uint32 per (session, kv head); kv_heads <= query_heads.  Rounded so the partials stay 256-byte aligned.
+    const size_t raw = static_cast<size_t>(sessions ? sessions : 1) * query_heads * sizeof(uint32_t);
+    return (raw + 255) / 256 * 256;
+}
+
+// Runs stage 1 (streaming kernel if available, else generic) into the workspace.
+// Workspace layout: [counters (zero between launches)] [m] [l] [acc].
 int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, void* workspace,
-                      size_t workspace_bytes, uint32_t num_splits_arg, cudaStream_t stream) {
-    const bool force_generic = (num_splits_arg & 0x80000000u) != 0;
-    uint32_t num_splits = num_splits_arg & 0x7fffffffu;
+                      size_t workspace_bytes, uint32_t num_splits_arg, const MergeParams& merge, bool* merged,
+                      cudaStream_t stream) {
+    *merged = false;
+    const bool force_generic = (num_splits_arg & B200KV_SPLITS_FORCE_GENERIC) != 0;
+    uint32_t num_splits = num_splits_arg & ~B200KV_SPLITS_FORCE_GENERIC;
     const uint32_t cap = max_splits_per_session(p.sessions);
     bool use_fast = !force_generic && q8_fast_path_ok(geometry, p.query_heads);
     if (num_splits == 0) {
@@ -187,22 +218,41 @@ int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max
         num_splits = use_fast ? fast : pick_splits_generic(p.query_heads, p.sessions, max_length);
     }
     if (num_splits > cap) num_splits = cap;
+    const size_t counter_bytes = decode_counter_bytes(p.query_heads, p.sessions);
     const size_t slots = static_cast<size_t>(p.sessions) * num_splits * p.query_heads;
-    const size_t need = slots * (geometry.head_dim + 2u) * sizeof(float);
+    const size_t need = counter_bytes + slots * (geometry.head_dim + 2u) * sizeof(float);
     if (workspace == nullptr || workspace_bytes < need) return B200KV_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return B200KV_ERR_INVALID;
     p.num_splits = num_splits;
-    p.ws_m = static_cast<float*>(workspace);
+    p.ws_m = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + counter_bytes);
     p.ws_l = p.ws_m + slots;
     p.ws_acc = p.ws_l + slots;
     if (use_fast) {
+        p.counters = static_cast<uint32_t*>(workspace);
+        p.fuse = merge;
         int rc = launch_decode_q8(p, geometry, max_length, stream);
+        if (rc == B200KV_OK) *merged = true;
         if (rc != B200KV_ERR_UNSUPPORTED) return rc;
+        p.counters = nullptr;
     }
     dim3 grid(p.query_heads, num_splits, p.sessions);
     if (geometry.head_dim == 128) launch_generic<128>(p, geometry.quant_mode, grid, stream);
     else launch_generic<256>(p, geometry.quant_mode, grid, stream);
     B200KV_CUDA_TRY(cudaGetLastError());
     return B200KV_OK;
+}
+
+// Stage 1 followed (unless the kernel merged by itself) by the merge kernel.
+int run_decode(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, void* workspace, size_t workspace_bytes,
+               uint32_t num_splits_arg, MergeParams mp, uint32_t groups, cudaStream_t stream) {
+    bool merged = false;
+    int rc = run_decode_stage1(p, geometry, max_length, workspace, workspace_bytes, num_splits_arg, mp, &merged, stream);
+    if (rc != B200KV_OK || merged) return rc;
+    mp.part_m = p.ws_m;
+    mp.part_l = p.ws_l;
+    mp.part_acc = p.ws_acc;
+    mp.num_parts = p.num_splits;
+    return launch_merge(mp, groups, stream);
 }
 
 static int check_heads(const b200kv_view* view, uint32_t query_heads, float scale) {
@@ -227,7 +277,7 @@ size_t b200kv_view_table_bytes(uint32_t sessions) { return sizeof(SessionEntry) 
 size_t b200kv_decode_workspace_bytes(uint32_t query_heads, uint32_t head_dim, uint32_t sessions) {
     if (sessions == 0) sessions = 1;
     const size_t slots = static_cast<size_t>(sessions) * max_splits_per_session(sessions) * query_heads;
-    return slots * (head_dim + 2u) * sizeof(float);
+    return decode_counter_bytes(query_heads, sessions) + slots * (head_dim + 2u) * sizeof(float);
 }
 
 int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
@@ -254,20 +304,13 @@ int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_dtype, cons
     p.scale = scale;
     // with a device-side length the launch is sized for the whole cache
     const uint32_t max_length = decode_state ? static_cast<uint32_t>(view->capacity) : cache_length;
-    rc = run_decode_stage1(p, *view, max_length, workspace, workspace_bytes, num_splits, s);
-    if (rc != B200KV_OK) return rc;
-
     MergeParams mp{};
-    mp.part_m = p.ws_m;
-    mp.part_l = p.ws_l;
-    mp.part_acc = p.ws_acc;
-    mp.num_parts = p.num_splits;
     mp.query_heads = query_heads;
     mp.head_dim = view->head_dim;
     mp.gate = gate;
     mp.output = output;
     mp.gated_output = gated_output;
-    return launch_merge(mp, 1, s);
+    return run_decode(p, *view, max_length, workspace, workspace_bytes, num_splits, mp, 1, s);
 }
 
 int b200kv_decode_attn_batched(const b200kv_view* views, void* view_table, const uint32_t* lengths,
@@ -331,20 +374,13 @@ int b200kv_decode_attn_batched(const b200kv_view* views, void* view_table, const
     p.query_heads = query_heads;
     p.scale = scale;
     if (!geometry_fast) num_splits |= B200KV_SPLITS_FORCE_GENERIC;
-    rc = run_decode_stage1(p, geometry, max_length, workspace, workspace_bytes, num_splits, s);
-    if (rc != B200KV_OK) return rc;
-
     MergeParams mp{};
-    mp.part_m = p.ws_m;
-    mp.part_l = p.ws_l;
-    mp.part_acc = p.ws_acc;
-    mp.num_parts = p.num_splits;
     mp.query_heads = query_heads;
     mp.head_dim = geometry.head_dim;
     mp.gate = gate;
     mp.output = output;
     mp.gated_output = gated_output;
-    return launch_merge(mp, sessions, s);
+    return run_decode(p, geometry, max_length, workspace, workspace_bytes, num_splits, mp, sessions, s);
 }
 
 int b200kv_decode_partials(const b200kv_view* view, const void* q, int q_dtype, uint32_t query_heads,
@@ -369,20 +405,13 @@ int b200kv_decode_partials(const b200kv_view* view, const void* q, int q_dtype, 
     p.q_is_f16 = (q_dtype == B200KV_F16);
     p.query_heads = query_heads;
     p.scale = scale;
-    rc = run_decode_stage1(p, *view, range_end - range_begin, workspace, workspace_bytes, num_splits, s);
-    if (rc != B200KV_OK) return rc;
-
     MergeParams mp{};
-    mp.part_m = p.ws_m;
-    mp.part_l = p.ws_l;
-    mp.part_acc = p.ws_acc;
-    mp.num_parts = p.num_splits;
     mp.query_heads = query_heads;
     mp.head_dim = view->head_dim;
     mp.out_m = part_m;
     mp.out_l = part_l;
     mp.out_acc = part_acc;
-    return launch_merge(mp, 1, s);
+    return run_decode(p, *view, range_end - range_begin, workspace, workspace_bytes, num_splits, mp, 1, s);
 }
 
 int b200kv_merge_partials(const float* part_m, const float* part_l, const float* part_acc,

@@ -26,6 +26,21 @@ inline uint32_t max_splits_per_session(uint32_t sessions) {
     return s ? s : 1;
 }
 
+struct MergeParams {
+    const float* part_m;   // [groups][num_parts][query_heads]
+    const float* part_l;
+    const float* part_acc; // [groups][num_parts][query_heads][d]
+    uint32_t num_parts;
+    uint32_t query_heads;
+    uint32_t head_dim;
+    const float* gate;     // [groups][query_heads][d] or null
+    float* output;         // normalised, or null
+    float* gated_output;   // normalised * sigmoid(gate), or null
+    float* out_m;          // when non-null: emit ONE merged partial per (group, head) instead
+    float* out_l;
+    float* out_acc;
+};
+
 struct DecodeParams {
     b200kv_view view;                        // single-session launch
     const SessionEntry* views;               // device table [sessions], or null
@@ -47,6 +62,12 @@ struct DecodeParams {
     float* ws_m;                             // [sessions][num_splits][query_heads]
     float* ws_l;
     float* ws_acc;                           // [sessions][num_splits][query_heads][d]
+    // Fused merge (streaming kernel only): when `counters` is non-null the last CTA of each
+    // (session, kv head) combines all splits and writes `fuse`'s outputs; the counters must be
+    // zero on entry and are zero again on exit.
+    uint32_t overlap_tail;                   // launch overlap: the last n positions of the range are read only after pdl_wait
+    uint32_t* counters;                      // [sessions][kv_heads]
+    MergeParams fuse;
 };
 
 // The scanned range [begin, end) of one session, resolved on the device the way
@@ -74,27 +95,19 @@ __device__ __forceinline__ const b200kv_view& session_view(const DecodeParams& p
     return p.views != nullptr ? p.views[session].view : p.view;
 }
 
-struct MergeParams {
-    const float* part_m;   // [groups][num_parts][query_heads]
-    const float* part_l;
-    const float* part_acc; // [groups][num_parts][query_heads][d]
-    uint32_t num_parts;
-    uint32_t query_heads;
-    uint32_t head_dim;
-    const float* gate;     // [groups][query_heads][d] or null
-    float* output;         // normalised, or null
-    float* gated_output;   // normalised * sigmoid(gate), or null
-    float* out_m;          // when non-null: emit ONE merged partial per (group, head) instead
-    float* out_l;
-    float* out_acc;
-};
 
 int launch_merge(const MergeParams& p, uint32_t groups, cudaStream_t stream);
 
 // Stage 1 into `workspace` (fills p.num_splits and p.ws_*).  num_splits_arg: 0 =
 // choose; top bit set = use the generic kernel even where a fast one exists.
+// `merge` describes where the combined result goes; *merged is set when the stage-1 kernel did the
+// combine itself (then no launch_merge is needed).
 int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, void* workspace,
-                      size_t workspace_bytes, uint32_t num_splits_arg, cudaStream_t stream);
+                      size_t workspace_bytes, uint32_t num_splits_arg, const MergeParams& merge, bool* merged,
+                      cudaStream_t stream);
+size_t decode_counter_bytes(uint32_t query_heads, uint32_t sessions);
+int run_decode(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, void* workspace, size_t workspace_bytes,
+               uint32_t num_splits_arg, MergeParams mp, uint32_t groups, cudaStream_t stream);
 
 // Fast path for int8 K and V (decode_q8.cu).  Returns B200KV_ERR_UNSUPPORTED when
 // the geometry has no specialised kernel, so the caller can use the generic one.

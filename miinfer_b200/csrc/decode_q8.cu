@@ -5,14 +5,23 @@
 // (gfx906/kernels/qwen3_primitives.hip:7371-7485) with block scales; how it is
 // laid out is specific to B200:
 //
-//  * One CTA = 4 warps = one (kv head, split).  ALL query heads of the kv-head
-//    group share every K/V byte the CTA loads (the reference re-reads the cache
-//    once per query head).
-//  * Each warp owns a private 3-stage ring of 32-position tiles in shared
-//    memory, filled by TMA: the K tile through a tensor map with the 128-byte
-//    swizzle (rows of 128 int8), V and both scale tiles with plain bulk copies.
-//    One lane issues the copies; completion is an mbarrier per stage.  Warps
-//    never synchronise with each other in the main loop.
+//  * One CTA = one (kv head, split) = 4 warp PAIRS.  ALL query heads of the
+//    kv-head group share every K/V byte the CTA loads (the reference re-reads
+//    the cache once per query head).
+//  * A pair is a K-warp and a V-warp working on the same sequence of
+//    32-position tiles.  The K-warp streams K tiles and block scales, computes
+//    the scores and the online softmax and hands (weights, rescale factors) to
+//    its V-warp through a 4-slot ring in shared memory; the V-warp streams V
+//    tiles and accumulates P.V.  Splitting the roles halves the registers each
+//    warp needs (Q lives only in K-warps, the output accumulators only in
+//    V-warps), so 16 warps are resident per SM instead of 8, and the integer
+//    (Q.K) and floating-point (P.V) instruction streams of different warps
+//    interleave on each scheduler.
+//  * Every warp owns a private 3-stage ring of tiles filled by TMA: the K tile
+//    through a tensor map with the 128-byte swizzle (rows of 128 int8), V and
+//    both scale tiles with plain bulk copies.  One lane issues the copies;
+//    completion is an mbarrier per stage.  Pairs never synchronise with each
+//    other in the main loop; the hand-off inside a pair is two mbarriers per slot.
 //  * Q.K runs on the integer dot-product pipe: Q is quantised once per launch to
 //    int16 with a per-head scale (15 bits + sign: finer than the fp16 inputs'
 //    11-bit mantissa for the elements that matter), and dp2a multiplies packed
@@ -26,9 +35,11 @@
 //    of 2^23 and one subtract (the conversion pipe is 8x slower than that), the
 //    multiply-adds as packed f32x2.  Accumulators are rescaled only on tiles
 //    where a head's running max moved.
-//  * Softmax is the online form in base 2; each warp keeps (m, l, acc) for the
-//    whole launch, the CTA merges its 4 warps in shared memory and writes one
+//  * Softmax is the online form in base 2; each pair keeps (m, l, acc) for the
+//    whole launch, the CTA merges its 4 pairs in shared memory and writes one
 //    partial per (split, query head) for the log-sum-exp merge kernel.
+//  * Every wait is bounded: a copy or hand-off that never arrives poisons the
+//    partial with NaN instead of hanging the GPU.
 #include "decode_common.cuh"
 
 #include <cstring>
@@ -38,26 +49,29 @@ namespace b200kv {
 
 namespace {
 
-constexpr int kWarps = 4;
-constexpr int kTile = 32;    // positions per warp tile
-constexpr int kStages = 3;
+constexpr int kPairs = 4;     // warp pairs per CTA: warps 0..3 are K-warps, 4..7 their V-warps
+constexpr int kTile = 32;     // positions per tile
+constexpr int kKStages = 3;   // TMA ring depth of a K-warp (K tile + both scale tiles)
+constexpr int kVStages = 2;   // TMA ring depth of a V-warp (V tile)
+constexpr int kSlots = 2;     // weight hand-off ring depth per pair
 constexpr int kD = 128;
 constexpr uint32_t kSpinLimit = 1u << 24;
 
 template <int NBLK>
 struct Smem {
-    static constexpr int kKTile = kTile * kD;              // 4096
-    static constexpr int kSTile = kTile * NBLK * 2;        // 256 (q8_0) or 64 (row scale)
-    static constexpr int kKBytes = kWarps * kStages * kKTile;
-    static constexpr int kOffV = kKBytes;
-    static constexpr int kOffKS = kOffV + kKBytes;
-    static constexpr int kOffVS = kOffKS + kWarps * kStages * kSTile;
-    static constexpr int kOffW = kOffVS + kWarps * kStages * kSTile;     // [warp][kTile][4] float weights
-    static constexpr int kOffAlpha = kOffW + kWarps * kTile * 4 * 4;     // [warp][4] float
-    static constexpr int kOffQ = kOffAlpha + kWarps * 4 * 4;             // [4][kD] int16
+    static constexpr int kKTile = kTile * kD;                    // 4096
+    static constexpr int kSTile = kTile * NBLK * 2;              // 256 (q8_0) or 64 (row scale)
+    static constexpr int kBlkStride = kTile * 4 * 4 + 64;          // ew[pos][head] fp32 of one block, padded against bank conflicts
+    static constexpr int kSlotBytes = NBLK * kBlkStride + 16;      // ew[blk][pos][head] + alpha[4]
+    static constexpr int kOffV = kPairs * kKStages * kKTile;
+    static constexpr int kOffS = kOffV + kPairs * kVStages * kKTile;     // [pair][stage][ks | vs]
+    static constexpr int kOffW = kOffS + kPairs * kKStages * 2 * kSTile;
+    static constexpr int kOffQ = kOffW + kPairs * kSlots * kSlotBytes;   // [4][kD] int16
     static constexpr int kOffQmul = kOffQ + 4 * kD * 2;                  // [4] float
-    static constexpr int kOffBar = kOffQmul + 16;                        // [warp][stage] mbarrier
-    static constexpr int kTotal = kOffBar + kWarps * kStages * 8;
+    static constexpr int kOffMisc = kOffQmul + 16;                       // merge scratch: m/l/a [4][128] floats x3
+    static constexpr int kOffBar = kOffMisc + 3 * 4 * 128 * 4;
+    static constexpr int kBarsPerPair = kKStages + kVStages + 2 * kSlots;  // kfull, vfull, wfull, wempty
+    static constexpr int kTotal = kOffBar + kPairs * kBarsPerPair * 8;
     static constexpr int kAlloc = kTotal + 1024;                         // slack to align the base to 1024
 };
 
@@ -68,6 +82,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // Bounded wait: returns false if the phase did not complete within the spin limit.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
@@ -89,284 +106,437 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 
+// Two int8 bytes of x (already offset by +128) to fp32: placed in the mantissa of
+// 2^23 they read 8388608 + u; one packed multiply-add removes the offset.
 __device__ __forceinline__ float2 cvt2(uint32_t x, uint32_t sel_lo, uint32_t sel_hi) {
-    // bytes of x are int8+128; placed in the mantissa of 2^23 they read 8388608 + u
     float2 f;
     f.x = __uint_as_float(__byte_perm(x, 0x4B000000u, sel_lo));
     f.y = __uint_as_float(__byte_perm(x, 0x4B000000u, sel_hi));
-    return __fadd2_rn(f, make_float2(-8388736.0f, -8388736.0f));
+    return __ffma2_rn(f, make_float2(1.0f, 1.0f), make_float2(-8388736.0f, -8388736.0f));
 }
 
 // G query heads per kv head (1, 2 or 4); NBLK scales per row (4 = q8_0 blocks of 32, 1 = one per row).
 template <int G, int NBLK, bool Q_F16>
-__global__ void __launch_bounds__(kWarps * 32, 2)
+__global__ void __launch_bounds__(kPairs * 64, 2)
 decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ CUtensorMap kmap_single) {
     using L = Smem<NBLK>;
-    constexpr int PPR = 32 / G;       // positions per Q.K round
+    constexpr int PPR = 32 / G;          // positions per Q.K round
     constexpr int ROUNDS = kTile / PPR;  // == G
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    __shared__ int s_last;
+
+    pdl_launch_dependents();   // the next kernel of the stream may become resident as SMs free up; it orders itself
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pair = warp & (kPairs - 1);
+    const bool is_k_warp = warp < kPairs;
     const uint32_t split = blockIdx.x, kv_head = blockIdx.y, session = blockIdx.z;
     const b200kv_view& view = session_view(p, session);
-    const CUtensorMap* kmap = p.views != nullptr ? &p.views[session].kmap : &kmap_single;
     uint32_t begin, end;
     resolve_range(p, session, view, &begin, &end);
 
-    // ---- this warp's tiles ---------------------------------------------------------
+    // ---- this pair's tiles -----------------------------------------------------------
     const uint32_t tile_begin = begin / kTile, tile_end = (end + kTile - 1) / kTile;
     const uint64_t total_tiles = end > begin ? tile_end - tile_begin : 0;
-    const uint32_t nwarps = p.num_splits * kWarps, gw = split * kWarps + warp;
-    const uint32_t t0 = tile_begin + static_cast<uint32_t>(total_tiles * gw / nwarps);
-    const uint32_t t1 = tile_begin + static_cast<uint32_t>(total_tiles * (gw + 1) / nwarps);
+    const uint32_t npairs = p.num_splits * kPairs, gp = split * kPairs + pair;
+    const uint32_t t0 = tile_begin + static_cast<uint32_t>(total_tiles * gp / npairs);
+    const uint32_t t1 = tile_begin + static_cast<uint32_t>(total_tiles * (gp + 1) / npairs);
     const int ntiles = static_cast<int>(t1 - t0);
+    // With launch overlap the previous kernel may still be appending: rows at or above early_end wait for it.
+    const uint32_t early_end = end > p.overlap_tail ? end - p.overlap_tail : 0;
 
-    uint8_t* k_stage = smem + warp * kStages * L::kKTile;
-    uint8_t* v_stage = smem + L::kOffV + warp * kStages * L::kKTile;
-    uint8_t* ks_stage = smem + L::kOffKS + warp * kStages * L::kSTile;
-    uint8_t* vs_stage = smem + L::kOffVS + warp * kStages * L::kSTile;
-    float* w_tile = reinterpret_cast<float*>(smem + L::kOffW) + warp * kTile * 4;
-    float* alpha_s = reinterpret_cast<float*>(smem + L::kOffAlpha) + warp * 4;
+    uint8_t* k_ring = smem + pair * kKStages * L::kKTile;
+    uint8_t* v_ring = smem + L::kOffV + pair * kVStages * L::kKTile;
+    uint8_t* s_ring = smem + L::kOffS + pair * kKStages * 2 * L::kSTile;
+    uint8_t* w_ring = smem + L::kOffW + pair * kSlots * L::kSlotBytes;
     int16_t* q16 = reinterpret_cast<int16_t*>(smem + L::kOffQ);
     float* qmul_s = reinterpret_cast<float*>(smem + L::kOffQmul);
-    const uint32_t bar0 = smem_u32(smem + L::kOffBar) + warp * kStages * 8;
+    const uint32_t bars = smem_u32(smem + L::kOffBar) + pair * L::kBarsPerPair * 8;
+    const uint32_t bar_kfull = bars, bar_vfull = bars + kKStages * 8;
+    const uint32_t bar_wfull = bar_vfull + kVStages * 8, bar_wempty = bar_wfull + kSlots * 8;
 
     const uint64_t head_row0 = static_cast<uint64_t>(kv_head) * view.capacity;
-    const int8_t* v_plane = view.value_q8 + head_row0 * kD;
-    const uint8_t* ks_plane = static_cast<const uint8_t*>(view.key_scales) + head_row0 * NBLK * 2;
-    const uint8_t* vs_plane = static_cast<const uint8_t*>(view.value_scales) + head_row0 * NBLK * 2;
 
-    auto issue = [&](int i) {
-        const int stage = i % kStages;
-        const uint32_t pos0 = (t0 + i) * kTile;
-        const uint32_t rows = min(static_cast<uint32_t>(kTile), static_cast<uint32_t>(view.capacity) - pos0);
-        const uint32_t bar = bar0 + stage * 8;
-        mbar_expect_tx(bar, L::kKTile + rows * kD + 2 * rows * NBLK * 2);
-        tma_load_2d(smem_u32(k_stage + stage * L::kKTile), kmap, 0, static_cast<int>(head_row0 + pos0), bar);
-        bulk_load(smem_u32(v_stage + stage * L::kKTile), v_plane + static_cast<size_t>(pos0) * kD, rows * kD, bar);
-        bulk_load(smem_u32(ks_stage + stage * L::kSTile), ks_plane + static_cast<size_t>(pos0) * NBLK * 2, rows * NBLK * 2, bar);
-        bulk_load(smem_u32(vs_stage + stage * L::kSTile), vs_plane + static_cast<size_t>(pos0) * NBLK * 2, rows * NBLK * 2, bar);
-    };
-
-    if (lane == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init(bar0 + s * 8, 1);
+    // barriers of a pair are initialised by its K-warp before either warp uses them
+    if (is_k_warp && lane == 0) {
+        for (int s = 0; s < L::kBarsPerPair; ++s) mbar_init(bars + s * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        for (int i = 0; i < kStages && i < ntiles; ++i) issue(i);   // the cache does not depend on Q: start streaming first
-    }
-
-    // ---- quantise Q to int16, one warp per head ---------------------------------------
-    if (warp < G) {
-        const uint32_t head = kv_head * G + warp;
-        const size_t qb = (static_cast<size_t>(session) * p.query_heads + head) * kD + lane * 4;
-        float q[4];
-        if (Q_F16) {
-            const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __half*>(p.q) + qb);
-            const __half2 a = *reinterpret_cast<const __half2*>(&raw.x), b = *reinterpret_cast<const __half2*>(&raw.y);
-            q[0] = __low2float(a); q[1] = __high2float(a); q[2] = __low2float(b); q[3] = __high2float(b);
-        } else {
-            const float4 raw = *reinterpret_cast<const float4*>(static_cast<const float*>(p.q) + qb);
-            q[0] = raw.x; q[1] = raw.y; q[2] = raw.z; q[3] = raw.w;
-        }
-        const float amax = warp_max(fmaxf(fmaxf(fabsf(q[0]), fabsf(q[1])), fmaxf(fabsf(q[2]), fabsf(q[3]))));
-        const float inv = amax > 0.0f ? 32767.0f / amax : 0.0f;
-        short4 packed;
-        packed.x = static_cast<short>(__float2int_rn(q[0] * inv));
-        packed.y = static_cast<short>(__float2int_rn(q[1] * inv));
-        packed.z = static_cast<short>(__float2int_rn(q[2] * inv));
-        packed.w = static_cast<short>(__float2int_rn(q[3] * inv));
-        *reinterpret_cast<short4*>(q16 + warp * kD + lane * 4) = packed;
-        // scores are kept in base-2 units: dot * (amax/32767) * softmax_scale * log2(e)
-        if (lane == 0) qmul_s[warp] = (amax / 32767.0f) * p.scale * 1.4426950408889634f;
     }
     __syncthreads();
 
-    const int g = lane % G, pl = lane / G;       // Q.K role: head g of position pl (+ PPR * round)
-    const int r4 = lane >> 3, c = lane & 7;      // P.V role: positions r4 + 4j, dims [16c, 16c+16)
-    int qreg[kD / 2];
-#pragma unroll
-    for (int i = 0; i < kD / 8; ++i) {
-        const uint4 t = reinterpret_cast<const uint4*>(q16 + g * kD)[i];
-        qreg[4 * i] = static_cast<int>(t.x); qreg[4 * i + 1] = static_cast<int>(t.y);
-        qreg[4 * i + 2] = static_cast<int>(t.z); qreg[4 * i + 3] = static_cast<int>(t.w);
-    }
-    const float qmul = qmul_s[g];
-
-    float2 acc[G][8];
-#pragma unroll
-    for (int h = 0; h < G; ++h)
-#pragma unroll
-        for (int k = 0; k < 8; ++k) acc[h][k] = make_float2(0.0f, 0.0f);
-    float m_run = -INFINITY, l_run = 0.0f;
     bool failed = false;
+    // merge area of the pair (reuses its K ring once the main loop is over): m[4], l[4], pad, acc[G][128]
+    float* mine = reinterpret_cast<float*>(k_ring);
 
-    for (int i = 0; i < ntiles; ++i) {
-        const int stage = i % kStages;
-        if (!mbar_wait(bar0 + stage * 8, (i / kStages) & 1)) { failed = true; break; }
-        const uint32_t pos0 = (t0 + i) * kTile;
-        const int lo = begin > pos0 ? static_cast<int>(begin - pos0) : 0;
-        const int hi = end - pos0 < static_cast<uint32_t>(kTile) ? static_cast<int>(end - pos0) : kTile;
-        const uint8_t* kt = k_stage + stage * L::kKTile;
-        const uint8_t* vt = v_stage + stage * L::kKTile;
-        const uint8_t* kst = ks_stage + stage * L::kSTile;
-        const uint8_t* vst = vs_stage + stage * L::kSTile;
+    if (is_k_warp) {
+        // =========================== K-warp: scores, softmax, weights ===========================
+        const CUtensorMap* kmap = p.views != nullptr ? &p.views[session].kmap : &kmap_single;
+        const uint8_t* ks_plane = static_cast<const uint8_t*>(view.key_scales) + head_row0 * NBLK * 2;
+        const uint8_t* vs_plane = static_cast<const uint8_t*>(view.value_scales) + head_row0 * NBLK * 2;
+        auto issue = [&](int i) {
+            const int stage = i % kKStages;
+            const uint32_t pos0 = (t0 + i) * kTile;
+            const uint32_t rows = min(static_cast<uint32_t>(kTile), static_cast<uint32_t>(view.capacity) - pos0);
+            const uint32_t bar = bar_kfull + stage * 8;
+            mbar_expect_tx(bar, L::kKTile + 2 * rows * NBLK * 2);
+            tma_load_2d(smem_u32(k_ring + stage * L::kKTile), kmap, 0, static_cast<int>(head_row0 + pos0), bar);
+            uint8_t* sdst = s_ring + stage * 2 * L::kSTile;
+            bulk_load(smem_u32(sdst), ks_plane + static_cast<size_t>(pos0) * NBLK * 2, rows * NBLK * 2, bar);
+            bulk_load(smem_u32(sdst + L::kSTile), vs_plane + static_cast<size_t>(pos0) * NBLK * 2, rows * NBLK * 2, bar);
+        };
+        // old cache rows do not depend on the preceding kernels: start streaming them before waiting for those
+        int issued = 0;
+        if (lane == 0)
+            while (issued < kKStages && issued < ntiles && (t0 + issued + 1) * kTile <= early_end) issue(issued++);
+        pdl_wait();
+        if (lane == 0)
+            while (issued < kKStages && issued < ntiles) issue(issued++);
 
-        // ---- Q.K: ROUNDS rounds of PPR positions x G heads -----------------------------
-        float s[ROUNDS];
-#pragma unroll
-        for (int r = 0; r < ROUNDS; ++r) {
-            const int pos = r * PPR + pl;
-            const uint4* krow = reinterpret_cast<const uint4*>(kt + pos * kD);
-            const int swz = pos & 7;
-            float ksf[NBLK];
-            if constexpr (NBLK == 4) {
-                const uint2 raw = *reinterpret_cast<const uint2*>(kst + pos * 8);
-                const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-                const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-                ksf[0] = a.x; ksf[1] = a.y; ksf[2] = b.x; ksf[3] = b.y;
+        // quantise Q to int16, one K-warp per head
+        if (pair < G) {
+            const uint32_t head = kv_head * G + pair;
+            const size_t qb = (static_cast<size_t>(session) * p.query_heads + head) * kD + lane * 4;
+            float q[4];
+            if (Q_F16) {
+                const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __half*>(p.q) + qb);
+                const __half2 a = *reinterpret_cast<const __half2*>(&raw.x), b = *reinterpret_cast<const __half2*>(&raw.y);
+                q[0] = __low2float(a); q[1] = __high2float(a); q[2] = __low2float(b); q[3] = __high2float(b);
             } else {
-                ksf[0] = __half2float(*reinterpret_cast<const __half*>(kst + pos * 2));
+                const float4 raw = *reinterpret_cast<const float4*>(static_cast<const float*>(p.q) + qb);
+                q[0] = raw.x; q[1] = raw.y; q[2] = raw.z; q[3] = raw.w;
             }
-            float total = 0.0f;
-            int isum = 0;
+            const float amax = warp_max(fmaxf(fmaxf(fabsf(q[0]), fabsf(q[1])), fmaxf(fabsf(q[2]), fabsf(q[3]))));
+            const float inv = amax > 0.0f ? 32767.0f / amax : 0.0f;
+            short4 packed;
+            packed.x = static_cast<short>(__float2int_rn(q[0] * inv));
+            packed.y = static_cast<short>(__float2int_rn(q[1] * inv));
+            packed.z = static_cast<short>(__float2int_rn(q[2] * inv));
+            packed.w = static_cast<short>(__float2int_rn(q[3] * inv));
+            *reinterpret_cast<short4*>(q16 + pair * kD + lane * 4) = packed;
+            // scores are kept in base-2 units: dot * (amax/32767) * softmax_scale * log2(e)
+            if (lane == 0) qmul_s[pair] = (amax / 32767.0f) * p.scale * 1.4426950408889634f;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kPairs * 32) : "memory");   // K-warps only
+
+        const int g = lane % G, pl = lane / G;   // head g of position pl (+ PPR * round)
+        int qreg[kD / 2];
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-                const uint4 kw = krow[ch ^ swz];
-                isum = __dp2a_lo(qreg[8 * ch + 0], static_cast<int>(kw.x), isum);
-                isum = __dp2a_hi(qreg[8 * ch + 1], static_cast<int>(kw.x), isum);
-                isum = __dp2a_lo(qreg[8 * ch + 2], static_cast<int>(kw.y), isum);
-                isum = __dp2a_hi(qreg[8 * ch + 3], static_cast<int>(kw.y), isum);
-                isum = __dp2a_lo(qreg[8 * ch + 4], static_cast<int>(kw.z), isum);
-                isum = __dp2a_hi(qreg[8 * ch + 5], static_cast<int>(kw.z), isum);
-                isum = __dp2a_lo(qreg[8 * ch + 6], static_cast<int>(kw.w), isum);
-                isum = __dp2a_hi(qreg[8 * ch + 7], static_cast<int>(kw.w), isum);
+        for (int i = 0; i < kD / 8; ++i) {
+            const uint4 t = reinterpret_cast<const uint4*>(q16 + g * kD)[i];
+            qreg[4 * i] = static_cast<int>(t.x); qreg[4 * i + 1] = static_cast<int>(t.y);
+            qreg[4 * i + 2] = static_cast<int>(t.z); qreg[4 * i + 3] = static_cast<int>(t.w);
+        }
+        const float qmul = qmul_s[g];
+        float m_run = -INFINITY, l_run = 0.0f;
+        // per-lane byte offsets that do not change from tile to tile
+        const uint32_t k_lane = static_cast<uint32_t>(pl) * kD;           // row of round 0
+        const uint32_t swz16 = static_cast<uint32_t>(pl & 7) << 4;        // 128-byte swizzle: chunk ^= row & 7 (PPR is a multiple of 8 or pl < 8)
+        const uint32_t s_lane = static_cast<uint32_t>(pl) * NBLK * 2;
+        const uint32_t w_lane = static_cast<uint32_t>(pl * 4 + g) * 4;
+
+        for (int i = 0; i < ntiles; ++i) {
+            const int stage = i % kKStages, slot = i % kSlots;
+            if (!mbar_wait(bar_kfull + stage * 8, (i / kKStages) & 1)) { failed = true; break; }
+            const uint32_t pos0 = (t0 + i) * kTile;
+            const int lo = begin > pos0 ? static_cast<int>(begin - pos0) : 0;
+            const int hi = end - pos0 < static_cast<uint32_t>(kTile) ? static_cast<int>(end - pos0) : kTile;
+            const uint8_t* kt = k_ring + stage * L::kKTile + k_lane;
+            const uint8_t* kst = s_ring + stage * 2 * L::kSTile + s_lane;
+
+            float s[ROUNDS];
+#ifdef B200KV_SKIP_QK
+#pragma unroll
+            for (int r = 0; r < ROUNDS; ++r) s[r] = static_cast<float>(kt[r * 16] + qreg[r]) * qmul;
+#else
+#pragma unroll
+            for (int r = 0; r < ROUNDS; ++r) {
+                const uint8_t* krow = kt + r * PPR * kD;
+                float ksf[NBLK];
                 if constexpr (NBLK == 4) {
-                    if (ch & 1) {   // a 32-dim block ends every second chunk
-                        total = fmaf(static_cast<float>(isum), ksf[ch >> 1], total);
-                        isum = 0;
+                    const uint2 raw = *reinterpret_cast<const uint2*>(kst + r * PPR * 8);
+                    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+                    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                    ksf[0] = a.x; ksf[1] = a.y; ksf[2] = b.x; ksf[3] = b.y;
+                } else {
+                    ksf[0] = __half2float(*reinterpret_cast<const __half*>(kst + r * PPR * 2));
+                }
+                float total = 0.0f;
+                int isum0 = 0, isum1 = 0;   // two chains per block keep the dot-product pipe busy
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch) {
+                    const uint4 kw = *reinterpret_cast<const uint4*>(krow + ((ch << 4) ^ swz16));
+                    isum0 = __dp2a_lo(qreg[8 * ch + 0], static_cast<int>(kw.x), isum0);
+                    isum1 = __dp2a_hi(qreg[8 * ch + 1], static_cast<int>(kw.x), isum1);
+                    isum0 = __dp2a_lo(qreg[8 * ch + 2], static_cast<int>(kw.y), isum0);
+                    isum1 = __dp2a_hi(qreg[8 * ch + 3], static_cast<int>(kw.y), isum1);
+                    isum0 = __dp2a_lo(qreg[8 * ch + 4], static_cast<int>(kw.z), isum0);
+                    isum1 = __dp2a_hi(qreg[8 * ch + 5], static_cast<int>(kw.z), isum1);
+                    isum0 = __dp2a_lo(qreg[8 * ch + 6], static_cast<int>(kw.w), isum0);
+                    isum1 = __dp2a_hi(qreg[8 * ch + 7], static_cast<int>(kw.w), isum1);
+                    if constexpr (NBLK == 4) {
+                        if (ch & 1) {   // a 32-dim block ends every second chunk
+                            total = fmaf(static_cast<float>(isum0 + isum1), ksf[ch >> 1], total);
+                            isum0 = 0; isum1 = 0;
+                        }
                     }
                 }
+                if constexpr (NBLK == 1) total = static_cast<float>(isum0 + isum1) * ksf[0];
+                const int pos = r * PPR + pl;
+                s[r] = (pos >= lo && pos < hi) ? total * qmul : -INFINITY;
             }
-            if constexpr (NBLK == 1) total = static_cast<float>(isum) * ksf[0];
-            s[r] = (pos >= lo && pos < hi) ? total * qmul : -INFINITY;
-        }
+#endif
 
-        // ---- online softmax (base 2) ------------------------------------------------------
-        float mt = s[0];
+            // online softmax, base 2
+            float mt = s[0];
 #pragma unroll
-        for (int r = 1; r < ROUNDS; ++r) mt = fmaxf(mt, s[r]);
+            for (int r = 1; r < ROUNDS; ++r) mt = fmaxf(mt, s[r]);
 #pragma unroll
-        for (int o = G; o < 32; o <<= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
-        const float m_new = fmaxf(m_run, mt);              // finite: every tile holds a valid position
-        const float alpha = exp2f(m_run - m_new);
-        float lsum = 0.0f;
+            for (int o = G; o < 32; o <<= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
+            const float m_new = fmaxf(m_run, mt);              // finite: every tile holds a valid position
+            const float alpha = exp2f(m_run - m_new);
+            float w[ROUNDS], lsum = 0.0f;
 #pragma unroll
-        for (int r = 0; r < ROUNDS; ++r) {
-            const float w = exp2f(s[r] - m_new);
-            lsum += w;
-            w_tile[(r * PPR + pl) * 4 + g] = w;
-        }
-        l_run = fmaf(l_run, alpha, lsum);
-        m_run = m_new;
-        if (pl == 0) alpha_s[g] = alpha;
-        __syncwarp();
+            for (int r = 0; r < ROUNDS; ++r) { w[r] = exp2f(s[r] - m_new); lsum += w[r]; }
+            l_run = fmaf(l_run, alpha, lsum);
+            m_run = m_new;
 
-        // ---- P.V -----------------------------------------------------------------------------
-        {
-            float al[G];
-            bool moved = false;
+            // effective weights w * value_scale[block] for the V-warp: ew[blk][pos][head]
+            if (!mbar_wait(bar_wempty + slot * 8, ((i / kSlots) & 1) ^ 1)) { failed = true; break; }
+            uint8_t* wt = w_ring + slot * L::kSlotBytes;
+            const uint8_t* vst = kst + L::kSTile;
 #pragma unroll
-            for (int h = 0; h < G; ++h) { al[h] = alpha_s[h]; moved = moved || (al[h] != 1.0f); }
-            if (moved) {
-#pragma unroll
-                for (int h = 0; h < G; ++h)
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) { acc[h][k].x *= al[h]; acc[h][k].y *= al[h]; }
-            }
-        }
-#pragma unroll 2
-        for (int j = 0; j < kTile / 4; ++j) {
-            const int pos = r4 + 4 * j;
-            const uint4 vw = *reinterpret_cast<const uint4*>(vt + pos * kD + c * 16);
-            const float vsf = __half2float(*reinterpret_cast<const __half*>(vst + (NBLK == 4 ? pos * 8 + (c >> 1) * 2 : pos * 2)));
-            const bool valid = pos >= lo && pos < hi;
-            float2 ew[G];
-#pragma unroll
-            for (int h = 0; h < G; ++h) {
-                const float e = valid ? w_tile[pos * 4 + h] * vsf : 0.0f;   // select, not multiply: stale scales may be inf/nan
-                ew[h] = make_float2(e, e);
-            }
-            const uint32_t words[4] = {vw.x ^ 0x80808080u, vw.y ^ 0x80808080u, vw.z ^ 0x80808080u, vw.w ^ 0x80808080u};
-#pragma unroll
-            for (int wi = 0; wi < 4; ++wi) {
-                const float2 f01 = cvt2(words[wi], 0x7440u, 0x7441u);
-                const float2 f23 = cvt2(words[wi], 0x7442u, 0x7443u);
-#pragma unroll
-                for (int h = 0; h < G; ++h) {
-                    acc[h][2 * wi] = __ffma2_rn(ew[h], f01, acc[h][2 * wi]);
-                    acc[h][2 * wi + 1] = __ffma2_rn(ew[h], f23, acc[h][2 * wi + 1]);
+            for (int r = 0; r < ROUNDS; ++r) {
+                const bool valid = w[r] > 0.0f;   // masked positions have weight exactly 0; their scales may be stale inf/nan
+                if constexpr (NBLK == 4) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(vst + r * PPR * 8);
+                    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+                    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                    float* dst = reinterpret_cast<float*>(wt + w_lane + r * PPR * 16);
+                    dst[0 * L::kBlkStride / 4] = valid ? w[r] * a.x : 0.0f;
+                    dst[1 * L::kBlkStride / 4] = valid ? w[r] * a.y : 0.0f;
+                    dst[2 * L::kBlkStride / 4] = valid ? w[r] * b.x : 0.0f;
+                    dst[3 * L::kBlkStride / 4] = valid ? w[r] * b.y : 0.0f;
+                } else {
+                    const float v = __half2float(*reinterpret_cast<const __half*>(vst + r * PPR * 2));
+                    *reinterpret_cast<float*>(wt + w_lane + r * PPR * 16) = valid ? w[r] * v : 0.0f;
                 }
             }
-        }
-        __syncwarp();   // every lane is done with this stage and with w_tile
-        if (lane == 0 && i + kStages < ntiles) issue(i + kStages);
-    }
-
-    // ---- reduce inside the warp: acc over the 4 position groups, l over the PPR position lanes -----------
-#pragma unroll
-    for (int h = 0; h < G; ++h)
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            acc[h][k].x += __shfl_xor_sync(0xffffffffu, acc[h][k].x, 8);
-            acc[h][k].y += __shfl_xor_sync(0xffffffffu, acc[h][k].y, 8);
-            acc[h][k].x += __shfl_xor_sync(0xffffffffu, acc[h][k].x, 16);
-            acc[h][k].y += __shfl_xor_sync(0xffffffffu, acc[h][k].y, 16);
+            if (pl == 0) reinterpret_cast<float*>(wt + NBLK * L::kBlkStride)[g] = alpha;
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar_wfull + slot * 8);
+                if (i + kKStages < ntiles) issue(i + kKStages);
+            }
         }
 #pragma unroll
-    for (int o = G; o < 32; o <<= 1) l_run += __shfl_xor_sync(0xffffffffu, l_run, o);
-    if (failed) { m_run = __int_as_float(0x7fc00000); l_run = m_run; }   // a copy never arrived: poison the partial
+        for (int o = G; o < 32; o <<= 1) l_run += __shfl_xor_sync(0xffffffffu, l_run, o);
+        if (failed) { m_run = __int_as_float(0x7fc00000); l_run = m_run; }   // poison the partial
+        if (pl == 0) { mine[g] = m_run; mine[4 + g] = l_run; }
+    } else {
+        // =========================== V-warp: P.V accumulation ============================
+        const int8_t* v_plane = view.value_q8 + head_row0 * kD;
+        auto issue = [&](int i) {
+            const int stage = i % kVStages;
+            const uint32_t pos0 = (t0 + i) * kTile;
+            const uint32_t rows = min(static_cast<uint32_t>(kTile), static_cast<uint32_t>(view.capacity) - pos0);
+            const uint32_t bar = bar_vfull + stage * 8;
+            mbar_expect_tx(bar, rows * kD);
+            bulk_load(smem_u32(v_ring + stage * L::kKTile), v_plane + static_cast<size_t>(pos0) * kD, rows * kD, bar);
+        };
+        int issued = 0;
+        if (lane == 0)
+            while (issued < kVStages && issued < ntiles && (t0 + issued + 1) * kTile <= early_end) issue(issued++);
+        pdl_wait();
+        if (lane == 0)
+            while (issued < kVStages && issued < ntiles) issue(issued++);
 
-    // ---- merge the CTA's warps through shared memory (each warp reuses its own K ring) ---------------------
-    // layout per warp: m[4], l[4], acc[G][128]
-    float* mine = reinterpret_cast<float*>(k_stage);
-    if (pl == 0) { mine[g] = m_run; mine[4 + g] = l_run; }
-    if (r4 == 0) {
+        const int r4 = lane >> 3, c = lane & 7;   // positions r4 + 4j, dims [16c, 16c+16)
+        const uint32_t v_lane = static_cast<uint32_t>(r4) * kD + c * 16;
+        const uint32_t w_lane = static_cast<uint32_t>(NBLK == 4 ? (c >> 1) : 0) * L::kBlkStride + r4 * 16;
+        float2 acc[G][8];
 #pragma unroll
         for (int h = 0; h < G; ++h)
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
-                *reinterpret_cast<float2*>(mine + 8 + h * kD + c * 16 + 2 * k) = acc[h][k];
+            for (int k = 0; k < 8; ++k) acc[h][k] = make_float2(0.0f, 0.0f);
+
+        for (int i = 0; i < ntiles; ++i) {
+            const int stage = i % kVStages, slot = i % kSlots;
+            if (!mbar_wait(bar_vfull + stage * 8, (i / kVStages) & 1)) { failed = true; break; }
+            if (!mbar_wait(bar_wfull + slot * 8, (i / kSlots) & 1)) { failed = true; break; }
+            const uint8_t* vt = v_ring + stage * L::kKTile + v_lane;
+            const uint8_t* wt = w_ring + slot * L::kSlotBytes;
+            {
+                float al[4];
+                *reinterpret_cast<float4*>(al) = *reinterpret_cast<const float4*>(wt + NBLK * L::kBlkStride);
+                bool moved = false;
+#pragma unroll
+                for (int h = 0; h < G; ++h) moved = moved || (al[h] != 1.0f);
+                if (moved) {
+#pragma unroll
+                    for (int h = 0; h < G; ++h) {
+                        const float2 a2 = make_float2(al[h], al[h]);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) acc[h][k] = __fmul2_rn(acc[h][k], a2);
+                    }
+                }
+            }
+            const uint8_t* wl = wt + w_lane;
+#ifdef B200KV_SKIP_PV
+            acc[0][0].x += static_cast<float>(vt[0]) * wl[0];
+#else
+#pragma unroll 2
+            for (int j = 0; j < kTile / 4; ++j) {
+                const uint4 vw = *reinterpret_cast<const uint4*>(vt + j * 4 * kD);
+                float wv[4];
+                *reinterpret_cast<float4*>(wv) = *reinterpret_cast<const float4*>(wl + j * 64);
+                float2 ew[G];
+#pragma unroll
+                for (int h = 0; h < G; ++h) ew[h] = make_float2(wv[h], wv[h]);
+                const uint32_t words[4] = {vw.x ^ 0x80808080u, vw.y ^ 0x80808080u, vw.z ^ 0x80808080u, vw.w ^ 0x80808080u};
+#pragma unroll
+                for (int wi = 0; wi < 4; ++wi) {
+                    const float2 f01 = cvt2(words[wi], 0x7440u, 0x7441u);
+                    const float2 f23 = cvt2(words[wi], 0x7442u, 0x7443u);
+#pragma unroll
+                    for (int h = 0; h < G; ++h) {
+                        acc[h][2 * wi] = __ffma2_rn(ew[h], f01, acc[h][2 * wi]);
+                        acc[h][2 * wi + 1] = __ffma2_rn(ew[h], f23, acc[h][2 * wi + 1]);
+                    }
+                }
+            }
+#endif
+            __syncwarp();   // every lane is done with this stage and this weight slot
+            if (lane == 0) {
+                mbar_arrive(bar_wempty + slot * 8);
+                if (i + kVStages < ntiles) issue(i + kVStages);
+            }
+        }
+        // sum the 4 position groups
+#pragma unroll
+        for (int h = 0; h < G; ++h)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                acc[h][k].x += __shfl_xor_sync(0xffffffffu, acc[h][k].x, 8);
+                acc[h][k].y += __shfl_xor_sync(0xffffffffu, acc[h][k].y, 8);
+                acc[h][k].x += __shfl_xor_sync(0xffffffffu, acc[h][k].x, 16);
+                acc[h][k].y += __shfl_xor_sync(0xffffffffu, acc[h][k].y, 16);
+            }
+        if (failed) acc[0][0].x = __int_as_float(0x7fc00000);
+        // the K-warp of this pair is past its last K tile once the last weights have arrived
+        if (r4 == 0) {
+#pragma unroll
+            for (int h = 0; h < G; ++h)
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    *reinterpret_cast<float2*>(mine + 16 + h * kD + c * 16 + 2 * k) = acc[h][k];
+        }
     }
     __syncthreads();
-    {
-        const int dim = threadIdx.x;   // 128 threads == 128 dims
+
+    // ---- merge the CTA's pairs: 256 threads = 2 head slots x 128 dims ---------------------------------------
+    const int dim = threadIdx.x & (kD - 1);
+    for (int h = threadIdx.x >> 7; h < G; h += 2) {
+        float mw[kPairs], M = -INFINITY;
 #pragma unroll
-        for (int h = 0; h < G; ++h) {
-            float mw[kWarps], M = -INFINITY;
+        for (int w = 0; w < kPairs; ++w) {
+            const float* src = reinterpret_cast<const float*>(smem + w * kKStages * L::kKTile);
+            mw[w] = src[h];
+            M = fmaxf(M, mw[w]);
+        }
+        float lt = 0.0f, at = 0.0f;
 #pragma unroll
-            for (int w = 0; w < kWarps; ++w) {
-                const float* src = reinterpret_cast<const float*>(smem + w * kStages * L::kKTile);
-                mw[w] = src[h];
-                M = fmaxf(M, mw[w]);   // NaN-poisoned partials propagate through l below
-            }
-            float lt = 0.0f, at = 0.0f;
+        for (int w = 0; w < kPairs; ++w) {
+            const float* src = reinterpret_cast<const float*>(smem + w * kKStages * L::kKTile);
+            const float a = (mw[w] == -INFINITY) ? 0.0f : exp2f(mw[w] - M);   // NaN (poison) propagates
+            lt = fmaf(src[4 + h], a, lt);
+            at = fmaf(src[16 + h * kD + dim], a, at);
+        }
+        const uint32_t head = kv_head * G + h;
+        const size_t slot_idx = (static_cast<size_t>(session) * p.num_splits + split) * p.query_heads + head;
+        p.ws_acc[slot_idx * kD + dim] = at;
+        if (dim == 0) {
+            p.ws_m[slot_idx] = M * 0.6931471805599453f;   // natural-log units, as the merge kernel expects
+            p.ws_l[slot_idx] = lt;
+        }
+    }
+    if (p.counters == nullptr) return;   // a separate merge kernel follows
+
+    // ---- the last CTA of this (session, kv head) to finish merges all splits -------------------------------------
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t prev = atomicAdd(p.counters + session * gridDim.y + kv_head, 1u);
+        s_last = (prev + 1 == p.num_splits);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const uint32_t S = p.num_splits;   // <= kMaxSplitsPerSession == 128
+    float* sm = reinterpret_cast<float*>(smem + L::kOffMisc);   // [4][128] m -> a
+    float* sl = sm + 4 * 128;                                   // [4][128] l
+    float* sg = sl + 4 * 128;                                   // [4] merged max, [4] merged sum
+    for (uint32_t idx = threadIdx.x; idx < G * S; idx += blockDim.x) {
+        const uint32_t h = idx / S, sp = idx % S;
+        const size_t slot_idx = (static_cast<size_t>(session) * S + sp) * p.query_heads + kv_head * G + h;
+        sm[h * 128 + sp] = __ldcg(p.ws_m + slot_idx);
+        sl[h * 128 + sp] = __ldcg(p.ws_l + slot_idx);
+    }
+    __syncthreads();
+    if (warp < G) {   // one warp per head: global max, rescale factors, merged sum
+        const int h = warp;
+        float M = -INFINITY;
+        for (uint32_t sp = lane; sp < S; sp += 32) {
+            const float m = sm[h * 128 + sp], l = sl[h * 128 + sp];
+            if (!(l <= 0.0f) && m != -INFINITY) M = fmaxf(M, m);   // keeps NaN partials in play
+        }
+        M = warp_max(M);
+        float lsum = 0.0f;
+        for (uint32_t sp = lane; sp < S; sp += 32) {
+            const float m = sm[h * 128 + sp], l = sl[h * 128 + sp];
+            const float a = (!(l <= 0.0f) && m != -INFINITY) ? __expf(m - M) : 0.0f;
+            sm[h * 128 + sp] = a;
+            lsum = fmaf(l, a, lsum);
+        }
+        lsum = warp_sum(lsum);
+        if (lane == 0) { sg[h] = M; sg[4 + h] = lsum; }
+    }
+    __syncthreads();
+    for (int h = threadIdx.x >> 7; h < G; h += 2) {
+        const uint32_t head = kv_head * G + h;
+        const float* accp = p.ws_acc + ((static_cast<size_t>(session) * S) * p.query_heads + head) * kD + dim;
+        const size_t stride = static_cast<size_t>(p.query_heads) * kD;
+        // in-order warps: issue a whole batch of independent loads (the partials sit in L2) before using any
+        float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (uint32_t sp0 = 0; sp0 < S; sp0 += 16) {
+            float v[16];
 #pragma unroll
-            for (int w = 0; w < kWarps; ++w) {
-                const float* src = reinterpret_cast<const float*>(smem + w * kStages * L::kKTile);
-                const float a = (mw[w] == -INFINITY) ? 0.0f : exp2f(mw[w] - M);
-                lt = fmaf(src[4 + h], a, lt);
-                at = fmaf(src[8 + h * kD + dim], a, at);
-            }
-            const uint32_t head = kv_head * G + h;
-            const size_t slot = (static_cast<size_t>(session) * p.num_splits + split) * p.query_heads + head;
-            p.ws_acc[slot * kD + dim] = at;
+            for (int u = 0; u < 16; ++u) v[u] = (sp0 + u < S) ? __ldcg(accp + (sp0 + u) * stride) : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 16; ++u) tot[u & 3] = fmaf(v[u], (sp0 + u < S) ? sm[h * 128 + sp0 + u] : 0.0f, tot[u & 3]);
+        }
+        const float t0s = tot[0], t1s = tot[1], t2s = tot[2], t3s = tot[3];
+        const float total = (t0s + t1s) + (t2s + t3s);
+        const float gsum = sg[4 + h];
+        const size_t out_idx = (static_cast<size_t>(session) * p.query_heads + head) * kD + dim;
+        if (p.fuse.out_m != nullptr) {   // sequence shard: one merged, unnormalised partial
+            p.fuse.out_acc[out_idx] = total;
             if (dim == 0) {
-                p.ws_m[slot] = M * 0.6931471805599453f;   // back to natural-log units for the merge
-                p.ws_l[slot] = lt;
+                p.fuse.out_m[static_cast<size_t>(session) * p.query_heads + head] = sg[h];
+                p.fuse.out_l[static_cast<size_t>(session) * p.query_heads + head] = gsum;
+            }
+        } else {
+            const float o = gsum > 0.0f ? total / gsum : (gsum == gsum ? 0.0f : gsum);
+            if (p.fuse.output != nullptr) p.fuse.output[out_idx] = o;
+            if (p.fuse.gated_output != nullptr) {
+                float gated = o;
+                if (p.fuse.gate != nullptr) gated = o * (1.0f / (1.0f + __expf(-p.fuse.gate[out_idx])));
+                p.fuse.gated_output[out_idx] = gated;
             }
         }
     }
+    if (threadIdx.x == 0) p.counters[session * gridDim.y + kv_head] = 0;   // leave the workspace ready for the next launch
 }
 
 // ---- host side -----------------------------------------------------------------------------------------
@@ -399,8 +569,7 @@ int launch_one(const DecodeParams& p, const CUtensorMap& kmap, dim3 grid, cudaSt
         attr_err = cudaFuncSetAttribute(decode_q8_kernel<G, NBLK, Q_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc);
     });
     if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err, "cudaFuncSetAttribute(decode_q8)"); return B200KV_ERR_CUDA; }
-    decode_q8_kernel<G, NBLK, Q_F16><<<grid, kWarps * 32, L::kAlloc, stream>>>(p, kmap);
-    B200KV_CUDA_TRY(cudaGetLastError());
+    B200KV_CUDA_TRY(launch_kernel(decode_q8_kernel<G, NBLK, Q_F16>, grid, dim3(kPairs * 64), L::kAlloc, stream, true, p, kmap));
     return B200KV_OK;
 }
 
@@ -437,13 +606,13 @@ int encode_k_map(const b200kv_view& view, CUtensorMap* out) {
 
 uint32_t pick_splits_q8(const b200kv_view& geometry, uint32_t query_heads, uint32_t sessions, uint32_t max_length) {
     if (!q8_fast_path_ok(geometry, query_heads)) return 0;
-    // two CTAs of 4 warps per SM; every warp should see at least two tiles
+    // two CTAs of 4 warp pairs per SM; every pair should see at least two tiles
     const uint32_t ctas = 148u * 2u;
     const uint32_t units = geometry.kv_heads * sessions;
     uint32_t s = (ctas + units / 2) / units;   // nearest to one full wave
     if (s == 0) s = 1;
     const uint32_t tiles = (max_length + kTile - 1) / kTile;
-    uint32_t by_tiles = tiles / (2 * kWarps);
+    uint32_t by_tiles = tiles / (2 * kPairs);
     if (by_tiles == 0) by_tiles = 1;
     if (s > by_tiles) s = by_tiles;
     const uint32_t cap = max_splits_per_session(sessions);
@@ -451,8 +620,10 @@ uint32_t pick_splits_q8(const b200kv_view& geometry, uint32_t query_heads, uint3
     return s ? s : 1;
 }
 
-int launch_decode_q8(const DecodeParams& p, const b200kv_view& geometry, uint32_t /*max_length*/, cudaStream_t stream) {
-    if (!q8_fast_path_ok(geometry, p.query_heads)) return B200KV_ERR_UNSUPPORTED;
+int launch_decode_q8(const DecodeParams& p_in, const b200kv_view& geometry, uint32_t /*max_length*/, cudaStream_t stream) {
+    if (!q8_fast_path_ok(geometry, p_in.query_heads)) return B200KV_ERR_UNSUPPORTED;
+    DecodeParams p = p_in;
+    p.overlap_tail = launch_overlap_tail();
     CUtensorMap kmap;
     if (p.views == nullptr) {
         int rc = encode_k_map(geometry, &kmap);

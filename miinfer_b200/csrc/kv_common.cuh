@@ -28,6 +28,33 @@ int ensure_device();  // B200KV_OK if the current device is sm_100; cached per d
 inline bool is_k_q8(uint32_t mode) { return mode == B200KV_Q8_F16 || mode == B200KV_Q8_Q8; }
 inline bool is_v_q8(uint32_t mode) { return mode == B200KV_F16_Q8 || mode == B200KV_Q8_Q8; }
 
+// Launch overlap (programmatic dependent launch): 0 = off, n > 0 = on with a guard of n trailing positions.
+uint32_t launch_overlap_tail();
+
+// Launches `kernel` on `stream`; with overlap enabled the launch carries the programmatic-stream-serialization
+// attribute, so the kernel may become resident before the previous kernel in the stream has finished (it must
+// execute griddepcontrol.wait before touching anything that kernel produces).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool allow_overlap,
+                          Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (allow_overlap && launch_overlap_tail() > 0) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Checks the geometry and the pointers a view needs for its mode.
 int validate_view(const b200kv_view* view);
 

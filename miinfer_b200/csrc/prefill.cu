@@ -42,19 +42,13 @@ int b200kv_prefill_attn(const b200kv_view* view, const void* q, int q_dtype, con
     p.scale = scale;
     uint64_t max_length = prefill_state ? view->capacity : static_cast<uint64_t>(base_position) + token_count;
     if (max_length > view->capacity) max_length = view->capacity;
-    rc = run_decode_stage1(p, *view, static_cast<uint32_t>(max_length), workspace, workspace_bytes, 0x80000000u, s);
-    if (rc != B200KV_OK) return rc;
-
     MergeParams mp{};
-    mp.part_m = p.ws_m;
-    mp.part_l = p.ws_l;
-    mp.part_acc = p.ws_acc;
-    mp.num_parts = p.num_splits;
     mp.query_heads = query_heads;
     mp.head_dim = view->head_dim;
     mp.gate = gate;
     mp.gated_output = gated_output;
-    return launch_merge(mp, token_count, s);
+    return run_decode(p, *view, static_cast<uint32_t>(max_length), workspace, workspace_bytes, B200KV_SPLITS_FORCE_GENERIC, mp,
+                      token_count, s);
 }
 
 }  // extern "C"

@@ -3,6 +3,7 @@
 // AttentionLayerKvCacheStorage, src/prefill_v2/kv_cache.cpp:10-130).
 #include "kv_common.cuh"
 
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -10,6 +11,9 @@
 namespace b200kv {
 
 static thread_local char g_last_error[256] = "";
+static std::atomic<uint32_t> g_overlap_tail{0};
+
+uint32_t launch_overlap_tail() { return g_overlap_tail.load(std::memory_order_relaxed); }
 
 void set_last_cuda_error(cudaError_t err, const char* where) {
     std::snprintf(g_last_error, sizeof g_last_error, "%s: %s (%s)", cudaGetErrorName(err),
@@ -62,6 +66,11 @@ struct b200kv_cache {
 extern "C" {
 
 int b200kv_version(void) { return B200KV_VERSION; }
+
+int b200kv_set_launch_overlap(uint32_t tail_positions) {
+    g_overlap_tail.store(tail_positions, std::memory_order_relaxed);
+    return B200KV_OK;
+}
 
 const char* b200kv_status_string(int status) {
     switch (status) {

@@ -22,7 +22,7 @@ __all__ = [
     "launch_kv_store_quant", "launch_decode_attention_quant", "launch_decode_attention_batched",
     "launch_decode_partials", "launch_merge_partials", "launch_suffix_attention_quant",
     "decode_workspace", "prefill_workspace", "view_table", "make_decode_state", "make_prefill_state",
-    "token_sequence_hash", "decode_kernel_kind", "B200KvError", "FORCE_GENERIC",
+    "token_sequence_hash", "decode_kernel_kind", "set_launch_overlap", "B200KvError", "FORCE_GENERIC",
 ]
 
 FORCE_GENERIC = 0x80000000
@@ -161,7 +161,7 @@ def make_prefill_state(base_position: int, token_count: int, kv_capacity: int = 
 
 def decode_workspace(query_heads: int, head_dim: int, sessions: int = 1, device=None) -> torch.Tensor:
     n = int(lib.b200kv_decode_workspace_bytes(query_heads, head_dim, sessions))
-    return torch.empty(n, dtype=torch.uint8, device=device or "cuda")
+    return torch.zeros(n, dtype=torch.uint8, device=device or "cuda")   # zero-filled once: arrival counters live at its head
 
 
 def view_table(sessions: int, device=None) -> torch.Tensor:
@@ -171,7 +171,7 @@ def view_table(sessions: int, device=None) -> torch.Tensor:
 
 def prefill_workspace(token_count: int, query_heads: int, head_dim: int, device=None) -> torch.Tensor:
     n = int(lib.b200kv_prefill_workspace_bytes(token_count, query_heads, head_dim))
-    return torch.empty(n, dtype=torch.uint8, device=device or "cuda")
+    return torch.zeros(n, dtype=torch.uint8, device=device or "cuda")
 
 
 def launch_kv_store_quant(view: View, key: torch.Tensor, value: torch.Tensor, k_norm_weight: Optional[torch.Tensor],
@@ -245,6 +245,11 @@ def launch_suffix_attention_quant(view: View, q: torch.Tensor, gate: Optional[to
     check(lib.b200kv_prefill_attn(C.byref(view), _ptr(q), _dtype(q), _ptr(gate), _ptr(gated_output), token_count,
                                   base_position, query_heads, scale, _ptr(prefill_state), _ptr(workspace),
                                   workspace.numel(), _stream(stream)), "b200kv_prefill_attn")
+
+
+def set_launch_overlap(tail_positions: int) -> None:
+    """b200kv_set_launch_overlap: let consecutive append/decode kernels of a stream overlap (0 = off)."""
+    check(lib.b200kv_set_launch_overlap(int(tail_positions)), "b200kv_set_launch_overlap")
 
 
 def decode_kernel_kind(view: View, query_heads: int) -> int:

@@ -219,3 +219,67 @@ def test_decode_workspace_too_small_and_bad_heads(cuda):
     with pytest.raises(kv.B200KvError):
         kv.launch_decode_attention_quant(st.view(), q, query_heads=30, scale=0.1, cache_length=64, output=out,
                                          workspace=kv.decode_workspace(32, 128))
+
+
+def test_decode_loop_with_launch_overlap_matches_serial(cuda):
+    """A short decode loop (append + attention per layer, positions from device state) with
+    programmatic launch overlap on must give the same caches and outputs as with it off,
+    eagerly and under CUDA-graph replay."""
+    rng = np.random.default_rng(33)
+    H, Hq, d, L0, layers, steps = 8, 32, 128, 1000, 3, 5
+    k0 = [to_dev(ko.normal_f16(rng, (L0, H * d))) for _ in range(layers)]
+    v0 = [to_dev(ko.normal_f16(rng, (L0, H * d))) for _ in range(layers)]
+    qs = to_dev(ko.normal_f16(rng, (steps, layers, Hq, d)))
+    kn = to_dev(ko.normal_f16(rng, (steps, layers, 1, H * d)))
+    vn = to_dev(ko.normal_f16(rng, (steps, layers, 1, H * d)))
+
+    def run(overlap, use_graph):
+        kv.set_launch_overlap(overlap)
+        try:
+            sts = [kv.AttentionLayerKvCacheStorage(1024, kv.KvCacheQuantMode.kQ8Q8, kv_heads=H, head_dim=d, qblock=32) for _ in range(layers)]
+            for l in range(layers):
+                kv.launch_kv_store_quant(sts[l].view(), k0[l], v0[l], None, L0, 0, rope_mode=kv.RopeMode.NEOX_FULL)
+            state = kv.make_decode_state(L0)
+            ws = kv.decode_workspace(Hq, d)
+            outs = torch.zeros(steps, layers, Hq, d, device="cuda")
+            q_cur = torch.zeros(layers, Hq, d, device="cuda", dtype=torch.float16)
+            k_cur = torch.zeros(layers, 1, H * d, device="cuda", dtype=torch.float16)
+            v_cur = torch.zeros_like(k_cur)
+            out_cur = torch.zeros(layers, Hq, d, device="cuda")
+
+            def step():
+                for l in range(layers):
+                    kv.launch_kv_store_quant(sts[l].view(), k_cur[l], v_cur[l], None, 1, 0, rope_mode=kv.RopeMode.NEOX_FULL,
+                                             decode_state=state)
+                    kv.launch_decode_attention_quant(sts[l].view(), q_cur[l], query_heads=Hq, scale=d ** -0.5,
+                                                     decode_state=state, output=out_cur[l], workspace=ws)
+                state[1] += 1
+
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                graph = None
+                if use_graph:
+                    q_cur.copy_(qs[0]); k_cur.copy_(kn[0]); v_cur.copy_(vn[0])
+                    step(); stream.synchronize()
+                    state[1] = L0
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=stream):
+                        step()
+                    state[1] = L0
+                for s in range(steps):
+                    q_cur.copy_(qs[s]); k_cur.copy_(kn[s]); v_cur.copy_(vn[s])
+                    graph.replay() if graph is not None else step()
+                    outs[s].copy_(out_cur)
+            torch.cuda.synchronize()
+            snap = [torch.cat([st.key_cache_q8.flatten().view(torch.uint8), st.value_cache_q8.flatten().view(torch.uint8),
+                               st.key_scales.flatten().view(torch.uint8), st.value_scales.flatten().view(torch.uint8)]).cpu() for st in sts]
+            return outs.cpu(), snap
+        finally:
+            kv.set_launch_overlap(0)
+
+    ref_out, ref_snap = run(0, False)
+    assert torch.isfinite(ref_out).all() and ref_out.abs().max() > 0
+    for overlap, use_graph in ((1, False), (1, True), (0, True)):
+        out, snap = run(overlap, use_graph)
+        assert all(torch.equal(a, b) for a, b in zip(snap, ref_snap)), (overlap, use_graph)
+        assert torch.equal(out, ref_out), (overlap, use_graph, (out - ref_out).abs().max())

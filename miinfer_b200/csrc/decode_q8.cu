@@ -32,9 +32,11 @@
 //    its head's Q in registers with static indices.
 //  * P.V stays in fp32: lane = (position mod 4, 16-dim chunk), 4 heads x 16
 //    dims of accumulators per lane; int8->fp32 by byte-permute into the mantissa
-//    of 2^23 and one subtract (the conversion pipe is 8x slower than that), the
-//    multiply-adds as packed f32x2.  Accumulators are rescaled only on tiles
-//    where a head's running max moved.
+//    of 2^23 and one packed multiply-add that removes the offset (the conversion
+//    pipe is 8x slower than that), the multiply-adds as packed f32x2.  Folding
+//    the offset into a per-block bias that is subtracted once per launch was
+//    measured: 2% faster, 10x less accurate (1.5e-4), so it is not used.
+//    Accumulators are rescaled only on tiles where a head's running max moved.
 //  * Softmax is the online form in base 2; each pair keeps (m, l, acc) for the
 //    whole launch, the CTA merges its 4 pairs in shared memory and writes one
 //    partial per (split, query head) for the log-sum-exp merge kernel.
@@ -56,6 +58,10 @@ constexpr int kVStages = 2;   // TMA ring depth of a V-warp (V tile)
 constexpr int kSlots = 2;     // weight hand-off ring depth per pair
 constexpr int kD = 128;
 constexpr uint32_t kSpinLimit = 1u << 24;
+#ifndef B200KV_PV_UNROLL
+#define B200KV_PV_UNROLL 2
+#endif
+constexpr int kPvUnroll = B200KV_PV_UNROLL;   // positions of the P.V loop in flight per lane
 
 template <int NBLK>
 struct Smem {
@@ -167,7 +173,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     __syncthreads();
 
     bool failed = false;
-    // merge area of the pair (reuses its K ring once the main loop is over): m[4], l[4], pad, acc[G][128]
+    // merge area of the pair (reuses its K ring once the main loop is over): m[4], l[4], pad[24], acc[G][128]
     float* mine = reinterpret_cast<float*>(k_ring);
 
     if (is_k_warp) {
@@ -231,8 +237,11 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
         const float qmul = qmul_s[g];
         float m_run = -INFINITY, l_run = 0.0f;
         // per-lane byte offsets that do not change from tile to tile
-        const uint32_t k_lane = static_cast<uint32_t>(pl) * kD;           // row of round 0
-        const uint32_t swz16 = static_cast<uint32_t>(pl & 7) << 4;        // 128-byte swizzle: chunk ^= row & 7 (PPR is a multiple of 8 or pl < 8)
+        // byte offset of logical 16-byte chunk ch of this lane's row in round 0; the 128-byte swizzle stores it
+        // at chunk (ch ^ (row & 7)), and row & 7 == pl & 7 in every round (PPR is a multiple of 8, or pl < 8)
+        uint32_t koff[8];
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) koff[ch] = static_cast<uint32_t>(pl) * kD + (static_cast<uint32_t>(ch ^ (pl & 7)) << 4);
         const uint32_t s_lane = static_cast<uint32_t>(pl) * NBLK * 2;
         const uint32_t w_lane = static_cast<uint32_t>(pl * 4 + g) * 4;
 
@@ -242,7 +251,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
             const uint32_t pos0 = (t0 + i) * kTile;
             const int lo = begin > pos0 ? static_cast<int>(begin - pos0) : 0;
             const int hi = end - pos0 < static_cast<uint32_t>(kTile) ? static_cast<int>(end - pos0) : kTile;
-            const uint8_t* kt = k_ring + stage * L::kKTile + k_lane;
+            const uint8_t* kt = k_ring + stage * L::kKTile;
             const uint8_t* kst = s_ring + stage * 2 * L::kSTile + s_lane;
 
             float s[ROUNDS];
@@ -263,10 +272,10 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
                     ksf[0] = __half2float(*reinterpret_cast<const __half*>(kst + r * PPR * 2));
                 }
                 float total = 0.0f;
-                int isum0 = 0, isum1 = 0;   // two chains per block keep the dot-product pipe busy
+                int isum0 = 0, isum1 = 0;
 #pragma unroll
                 for (int ch = 0; ch < 8; ++ch) {
-                    const uint4 kw = *reinterpret_cast<const uint4*>(krow + ((ch << 4) ^ swz16));
+                    const uint4 kw = *reinterpret_cast<const uint4*>(krow + koff[ch]);
                     isum0 = __dp2a_lo(qreg[8 * ch + 0], static_cast<int>(kw.x), isum0);
                     isum1 = __dp2a_hi(qreg[8 * ch + 1], static_cast<int>(kw.x), isum1);
                     isum0 = __dp2a_lo(qreg[8 * ch + 2], static_cast<int>(kw.y), isum0);
@@ -314,13 +323,15 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
                     const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
                     const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
                     float* dst = reinterpret_cast<float*>(wt + w_lane + r * PPR * 16);
-                    dst[0 * L::kBlkStride / 4] = valid ? w[r] * a.x : 0.0f;
-                    dst[1 * L::kBlkStride / 4] = valid ? w[r] * a.y : 0.0f;
-                    dst[2 * L::kBlkStride / 4] = valid ? w[r] * b.x : 0.0f;
-                    dst[3 * L::kBlkStride / 4] = valid ? w[r] * b.y : 0.0f;
+                    const float e0 = valid ? w[r] * a.x : 0.0f, e1 = valid ? w[r] * a.y : 0.0f;
+                    const float e2 = valid ? w[r] * b.x : 0.0f, e3 = valid ? w[r] * b.y : 0.0f;
+                    dst[0 * L::kBlkStride / 4] = e0; dst[1 * L::kBlkStride / 4] = e1;
+                    dst[2 * L::kBlkStride / 4] = e2; dst[3 * L::kBlkStride / 4] = e3;
+
                 } else {
                     const float v = __half2float(*reinterpret_cast<const __half*>(vst + r * PPR * 2));
-                    *reinterpret_cast<float*>(wt + w_lane + r * PPR * 16) = valid ? w[r] * v : 0.0f;
+                    const float e0 = valid ? w[r] * v : 0.0f;
+                    *reinterpret_cast<float*>(wt + w_lane + r * PPR * 16) = e0;
                 }
             }
             if (pl == 0) reinterpret_cast<float*>(wt + NBLK * L::kBlkStride)[g] = alpha;
@@ -386,7 +397,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
 #ifdef B200KV_SKIP_PV
             acc[0][0].x += static_cast<float>(vt[0]) * wl[0];
 #else
-#pragma unroll 2
+#pragma unroll kPvUnroll
             for (int j = 0; j < kTile / 4; ++j) {
                 const uint4 vw = *reinterpret_cast<const uint4*>(vt + j * 4 * kD);
                 float wv[4];
@@ -430,7 +441,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
             for (int h = 0; h < G; ++h)
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
-                    *reinterpret_cast<float2*>(mine + 16 + h * kD + c * 16 + 2 * k) = acc[h][k];
+                    *reinterpret_cast<float2*>(mine + 32 + h * kD + c * 16 + 2 * k) = acc[h][k];
         }
     }
     __syncthreads();
@@ -451,7 +462,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
             const float* src = reinterpret_cast<const float*>(smem + w * kKStages * L::kKTile);
             const float a = (mw[w] == -INFINITY) ? 0.0f : exp2f(mw[w] - M);   // NaN (poison) propagates
             lt = fmaf(src[4 + h], a, lt);
-            at = fmaf(src[16 + h * kD + dim], a, at);
+            at = fmaf(src[32 + h * kD + dim], a, at);
         }
         const uint32_t head = kv_head * G + h;
         const size_t slot_idx = (static_cast<size_t>(session) * p.num_splits + split) * p.query_heads + head;
@@ -503,36 +514,59 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
         if (lane == 0) { sg[h] = M; sg[4 + h] = lsum; }
     }
     __syncthreads();
-    for (int h = threadIdx.x >> 7; h < G; h += 2) {
-        const uint32_t head = kv_head * G + h;
-        const float* accp = p.ws_acc + ((static_cast<size_t>(session) * S) * p.query_heads + head) * kD + dim;
-        const size_t stride = static_cast<size_t>(p.query_heads) * kD;
-        // in-order warps: issue a whole batch of independent loads (the partials sit in L2) before using any
-        float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        for (uint32_t sp0 = 0; sp0 < S; sp0 += 16) {
-            float v[16];
+    // 256 threads = 4 heads x 2 halves of the splits x 32 float4 columns: each thread issues its loads
+    // in batches of 10 -- warps issue in order, so a loop of dependent load/use pairs would pay the L2 latency per step
+    {
+        const int col = threadIdx.x & 31, part = (threadIdx.x >> 5) & 1, h = threadIdx.x >> 6;
+        float4 tot = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (h < G) {
+            const uint32_t head = kv_head * G + h;
+            const size_t stride = static_cast<size_t>(p.query_heads) * kD;
+            const float* accp = p.ws_acc + ((static_cast<size_t>(session) * S) * p.query_heads + head) * kD + col * 4;
+            for (uint32_t sp0 = part; sp0 < S; sp0 += 20) {
+                float4 v[10];
 #pragma unroll
-            for (int u = 0; u < 16; ++u) v[u] = (sp0 + u < S) ? __ldcg(accp + (sp0 + u) * stride) : 0.0f;
+                for (int u = 0; u < 10; ++u) {
+                    const uint32_t sp = sp0 + 2 * u;
+                    v[u] = sp < S ? __ldcg(reinterpret_cast<const float4*>(accp + sp * stride)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
 #pragma unroll
-            for (int u = 0; u < 16; ++u) tot[u & 3] = fmaf(v[u], (sp0 + u < S) ? sm[h * 128 + sp0 + u] : 0.0f, tot[u & 3]);
-        }
-        const float t0s = tot[0], t1s = tot[1], t2s = tot[2], t3s = tot[3];
-        const float total = (t0s + t1s) + (t2s + t3s);
-        const float gsum = sg[4 + h];
-        const size_t out_idx = (static_cast<size_t>(session) * p.query_heads + head) * kD + dim;
-        if (p.fuse.out_m != nullptr) {   // sequence shard: one merged, unnormalised partial
-            p.fuse.out_acc[out_idx] = total;
-            if (dim == 0) {
-                p.fuse.out_m[static_cast<size_t>(session) * p.query_heads + head] = sg[h];
-                p.fuse.out_l[static_cast<size_t>(session) * p.query_heads + head] = gsum;
+                for (int u = 0; u < 10; ++u) {
+                    const uint32_t sp = sp0 + 2 * u;
+                    const float a = sp < S ? sm[h * 128 + sp] : 0.0f;
+                    tot.x = fmaf(v[u].x, a, tot.x); tot.y = fmaf(v[u].y, a, tot.y);
+                    tot.z = fmaf(v[u].z, a, tot.z); tot.w = fmaf(v[u].w, a, tot.w);
+                }
             }
-        } else {
-            const float o = gsum > 0.0f ? total / gsum : (gsum == gsum ? 0.0f : gsum);
-            if (p.fuse.output != nullptr) p.fuse.output[out_idx] = o;
-            if (p.fuse.gated_output != nullptr) {
-                float gated = o;
-                if (p.fuse.gate != nullptr) gated = o * (1.0f / (1.0f + __expf(-p.fuse.gate[out_idx])));
-                p.fuse.gated_output[out_idx] = gated;
+        }
+        // fold the two halves through shared memory (the pairs' merge areas are free by now)
+        float4* fold = reinterpret_cast<float4*>(smem);
+        if (part == 1) fold[h * 32 + col] = tot;
+        __syncthreads();
+        if (part == 0 && h < G) {
+            const float4 o2 = fold[h * 32 + col];
+            tot.x += o2.x; tot.y += o2.y; tot.z += o2.z; tot.w += o2.w;
+            const uint32_t head = kv_head * G + h;
+            const float gsum = sg[4 + h];
+            const size_t out_idx = (static_cast<size_t>(session) * p.query_heads + head) * kD + col * 4;
+            if (p.fuse.out_m != nullptr) {   // sequence shard: one merged, unnormalised partial
+                *reinterpret_cast<float4*>(p.fuse.out_acc + out_idx) = tot;
+                if (col == 0) {
+                    p.fuse.out_m[static_cast<size_t>(session) * p.query_heads + head] = sg[h];
+                    p.fuse.out_l[static_cast<size_t>(session) * p.query_heads + head] = gsum;
+                }
+            } else {
+                const float inv = gsum > 0.0f ? 1.0f / gsum : (gsum == gsum ? 0.0f : gsum);
+                float4 o = make_float4(tot.x * inv, tot.y * inv, tot.z * inv, tot.w * inv);
+                if (p.fuse.output != nullptr) *reinterpret_cast<float4*>(p.fuse.output + out_idx) = o;
+                if (p.fuse.gated_output != nullptr) {
+                    if (p.fuse.gate != nullptr) {
+                        const float4 gt = *reinterpret_cast<const float4*>(p.fuse.gate + out_idx);
+                        o.x *= 1.0f / (1.0f + __expf(-gt.x)); o.y *= 1.0f / (1.0f + __expf(-gt.y));
+                        o.z *= 1.0f / (1.0f + __expf(-gt.z)); o.w *= 1.0f / (1.0f + __expf(-gt.w));
+                    }
+                    *reinterpret_cast<float4*>(p.fuse.gated_output + out_idx) = o;
+                }
             }
         }
     }

@@ -241,6 +241,9 @@ B200KV_API int b200kv_merge_partials(const float* part_m, const float* part_l, c
 
 /* ---- suffix / prefill attention -------------------------------------------- */
 
+/* Kept for call-site symmetry with the reference (which needs 32*T*heads*(2+d)
+ * floats of split partials, .hip:7154-7157): this kernel keeps its running
+ * state in registers, so the answer is 0 and `workspace` may be NULL. */
 B200KV_API size_t b200kv_prefill_workspace_bytes(uint32_t token_count, uint32_t query_heads, uint32_t head_dim);
 
 /* Replaces launch_qwen35_splitk_suffix_attention_quant

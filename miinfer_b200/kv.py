@@ -238,13 +238,13 @@ def launch_merge_partials(part_m: torch.Tensor, part_l: torch.Tensor, part_acc: 
 
 
 def launch_suffix_attention_quant(view: View, q: torch.Tensor, gate: Optional[torch.Tensor], gated_output: torch.Tensor,
-                                  workspace: torch.Tensor, token_count: int, base_position: int, *, query_heads: int,
+                                  workspace: Optional[torch.Tensor], token_count: int, base_position: int, *, query_heads: int,
                                   scale: float, prefill_state: Optional[torch.Tensor] = None,
                                   stream: Optional[torch.cuda.Stream] = None) -> None:
     """launch_qwen35_splitk_suffix_attention_quant (qwen3_gpu_primitives.hpp:670-692)."""
     check(lib.b200kv_prefill_attn(C.byref(view), _ptr(q), _dtype(q), _ptr(gate), _ptr(gated_output), token_count,
                                   base_position, query_heads, scale, _ptr(prefill_state), _ptr(workspace),
-                                  workspace.numel(), _stream(stream)), "b200kv_prefill_attn")
+                                  0 if workspace is None else workspace.numel(), _stream(stream)), "b200kv_prefill_attn")
 
 
 def set_launch_overlap(tail_positions: int) -> None:

@@ -1,0 +1,81 @@
+"""Host-side partitioning of the KV path across the GPUs of one box.
+
+The reference runs on one GPU; its design notes only sketch sharding by kv head
+(docs/architecture.md:1035-1092).  Three partitions are used here:
+
+* sessions  -> ranks, length-balanced (batched serving; no data-path collective);
+* kv heads  -> ranks (no collective inside attention);
+* positions -> ranks in contiguous, tile-aligned blocks (one long context); each
+  rank produces one (m, l, acc) partial per query head and the partials are
+  all-gathered and merged with the same log-sum-exp rule as the split-K stage 2
+  (gfx906/kernels/qwen3_primitives.hip:2295-2352).
+
+Pure Python (no CUDA): exercised on CPU with gloo in tests/test_partition_cpu.py.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence, Tuple
+
+TILE = 32  # the streaming decode kernel works in tiles of 32 positions
+
+
+def shard_range(length: int, rank: int, world: int, align: int = TILE) -> Tuple[int, int]:
+    """Positions [begin, end) of `rank` when [0, length) is cut into `world` contiguous blocks
+    whose boundaries are multiples of `align` (the last block takes the ragged tail)."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError("bad rank/world")
+    tiles = (length + align - 1) // align
+    t0 = tiles * rank // world
+    t1 = tiles * (rank + 1) // world
+    return min(t0 * align, length), min(t1 * align, length)
+
+
+def owner_of_position(position: int, length: int, world: int, align: int = TILE) -> int:
+    """Rank whose shard holds `position` (where an appended token's K/V row goes)."""
+    for r in range(world):
+        b, e = shard_range(length, r, world, align)
+        if b <= position < e:
+            return r
+    return world - 1
+
+
+def partition_sessions(lengths: Sequence[int], world: int) -> List[List[int]]:
+    """Longest-processing-time greedy bin packing of sessions by context length: returns, per rank,
+    the indices of its sessions (each rank owns whole caches; outputs stay with the session)."""
+    bins: List[List[int]] = [[] for _ in range(world)]
+    load = [0] * world
+    for i in sorted(range(len(lengths)), key=lambda j: (-lengths[j], j)):
+        r = min(range(world), key=lambda k: (load[k], k))
+        bins[r].append(i)
+        load[r] += lengths[i]
+    return [sorted(b) for b in bins]
+
+
+def kv_head_range(kv_heads: int, rank: int, world: int) -> Tuple[int, int]:
+    if kv_heads % world:
+        raise ValueError("kv heads must divide evenly over the ranks")
+    per = kv_heads // world
+    return rank * per, (rank + 1) * per
+
+
+def pack_partial(m, l, acc):
+    """One rank's partial as a single [query_heads, d + 2] tensor (one all-gather instead of three)."""
+    import torch
+
+    return torch.cat([m.unsqueeze(-1), l.unsqueeze(-1), acc], dim=-1).contiguous()
+
+
+def unpack_partials(gathered):
+    """[parts, query_heads, d + 2] -> (m [parts, H], l [parts, H], acc [parts, H, d]), contiguous."""
+    return gathered[..., 0].contiguous(), gathered[..., 1].contiguous(), gathered[..., 2:].contiguous()
+
+
+def all_gather_partials(dist, packed):
+    """All-gather of the per-rank partials: the one exchange step of sequence-sharded decode
+    (query_heads * (d + 2) fp32 per rank and layer)."""
+    import torch
+
+    world = dist.get_world_size()
+    out = torch.empty((world * packed.shape[0],) + tuple(packed.shape[1:]), dtype=packed.dtype, device=packed.device)
+    dist.all_gather_into_tensor(out, packed)   # concatenated along dim 0 (the form every backend accepts)
+    return out.view((world,) + tuple(packed.shape))

@@ -36,9 +36,9 @@ LAYERS, HQ, HKV, D, QB = 36, 32, 8, 128, 32
 ROW = D + 2 * (D // QB)  # 136 bytes per head-row
 THETA = 1.0e6
 
-# dram bytes per decode-attention launch measured by ncu (profiles/), scaled to a
-# 32K-context launch; None until a capture exists for the current kernel.
-NCU_TRAFFIC_BYTES_32K = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch at 32K context, from the ncu
+# capture summarised in profiles/decode_q8_kernel_32k_context.md (71.45 MB read + 1.28 MB written)
+NCU_TRAFFIC_BYTES_32K = 72_737_792
 
 
 def measured_peak_gbs() -> tuple[float, str]:
@@ -251,7 +251,7 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
     ms_total = e0.elapsed_time(e1)
     clocks = sampler.stop()
 
-    # ---- dominant kernel: decode attention alone (stage 1 + merge launches), for the roofline -----
+    # ---- dominant kernel: decode attention alone (one launch per layer), for the roofline -----
     with torch.cuda.stream(stream):
         for _ in range(3):
             attn_graph.replay()
@@ -306,12 +306,12 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
         "hbm_frac_whole_step": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES_32K, "peak_kind": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs, burst copy)",
-                     "kernel": "decode attention launch (split-K stage 1 + merge)", "us_per_launch": attn_us,
+                     "kernel": "decode_q8_kernel (split-K stage 1 with the merge fused into its last CTA)", "us_per_launch": attn_us,
                      "algorithmic_bytes_per_launch": attn_bytes, "frac_of_nominal_8TBs": achieved / 8000.0},
         "e2e": {"value": world * 1000.0 / e2e_ms, "unit": "tokens/s",
                 "h2d_bytes_per_step": int(h_q.numel() * 2 + h_k.numel() * 2 + h_v.numel() * 2),
                 "d2h_bytes_per_step": int(h_out.numel() * 4), "ms_per_step": e2e_ms},
-        "gpu_launches": args.steps * LAYERS * 3,
+        "gpu_launches": args.steps * LAYERS * 2,   # append + decode attention (merge fused) per layer
         "clocks": clocks,
     }
     return line

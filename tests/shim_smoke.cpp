@@ -1,0 +1,64 @@
+// Compiled and run by tests/test_shim_gpu.py: a reference-style call sequence (the names and argument order of
+// src/prefill_v2/attention_layer.cpp:297-343, 599-632) through miinfer_shim.hpp on a real device.
+// Prints "shim ok <checksum>"; the Python test checks the numbers against the oracle.
+#include <cmath>
+#include <cstdio>
+#include <vector>
+
+#include "miinfer_shim.hpp"
+
+template <class T>
+static T* dalloc(std::size_t count) {
+    void* p = nullptr;
+    cudaMalloc(&p, count * sizeof(T));
+    return static_cast<T*>(p);
+}
+
+int main() {
+    using namespace miinfer;
+    using namespace miinfer::prefill_v2;
+    constexpr std::uint32_t kQ = 24, kKv = 4, kD = 256, kPrefix = 96, kChunk = 8, kCap = 128;
+    AttentionLayerKvCacheStorage cache(kCap, KvCacheQuantMode::kQ8Q8);   // reference defaults: 4 kv heads, d=256, row scales
+    const AttentionKvCacheView v = cache.view();
+    std::vector<float> k((kPrefix + kChunk) * kKv * kD), val(k.size()), w(kD, 1.0f), q(kChunk * kQ * kD), gate(q.size());
+    unsigned s = 12345u;
+    auto rnd = [&]() { s = s * 1664525u + 1013904223u; return (static_cast<float>(s >> 8) / 8388608.0f - 1.0f); };
+    for (auto& x : k) x = rnd();
+    for (auto& x : val) x = rnd();
+    for (auto& x : q) x = rnd();
+    for (auto& x : gate) x = rnd();
+    float *dk = dalloc<float>(k.size()), *dv = dalloc<float>(val.size()), *dw = dalloc<float>(kD), *dq = dalloc<float>(q.size());
+    float *dg = dalloc<float>(gate.size()), *dout = dalloc<float>(q.size()), *ddec = dalloc<float>(kQ * kD);
+    cudaMemcpy(dk, k.data(), k.size() * 4, cudaMemcpyHostToDevice); cudaMemcpy(dv, val.data(), val.size() * 4, cudaMemcpyHostToDevice);
+    cudaMemcpy(dw, w.data(), kD * 4, cudaMemcpyHostToDevice); cudaMemcpy(dq, q.data(), q.size() * 4, cudaMemcpyHostToDevice);
+    cudaMemcpy(dg, gate.data(), gate.size() * 4, cudaMemcpyHostToDevice);
+    // prefix, then the chunk (store first, attend second -- attention_layer.cpp:297-343)
+    launch_qwen35_decoupled_k_norm_rope_kv_store_batch_quant(dk, dv, dw, v.key_cache, v.value_cache, v.key_cache_q8, v.key_scales,
+        v.value_cache_q8, v.value_scales, kPrefix + kChunk, 0, kCap, kKv, kD, 1.0e6f, 1.0e-6f, v.is_k_q8(), v.is_v_q8());
+    launch_qwen35_splitk_suffix_attention_quant(dq, v.key_cache, v.value_cache, v.key_cache_q8, v.key_scales, v.value_cache_q8,
+        v.value_scales, dg, dout, nullptr, kChunk, kPrefix, kCap, kQ, kKv, kD, 1.0f / 16.0f, v.is_k_q8(), v.is_v_q8(), 32);
+    // one decode step with the device-side position (attention_layer.cpp:613-632)
+    DeviceDecodeState st{}; st.position = kPrefix + kChunk - 1;
+    DeviceDecodeState* dst = dalloc<DeviceDecodeState>(1); cudaMemcpy(dst, &st, sizeof st, cudaMemcpyHostToDevice);
+    const std::size_t ws_bytes = b200kv_decode_workspace_bytes(kQ, kD, 1);
+    void* ws = dalloc<unsigned char>(ws_bytes); cudaMemset(ws, 0, ws_bytes);
+    set_decode_workspace(ws, ws_bytes);
+    launch_qwen35_tiled_online_attention_quant_dynamic(dq + (kChunk - 1) * kQ * kD, v.key_cache, v.value_cache, v.key_cache_q8, v.key_scales,
+        v.value_cache_q8, v.value_scales, dst, kCap, ddec, nullptr, nullptr, kQ, kKv, kD, 1.0f / 16.0f, v.is_k_q8(), v.is_v_q8());
+    if (cudaDeviceSynchronize() != cudaSuccess) { std::printf("shim FAILED: %s\n", cudaGetErrorString(cudaGetLastError())); return 1; }
+    std::vector<float> out(q.size()), dec(kQ * kD);
+    cudaMemcpy(out.data(), dout, out.size() * 4, cudaMemcpyDeviceToHost); cudaMemcpy(dec.data(), ddec, dec.size() * 4, cudaMemcpyDeviceToHost);
+    // the last chunk token's ungated decode output must equal its suffix output divided by sigmoid(gate)
+    double worst = 0.0, checksum = 0.0;
+    for (std::uint32_t i = 0; i < kQ * kD; ++i) {
+        const std::size_t j = static_cast<std::size_t>(kChunk - 1) * kQ * kD + i;
+        const double gated = dec[i] / (1.0 + std::exp(-static_cast<double>(gate[j])));
+        worst = std::fmax(worst, std::fabs(gated - out[j]));
+        checksum += out[j];
+    }
+    bool threw = false;
+    try { cache.download_raw(out.data(), kCap + 1); } catch (const std::runtime_error&) { threw = true; }
+    std::printf("shim %s worst=%.3e checksum=%.6f bytes=%zu\n", (worst < 2e-3 && threw) ? "ok" : "MISMATCH", worst, checksum,
+                cache.raw_tokens_bytes(kPrefix));
+    return (worst < 2e-3 && threw) ? 0 : 2;
+}

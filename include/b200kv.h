@@ -196,6 +196,27 @@ B200KV_API int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_
                        uint32_t cache_length, const b200kv_decode_state* decode_state,
                        void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream);
 
+/* Decode attention without a caller-supplied workspace and without any allocation (no counterpart in the
+ * reference).  For hosts that cannot allocate device memory once they are running -- a serving process
+ * that gave all device memory to its own pool at start-up and forbids driver allocations afterwards, or a
+ * sandbox in which allocation calls are not allowed -- and so cannot provide the split-K scratch of
+ * b200kv_decode_attn.  Same arguments and results as b200kv_decode_attn, minus the workspace pair; the scratch
+ * is a fixed 4 MiB array inside the library (b200kv_decode_static_scratch_bytes), present on every GPU
+ * that loads the library until the process exits.
+ *   - Limit: b200kv_decode_workspace_bytes(query_heads, head_dim, 1) must not exceed that size (32 query heads
+ *     at head_dim 128 and 24 at head_dim 256 fit); larger shapes return B200KV_ERR_WORKSPACE.
+ *   - The first call on each device looks up the array's device address (the device must be current); make
+ *     that first call before starting any stream capture.
+ *   - All calls on a device share the one array: two calls whose kernels overlap on the GPU (different
+ *     streams, or launch overlap between them) race on it.  Calls ordered on one stream are safe.
+ *   - It calls no cudaMalloc, cudaFree or allocating library routine; it issues one cudaMemsetAsync on
+ *     `stream` to clear the arrival counters and then the same kernels as b200kv_decode_attn. */
+B200KV_API size_t b200kv_decode_static_scratch_bytes(void);
+B200KV_API int b200kv_decode_attn_static(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
+                              float* output, float* gated_output, uint32_t query_heads, float scale,
+                              uint32_t cache_length, const b200kv_decode_state* decode_state,
+                              uint32_t num_splits, void* stream);
+
 /* Which stage-1 kernel b200kv_decode_attn picks for this view: 1 = the streaming
  * int8 kernel (int8 K and V, head_dim 128, 1/2/4 query heads per kv head,
  * capacity a multiple of 8), 0 = the generic kernel (every other mode and shape).

@@ -260,6 +260,14 @@ B200KV_API int b200kv_merge_partials(const float* part_m, const float* part_l, c
                           uint32_t num_parts, uint32_t query_heads, uint32_t head_dim,
                           const float* gate, float* output, float* gated_output, void* stream);
 
+/* The same merge over PACKED partials: part r occupies query_heads*(head_dim+2) consecutive floats laid out
+ * [m[query_heads] | l[query_heads] | acc[query_heads][head_dim]].  This is the buffer an all-gather of one
+ * packed partial per rank produces, so sequence-sharded decode is three launches per layer:
+ * b200kv_decode_partials (with part_m/part_l/part_acc pointing into the rank's packed buffer), the
+ * all-gather, and this call.  No counterpart in the reference (single GPU). */
+B200KV_API int b200kv_merge_partials_packed(const float* packed, uint32_t num_parts, uint32_t query_heads, uint32_t head_dim,
+                                 const float* gate, float* output, float* gated_output, void* stream);
+
 /* ---- suffix / prefill attention -------------------------------------------- */
 
 /* Kept for call-site symmetry with the reference (which needs 32*T*heads*(2+d)

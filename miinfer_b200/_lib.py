@@ -51,6 +51,7 @@ SIGNATURES = {
     "b200kv_decode_attn_batched": (i32, [VP, vp, vp, u32, u32, vp, i32, vp, vp, vp, u32, fl, vp, sz, u32, vp]),
     "b200kv_decode_partials": (i32, [VP, vp, i32, u32, fl, u32, u32, vp, vp, vp, vp, sz, u32, vp]),
     "b200kv_merge_partials": (i32, [vp, vp, vp, u32, u32, u32, vp, vp, vp, vp]),
+    "b200kv_merge_partials_packed": (i32, [vp, u32, u32, u32, vp, vp, vp, vp]),
     "b200kv_prefill_workspace_bytes": (sz, [u32, u32, u32]),
     "b200kv_prefill_attn": (i32, [VP, vp, i32, vp, vp, u32, u32, u32, fl, vp, vp, sz, vp]),
     "b200kv_snapshot_bytes": (sz, [VP, u64]),

@@ -117,11 +117,12 @@ __global__ void merge_kernel(const __grid_constant__ MergeParams p) {
     const uint32_t head = blockIdx.x, group = blockIdx.y, dim = threadIdx.x;
     const uint32_t H = p.query_heads, D = p.head_dim, S = p.num_parts;
     const size_t base = static_cast<size_t>(group) * S * H + head;
+    const size_t ml_stride = p.part_stride ? p.part_stride : H;   // packed parts (one buffer per rank) or dense arrays
     float* sa = sh;
     float* sl = sh + S;
     for (uint32_t s = dim; s < S; s += blockDim.x) {
-        sa[s] = p.part_m[base + static_cast<size_t>(s) * H];
-        sl[s] = p.part_l[base + static_cast<size_t>(s) * H];
+        sa[s] = p.part_m[base + static_cast<size_t>(s) * ml_stride];
+        sl[s] = p.part_l[base + static_cast<size_t>(s) * ml_stride];
     }
     __syncthreads();
     if (dim < 32) {
@@ -141,7 +142,7 @@ __global__ void merge_kernel(const __grid_constant__ MergeParams p) {
     __syncthreads();
     const float gmax = sh[2 * S], gsum = sh[2 * S + 1];
     const float* accp = p.part_acc + base * D + dim;
-    const size_t stride = static_cast<size_t>(H) * D;
+    const size_t stride = p.part_stride ? p.part_stride : static_cast<size_t>(H) * D;
     float t0 = 0.0f, t1 = 0.0f, t2 = 0.0f, t3 = 0.0f;
     uint32_t s = 0;
     for (; s + 4 <= S; s += 4) {
@@ -427,6 +428,27 @@ int b200kv_merge_partials(const float* part_m, const float* part_l, const float*
     mp.part_m = part_m;
     mp.part_l = part_l;
     mp.part_acc = part_acc;
+    mp.num_parts = num_parts;
+    mp.query_heads = query_heads;
+    mp.head_dim = head_dim;
+    mp.gate = gate;
+    mp.output = output;
+    mp.gated_output = gated_output;
+    return launch_merge(mp, 1, static_cast<cudaStream_t>(stream));
+}
+
+int b200kv_merge_partials_packed(const float* packed, uint32_t num_parts, uint32_t query_heads, uint32_t head_dim,
+                                 const float* gate, float* output, float* gated_output, void* stream) {
+    if (packed == nullptr || num_parts == 0 || query_heads == 0) return B200KV_ERR_INVALID;
+    if (output == nullptr && gated_output == nullptr) return B200KV_ERR_INVALID;
+    if (head_dim == 0 || head_dim > 1024) return B200KV_ERR_UNSUPPORTED;
+    int rc;
+    if ((rc = ensure_device()) != B200KV_OK) return rc;
+    MergeParams mp{};
+    mp.part_m = packed;
+    mp.part_l = packed + query_heads;
+    mp.part_acc = packed + 2 * static_cast<size_t>(query_heads);
+    mp.part_stride = static_cast<size_t>(query_heads) * (head_dim + 2u);
     mp.num_parts = num_parts;
     mp.query_heads = query_heads;
     mp.head_dim = head_dim;

@@ -33,6 +33,7 @@ struct MergeParams {
     uint32_t num_parts;
     uint32_t query_heads;
     uint32_t head_dim;
+    size_t part_stride;    // floats between consecutive parts in ALL three arrays; 0 = dense (H for m/l, H*d for acc)
     const float* gate;     // [groups][query_heads][d] or null
     float* output;         // normalised, or null
     float* gated_output;   // normalised * sigmoid(gate), or null

@@ -58,6 +58,7 @@ constexpr int kVStages = 2;   // TMA ring depth of a V-warp (V tile)
 constexpr int kSlots = 2;     // weight hand-off ring depth per pair
 constexpr int kD = 128;
 constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kPositionsPerSplit = 2048;   // batched launches: one split per this many positions of a session
 #ifndef B200KV_PV_UNROLL
 #define B200KV_PV_UNROLL 2
 #endif
@@ -142,10 +143,19 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     uint32_t begin, end;
     resolve_range(p, session, view, &begin, &end);
 
+    // Batched launches size the grid for the longest session; a shorter session uses only as many splits as its
+    // own length warrants (every CTA of the session derives the same number) and the surplus CTAs leave at once.
+    uint32_t num_splits = p.num_splits;
+    if (p.lengths != nullptr) {
+        const uint32_t want = (end - begin + kPositionsPerSplit - 1) / kPositionsPerSplit;
+        num_splits = min(num_splits, max(want, 1u));
+        if (split >= num_splits) return;
+    }
+
     // ---- this pair's tiles -----------------------------------------------------------
     const uint32_t tile_begin = begin / kTile, tile_end = (end + kTile - 1) / kTile;
     const uint64_t total_tiles = end > begin ? tile_end - tile_begin : 0;
-    const uint32_t npairs = p.num_splits * kPairs, gp = split * kPairs + pair;
+    const uint32_t npairs = num_splits * kPairs, gp = split * kPairs + pair;
     const uint32_t t0 = tile_begin + static_cast<uint32_t>(total_tiles * gp / npairs);
     const uint32_t t1 = tile_begin + static_cast<uint32_t>(total_tiles * (gp + 1) / npairs);
     const int ntiles = static_cast<int>(t1 - t0);
@@ -479,18 +489,18 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     __syncthreads();
     if (threadIdx.x == 0) {
         const uint32_t prev = atomicAdd(p.counters + session * gridDim.y + kv_head, 1u);
-        s_last = (prev + 1 == p.num_splits);
+        s_last = (prev + 1 == num_splits);
     }
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    const uint32_t S = p.num_splits;   // <= kMaxSplitsPerSession == 128
+    const uint32_t S = num_splits;     // <= kMaxSplitsPerSession == 128; the partial arrays keep the launch-wide stride
     float* sm = reinterpret_cast<float*>(smem + L::kOffMisc);   // [4][128] m -> a
     float* sl = sm + 4 * 128;                                   // [4][128] l
     float* sg = sl + 4 * 128;                                   // [4] merged max, [4] merged sum
     for (uint32_t idx = threadIdx.x; idx < G * S; idx += blockDim.x) {
         const uint32_t h = idx / S, sp = idx % S;
-        const size_t slot_idx = (static_cast<size_t>(session) * S + sp) * p.query_heads + kv_head * G + h;
+        const size_t slot_idx = (static_cast<size_t>(session) * p.num_splits + sp) * p.query_heads + kv_head * G + h;
         sm[h * 128 + sp] = __ldcg(p.ws_m + slot_idx);
         sl[h * 128 + sp] = __ldcg(p.ws_l + slot_idx);
     }
@@ -522,7 +532,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
         if (h < G) {
             const uint32_t head = kv_head * G + h;
             const size_t stride = static_cast<size_t>(p.query_heads) * kD;
-            const float* accp = p.ws_acc + ((static_cast<size_t>(session) * S) * p.query_heads + head) * kD + col * 4;
+            const float* accp = p.ws_acc + ((static_cast<size_t>(session) * p.num_splits) * p.query_heads + head) * kD + col * 4;
             for (uint32_t sp0 = part; sp0 < S; sp0 += 20) {
                 float4 v[10];
 #pragma unroll
@@ -645,6 +655,10 @@ uint32_t pick_splits_q8(const b200kv_view& geometry, uint32_t query_heads, uint3
     const uint32_t units = geometry.kv_heads * sessions;
     uint32_t s = (ctas + units / 2) / units;   // nearest to one full wave
     if (s == 0) s = 1;
+    if (sessions > 1) {   // mixed lengths: enough splits that the longest session is cut into kPositionsPerSplit pieces
+        const uint32_t by_length = (max_length + kPositionsPerSplit - 1) / kPositionsPerSplit;
+        if (by_length > s) s = by_length;
+    }
     const uint32_t tiles = (max_length + kTile - 1) / kTile;
     uint32_t by_tiles = tiles / (2 * kPairs);
     if (by_tiles == 0) by_tiles = 1;

@@ -20,7 +20,7 @@ from ._lib import B200KvError, View, check, lib
 __all__ = [
     "KvCacheQuantMode", "RopeMode", "AttentionKvCacheView", "AttentionLayerKvCacheStorage",
     "launch_kv_store_quant", "launch_decode_attention_quant", "launch_decode_attention_batched",
-    "launch_decode_partials", "launch_merge_partials", "launch_suffix_attention_quant",
+    "launch_decode_partials", "launch_merge_partials", "launch_merge_partials_packed", "packed_partial", "partial_views", "launch_suffix_attention_quant",
     "decode_workspace", "prefill_workspace", "view_table", "make_decode_state", "make_prefill_state",
     "token_sequence_hash", "decode_kernel_kind", "set_launch_overlap", "B200KvError", "FORCE_GENERIC",
 ]
@@ -235,6 +235,26 @@ def launch_merge_partials(part_m: torch.Tensor, part_l: torch.Tensor, part_acc: 
     check(lib.b200kv_merge_partials(_ptr(part_m), _ptr(part_l), _ptr(part_acc), num_parts, query_heads, head_dim,
                                     _ptr(gate), _ptr(output), _ptr(gated_output), _stream(stream)),
           "b200kv_merge_partials")
+
+
+def packed_partial(query_heads: int, head_dim: int, parts: int = 1, device=None) -> torch.Tensor:
+    """[parts][ m[H] | l[H] | acc[H][d] ] fp32: one rank's partial (parts=1) or the all-gathered set."""
+    return torch.zeros(parts, query_heads * (head_dim + 2), dtype=torch.float32, device=device or "cuda")
+
+
+def partial_views(packed_row: torch.Tensor, query_heads: int, head_dim: int):
+    """(m, l, acc) views into one packed partial, to pass to launch_decode_partials."""
+    m = packed_row[:query_heads]
+    l = packed_row[query_heads:2 * query_heads]
+    acc = packed_row[2 * query_heads:].view(query_heads, head_dim)
+    return m, l, acc
+
+
+def launch_merge_partials_packed(packed: torch.Tensor, *, num_parts: int, query_heads: int, head_dim: int,
+                                 output: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                                 gated_output: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None) -> None:
+    check(lib.b200kv_merge_partials_packed(_ptr(packed), num_parts, query_heads, head_dim, _ptr(gate), _ptr(output),
+                                           _ptr(gated_output), _stream(stream)), "b200kv_merge_partials_packed")
 
 
 def launch_suffix_attention_quant(view: View, q: torch.Tensor, gate: Optional[torch.Tensor], gated_output: torch.Tensor,

@@ -98,7 +98,7 @@ def run_seqshard(args, torch, dist, rank, world, local_rank):
     """One 131072-token session, KV sharded by position over the ranks; per layer each rank reduces its shard to one
     (m, l, acc) partial per query head, the partials are all-gathered (NCCL) and merged on every rank."""
     from miinfer_b200 import kv
-    from miinfer_b200.partition import all_gather_partials, pack_partial, shard_range, unpack_partials
+    from miinfer_b200.partition import shard_range
 
     L, HQ, HKV, D, LAYERS = args.context if args.context != 32768 else 131072, 32, 8, 128, args.layers
     b, e = shard_range(L, rank, world)
@@ -110,24 +110,33 @@ def run_seqshard(args, torch, dist, rank, world, local_rank):
     g = torch.Generator(device="cuda"); g.manual_seed(99)
     q = torch.randn(LAYERS, HQ, D, generator=g, device="cuda").half()      # replicated query (same seed on every rank)
     out = torch.zeros(LAYERS, HQ, D, device="cuda")
-    pm = torch.zeros(HQ, device="cuda"); pl = torch.zeros(HQ, device="cuda"); pa = torch.zeros(HQ, D, device="cuda")
+    mine = kv.packed_partial(HQ, D, 1)                 # this rank's (m | l | acc), written in place by the kernel
+    pm, pl, pa = kv.partial_views(mine[0], HQ, D)
+    gathered = kv.packed_partial(HQ, D, world)
     ws = kv.decode_workspace(HQ, D)
     views = [c.view() for c in caches]
     kv.set_launch_overlap(0)
 
     def step():
         for l in range(LAYERS):
+            if dist is None:
+                kv.launch_decode_attention_quant(views[l], q[l], query_heads=HQ, scale=D ** -0.5, cache_length=n, output=out[l], workspace=ws)
+                continue
             kv.launch_decode_partials(views[l], q[l], query_heads=HQ, scale=D ** -0.5, range_begin=0, range_end=n,
                                       part_m=pm, part_l=pl, part_acc=pa, workspace=ws)
-            if dist is not None:
-                gathered = all_gather_partials(dist, pack_partial(pm, pl, pa))
-                m, l_, acc = unpack_partials(gathered)
-                kv.launch_merge_partials(m, l_, acc, num_parts=world, query_heads=HQ, head_dim=D, output=out[l])
-            else:
-                kv.launch_merge_partials(pm.unsqueeze(0), pl.unsqueeze(0), pa.unsqueeze(0), num_parts=1, query_heads=HQ, head_dim=D, output=out[l])
+            dist.all_gather_into_tensor(gathered.view(-1), mine.view(-1))     # 16.6 KB per rank: the one exchange step
+            kv.launch_merge_partials_packed(gathered, num_parts=world, query_heads=HQ, head_dim=D, output=out[l])
 
-    stream = torch.cuda.current_stream()
-    ms = _time(torch, dist, stream, step, args.warmup, args.steps)
+    # the whole decode step (kernels and collectives) is captured once and replayed: the exchange is latency-bound
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+    torch.cuda.synchronize()
+    ms = _time(torch, dist, stream, graph.replay, args.warmup, args.steps)
     bw_peak, _, kind = _peaks()
     bytes_total = LAYERS * L * HKV * 136 * 2
     achieved = bytes_total / (ms * 1e-3) / 1e9

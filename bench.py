@@ -202,10 +202,14 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
 
     def layer_pass():
         for l in range(LAYERS):
-            kv.launch_kv_store_quant(views[l], k_new[l], v_new[l], None, 1, 0, rope_mode=kv.RopeMode.NEOX_FULL,
-                                     theta=THETA, decode_state=state)
-            kv.launch_decode_attention_quant(views[l], q[l], query_heads=HQ, scale=scale, decode_state=state,
-                                             output=out[l], workspace=ws)
+            if args.two_launches:   # the reference's call pair: store kernel, then decode attention
+                kv.launch_kv_store_quant(views[l], k_new[l], v_new[l], None, 1, 0, rope_mode=kv.RopeMode.NEOX_FULL,
+                                         theta=THETA, decode_state=state)
+                kv.launch_decode_attention_quant(views[l], q[l], query_heads=HQ, scale=scale, decode_state=state,
+                                                 output=out[l], workspace=ws)
+            else:                   # the same work as one launch (append fused into the streaming kernel)
+                kv.launch_decode_step(views[l], k_new[l], v_new[l], q[l], query_heads=HQ, scale=scale, decode_state=state,
+                                      rope_mode=kv.RopeMode.NEOX_FULL, theta=THETA, output=out[l], workspace=ws)
 
     def attention_only_pass():
         for l in range(LAYERS):
@@ -311,7 +315,7 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
         "e2e": {"value": world * 1000.0 / e2e_ms, "unit": "tokens/s",
                 "h2d_bytes_per_step": int(h_q.numel() * 2 + h_k.numel() * 2 + h_v.numel() * 2),
                 "d2h_bytes_per_step": int(h_out.numel() * 4), "ms_per_step": e2e_ms},
-        "gpu_launches": args.steps * LAYERS * 2,   # append + decode attention (merge fused) per layer
+        "gpu_launches": args.steps * LAYERS * (2 if args.two_launches else 1),   # per layer: fused append+attention+merge
         "clocks": clocks,
     }
     return line
@@ -326,6 +330,7 @@ def main() -> None:
     ap.add_argument("--workload", default="decode32k")
     ap.add_argument("--context", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--two-launches", action="store_true", help="append and attention as two launches per layer (A/B of the fused step)")
     ap.add_argument("--no-overlap", action="store_true", help="launch every kernel fully serialised (A/B of launch overlap)")
     ap.add_argument("--layers", type=int, default=36, help="layers per step (36 = the benchmark; fewer only for ncu captures)")
     args = ap.parse_args()

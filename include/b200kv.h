@@ -196,6 +196,19 @@ B200KV_API int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_
                        uint32_t cache_length, const b200kv_decode_state* decode_state,
                        void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream);
 
+/* One decode step of a layer in ONE launch: append the new token's K/V row at `position` (or at
+ * decode_state->position, read on the device) and attend positions [0, position].  Equivalent to b200kv_append
+ * (one token) followed by b200kv_decode_attn(cache_length = position + 1) -- the call pair of
+ * src/prefill_v2/attention_layer.cpp:599-632 -- with bit-identical cache contents; the streaming kernel does the
+ * append inside the CTA that owns the last tile, which removes a launch and its latency from every layer.
+ * key/value: [kv_heads*head_dim] of kv_dtype.  Caches the streaming kernel does not support fall back to the two
+ * launches.  If decode_state is given the position must be below the capacity (the kernel cannot report it). */
+B200KV_API int b200kv_decode_step(const b200kv_view* view, const void* key, const void* value, int kv_dtype,
+                       const float* k_norm_weight, int rope_mode, float theta, float epsilon,
+                       const void* q, int q_dtype, const float* gate, float* output, float* gated_output,
+                       uint32_t query_heads, float scale, uint32_t position, const b200kv_decode_state* decode_state,
+                       void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream);
+
 /* Decode attention without a caller-supplied workspace and without any allocation (no counterpart in the
  * reference).  For hosts that cannot allocate device memory once they are running -- a serving process
  * that gave all device memory to its own pool at start-up and forbids driver allocations afterwards, or a

@@ -15,7 +15,7 @@
 //     exactly the same pairs in the same order (bit-identical sum).
 // Rows are staged through shared memory so the cache is written with one 4- or
 // 8-byte store per lane (a full 128/256-byte line per row).
-#include "kv_common.cuh"
+#include "append_row.cuh"
 
 #include <cmath>
 #include <type_traits>
@@ -42,34 +42,19 @@ constexpr int kAppendWarps = 4;
 template <int NJ>
 __device__ __forceinline__ void quantize_and_stage(const float (&x)[NJ], uint32_t qblock_is_row, int lane,
                                                    int8_t* stage, __half* scale_dst) {
+    int8_t q[NJ];
     float scale[NJ];
+    quantize_row<NJ>(x, qblock_is_row != 0, q, scale);
     if (qblock_is_row) {
-        float amax = 0.0f;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) amax = fmaxf(amax, fabsf(x[j]));
-        amax = warp_max(amax);
-        const float s = (amax > 0.0f) ? __fdiv_rn(amax, 127.0f) : 1.0f;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) scale[j] = s;
-        if (lane == 0) scale_dst[0] = __float2half_rn(s);
+        if (lane == 0) scale_dst[0] = __float2half_rn(scale[0]);
     } else {
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-            const float amax = warp_max(fabsf(x[j]));
-            scale[j] = (amax > 0.0f) ? __fdiv_rn(amax, 127.0f) : 1.0f;
-        }
         // lane j stores the scale of block j (NJ <= 8 lanes take part)
 #pragma unroll
         for (int j = 0; j < NJ; ++j)
             if (lane == j) scale_dst[j] = __float2half_rn(scale[j]);
     }
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-        const float inv = (scale[j] > 0.0f) ? __fdiv_rn(1.0f, scale[j]) : 1.0f;
-        int q = __float2int_rn(__fmul_rn(x[j], inv));
-        q = max(-128, min(127, q));
-        stage[lane + 32 * j] = static_cast<int8_t>(q);
-    }
+    for (int j = 0; j < NJ; ++j) stage[lane + 32 * j] = q[j];
 }
 
 template <int D, bool IN_F16>
@@ -115,43 +100,7 @@ append_kernel(const __grid_constant__ AppendParams p) {
         }
     }
 
-    if (p.k_norm_weight != nullptr) {
-        float sq[NJ];
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) sq[j] = __fmul_rn(k[j], k[j]);
-#pragma unroll
-        for (int half = NJ / 2; half >= 1; half >>= 1)
-#pragma unroll
-            for (int j = 0; j < half; ++j) sq[j] = __fadd_rn(sq[j], sq[j + half]);
-        float ss = sq[0];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, o));
-        ss = __shfl_sync(0xffffffffu, ss, 0);
-        const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(D)), p.epsilon)));
-#pragma unroll
-        for (int j = 0; j < NJ; ++j)
-            k[j] = __fmul_rn(__fmul_rn(k[j], r), p.k_norm_weight[lane + 32 * j]);
-    }
-
-    if (p.rope_mode == B200KV_ROPE_NEOX_FULL) {
-#pragma unroll
-        for (int j = 0; j < NJ / 2; ++j) {
-            const float angle = __fmul_rn(static_cast<float>(static_cast<uint32_t>(position)), p.inv_freq[lane + 32 * j]);
-            float s, c;
-            sincos_pinned(angle, &s, &c);
-            const float x0 = k[j], x1 = k[j + NJ / 2];
-            k[j] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
-            k[j + NJ / 2] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
-        }
-    } else if (p.rope_mode == B200KV_ROPE_SECTIONED64) {
-        float angle = static_cast<float>(static_cast<uint32_t>(position));
-        for (int i = 0; i < lane; ++i) angle = __fmul_rn(angle, p.sectioned_step);
-        float s, c;
-        sincos_pinned(angle, &s, &c);
-        const float x0 = k[0], x1 = k[1];
-        k[0] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
-        k[1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
-    }
+    transform_k_row<D>(k, lane, static_cast<uint32_t>(position), p.k_norm_weight, p.epsilon, p.rope_mode, p.inv_freq, p.sectioned_step);
 
     const uint32_t mode = p.view.quant_mode;
     const bool k_q8 = (mode == B200KV_Q8_F16 || mode == B200KV_Q8_Q8);

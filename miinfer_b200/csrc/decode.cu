@@ -314,6 +314,60 @@ int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_dtype, cons
     return run_decode(p, *view, max_length, workspace, workspace_bytes, num_splits, mp, 1, s);
 }
 
+int b200kv_decode_step(const b200kv_view* view, const void* key, const void* value, int kv_dtype,
+                       const float* k_norm_weight, int rope_mode, float theta, float epsilon,
+                       const void* q, int q_dtype, const float* gate, float* output, float* gated_output,
+                       uint32_t query_heads, float scale, uint32_t position, const b200kv_decode_state* decode_state,
+                       void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream) {
+    int rc = validate_view(view);
+    if (rc != B200KV_OK) return rc;
+    if (key == nullptr || value == nullptr || q == nullptr || (output == nullptr && gated_output == nullptr)) return B200KV_ERR_INVALID;
+    if ((kv_dtype != B200KV_F16 && kv_dtype != B200KV_F32) || (q_dtype != B200KV_F16 && q_dtype != B200KV_F32)) return B200KV_ERR_INVALID;
+    if (rope_mode < B200KV_ROPE_NONE || rope_mode > B200KV_ROPE_SECTIONED64) return B200KV_ERR_INVALID;
+    if (!std::isfinite(theta) || !std::isfinite(epsilon) || (rope_mode != B200KV_ROPE_NONE && !(theta > 0.0f))) return B200KV_ERR_INVALID;
+    if ((rc = check_heads(view, query_heads, scale)) != B200KV_OK) return rc;
+    if (decode_state == nullptr && position >= view->capacity) return B200KV_ERR_RANGE;
+    const bool force_generic = (num_splits & B200KV_SPLITS_FORCE_GENERIC) != 0;
+    if (force_generic || !q8_fast_path_ok(*view, query_heads)) {
+        // no fused kernel for this cache: the two launches the fused one stands for
+        rc = b200kv_append(view, key, value, kv_dtype, k_norm_weight, rope_mode, theta, epsilon, 1, position, nullptr, decode_state, stream);
+        if (rc != B200KV_OK) return rc;
+        return b200kv_decode_attn(view, q, q_dtype, gate, output, gated_output, query_heads, scale, position + 1, decode_state,
+                                  workspace, workspace_bytes, num_splits, stream);
+    }
+    if ((rc = ensure_device()) != B200KV_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    DecodeParams p{};
+    p.view = *view;
+    p.decode_state = decode_state;
+    p.cache_length = position + 1;
+    p.sessions = 1;
+    p.q = q;
+    p.q_is_f16 = (q_dtype == B200KV_F16);
+    p.query_heads = query_heads;
+    p.scale = scale;
+    p.new_key = key;
+    p.new_value = value;
+    p.new_is_f16 = (kv_dtype == B200KV_F16);
+    p.k_norm_weight = k_norm_weight;
+    p.rope_mode = rope_mode;
+    p.epsilon = epsilon;
+    if (rope_mode == B200KV_ROPE_NEOX_FULL) {
+        for (uint32_t i = 0; i < view->head_dim / 2; ++i)
+            p.inv_freq[i] = std::pow(theta, -static_cast<float>(2 * i) / static_cast<float>(view->head_dim));
+    } else if (rope_mode == B200KV_ROPE_SECTIONED64) {
+        p.sectioned_step = std::pow(theta, -2.0f / 64.0f);
+    }
+    const uint32_t max_length = decode_state ? static_cast<uint32_t>(view->capacity) : position + 1;
+    MergeParams mp{};
+    mp.query_heads = query_heads;
+    mp.head_dim = view->head_dim;
+    mp.gate = gate;
+    mp.output = output;
+    mp.gated_output = gated_output;
+    return run_decode(p, *view, max_length, workspace, workspace_bytes, num_splits, mp, 1, s);
+}
+
 int b200kv_decode_attn_batched(const b200kv_view* views, void* view_table, const uint32_t* lengths,
                                uint32_t sessions, uint32_t max_length, const void* q, int q_dtype,
                                const float* gate, float* output, float* gated_output,

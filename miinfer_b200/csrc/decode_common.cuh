@@ -66,6 +66,16 @@ struct DecodeParams {
     // Fused merge (streaming kernel only): when `counters` is non-null the last CTA of each
     // (session, kv head) combines all splits and writes `fuse`'s outputs; the counters must be
     // zero on entry and are zero again on exit.
+    // Fused single-token append (streaming kernel, one session): the pair that owns the last tile quantises the new
+    // token's K/V row of its kv head, stores it at position end-1 and patches its shared-memory tiles with it.
+    const void* new_key;                     // [kv_heads*d] of new_is_f16 ? fp16 : fp32, or null = no fused append
+    const void* new_value;
+    int new_is_f16;
+    const float* k_norm_weight;
+    int rope_mode;
+    float epsilon;
+    float sectioned_step;
+    float inv_freq[64];                      // NeoX frequencies for d = 128
     uint32_t overlap_tail;                   // launch overlap: the last n positions of the range are read only after pdl_wait
     uint32_t* counters;                      // [sessions][kv_heads]
     MergeParams fuse;

@@ -42,6 +42,7 @@
 //    partial per (split, query head) for the log-sum-exp merge kernel.
 //  * Every wait is bounded: a copy or hand-off that never arrives poisons the
 //    partial with NaN instead of hanging the GPU.
+#include "append_row.cuh"
 #include "decode_common.cuh"
 
 #include <cstring>
@@ -57,7 +58,7 @@ constexpr int kKStages = 3;   // TMA ring depth of a K-warp (K tile + both scale
 constexpr int kVStages = 2;   // TMA ring depth of a V-warp (V tile)
 constexpr int kSlots = 2;     // weight hand-off ring depth per pair
 constexpr int kD = 128;
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kSpinLimit = 1u << 20;   // bounded waits: a lost copy or hand-off ends the kernel with a poisoned partial
 constexpr uint32_t kPositionsPerSplit = 2048;   // batched launches: one split per this many positions of a session
 #ifndef B200KV_PV_UNROLL
 #define B200KV_PV_UNROLL 2
@@ -122,6 +123,40 @@ __device__ __forceinline__ float2 cvt2(uint32_t x, uint32_t sel_lo, uint32_t sel
     return __ffma2_rn(f, make_float2(1.0f, 1.0f), make_float2(-8388736.0f, -8388736.0f));
 }
 
+// ---- fused single-token append -----------------------------------------------------------------------------
+// Kept out of line so the rarely-taken path does not widen the register allocation of the streaming loops.
+// Loads the new row of `kv_head` (lane L: elements L, L+32, L+64, L+96).
+__device__ __noinline__ void load_new_row(const void* src, int is_f16, uint32_t kv_head, int lane, float (&x)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const size_t i = static_cast<size_t>(kv_head) * kD + lane + 32 * j;
+        x[j] = is_f16 ? __half2float(static_cast<const __half*>(src)[i]) : static_cast<const float*>(src)[i];
+    }
+}
+
+// Quantises the new K and V rows of `kv_head` and stores them (int8 + fp16 block scales) at cache row `row_index`.
+template <int NBLK>
+__device__ __noinline__ void fused_append_row(const DecodeParams& p, const b200kv_view& view, uint32_t kv_head, uint32_t position,
+                                              uint64_t row_index, int lane) {
+    float k[4], v[4];
+    load_new_row(p.new_key, p.new_is_f16, kv_head, lane, k);
+    load_new_row(p.new_value, p.new_is_f16, kv_head, lane, v);
+    transform_k_row<kD>(k, lane, position, p.k_norm_weight, p.epsilon, p.rope_mode, p.inv_freq, p.sectioned_step);
+    int8_t kq[4], vq[4];
+    float ksc[4], vsc[4];
+    quantize_row<4>(k, NBLK == 1, kq, ksc);
+    quantize_row<4>(v, NBLK == 1, vq, vsc);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        view.key_q8[row_index * kD + lane + 32 * j] = kq[j];
+        view.value_q8[row_index * kD + lane + 32 * j] = vq[j];
+    }
+    if (lane < NBLK) {
+        static_cast<__half*>(view.key_scales)[row_index * NBLK + lane] = __float2half_rn(ksc[NBLK == 1 ? 0 : lane]);
+        static_cast<__half*>(view.value_scales)[row_index * NBLK + lane] = __float2half_rn(vsc[NBLK == 1 ? 0 : lane]);
+    }
+}
+
 // G query heads per kv head (1, 2 or 4); NBLK scales per row (4 = q8_0 blocks of 32, 1 = one per row).
 template <int G, int NBLK, bool Q_F16>
 __global__ void __launch_bounds__(kPairs * 64, 2)
@@ -156,11 +191,19 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     const uint32_t tile_begin = begin / kTile, tile_end = (end + kTile - 1) / kTile;
     const uint64_t total_tiles = end > begin ? tile_end - tile_begin : 0;
     const uint32_t npairs = num_splits * kPairs, gp = split * kPairs + pair;
-    const uint32_t t0 = tile_begin + static_cast<uint32_t>(total_tiles * gp / npairs);
-    const uint32_t t1 = tile_begin + static_cast<uint32_t>(total_tiles * (gp + 1) / npairs);
+    // A fused append costs its pair about one tile's time: it is counted as one extra unit at the end of the range,
+    // so the pair that does it is handed one tile less.
+    const bool fuse = p.new_key != nullptr;
+    const uint64_t units = total_tiles + (fuse ? 1 : 0);
+    const uint64_t u0 = units * gp / npairs, u1 = units * (gp + 1) / npairs;
+    const uint32_t t0 = tile_begin + static_cast<uint32_t>(u0 < total_tiles ? u0 : total_tiles);
+    const uint32_t t1 = tile_begin + static_cast<uint32_t>(u1 < total_tiles ? u1 : total_tiles);
     const int ntiles = static_cast<int>(t1 - t0);
-    // With launch overlap the previous kernel may still be appending: rows at or above early_end wait for it.
-    const uint32_t early_end = end > p.overlap_tail ? end - p.overlap_tail : 0;
+    const bool owner = fuse && ntiles > 0 && t1 == tile_end;   // this pair holds the tile of the appended token
+    // With launch overlap the previous kernel may still be appending: rows at or above early_end wait for it.  The
+    // row a fused append writes is never loaded early either.
+    uint32_t early_end = end > p.overlap_tail ? end - p.overlap_tail : 0;
+    if (fuse && early_end >= end) early_end = end - 1;
 
     uint8_t* k_ring = smem + pair * kKStages * L::kKTile;
     uint8_t* v_ring = smem + L::kOffV + pair * kVStages * L::kKTile;
@@ -207,6 +250,15 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
         if (lane == 0)
             while (issued < kKStages && issued < ntiles && (t0 + issued + 1) * kTile <= early_end) issue(issued++);
         pdl_wait();
+        if (owner) {
+            // the new row goes to the cache first; its tile is loaded (by TMA, an asynchronous-proxy read) only afterwards
+            fused_append_row<NBLK>(p, view, kv_head, end - 1, head_row0 + end - 1, lane);
+            __threadfence();
+            asm volatile("fence.proxy.async;" ::: "memory");
+            // arrive without waiting: the V-warp joins this barrier only before its LAST tile, long after it has
+            // consumed weights this warp still has to produce
+            asm volatile("bar.arrive %0, 64;" ::"r"(2 + pair) : "memory");
+        }
         if (lane == 0)
             while (issued < kKStages && issued < ntiles) issue(issued++);
 
@@ -366,12 +418,18 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
             mbar_expect_tx(bar, rows * kD);
             bulk_load(smem_u32(v_ring + stage * L::kKTile), v_plane + static_cast<size_t>(pos0) * kD, rows * kD, bar);
         };
-        int issued = 0;
-        if (lane == 0)
-            while (issued < kVStages && issued < ntiles && (t0 + issued + 1) * kTile <= early_end) issue(issued++);
+        int issued = 0;   // kept identical in all lanes: the hand-shake below is warp-wide
+        while (issued < kVStages && issued < ntiles && (t0 + issued + 1) * kTile <= early_end) {
+            if (lane == 0) issue(issued);
+            ++issued;
+        }
         pdl_wait();
-        if (lane == 0)
-            while (issued < kVStages && issued < ntiles) issue(issued++);
+        while (issued < kVStages && issued < ntiles) {
+            // the tile of a fused append is loaded only after the K-warp has stored the new row
+            if (owner && issued == ntiles - 1) asm volatile("bar.sync %0, 64;" ::"r"(2 + pair) : "memory");
+            if (lane == 0) issue(issued);
+            ++issued;
+        }
 
         const int r4 = lane >> 3, c = lane & 7;   // positions r4 + 4j, dims [16c, 16c+16)
         const uint32_t v_lane = static_cast<uint32_t>(r4) * kD + c * 16;
@@ -429,6 +487,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
             }
 #endif
             __syncwarp();   // every lane is done with this stage and this weight slot
+            if (owner && i + kVStages == ntiles - 1) asm volatile("bar.sync %0, 64;" ::"r"(2 + pair) : "memory");
             if (lane == 0) {
                 mbar_arrive(bar_wempty + slot * 8);
                 if (i + kVStages < ntiles) issue(i + kVStages);

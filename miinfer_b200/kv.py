@@ -19,7 +19,7 @@ from ._lib import B200KvError, View, check, lib
 
 __all__ = [
     "KvCacheQuantMode", "RopeMode", "AttentionKvCacheView", "AttentionLayerKvCacheStorage",
-    "launch_kv_store_quant", "launch_decode_attention_quant", "launch_decode_attention_batched",
+    "launch_kv_store_quant", "launch_decode_attention_quant", "launch_decode_attention_batched", "launch_decode_step",
     "launch_decode_partials", "launch_merge_partials", "launch_merge_partials_packed", "packed_partial", "partial_views", "launch_suffix_attention_quant",
     "decode_workspace", "prefill_workspace", "view_table", "make_decode_state", "make_prefill_state",
     "token_sequence_hash", "decode_kernel_kind", "set_launch_overlap", "B200KvError", "FORCE_GENERIC",
@@ -199,6 +199,22 @@ def launch_decode_attention_quant(view: View, q: torch.Tensor, *, query_heads: i
     check(lib.b200kv_decode_attn(C.byref(view), _ptr(q), _dtype(q), _ptr(gate), _ptr(output), _ptr(gated_output),
                                  query_heads, scale, cache_length, _ptr(decode_state), _ptr(workspace),
                                  workspace.numel(), num_splits, _stream(stream)), "b200kv_decode_attn")
+
+
+def launch_decode_step(view: View, key: torch.Tensor, value: torch.Tensor, q: torch.Tensor, *, query_heads: int, scale: float,
+                       position: int = 0, decode_state: Optional[torch.Tensor] = None, k_norm_weight: Optional[torch.Tensor] = None,
+                       rope_mode: RopeMode = RopeMode.NEOX_FULL, theta: float = 1.0e6, epsilon: float = 1.0e-6,
+                       output: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                       gated_output: Optional[torch.Tensor] = None, workspace: torch.Tensor, num_splits: int = 0,
+                       stream: Optional[torch.cuda.Stream] = None) -> None:
+    """Append one token and attend in one launch (b200kv_decode_step): the fused form of the store + decode-attention
+    call pair of src/prefill_v2/attention_layer.cpp:599-632."""
+    if key.dtype != value.dtype:
+        raise ValueError("key and value must share a dtype")
+    check(lib.b200kv_decode_step(C.byref(view), _ptr(key), _ptr(value), _dtype(key), _ptr(k_norm_weight), int(rope_mode), theta,
+                                 epsilon, _ptr(q), _dtype(q), _ptr(gate), _ptr(output), _ptr(gated_output), query_heads, scale,
+                                 position, _ptr(decode_state), _ptr(workspace), workspace.numel(), num_splits, _stream(stream)),
+          "b200kv_decode_step")
 
 
 def launch_decode_attention_batched(views, view_table: torch.Tensor, lengths: torch.Tensor, max_length: int,

@@ -283,3 +283,85 @@ def test_decode_loop_with_launch_overlap_matches_serial(cuda):
         out, snap = run(overlap, use_graph)
         assert all(torch.equal(a, b) for a, b in zip(snap, ref_snap)), (overlap, use_graph)
         assert torch.equal(out, ref_out), (overlap, use_graph, (out - ref_out).abs().max())
+
+
+@pytest.mark.parametrize("qb,norm,rope,dtype", [(32, False, 1, np.float16), (128, True, 2, np.float32), (32, True, 1, np.float32)])
+def test_fused_decode_step_appends_bit_exact_and_attends(cuda, qb, norm, rope, dtype):
+    """b200kv_decode_step == append + decode attention: cache rows bit-equal to the oracle, output within tolerance,
+    at positions that fall first, in the middle and last in a 32-position tile, eagerly and from device state."""
+    rng = np.random.default_rng(91)
+    H, Hq, d, L0, cap = 8, 32, 128, 700, 1024
+    k0 = ko.normal_f16(rng, (L0, H * d)).astype(np.float32); v0 = ko.normal_f16(rng, (L0, H * d)).astype(np.float32)
+    w = (1.0 + 0.1 * rng.standard_normal(d)).astype(np.float32) if norm else None
+    host = ko.HostCache(cap, H, d, qb, 3)
+    host.append(k0, v0, w, 0, rope_mode=rope)
+    st = upload(host)
+    ws = kv.decode_workspace(Hq, d)
+    state = kv.make_decode_state(0)
+    wd = None if w is None else to_dev(w)
+    for step, position in enumerate(range(L0, L0 + 70)):
+        kn = ko.normal_f16(rng, (1, H * d)) if dtype == np.float16 else rng.standard_normal((1, H * d), dtype=np.float32)
+        vn = ko.normal_f16(rng, (1, H * d)) if dtype == np.float16 else rng.standard_normal((1, H * d), dtype=np.float32)
+        q16 = ko.normal_f16(rng, (Hq, d))
+        host.append(kn.astype(np.float32), vn.astype(np.float32), w, position, rope_mode=rope)
+        out = torch.full((Hq, d), float("nan"), device="cuda")
+        if step % 2:
+            state[1] = position
+            kv.launch_decode_step(st.view(), to_dev(kn), to_dev(vn), to_dev(q16), query_heads=Hq, scale=d ** -0.5, decode_state=state,
+                                  k_norm_weight=wd, rope_mode=kv.RopeMode(rope), output=out, workspace=ws)
+        else:
+            kv.launch_decode_step(st.view(), to_dev(kn), to_dev(vn), to_dev(q16), query_heads=Hq, scale=d ** -0.5, position=position,
+                                  k_norm_weight=wd, rope_mode=kv.RopeMode(rope), output=out, workspace=ws)
+        torch.cuda.synchronize()
+        if step in (0, 1, 27, 28, 29, 60, 69):     # 700 % 32 == 28: steps 27/28/29 straddle a tile boundary
+            ref, _ = host.decode_ref(q16.astype(np.float32), d ** -0.5, position + 1)
+            assert np.max(np.abs(out.cpu().numpy() - ref)) <= TOL, position
+    from gpu_util import assert_planes_equal
+    assert_planes_equal(st, host, "after 70 fused decode steps")
+    # the fallback (generic kernel) gives the same planes and outputs
+    st2 = upload(host)
+    kn, vn, q16 = ko.normal_f16(rng, (1, H * d)), ko.normal_f16(rng, (1, H * d)), ko.normal_f16(rng, (Hq, d))
+    host.append(kn.astype(np.float32), vn.astype(np.float32), w, L0 + 70, rope_mode=rope)
+    out = torch.empty(Hq, d, device="cuda")
+    kv.launch_decode_step(st2.view(), to_dev(kn), to_dev(vn), to_dev(q16), query_heads=Hq, scale=d ** -0.5, position=L0 + 70,
+                          k_norm_weight=wd, rope_mode=kv.RopeMode(rope), output=out, workspace=ws, num_splits=kv.FORCE_GENERIC)
+    torch.cuda.synchronize()
+    assert_planes_equal(st2, host, "fallback decode step")
+    ref, _ = host.decode_ref(q16.astype(np.float32), d ** -0.5, L0 + 71)
+    assert np.max(np.abs(out.cpu().numpy() - ref)) <= TOL
+
+
+def test_fused_decode_step_long_context_many_tiles_per_pair(cuda):
+    """The appended token's tile is the last of MANY tiles of its warp pair (the hand-shake between the pair's warps
+    must not stall the earlier tiles), with launch overlap on and under graph replay."""
+    rng = np.random.default_rng(92)
+    H, Hq, d, L0, cap = 8, 32, 128, 20000, 20480
+    host = ko.HostCache(cap, H, d, 32, 3)
+    host.append(ko.normal_f16(rng, (L0, H * d)).astype(np.float32), ko.normal_f16(rng, (L0, H * d)).astype(np.float32), None, 0, rope_mode=1)
+    st = upload(host)
+    ws = kv.decode_workspace(Hq, d)
+    state = kv.make_decode_state(L0)
+    kn = to_dev(ko.normal_f16(rng, (1, H * d))); vn = to_dev(ko.normal_f16(rng, (1, H * d))); q = to_dev(ko.normal_f16(rng, (Hq, d)))
+    out = torch.zeros(Hq, d, device="cuda")
+    kv.set_launch_overlap(1)
+    try:
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            kv.launch_decode_step(st.view(), kn, vn, q, query_heads=Hq, scale=d ** -0.5, decode_state=state, output=out, workspace=ws)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                kv.launch_decode_step(st.view(), kn, vn, q, query_heads=Hq, scale=d ** -0.5, decode_state=state, output=out, workspace=ws)
+                state[1] += 1
+            for _ in range(3):
+                graph.replay()
+        torch.cuda.synchronize()
+    finally:
+        kv.set_launch_overlap(0)
+    kf, vf = kn.float().cpu().numpy(), vn.float().cpu().numpy()
+    for pos in (L0, L0 + 1, L0 + 2):      # the eager call wrote L0, the replays L0, L0+1, L0+2
+        host.append(kf, vf, None, pos, rope_mode=1)
+    from gpu_util import assert_planes_equal
+    assert_planes_equal(st, host, "graph-replayed fused steps")
+    ref, _ = host.decode_ref(q.float().cpu().numpy(), d ** -0.5, L0 + 3)
+    assert np.max(np.abs(out.cpu().numpy() - ref)) <= TOL

@@ -331,6 +331,7 @@ def main() -> None:
     ap.add_argument("--context", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--two-launches", action="store_true", help="append and attention as two launches per layer (A/B of the fused step)")
+    ap.add_argument("--prefill-kernel", default="tcgen05", choices=["tcgen05", "mma"], help="prefill workload: which attention kernel")
     ap.add_argument("--no-overlap", action="store_true", help="launch every kernel fully serialised (A/B of launch overlap)")
     ap.add_argument("--layers", type=int, default=36, help="layers per step (36 = the benchmark; fewer only for ncu captures)")
     args = ap.parse_args()

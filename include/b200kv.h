@@ -283,10 +283,15 @@ B200KV_API int b200kv_merge_partials_packed(const float* packed, uint32_t num_pa
 
 /* ---- suffix / prefill attention -------------------------------------------- */
 
-/* Kept for call-site symmetry with the reference (which needs 32*T*heads*(2+d)
- * floats of split partials, .hip:7154-7157): this kernel keeps its running
- * state in registers, so the answer is 0 and `workspace` may be NULL. */
+/* Minimum workspace of b200kv_prefill_attn: 0 (`workspace` may be NULL; the reference needs 32*T*heads*(2+d)
+ * floats of split partials, .hip:7154-7157).  Without a workspace the mma.sync kernel runs, which keeps its
+ * running state in registers. */
 B200KV_API size_t b200kv_prefill_workspace_bytes(uint32_t token_count, uint32_t query_heads, uint32_t head_dim);
+/* Workspace that enables the tcgen05 kernel: room for the fp16 copy of the `rows` cache positions the chunk can see
+ * (rows = base_position + token_count; the whole capacity when a device-side prefill_state is used).  35.6 MB for
+ * 8704 rows x 4 kv heads x d=256.  The scratch is rewritten by every call; calls that overlap on the GPU need
+ * separate workspaces.  Cache rows below `rows` must hold finite values (freshly created caches are zero). */
+B200KV_API size_t b200kv_prefill_scratch_bytes(uint64_t rows, uint32_t kv_heads, uint32_t head_dim);
 
 /* Replaces launch_qwen35_splitk_suffix_attention_quant
  * (qwen3_gpu_primitives.hpp:670-692; kernels .hip:6788-7119 and 6637-6725).

@@ -86,18 +86,24 @@ inline void launch_qwen35_tiled_online_attention_quant_dynamic(
                        "launch_qwen35_tiled_online_attention_quant_dynamic");
 }
 
-// qwen3_gpu_primitives.hpp:670-692 (d_split_workspace and num_splits are accepted and ignored: the kernel keeps its
-// running state in registers)
+// qwen3_gpu_primitives.hpp:670-692.  d_split_workspace is sized by the reference's contract,
+// num_splits * token_count * query_heads * (2 + head_dim) floats (gfx906/kernels/qwen3_primitives.hip:7154-7157); when
+// that is enough for the fp16 scratch of the visible prefix the tcgen05 kernel uses it, otherwise (or when it is null)
+// the register-resident kernel runs.
 inline void launch_qwen35_splitk_suffix_attention_quant(
     const float* q, const __half* key_cache_f16, const __half* value_cache_f16, const int8_t* key_cache_q8, const __half* key_scales,
-    const int8_t* value_cache_q8, const __half* value_scales, const float* gate, float* gated_output, float* /*d_split_workspace*/,
+    const int8_t* value_cache_q8, const __half* value_scales, const float* gate, float* gated_output, float* d_split_workspace,
     std::uint32_t token_count, std::uint32_t base_position, std::uint32_t cache_capacity, std::uint32_t query_heads,
-    std::uint32_t kv_heads, std::uint32_t head_dim, float scale, bool is_k_q8, bool is_v_q8, std::uint32_t /*num_splits*/ = 64,
+    std::uint32_t kv_heads, std::uint32_t head_dim, float scale, bool is_k_q8, bool is_v_q8, std::uint32_t num_splits = 64,
     cudaStream_t stream = nullptr, const DevicePrefillState* prefill_state = nullptr) {
     const b200kv_view v = shim_detail::make_view(key_cache_f16, value_cache_f16, key_cache_q8, key_scales, value_cache_q8,
                                                  value_scales, cache_capacity, kv_heads, head_dim, kv_qblock(), is_k_q8, is_v_q8);
     shim_detail::check(b200kv_prefill_attn(&v, q, B200KV_F32, gate, gated_output, token_count, base_position, query_heads, scale,
-                                           prefill_state, nullptr, 0, stream),
+                                           prefill_state, d_split_workspace,
+                                           d_split_workspace ? static_cast<std::size_t>(num_splits ? (num_splits > 64 ? 64 : num_splits) : 64) * token_count *
+                                                                   query_heads * (2 + head_dim) * sizeof(float)
+                                                             : 0,
+                                           stream),
                        "launch_qwen35_splitk_suffix_attention_quant");
 }
 

@@ -1,0 +1,537 @@
+// Suffix / prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
+//
+// Same function as prefill_mma.cu (MIInfer's suffix kernels,
+// gfx906/kernels/qwen3_primitives.hip:6788-7119 and 6637-6725), built for sm_100a:
+//
+//  1. A streaming pre-pass dequantises the positions the chunk can see, [0, kv_end), once per launch into an
+//     fp16 scratch in the caller's workspace (K and V planes, [kv_head][row][d]); with int8 -> fp16 exact up to
+//     the one rounding of q * scale.  The scratch (35.6 MB at 8704 x 4 x 256) stays in the 126 MB L2.
+//  2. The attention kernel gives each CTA 128 query ROWS of one kv head (a row is a (token, head-of-group)
+//     pair, so the G heads of a group share every K/V tile) and walks the causal range in tiles of 64 positions:
+//       - one thread feeds a 2-stage ring of K and V tiles with TMA tensor copies (64x64 boxes, 128-byte
+//         swizzle: exactly the canonical shared-memory layout of the MMA operands);
+//       - one thread issues tcgen05.mma: S = Q.K^T (M128 x N64, K = d) into one of two S buffers in TMEM,
+//         and O += P.V (M128 x N = d, K = 64; V consumed MN-major, as stored) into the O accumulator in TMEM;
+//         completion is tracked by tcgen05.commit on mbarriers;
+//       - 128 softmax threads own one row each: tcgen05.ld the S row, scale/mask (causal length per row,
+//         .hip:6829), online softmax in base 2 with LAZY rescaling (O and the running sum are only rescaled
+//         when a row's maximum grows by more than 2^8; P <= 256 fits fp16), write P as fp16 into the
+//         swizzled A-operand tile, and at the end scale O by 1/sum, apply the sigmoid gate (.hip:6714-6723)
+//         and store.
+//     TMEM: S0 | S1 | O = 64 + 64 + d columns.  Shared memory: Q (64 KB at d=256) + 2 x (K + V) + P.
+// Every mbarrier wait is bounded; a wait that runs out poisons the output rows with NaN, and the CTA still frees
+// its TMEM and exits.
+#include "decode_common.cuh"
+#include "dequant.cuh"
+
+#include <cstring>
+#include <mutex>
+
+namespace b200kv {
+
+namespace {
+
+constexpr int kBM = 128;          // query rows per CTA
+constexpr int kBN = 64;           // positions per KV tile
+constexpr int kSoftmaxThreads = 128;
+constexpr int kThreads = kSoftmaxThreads + 64;   // + warp 4: TMA producer, warp 5: MMA issuer / TMEM owner
+constexpr uint32_t kSpin = 1u << 20;
+constexpr float kRescaleThreshold = 8.0f;        // log2 units
+
+struct Tc5Params {
+    CUtensorMap kmap, vmap;      // fp16 [kv_heads * rows][d], box 64 x 64, 128-byte swizzle
+    const void* q;               // [token][query_heads][D]
+    int q_is_f16;
+    const float* gate;
+    float* out;
+    uint32_t token_count, base_position;
+    const b200kv_prefill_state* prefill_state;
+    uint32_t query_heads, kv_heads;
+    uint64_t capacity;           // cache capacity (causal ranges past it give zero rows)
+    uint32_t scratch_rows;       // rows per kv head in the fp16 scratch
+    float scale_log2;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t spin = 0; spin < kSpin; ++spin) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading/stride byte offsets (all >> 4),
+// descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+// Instruction descriptor for kind::f16: fp32 accumulate, fp16 A and B, M x N, operand majors (0 = K-major, 1 = MN-major).
+__host__ __device__ constexpr uint32_t umma_idesc(uint32_t m, uint32_t n, uint32_t a_mn_major, uint32_t b_mn_major) {
+    return (1u << 4) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+        "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
+        "%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int D>
+struct Layout {
+    static constexpr int kSlabs = D / 64;                  // 128-byte (64 x fp16) slabs along d
+    static constexpr int kQBytes = kSlabs * kBM * 128;     // [slab][row][128 B]
+    static constexpr int kTileBytes = kSlabs * kBN * 128;  // one K or V tile
+    static constexpr int kOffK = kQBytes;
+    static constexpr int kOffV = kOffK + 2 * kTileBytes;
+    static constexpr int kOffP = kOffV + 2 * kTileBytes;   // [row][128 B] fp16 P tile
+    static constexpr int kOffBar = kOffP + kBM * 128;
+    static constexpr int kNumBars = 12;   // k_full[2] k_empty[2] v_full[2] v_empty[2] s_full[2] s_empty[2] -> 12, p_full, p_empty -> 14
+    static constexpr int kTotal = kOffBar + 16 * 8 + 16;
+    static constexpr int kAlloc = kTotal + 1024;
+    static constexpr uint32_t kTmemCols = 512;
+    static constexpr uint32_t kColS = 0, kColO = 128;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_constant__ Tc5Params p) {
+    using L = Layout<D>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar0 = sbase + L::kOffBar;
+    auto bar = [&](int i) { return bar0 + i * 8; };
+    enum { K_FULL = 0, K_EMPTY = 2, V_FULL = 4, V_EMPTY = 6, S_FULL = 8, S_EMPTY = 10, P_FULL = 12, P_EMPTY = 13 };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffBar + 16 * 8);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t kv_head = blockIdx.y;
+    const uint32_t G = p.query_heads / p.kv_heads;
+    uint32_t base = p.base_position, count = p.token_count;
+    if (p.prefill_state != nullptr) {
+        base = p.prefill_state->base_position;
+        count = min(count, p.prefill_state->token_count);
+    }
+    const uint32_t total_rows = p.token_count * G;
+    const uint32_t row0 = blockIdx.x * kBM;
+    if (row0 >= total_rows) return;
+
+    // longest causal range among this CTA's rows (rows are token-major; see prefill_mma.cu)
+    uint32_t kv_end = 0;
+    if (count > 0 && p.capacity > base) {
+        const uint32_t t_first = row0 / G, t_last = (min(row0 + kBM, total_rows) - 1) / G;
+        const uint64_t t_cap = p.capacity - base - 1;
+        uint64_t t_max = t_last;
+        if (t_max > count - 1) t_max = count - 1;
+        if (t_max > t_cap) t_max = t_cap;
+        if (t_max >= t_first) kv_end = base + static_cast<uint32_t>(t_max) + 1u;
+    }
+    if (kv_end > p.scratch_rows) kv_end = p.scratch_rows;   // never read past what the pre-pass wrote
+    const int ntiles = static_cast<int>((kv_end + kBN - 1) / kBN);
+
+    // ---- set-up: barriers, TMEM, Q tile -----------------------------------------------------------------
+    if (tid == 0) {
+        for (int i = 0; i < 14; ++i) mbar_init(bar(i), (i == S_EMPTY || i == S_EMPTY + 1 || i == P_FULL) ? kSoftmaxThreads : 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(L::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // Q: rows of this CTA as fp16 in the canonical K-major layout [slab][row][64], 16-byte chunks XORed with row & 7
+    {
+        constexpr int CPR = D / 8;
+        for (int idx = tid; idx < kBM * CPR; idx += kThreads) {
+            const int r = idx / CPR, c = idx % CPR;
+            const uint32_t gr = row0 + r;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (gr < total_rows) {
+                const uint32_t token = gr / G, head = kv_head * G + gr % G;
+                const size_t off = (static_cast<size_t>(token) * p.query_heads + head) * D + c * 8;
+                if (p.q_is_f16) {
+                    v = *reinterpret_cast<const uint4*>(static_cast<const __half*>(p.q) + off);
+                } else {
+                    const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(p.q) + off);
+                    const float4 b = *reinterpret_cast<const float4*>(static_cast<const float*>(p.q) + off + 4);
+                    v = make_uint4(pack_half2(a.x, a.y), pack_half2(a.z, a.w), pack_half2(b.x, b.y), pack_half2(b.z, b.w));
+                }
+            }
+            const int slab = c >> 3, cc = c & 7;
+            *reinterpret_cast<uint4*>(smem + slab * (kBM * 128) + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+        }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // Q was written by ordinary stores, the MMA reads it through the async proxy
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    bool failed = false;
+
+    if (warp == 4) {
+        // =============================== TMA producer ===============================
+        if (lane == 0) {
+            const int row_base = static_cast<int>(kv_head * p.scratch_rows);
+            for (int j = 0; j < ntiles && !failed; ++j) {
+                const int st = j & 1;
+                const uint32_t ph = static_cast<uint32_t>((j >> 1) & 1);
+                if (!mbar_wait(bar(K_EMPTY + st), ph ^ 1)) { failed = true; break; }
+                mbar_expect_tx(bar(K_FULL + st), L::kTileBytes);
+                for (int s = 0; s < L::kSlabs; ++s)
+                    tma_load_2d(sbase + L::kOffK + st * L::kTileBytes + s * (kBN * 128), &p.kmap, s * 64, row_base + j * kBN, bar(K_FULL + st));
+                if (!mbar_wait(bar(V_EMPTY + st), ph ^ 1)) { failed = true; break; }
+                mbar_expect_tx(bar(V_FULL + st), L::kTileBytes);
+                for (int s = 0; s < L::kSlabs; ++s)
+                    tma_load_2d(sbase + L::kOffV + st * L::kTileBytes + s * (kBN * 128), &p.vmap, s * 64, row_base + j * kBN, bar(V_FULL + st));
+            }
+        }
+    } else if (warp == 5) {
+        // =============================== MMA issuer ===============================
+        if (lane == 0 && ntiles > 0) {
+            constexpr uint32_t idesc_s = umma_idesc(kBM, kBN, 0, 0);
+            constexpr uint32_t idesc_o = umma_idesc(kBM, D, 0, 1);
+            auto issue_s = [&](int j) -> bool {
+                const int st = j & 1;
+                const uint32_t ph = static_cast<uint32_t>((j >> 1) & 1);
+                if (!mbar_wait(bar(K_FULL + st), ph)) return false;
+                if (!mbar_wait(bar(S_EMPTY + st), ph ^ 1)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t a = sbase + (kk >> 2) * (kBM * 128) + (kk & 3) * 32;
+                    const uint32_t b = sbase + L::kOffK + st * L::kTileBytes + (kk >> 2) * (kBN * 128) + (kk & 3) * 32;
+                    umma_f16(tmem_base + L::kColS + st * kBN, umma_desc(a, 16, 1024), umma_desc(b, 16, 1024), idesc_s, kk > 0);
+                }
+                umma_commit(bar(S_FULL + st));    // S tile ready for the softmax rows
+                umma_commit(bar(K_EMPTY + st));   // K stage may be refilled
+                return true;
+            };
+            if (!issue_s(0)) failed = true;
+            for (int j = 0; j < ntiles && !failed; ++j) {
+                if (j + 1 < ntiles && !issue_s(j + 1)) { failed = true; break; }
+                const int st = j & 1;
+                if (!mbar_wait(bar(V_FULL + st), static_cast<uint32_t>((j >> 1) & 1))) { failed = true; break; }
+                if (!mbar_wait(bar(P_FULL), static_cast<uint32_t>(j & 1))) { failed = true; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kBN / 16; ++kk) {
+                    const uint32_t a = sbase + L::kOffP + kk * 32;                                   // P: K-major, one 128-byte slab
+                    const uint32_t b = sbase + L::kOffV + st * L::kTileBytes + kk * (16 * 128);      // V: MN-major, 16 positions per step
+                    umma_f16(tmem_base + L::kColO, umma_desc(a, 16, 1024), umma_desc(b, kBN * 128, 1024), idesc_o, (j > 0 || kk > 0));
+                }
+                umma_commit(bar(P_EMPTY));        // P tile free, O stable
+                umma_commit(bar(V_EMPTY + st));
+            }
+        }
+    } else {
+        // =============================== softmax rows ===============================
+        const int r = tid;                                   // row of this thread == its TMEM lane
+        const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+        const uint32_t gr = row0 + r;
+        uint32_t len = 0;
+        if (gr < total_rows) {
+            const uint32_t token = gr / G;
+            const uint64_t l64 = static_cast<uint64_t>(base) + token + 1u;
+            len = (token < count && l64 <= p.capacity) ? static_cast<uint32_t>(l64) : 0u;
+        }
+        float m_ref = -INFINITY, l_sum = 0.0f;
+        for (int j = 0; j < ntiles; ++j) {
+            const int st = j & 1;
+            if (!mbar_wait(bar(S_FULL + st), static_cast<uint32_t>((j >> 1) & 1))) { failed = true; break; }
+            tc_fence_after();
+            float s[kBN];
+            {
+                float t[32];
+                tmem_ld32(tmem_base + lane_addr + L::kColS + st * kBN, t);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[i] = t[i];
+                tmem_ld32(tmem_base + lane_addr + L::kColS + st * kBN + 32, t);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[32 + i] = t[i];
+            }
+            tc_fence_before();
+            mbar_arrive(bar(S_EMPTY + st));   // this row's copy of S is in registers
+            const uint32_t pos0 = static_cast<uint32_t>(j) * kBN;
+            float mt = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < kBN; ++i) {
+                s[i] = (pos0 + i < len) ? s[i] * p.scale_log2 : -INFINITY;
+                mt = fmaxf(mt, s[i]);
+            }
+            // lazy rescale: keep the old reference unless the row maximum outgrew it by more than the threshold
+            float alpha = 1.0f;
+            if (mt > m_ref + kRescaleThreshold || (m_ref == -INFINITY && mt > -INFINITY)) {
+                alpha = (m_ref == -INFINITY) ? 0.0f : exp2f(m_ref - mt);
+                m_ref = mt;
+            }
+            const float mref_safe = (m_ref == -INFINITY) ? 0.0f : m_ref;
+            float sum = 0.0f;
+            uint32_t ph[kBN / 2];
+#pragma unroll
+            for (int i = 0; i < kBN; i += 2) {
+                const float p0 = exp2f(s[i] - mref_safe), p1 = exp2f(s[i + 1] - mref_safe);
+                const __half2 h = __floats2half2_rn(p0, p1);
+                // the sum uses the rounded values the MMA will multiply, so numerator and denominator stay consistent
+                sum += __low2float(h) + __high2float(h);
+                ph[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            l_sum = fmaf(l_sum, alpha, sum);
+            // P tile and O are free once the previous P.V has completed
+            if (!mbar_wait(bar(P_EMPTY), static_cast<uint32_t>((j & 1) ^ 1))) { failed = true; break; }
+            tc_fence_after();
+            if (__any_sync(0xffffffffu, alpha != 1.0f) && j > 0) {
+                // rare: rescale this warp's 32 rows of O in TMEM
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    float o[32];
+                    tmem_ld32(tmem_base + lane_addr + L::kColO + c0, o);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] *= alpha;
+                    tmem_st32(tmem_base + lane_addr + L::kColO + c0, o);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+            uint8_t* prow = smem + L::kOffP + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(ph[4 * c], ph[4 * c + 1], ph[4 * c + 2], ph[4 * c + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(bar(P_FULL));
+        }
+        // ---- epilogue: O / sum, gate, store ----
+        if (!failed && ntiles > 0 && !mbar_wait(bar(P_EMPTY), static_cast<uint32_t>((ntiles - 1) & 1))) failed = true;
+        tc_fence_after();
+        {
+            // tcgen05.ld is warp-collective: every lane takes part, rows past the launch only skip the store
+            const bool live = gr < total_rows;
+            const uint32_t token = live ? gr / G : 0, head = kv_head * G + (live ? gr % G : 0);
+            const size_t off = (static_cast<size_t>(token) * p.query_heads + head) * D;
+            const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
+            const bool have_o = ntiles > 0 && !__any_sync(0xffffffffu, failed);
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                float o[32];
+                if (have_o) {
+                    tmem_ld32(tmem_base + lane_addr + L::kColO + c0, o);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = failed ? __int_as_float(0x7fc00000) : 0.0f;
+                }
+                if (!live) continue;
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    float4 v = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
+                    if (failed) v = make_float4(o[i], o[i], o[i], o[i]);
+                    else if (len == 0) v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    if (p.gate != nullptr) {
+                        const float4 g = *reinterpret_cast<const float4*>(p.gate + off + c0 + i);
+                        v.x *= 1.0f / (1.0f + __expf(-g.x)); v.y *= 1.0f / (1.0f + __expf(-g.y));
+                        v.z *= 1.0f / (1.0f + __expf(-g.z)); v.w *= 1.0f / (1.0f + __expf(-g.w));
+                    }
+                    *reinterpret_cast<float4*>(p.out + off + c0 + i) = v;
+                }
+            }
+        }
+    }
+
+    // ---- teardown: every role arrives here, with or without a timeout; TMEM is always released ----
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::kTmemCols) : "memory");
+    }
+}
+
+// ---- pre-pass: dequantise [0, rows) of every kv head to fp16 ---------------------------------------------------------
+struct DequantParams {
+    b200kv_view view;
+    __half* k_out;       // [kv_heads][scratch_rows][D]
+    __half* v_out;
+    uint32_t rows;       // positions to convert
+    uint32_t scratch_rows;
+};
+
+template <int D>
+__global__ void __launch_bounds__(256) dequant_prefix_kernel(const __grid_constant__ DequantParams p) {
+    constexpr int CPR = D / 16;
+    const uint32_t head = blockIdx.y, side = blockIdx.z;   // side 0 = K, 1 = V
+    const uint32_t mode = p.view.quant_mode;
+    const bool q8 = side == 0 ? (mode == B200KV_Q8_F16 || mode == B200KV_Q8_Q8) : (mode == B200KV_F16_Q8 || mode == B200KV_Q8_Q8);
+    const int8_t* q = side == 0 ? p.view.key_q8 : p.view.value_q8;
+    const __half* sc = static_cast<const __half*>(side == 0 ? p.view.key_scales : p.view.value_scales);
+    const __half* f16 = static_cast<const __half*>(side == 0 ? p.view.key_f16 : p.view.value_f16);
+    __half* out = (side == 0 ? p.k_out : p.v_out) + static_cast<size_t>(head) * p.scratch_rows * D;
+    const uint32_t nblk = D / p.view.qblock;
+    const uint64_t head_row0 = static_cast<uint64_t>(head) * p.view.capacity;
+    const size_t total = static_cast<size_t>(p.scratch_rows) * CPR;   // rows past `rows` are zero-filled: the last tile reads them
+    for (size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const uint32_t pos = static_cast<uint32_t>(idx / CPR), c16 = static_cast<uint32_t>(idx % CPR);
+        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+        if (pos >= p.rows) {
+            // padding row of the last tile: P is 0 there, but 0 * (stale NaN) would still poison O
+        } else if (q8) {
+            const uint64_t grow = head_row0 + pos;
+            const uint4 raw = *reinterpret_cast<const uint4*>(q + grow * D + c16 * 16);
+            dequant16(raw, sc[grow * nblk + (nblk == 1 ? 0 : c16 / 2)], &lo, &hi);
+        } else {
+            const uint4* src = reinterpret_cast<const uint4*>(f16 + (head_row0 + pos) * D + c16 * 16);
+            lo = src[0]; hi = src[1];
+        }
+        uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(pos) * D + c16 * 16);
+        dst[0] = lo; dst[1] = hi;
+    }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn tc5_encoder() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(sym);
+        else
+            (void)cudaGetLastError();
+    });
+    return fn;
+}
+
+bool encode_f16_plane(CUtensorMap* map, void* base, uint32_t d, uint64_t rows) {
+    EncodeFn fn = tc5_encoder();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {d, rows};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(d) * 2};
+    const cuuint32_t box[2] = {64, kBN};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D>
+int launch_tc5(const b200kv_view& view, Tc5Params& p, __half* k_scratch, __half* v_scratch, uint32_t rows, cudaStream_t stream) {
+    using L = Layout<D>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(prefill_tc5_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc); });
+    if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err, "cudaFuncSetAttribute(prefill_tc5)"); return B200KV_ERR_CUDA; }
+    if (rows > 0) {
+        DequantParams dp{};
+        dp.view = view;
+        dp.k_out = k_scratch;
+        dp.v_out = v_scratch;
+        dp.rows = rows;
+        dp.scratch_rows = p.scratch_rows;
+        const size_t units = static_cast<size_t>(p.scratch_rows) * (D / 16);
+        unsigned blocks = static_cast<unsigned>((units + 255) / 256);
+        if (blocks > 148u * 4u) blocks = 148u * 4u;
+        dequant_prefix_kernel<D><<<dim3(blocks, view.kv_heads, 2), 256, 0, stream>>>(dp);
+        B200KV_CUDA_TRY(cudaGetLastError());
+    }
+    const uint32_t G = p.query_heads / p.kv_heads;
+    const uint32_t row_tiles = (p.token_count * G + kBM - 1) / kBM;
+    prefill_tc5_kernel<D><<<dim3(row_tiles, p.kv_heads), kThreads, L::kAlloc, stream>>>(p);
+    B200KV_CUDA_TRY(cudaGetLastError());
+    return B200KV_OK;
+}
+
+}  // namespace
+
+size_t prefill_tc5_workspace_bytes(uint32_t rows, uint32_t kv_heads, uint32_t head_dim) {
+    const size_t r = (static_cast<size_t>(rows) + kBN - 1) / kBN * kBN;
+    return 2 * r * kv_heads * head_dim * sizeof(__half) + 1024;   // K and V planes, 1 KB to align the base
+}
+
+// Returns B200KV_ERR_UNSUPPORTED when this path cannot run (no workspace, no TMA encoder); the caller then uses the
+// register-resident mma.sync kernel.
+int launch_prefill_tc5(const b200kv_view& view, const void* q, int q_is_f16, const float* gate, float* out,
+                       uint32_t token_count, uint32_t base_position, const b200kv_prefill_state* prefill_state,
+                       uint32_t query_heads, float scale, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    // rows the chunk can see: known on the host unless a device-side state overrides it (then: the whole cache)
+    uint64_t rows = prefill_state ? view.capacity : static_cast<uint64_t>(base_position) + token_count;
+    if (rows > view.capacity) rows = view.capacity;
+    const uint32_t scratch_rows = static_cast<uint32_t>((rows + kBN - 1) / kBN * kBN);
+    if (workspace == nullptr || workspace_bytes < prefill_tc5_workspace_bytes(static_cast<uint32_t>(rows), view.kv_heads, view.head_dim))
+        return B200KV_ERR_UNSUPPORTED;
+    if (static_cast<uint64_t>(view.kv_heads) * scratch_rows > 0x7fffffffull) return B200KV_ERR_UNSUPPORTED;
+    uint8_t* ws = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~static_cast<uintptr_t>(1023));
+    __half* k_scratch = reinterpret_cast<__half*>(ws);
+    __half* v_scratch = k_scratch + static_cast<size_t>(view.kv_heads) * scratch_rows * view.head_dim;
+    Tc5Params p{};
+    if (!encode_f16_plane(&p.kmap, k_scratch, view.head_dim, static_cast<uint64_t>(view.kv_heads) * scratch_rows) ||
+        !encode_f16_plane(&p.vmap, v_scratch, view.head_dim, static_cast<uint64_t>(view.kv_heads) * scratch_rows))
+        return B200KV_ERR_UNSUPPORTED;
+    p.q = q;
+    p.q_is_f16 = q_is_f16;
+    p.gate = gate;
+    p.out = out;
+    p.token_count = token_count;
+    p.base_position = base_position;
+    p.prefill_state = prefill_state;
+    p.query_heads = query_heads;
+    p.kv_heads = view.kv_heads;
+    p.capacity = view.capacity;
+    p.scratch_rows = scratch_rows;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    return view.head_dim == 128 ? launch_tc5<128>(view, p, k_scratch, v_scratch, static_cast<uint32_t>(rows), stream)
+                                : launch_tc5<256>(view, p, k_scratch, v_scratch, static_cast<uint32_t>(rows), stream);
+}
+
+}  // namespace b200kv

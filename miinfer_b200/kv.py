@@ -169,8 +169,9 @@ def view_table(sessions: int, device=None) -> torch.Tensor:
     return torch.zeros(int(lib.b200kv_view_table_bytes(sessions)), dtype=torch.uint8, device=device or "cuda")
 
 
-def prefill_workspace(token_count: int, query_heads: int, head_dim: int, device=None) -> torch.Tensor:
-    n = int(lib.b200kv_prefill_workspace_bytes(token_count, query_heads, head_dim))
+def prefill_workspace(rows: int, kv_heads: int, head_dim: int, device=None) -> torch.Tensor:
+    """Scratch that lets launch_suffix_attention_quant run the tcgen05 kernel: `rows` = base_position + token_count."""
+    n = int(lib.b200kv_prefill_scratch_bytes(rows, kv_heads, head_dim))
     return torch.zeros(n, dtype=torch.uint8, device=device or "cuda")
 
 

@@ -73,11 +73,13 @@ def run_prefill(args, torch, dist, rank, world, local_rank):
     w = torch.ones(D, device="cuda")
     out = torch.zeros(LAYERS, T, hq, D, device="cuda")
     views = [c.view() for c in caches]
+    # the fp16 scratch of the visible prefix selects the tcgen05 kernel; --prefill-kernel mma runs the mma.sync one
+    ws = None if args.prefill_kernel == "mma" else kv.prefill_workspace(P + T, hkv, D)
 
     def step():
         for l in range(LAYERS):
             kv.launch_kv_store_quant(views[l], k_new[l], v_new[l], w, T, P, rope_mode=kv.RopeMode.SECTIONED64, theta=1.0e6)
-            kv.launch_suffix_attention_quant(views[l], q[l], gate[l], out[l], None, T, P, query_heads=hq, scale=D ** -0.5)
+            kv.launch_suffix_attention_quant(views[l], q[l], gate[l], out[l], ws, T, P, query_heads=hq, scale=D ** -0.5)
 
     stream = torch.cuda.Stream()
     ms = _time(torch, dist, stream, step, args.warmup, args.steps)
@@ -88,10 +90,10 @@ def run_prefill(args, torch, dist, rank, world, local_rank):
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int8 KV dequantised to fp16, fp32 accumulate", "data": "synthetic",
             "config": {"workload": f"prefill: {T}-token chunk over {P}-token q8_0 prefix, {HQ} Q / {HKV} KV heads, d={D}, {LAYERS} layers "
-                                   f"(BASELINE configs[2]); kv heads split over {world} GPU(s)", "l2": "L2 flushed implicitly: 16 layer caches of 19 MB rotate"},
+                                   f"(BASELINE configs[2]); kv heads split over {world} GPU(s); kernel {args.prefill_kernel}", "l2": "L2 flushed implicitly: 16 layer caches of 19 MB rotate"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak,
                          "traffic": None, "peak_kind": f"{kind} (bf16_tflops_sustained)"},
-            "gpu_launches": args.steps * LAYERS * 2}
+            "gpu_launches": args.steps * LAYERS * (2 if ws is None else 3)}
 
 
 def run_seqshard(args, torch, dist, rank, world, local_rank):
@@ -148,7 +150,7 @@ def run_seqshard(args, torch, dist, rank, world, local_rank):
                        "l2": "inputs larger than L2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": bw_peak * world, "unit": "GB/s", "frac": achieved / (bw_peak * world),
                          "traffic": None, "peak_kind": f"{kind} x {world} GPUs"},
-            "merge_bytes_per_layer_per_rank": HQ * (D + 2) * 4, "gpu_launches": args.steps * LAYERS * 2}
+            "merge_bytes_per_layer_per_rank": HQ * (D + 2) * 4, "gpu_launches": args.steps * LAYERS * (2 if ws is None else 3)}
 
 
 def run_batched(args, torch, dist, rank, world, local_rank):

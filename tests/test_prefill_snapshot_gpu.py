@@ -31,8 +31,9 @@ SUFFIX = [
 ]
 
 
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
 @pytest.mark.parametrize("P,T,d,H,Hq,qb,mode", SUFFIX)
-def test_suffix_attention_matches_reference(cuda, P, T, d, H, Hq, qb, mode):
+def test_suffix_attention_matches_reference(cuda, P, T, d, H, Hq, qb, mode, kernel):
     rng = np.random.default_rng(P + T + mode)
     host = filled(rng, P + T, H, d, qb, mode, cap=P + T + 128, std=0.5)   # N(0, 0.5) as the reference's test
     st = upload(host)
@@ -40,7 +41,8 @@ def test_suffix_attention_matches_reference(cuda, P, T, d, H, Hq, qb, mode):
     gate = (rng.standard_normal((T, Hq, d)) * 0.5).astype(np.float32)
     ref = host.suffix_ref(q, gate, P, d ** -0.5)
     out = torch.full((T, Hq, d), float("nan"), device="cuda")
-    ws = kv.prefill_workspace(T, Hq, d)
+    # with the fp16 scratch the tcgen05 kernel runs; without a workspace the register-resident mma.sync kernel
+    ws = kv.prefill_workspace(host.capacity, H, d) if kernel == "tcgen05" else None
     kv.launch_suffix_attention_quant(st.view(), to_dev(q), to_dev(gate), out, ws, T, P, query_heads=Hq, scale=d ** -0.5)
     torch.cuda.synchronize()
     got = out.cpu().numpy()
@@ -65,7 +67,7 @@ def test_suffix_is_causal_inside_the_chunk(cuda):
     host = filled(rng, P + T, H, d, 32, 3)
     st = upload(host)
     q = to_dev(ko.normal_f16(rng, (T, Hq, d)))
-    ws = kv.prefill_workspace(T, Hq, d)
+    ws = kv.prefill_workspace(P + T, H, d)
     a = torch.empty((T, Hq, d), device="cuda")
     kv.launch_suffix_attention_quant(st.view(), q, None, a, ws, T, P, query_heads=Hq, scale=d ** -0.5)
     st.value_cache_q8[:, P + 6:] = 77
@@ -146,3 +148,26 @@ def test_native_cache_object_lifecycle(cuda):
     torch.cuda.synchronize()
     assert blob.count_nonzero().item() == 0
     assert lib.b200kv_cache_destroy(handle) == 0
+
+
+def test_suffix_tcgen05_many_tiles_rescale_and_ragged_rows(cuda):
+    """Long prefix (many KV tiles, both ring stages reused many times), a query whose score maximum keeps growing
+    (exercises the lazy O rescale in TMEM), and a row count that is not a multiple of 128."""
+    rng = np.random.default_rng(77)
+    P, T, d, H, Hq = 3000, 70, 256, 4, 24
+    kf = ko.normal_f16(rng, (P + T, H * d), 0.5).astype(np.float32)
+    vf = ko.normal_f16(rng, (P + T, H * d), 1.0).astype(np.float32)
+    q = (rng.standard_normal((T, Hq, d)) * 0.5).astype(np.float32)
+    # keys aligned with token 3's query of head 0, growing along the sequence: the running maximum jumps by > 2^8 repeatedly
+    for i, pos in enumerate(range(100, P, 400)):
+        kf[pos, :d] = q[3, 0] * (0.8 + 0.45 * i)
+    host = ko.HostCache(P + T, H, d, 32, 3)
+    host.append(kf, vf, None, 0, rope_mode=0)
+    st = upload(host)
+    ref = host.suffix_ref(q, None, P, d ** -0.5)
+    out = torch.full((T, Hq, d), float("nan"), device="cuda")
+    kv.launch_suffix_attention_quant(st.view(), to_dev(q), None, out, kv.prefill_workspace(P + T, H, d), T, P, query_heads=Hq, scale=d ** -0.5)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.max(np.abs(got - ref)) <= TOL * max(1.0, float(np.abs(ref).max()))

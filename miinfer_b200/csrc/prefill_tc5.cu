@@ -305,27 +305,32 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
             tc_fence_before();
             mbar_arrive(bar(S_EMPTY + st));   // this row's copy of S is in registers
             const uint32_t pos0 = static_cast<uint32_t>(j) * kBN;
+            // Raw scores stay unscaled; the softmax scale is folded into the exponent: p = 2^(s*c - m*c).
+            // Only the tiles that straddle this row's causal length need the mask.
+            if (pos0 + kBN > len) {
+#pragma unroll
+                for (int i = 0; i < kBN; ++i) s[i] = (pos0 + i < len) ? s[i] : -INFINITY;
+            }
             float mt = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < kBN; ++i) {
-                s[i] = (pos0 + i < len) ? s[i] * p.scale_log2 : -INFINITY;
-                mt = fmaxf(mt, s[i]);
-            }
+            for (int i = 0; i < kBN; ++i) mt = fmaxf(mt, s[i]);
+            mt *= p.scale_log2;   // scale > 0: the maximum commutes with it
             // lazy rescale: keep the old reference unless the row maximum outgrew it by more than the threshold
             float alpha = 1.0f;
             if (mt > m_ref + kRescaleThreshold || (m_ref == -INFINITY && mt > -INFINITY)) {
                 alpha = (m_ref == -INFINITY) ? 0.0f : exp2f(m_ref - mt);
                 m_ref = mt;
             }
-            const float mref_safe = (m_ref == -INFINITY) ? 0.0f : m_ref;
+            const float neg_ref = (m_ref == -INFINITY) ? 0.0f : -m_ref;
             float sum = 0.0f;
             uint32_t ph[kBN / 2];
 #pragma unroll
             for (int i = 0; i < kBN; i += 2) {
-                const float p0 = exp2f(s[i] - mref_safe), p1 = exp2f(s[i + 1] - mref_safe);
+                const float p0 = exp2f(fmaf(s[i], p.scale_log2, neg_ref)), p1 = exp2f(fmaf(s[i + 1], p.scale_log2, neg_ref));
                 const __half2 h = __floats2half2_rn(p0, p1);
                 // the sum uses the rounded values the MMA will multiply, so numerator and denominator stay consistent
-                sum += __low2float(h) + __high2float(h);
+                const float2 hf = __half22float2(h);
+                sum += hf.x + hf.y;
                 ph[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
             }
             l_sum = fmaf(l_sum, alpha, sum);

@@ -329,6 +329,68 @@ B200KV_API int b200kv_snapshot_clone(const b200kv_view* dst, const b200kv_view* 
  * compute_token_sequence_hash, include/miinfer/prefill_v2/reusable_context.hpp:38-45. */
 B200KV_API uint64_t b200kv_token_sequence_hash(const uint32_t* tokens, size_t count);
 
+/* ReusableContext::MatchResult, include/miinfer/prefill_v2/reusable_context.hpp:97-105 (same seven outcomes, same order). */
+typedef enum b200kv_match {
+    B200KV_MATCH_EXACT = 0,
+    B200KV_MATCH_PREFIX_MISMATCH = 1,
+    B200KV_MATCH_MODEL_MISMATCH = 2,
+    B200KV_MATCH_QUANTIZATION_MISMATCH = 3,
+    B200KV_MATCH_EMPTY_CACHE = 4,
+    B200KV_MATCH_PROMPT_SHORTER = 5,
+    B200KV_MATCH_VERSION_MISMATCH = 6
+} b200kv_match;
+
+/* ReusableContext::check_match, src/prefill_v2/reusable_context.cpp:155-185: can the cached prefix (its model id,
+ * quantization id, state layout version -- 20260925 is the current one -- and tokens) be reused for `prompt`?
+ * Returns a b200kv_match.  Host only. */
+B200KV_API int b200kv_prefix_match(const char* cached_model_id, const char* cached_quantization, uint32_t cached_layout_version,
+                        const uint32_t* cached_tokens, uint32_t cached_length, const char* model_id, const char* quantization,
+                        const uint32_t* prompt, uint32_t prompt_length);
+
+/* PersistentSessionHeader, include/miinfer/prefill_v2/persistent_session.hpp:19-33: same packed 157 bytes. */
+#pragma pack(push, 1)
+typedef struct b200kv_session_header {
+    char magic[4];              /* "MISS" */
+    uint32_t version;           /* 20260928 */
+    char model_id[64];
+    char quantization[32];
+    uint32_t prefix_length;
+    uint64_t token_hash;
+    uint32_t gdn_layers;        /* 0 here: recurrent layers are outside this path */
+    uint64_t gdn_state_bytes;   /* 0 */
+    uint32_t gqa_layers;
+    uint8_t kv_quant_mode;
+    uint64_t kv_bytes;
+    uint64_t tokens_bytes;
+    uint64_t created_timestamp;
+} b200kv_session_header;
+#pragma pack(pop)
+
+/* PersistentSession::format_session_filename, persistent_session.cpp:27-32: "sess_<hash:016x>_p<length>.miinfer". */
+B200KV_API int b200kv_session_filename(uint64_t token_hash, uint32_t prefix_length, char* out, size_t out_bytes);
+/* save_to_file, persistent_session.cpp:34-142: snapshot the first `prefix_length` positions of every layer and write
+ * header | tokens | KV | trailer atomically (tmp file + rename).  Synchronises `stream`. */
+B200KV_API int b200kv_session_save(const char* path, const char* model_id, const char* quantization, const uint32_t* tokens,
+                        uint32_t prefix_length, const b200kv_view* layer_views, uint32_t layers, void* stream);
+/* inspect_file, persistent_session.cpp:144-166: header (and tokens, if tokens_out != NULL) without touching a GPU. */
+B200KV_API int b200kv_session_inspect(const char* path, b200kv_session_header* header, uint32_t* tokens_out, uint32_t tokens_capacity);
+/* load_from_file, persistent_session.cpp:168-267: validates magic, version, model, quantization, layer count, token
+ * hash -- and, beyond the reference, the KV quant mode, geometry and a payload checksum -- then restores every layer.
+ * B200KV_ERR_FORMAT = damaged file, B200KV_ERR_MISMATCH = a valid file for something else. */
+B200KV_API int b200kv_session_load(const char* path, const char* model_id, const char* quantization, const b200kv_view* layer_views,
+                        uint32_t layers, uint32_t* tokens_out, uint32_t tokens_capacity, uint32_t* prefix_length_out, void* stream);
+/* find_matching_session, persistent_session.cpp:269-320: the file in `session_dir` with the longest prefix of `prompt`. */
+B200KV_API int b200kv_session_find(const char* session_dir, const char* model_id, const char* quantization, const uint32_t* prompt,
+                        uint32_t prompt_length, char* path_out, size_t path_bytes, uint32_t* prefix_length_out);
+/* The file format without a GPU: write/read with the KV payload in host memory (what save/load do around the
+ * device copies).  layer_bytes = b200kv_snapshot_bytes of one layer. */
+B200KV_API int b200kv_session_write(const char* path, const char* model_id, const char* quantization, const uint32_t* tokens,
+                         uint32_t prefix_length, const void* kv_payload, uint64_t layer_bytes, uint32_t layers,
+                         uint32_t kv_heads, uint32_t head_dim, uint32_t qblock, uint32_t quant_mode);
+B200KV_API int b200kv_session_read(const char* path, const char* model_id, const char* quantization, uint32_t layers, uint32_t kv_heads,
+                        uint32_t head_dim, uint32_t qblock, uint32_t quant_mode, uint32_t* tokens_out, uint32_t tokens_capacity,
+                        uint32_t* prefix_length_out, void* kv_payload_out, uint64_t payload_capacity);
+
 #ifdef __cplusplus
 }
 #endif

@@ -61,6 +61,14 @@ SIGNATURES = {
     "b200kv_snapshot_restore": (i32, [VP, u64, vp, vp]),
     "b200kv_snapshot_clone": (i32, [VP, VP, u64, vp]),
     "b200kv_token_sequence_hash": (u64, [C.POINTER(u32), sz]),
+    "b200kv_prefix_match": (i32, [C.c_char_p, C.c_char_p, u32, vp, u32, C.c_char_p, C.c_char_p, vp, u32]),
+    "b200kv_session_filename": (i32, [u64, u32, C.c_char_p, sz]),
+    "b200kv_session_save": (i32, [C.c_char_p, C.c_char_p, C.c_char_p, vp, u32, VP, u32, vp]),
+    "b200kv_session_inspect": (i32, [C.c_char_p, vp, vp, u32]),
+    "b200kv_session_load": (i32, [C.c_char_p, C.c_char_p, C.c_char_p, VP, u32, vp, u32, C.POINTER(u32), vp]),
+    "b200kv_session_find": (i32, [C.c_char_p, C.c_char_p, C.c_char_p, vp, u32, C.c_char_p, sz, C.POINTER(u32)]),
+    "b200kv_session_write": (i32, [C.c_char_p, C.c_char_p, C.c_char_p, vp, u32, vp, u64, u32, u32, u32, u32, u32]),
+    "b200kv_session_read": (i32, [C.c_char_p, C.c_char_p, C.c_char_p, u32, u32, u32, u32, u32, vp, u32, C.POINTER(u32), vp, u64]),
 }
 
 

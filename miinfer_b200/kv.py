@@ -22,7 +22,7 @@ __all__ = [
     "launch_kv_store_quant", "launch_decode_attention_quant", "launch_decode_attention_batched", "launch_decode_step",
     "launch_decode_partials", "launch_merge_partials", "launch_merge_partials_packed", "packed_partial", "partial_views", "launch_suffix_attention_quant",
     "decode_workspace", "prefill_workspace", "view_table", "make_decode_state", "make_prefill_state",
-    "token_sequence_hash", "decode_kernel_kind", "set_launch_overlap", "B200KvError", "FORCE_GENERIC",
+    "token_sequence_hash", "save_session", "load_session", "find_matching_session", "decode_kernel_kind", "set_launch_overlap", "B200KvError", "FORCE_GENERIC",
 ]
 
 FORCE_GENERIC = 0x80000000
@@ -292,6 +292,41 @@ def set_launch_overlap(tail_positions: int) -> None:
 def decode_kernel_kind(view: View, query_heads: int) -> int:
     """1 if decode attention on this view runs the streaming int8 kernel, 0 for the generic one."""
     return int(lib.b200kv_decode_kernel_kind(C.byref(view), query_heads))
+
+
+def _views(storages):
+    return (View * len(storages))(*[st.view() for st in storages])
+
+
+def save_session(path: str, model_id: str, quantization: str, prefix_tokens, storages,
+                 stream: Optional[torch.cuda.Stream] = None) -> None:
+    """PersistentSession::save_to_file (src/prefill_v2/persistent_session.cpp:34-142) for the attention layers."""
+    toks = (C.c_uint32 * len(prefix_tokens))(*prefix_tokens)
+    check(lib.b200kv_session_save(path.encode(), model_id.encode(), quantization.encode(), toks, len(prefix_tokens), _views(storages),
+                                  len(storages), _stream(stream)), "b200kv_session_save")
+
+
+def load_session(path: str, model_id: str, quantization: str, storages, stream: Optional[torch.cuda.Stream] = None):
+    """PersistentSession::load_from_file (:168-267).  Returns the prefix tokens, or None when the file does not match
+    or is damaged (the reference returns false); other errors raise."""
+    cap = 1 << 20
+    toks = (C.c_uint32 * cap)()
+    n = C.c_uint32()
+    rc = lib.b200kv_session_load(path.encode(), model_id.encode(), quantization.encode(), _views(storages), len(storages), toks, cap,
+                                 C.byref(n), _stream(stream))
+    if rc in (-7, -8, -9):
+        return None
+    check(rc, "b200kv_session_load")
+    return list(toks[:n.value])
+
+
+def find_matching_session(session_dir: str, model_id: str, quantization: str, prompt):
+    """PersistentSession::find_matching_session (:269-320): (path, prefix_length) of the longest stored prefix, or None."""
+    p = (C.c_uint32 * len(prompt))(*prompt)
+    out = C.create_string_buffer(4096)
+    n = C.c_uint32()
+    rc = lib.b200kv_session_find(session_dir.encode(), model_id.encode(), quantization.encode(), p, len(prompt), out, 4096, C.byref(n))
+    return (out.value.decode(), n.value) if rc == 0 else None
 
 
 def token_sequence_hash(tokens) -> int:

@@ -171,3 +171,34 @@ def test_suffix_tcgen05_many_tiles_rescale_and_ragged_rows(cuda):
     got = out.cpu().numpy()
     assert np.isfinite(got).all()
     assert np.max(np.abs(got - ref)) <= TOL * max(1.0, float(np.abs(ref).max()))
+
+
+def test_session_file_save_find_load_gives_identical_decode(cuda, tmp_path):
+    """Cold vs restored-from-disk must decode identically (the reference's persistent-session gate,
+    bench/v2_0028_persistent_session_bench.cpp:235-257), and a file for another quant mode must be refused."""
+    rng = np.random.default_rng(29)
+    H, Hq, d, P, layers = 8, 32, 128, 600, 3
+    hosts = [filled(rng, P, H, d, 32, 3, cap=640) for _ in range(layers)]
+    sts = [upload(h) for h in hosts]
+    tokens = [int(t) for t in rng.integers(0, 150000, P)]
+    name = f"sess_{kv.token_sequence_hash(tokens):016x}_p{P}.miinfer"
+    kv.save_session(str(tmp_path / name), "qwen3-8b", "q4_0", tokens, sts)
+    prompt = tokens + [11, 12, 13]
+    found = kv.find_matching_session(str(tmp_path), "qwen3-8b", "q4_0", prompt)
+    assert found is not None and found[1] == P and found[0].endswith(name)
+    fresh = [device_storage_like(ko.HostCache(1024, H, d, 32, 3)) for _ in range(layers)]
+    assert kv.load_session(found[0], "qwen3-8b", "q4_0", fresh) == tokens
+    q = to_dev(ko.normal_f16(rng, (Hq, d)))
+    ws = kv.decode_workspace(Hq, d)
+    for a, b in zip(sts, fresh):
+        oa, ob = torch.empty(Hq, d, device="cuda"), torch.empty(Hq, d, device="cuda")
+        kv.launch_decode_attention_quant(a.view(), q, query_heads=Hq, scale=d ** -0.5, cache_length=P, output=oa, workspace=ws)
+        kv.launch_decode_attention_quant(b.view(), q, query_heads=Hq, scale=d ** -0.5, cache_length=P, output=ob, workspace=ws)
+        torch.cuda.synchronize()
+        assert torch.equal(oa, ob)
+    other_mode = [kv.AttentionLayerKvCacheStorage(1024, kv.KvCacheQuantMode.kQ8Fp16, kv_heads=H, head_dim=d, qblock=32) for _ in range(layers)]
+    assert kv.load_session(found[0], "qwen3-8b", "q4_0", other_mode) is None
+    assert kv.load_session(found[0], "another-model", "q4_0", fresh) is None
+    too_small = [kv.AttentionLayerKvCacheStorage(512, kv.KvCacheQuantMode.kQ8Q8, kv_heads=H, head_dim=d, qblock=32) for _ in range(layers)]
+    with pytest.raises(kv.B200KvError):
+        kv.load_session(found[0], "qwen3-8b", "q4_0", too_small)

@@ -398,10 +398,10 @@ int b200kv_decode_attn_batched(const b200kv_view* views, void* view_table, const
         for (uint32_t i = 0; i < sessions; ++i) {
             std::memset(&staged[i], 0, sizeof(SessionEntry));
             staged[i].view = views[i];
-            if (!q8_fast_path_ok(views[i], query_heads) || encode_k_map(views[i], &staged[i].kmap) != B200KV_OK) fast_ok = false;
+            if (!q8_fast_path_ok(views[i], query_heads) || encode_kv_maps(views[i], &staged[i].kmap, &staged[i].vmap) != B200KV_OK) fast_ok = false;
         }
         if (!fast_ok)
-            for (uint32_t i = 0; i < sessions; ++i) std::memset(&staged[i].kmap, 0, sizeof(CUtensorMap));
+            for (uint32_t i = 0; i < sessions; ++i) std::memset(&staged[i].kmap, 0, 2 * sizeof(CUtensorMap));
         geometry_fast = fast_ok;
         B200KV_CUDA_TRY(cudaMemcpyAsync(view_table, staged.data(), sizeof(SessionEntry) * sessions, cudaMemcpyHostToDevice, s));
         B200KV_CUDA_TRY(cudaStreamSynchronize(s));

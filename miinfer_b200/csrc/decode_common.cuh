@@ -8,13 +8,14 @@
 namespace b200kv {
 
 // One session of a batched launch as it sits in the device-side view table: the
-// TMA descriptor of its int8 K plane followed by its view.
+// TMA descriptors of its int8 K and V planes followed by its view.
 struct alignas(128) SessionEntry {
     CUtensorMap kmap;
+    CUtensorMap vmap;
     b200kv_view view;
     uint8_t pad[128 - sizeof(b200kv_view)];
 };
-static_assert(sizeof(SessionEntry) == 256, "table entry layout");
+static_assert(sizeof(SessionEntry) == 384, "table entry layout");
 
 // Upper bound on split slots per launch: slots = sessions * splits_per_session.
 constexpr uint32_t kMaxSplitsPerSession = 128;
@@ -66,8 +67,8 @@ struct DecodeParams {
     // Fused merge (streaming kernel only): when `counters` is non-null the last CTA of each
     // (session, kv head) combines all splits and writes `fuse`'s outputs; the counters must be
     // zero on entry and are zero again on exit.
-    // Fused single-token append (streaming kernel, one session): the pair that owns the last tile quantises the new
-    // token's K/V row of its kv head, stores it at position end-1 and patches its shared-memory tiles with it.
+    // Fused single-token append (streaming kernel, one session): the warp that owns the last tile quantises the new
+    // token's K/V row of its kv head and stores it at position end-1 before it loads that tile.
     const void* new_key;                     // [kv_heads*d] of new_is_f16 ? fp16 : fp32, or null = no fused append
     const void* new_value;
     int new_is_f16;
@@ -124,9 +125,9 @@ int run_decode(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length
 // the geometry has no specialised kernel, so the caller can use the generic one.
 int launch_decode_q8(const DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, cudaStream_t stream);
 uint32_t pick_splits_q8(const b200kv_view& geometry, uint32_t query_heads, uint32_t sessions, uint32_t max_length);
-// TMA descriptor of a view's int8 K plane (rows of head_dim bytes, 128-byte swizzle).  B200KV_ERR_UNSUPPORTED
-// when the view cannot take the streaming kernel (then `out` is zeroed and the generic kernel is used).
-int encode_k_map(const b200kv_view& view, CUtensorMap* out);
+// TMA descriptors of a view's int8 K and V planes (rows of head_dim bytes, 128-byte swizzle).
+// B200KV_ERR_UNSUPPORTED when the view cannot take the streaming kernel (then the generic kernel is used).
+int encode_kv_maps(const b200kv_view& view, CUtensorMap* kmap, CUtensorMap* vmap);
 bool q8_fast_path_ok(const b200kv_view& view, uint32_t query_heads);
 
 }  // namespace b200kv

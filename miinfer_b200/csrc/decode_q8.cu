@@ -5,43 +5,47 @@
 // (gfx906/kernels/qwen3_primitives.hip:7371-7485) with block scales; how it is
 // laid out is specific to B200:
 //
-//  * One CTA = one (kv head, split) = 4 warp PAIRS.  ALL query heads of the
-//    kv-head group share every K/V byte the CTA loads (the reference re-reads
-//    the cache once per query head).
-//  * A pair is a K-warp and a V-warp working on the same sequence of
-//    32-position tiles.  The K-warp streams K tiles and block scales, computes
-//    the scores and the online softmax and hands (weights, rescale factors) to
-//    its V-warp through a 4-slot ring in shared memory; the V-warp streams V
-//    tiles and accumulates P.V.  Splitting the roles halves the registers each
-//    warp needs (Q lives only in K-warps, the output accumulators only in
-//    V-warps), so 16 warps are resident per SM instead of 8, and the integer
-//    (Q.K) and floating-point (P.V) instruction streams of different warps
-//    interleave on each scheduler.
-//  * Every warp owns a private 3-stage ring of tiles filled by TMA: the K tile
-//    through a tensor map with the 128-byte swizzle (rows of 128 int8), V and
-//    both scale tiles with plain bulk copies.  One lane issues the copies;
-//    completion is an mbarrier per stage.  Pairs never synchronise with each
-//    other in the main loop; the hand-off inside a pair is two mbarriers per slot.
-//  * Q.K runs on the integer dot-product pipe: Q is quantised once per launch to
-//    int16 with a per-head scale (15 bits + sign: finer than the fp16 inputs'
-//    11-bit mantissa for the elements that matter), and dp2a multiplies packed
-//    int16 pairs by K's int8 bytes directly -- no int8->float conversion at all
-//    on the K side.  The exact int32 block sums are scaled by the fp16 block
-//    scales in fp32.  Lane layout: 8 positions x 4 heads per round; the swizzle
-//    makes the 8 rows' 16-byte chunks hit distinct banks while every lane keeps
-//    its head's Q in registers with static indices.
-//  * P.V stays in fp32: lane = (position mod 4, 16-dim chunk), 4 heads x 16
-//    dims of accumulators per lane; int8->fp32 by byte-permute into the mantissa
-//    of 2^23 and one packed multiply-add that removes the offset (the conversion
-//    pipe is 8x slower than that), the multiply-adds as packed f32x2.  Folding
-//    the offset into a per-block bias that is subtracted once per launch was
-//    measured: 2% faster, 10x less accurate (1.5e-4), so it is not used.
-//    Accumulators are rescaled only on tiles where a head's running max moved.
-//  * Softmax is the online form in base 2; each pair keeps (m, l, acc) for the
-//    whole launch, the CTA merges its 4 pairs in shared memory and writes one
-//    partial per (split, query head) for the log-sum-exp merge kernel.
-//  * Every wait is bounded: a copy or hand-off that never arrives poisons the
-//    partial with NaN instead of hanging the GPU.
+//  * One CTA = one (kv head, split) = 8 independent warps.  ALL query heads of
+//    the kv-head group share every K/V byte the CTA loads (the reference
+//    re-reads the cache once per query head).
+//  * Every warp owns a private 3-stage ring of 16-position tiles filled by TMA:
+//    K and V tiles through tensor maps with the 128-byte swizzle (rows of 128
+//    int8), both scale tiles with plain bulk copies; one mbarrier per stage.
+//    One lane issues the copies.  Warps never synchronise with each other in
+//    the main loop.
+//  * Both contractions run on the tensor cores through warp-level mma, which is
+//    what lets 16 warps per SM keep up with HBM: with scalar integer dot
+//    products and packed fp32 multiply-adds the same loop was bound by the FMA
+//    pipe at about half of the memory rate.  The arithmetic is arranged so that
+//    nothing is lost against that scalar version:
+//      - Q.K^T is m16n8k32 int8 x int8 -> int32 (exact).  Q is quantised once
+//        per launch to 15 bits per head (q = 128*hi + lo, two int8 planes); the
+//        hi plane sits in rows 0-7 of the A operand and the lo plane in rows
+//        8-15, so one instruction yields both partial sums, recombined exactly
+//        in int32.  K is the B operand straight from the swizzled tile
+//        (ldmatrix), no conversion.  One k-step of 32 is one q8_0 block; its
+//        int32 sum is scaled by the fp16 block scale in fp32.
+//      - P.V is m16n8k16 fp16 x fp16 -> fp32 with V^T as the A operand (16 dims
+//        x 16 positions) and the weights as B (16 positions x 8 columns).  V's
+//        int8 bytes become EXACT fp16 integers (byte-permute two positions'
+//        bytes into one word, one logic op to form 0x64xx, one packed subtract).
+//        The weight w * value_scale is split into an fp16 high part and an fp16
+//        remainder; the high parts of the 4 heads use columns 0-3 and the
+//        remainders columns 4-7, so the split costs no extra instructions and
+//        keeps 22 bits of each weight.  The two column groups are added once,
+//        when the warp stores its result.
+//      - The score fragment (rows = heads, columns = positions) is already the
+//        layout the weight operand needs (rows = positions, columns = heads):
+//        rows 4-7 of the Q operand repeat rows 0-3, so lanes 16-31 hold the
+//        same scores as lanes 0-15 and produce the remainder columns without
+//        any exchange.  Weights never leave registers.
+//  * Softmax is the online form in base 2 with a lazily updated reference
+//    maximum (accumulators are rescaled only when a head's maximum has grown by
+//    more than 2^6); each warp keeps (m, l, acc) for the whole launch, the CTA
+//    merges its 8 warps in shared memory and writes one partial per (split,
+//    query head); the last CTA of a kv head to finish merges all splits.
+//  * Every wait is bounded: a copy that never arrives poisons the partial with
+//    NaN instead of hanging the GPU.
 #include "append_row.cuh"
 #include "decode_common.cuh"
 
@@ -52,36 +56,30 @@ namespace b200kv {
 
 namespace {
 
-constexpr int kPairs = 4;     // warp pairs per CTA: warps 0..3 are K-warps, 4..7 their V-warps
-constexpr int kTile = 32;     // positions per tile
-constexpr int kKStages = 3;   // TMA ring depth of a K-warp (K tile + both scale tiles)
-constexpr int kVStages = 2;   // TMA ring depth of a V-warp (V tile)
-constexpr int kSlots = 2;     // weight hand-off ring depth per pair
+constexpr int kWarps = 8;     // warps per CTA, each with its own tile ring
+constexpr int kTile = 16;     // positions per tile: one P.V k-step, two Q.K n-tiles
+constexpr int kStages = 3;    // TMA ring depth per warp
 constexpr int kD = 128;
-constexpr uint32_t kSpinLimit = 1u << 20;   // bounded waits: a lost copy or hand-off ends the kernel with a poisoned partial
+constexpr uint32_t kSpinLimit = 1u << 20;   // bounded waits: a lost copy ends the kernel with a poisoned partial
 constexpr uint32_t kPositionsPerSplit = 2048;   // batched launches: one split per this many positions of a session
-#ifndef B200KV_PV_UNROLL
-#define B200KV_PV_UNROLL 2
-#endif
-constexpr int kPvUnroll = B200KV_PV_UNROLL;   // positions of the P.V loop in flight per lane
+constexpr int kAppendUnits = 2;    // a fused append is balanced as this many tiles of work
+constexpr float kRescaleSlack = 6.0f;   // log2 units a head's maximum may exceed the reference before a rescale
 
 template <int NBLK>
 struct Smem {
-    static constexpr int kKTile = kTile * kD;                    // 4096
-    static constexpr int kSTile = kTile * NBLK * 2;              // 256 (q8_0) or 64 (row scale)
-    static constexpr int kBlkStride = kTile * 4 * 4 + 64;          // ew[pos][head] fp32 of one block, padded against bank conflicts
-    static constexpr int kSlotBytes = NBLK * kBlkStride + 16;      // ew[blk][pos][head] + alpha[4]
-    static constexpr int kOffV = kPairs * kKStages * kKTile;
-    static constexpr int kOffS = kOffV + kPairs * kVStages * kKTile;     // [pair][stage][ks | vs]
-    static constexpr int kOffW = kOffS + kPairs * kKStages * 2 * kSTile;
-    static constexpr int kOffQ = kOffW + kPairs * kSlots * kSlotBytes;   // [4][kD] int16
-    static constexpr int kOffQmul = kOffQ + 4 * kD * 2;                  // [4] float
-    static constexpr int kOffMisc = kOffQmul + 16;                       // merge scratch: m/l/a [4][128] floats x3
-    static constexpr int kOffBar = kOffMisc + 3 * 4 * 128 * 4;
-    static constexpr int kBarsPerPair = kKStages + kVStages + 2 * kSlots;  // kfull, vfull, wfull, wempty
-    static constexpr int kTotal = kOffBar + kPairs * kBarsPerPair * 8;
+    static constexpr int kKTile = kTile * kD;                    // 2048
+    static constexpr int kSTile = kTile * NBLK * 2;              // 128 (q8_0) or 32 (row scale)
+    static constexpr int kOffV = kWarps * kStages * kKTile;
+    static constexpr int kOffS = 2 * kOffV;                              // [warp][stage][ks | vs]
+    static constexpr int kOffQ = kOffS + kWarps * kStages * 2 * kSTile;  // int8 hi[4][kD], lo[4][kD]
+    static constexpr int kOffQmul = kOffQ + 2 * 4 * kD;                  // [4] float
+    static constexpr int kOffMisc = kOffQmul + 16;                       // last-CTA merge scratch: m/l [4][128] floats, totals
+    static constexpr int kOffBar = kOffMisc + (2 * 4 * 128 + 8) * 4;
+    static constexpr int kTotal = kOffBar + kWarps * kStages * 8;
     static constexpr int kAlloc = kTotal + 1024;                         // slack to align the base to 1024
+    static constexpr int kWarpArea = kStages * kKTile;                   // a warp's K ring doubles as its merge area
 };
+static_assert(Smem<4>::kWarpArea >= (8 * kD + 8) * 4, "merge area of a warp: 8 columns x 128 dims + m[4] + l[4]");
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -90,9 +88,6 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // Bounded wait: returns false if the phase did not complete within the spin limit.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
@@ -113,14 +108,36 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// c (+)= A(16x32 int8, row) * B(32x8 int8, col), int32 accumulators
+__device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// c += A(16x16 fp16, row) * B(16x8 fp16, col), fp32 accumulators
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
-// Two int8 bytes of x (already offset by +128) to fp32: placed in the mantissa of
-// 2^23 they read 8388608 + u; one packed multiply-add removes the offset.
-__device__ __forceinline__ float2 cvt2(uint32_t x, uint32_t sel_lo, uint32_t sel_hi) {
-    float2 f;
-    f.x = __uint_as_float(__byte_perm(x, 0x4B000000u, sel_lo));
-    f.y = __uint_as_float(__byte_perm(x, 0x4B000000u, sel_hi));
-    return __ffma2_rn(f, make_float2(1.0f, 1.0f), make_float2(-8388736.0f, -8388736.0f));
+// Byte `B` of two int8 words (two consecutive positions of one dim) as an exact half2: the bytes land in the
+// mantissas of 0x64xx (= 1024 + u) with their sign bits flipped (u = x + 128), and 1152 is subtracted.
+template <int B>
+__device__ __forceinline__ uint32_t s8_pair_to_half2(uint32_t first, uint32_t second) {
+    constexpr uint32_t sel = B | (B << 4) | ((4 + B) << 8) | ((4 + B) << 12);
+    uint32_t r = __byte_perm(first, second, sel);
+    r = (r & 0x00FF00FFu) ^ 0x64806480u;
+    const __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&r), __half2half2(__ushort_as_half(0x6480)));   // 0x6480 = 1152
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
 }
 
 // ---- fused single-token append -----------------------------------------------------------------------------
@@ -159,11 +176,10 @@ __device__ __noinline__ void fused_append_row(const DecodeParams& p, const b200k
 
 // G query heads per kv head (1, 2 or 4); NBLK scales per row (4 = q8_0 blocks of 32, 1 = one per row).
 template <int G, int NBLK, bool Q_F16>
-__global__ void __launch_bounds__(kPairs * 64, 2)
-decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ CUtensorMap kmap_single) {
+__global__ void __launch_bounds__(kWarps * 32, 2)
+decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ CUtensorMap kmap_single,
+                 const __grid_constant__ CUtensorMap vmap_single) {
     using L = Smem<NBLK>;
-    constexpr int PPR = 32 / G;          // positions per Q.K round
-    constexpr int ROUNDS = kTile / PPR;  // == G
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     __shared__ int s_last;
@@ -171,8 +187,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     pdl_launch_dependents();   // the next kernel of the stream may become resident as SMs free up; it orders itself
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int pair = warp & (kPairs - 1);
-    const bool is_k_warp = warp < kPairs;
+    const int g = lane >> 2, t = lane & 3;   // mma fragment coordinates
     const uint32_t split = blockIdx.x, kv_head = blockIdx.y, session = blockIdx.z;
     const b200kv_view& view = session_view(p, session);
     uint32_t begin, end;
@@ -187,84 +202,76 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
         if (split >= num_splits) return;
     }
 
-    // ---- this pair's tiles -----------------------------------------------------------
+    // ---- this warp's tiles -----------------------------------------------------------
     const uint32_t tile_begin = begin / kTile, tile_end = (end + kTile - 1) / kTile;
     const uint64_t total_tiles = end > begin ? tile_end - tile_begin : 0;
-    const uint32_t npairs = num_splits * kPairs, gp = split * kPairs + pair;
-    // A fused append costs its pair about one tile's time: it is counted as one extra unit at the end of the range,
-    // so the pair that does it is handed one tile less.
+    const uint32_t nworkers = num_splits * kWarps, gw = split * kWarps + warp;
+    // A fused append is counted as extra units at the end of the range, so the warp that does it is handed fewer tiles.
     const bool fuse = p.new_key != nullptr;
-    const uint64_t units = total_tiles + (fuse ? 1 : 0);
-    const uint64_t u0 = units * gp / npairs, u1 = units * (gp + 1) / npairs;
+    const uint64_t units = total_tiles + (fuse ? kAppendUnits : 0);
+    const uint64_t u0 = units * gw / nworkers, u1 = units * (gw + 1) / nworkers;
     const uint32_t t0 = tile_begin + static_cast<uint32_t>(u0 < total_tiles ? u0 : total_tiles);
     const uint32_t t1 = tile_begin + static_cast<uint32_t>(u1 < total_tiles ? u1 : total_tiles);
     const int ntiles = static_cast<int>(t1 - t0);
-    const bool owner = fuse && ntiles > 0 && t1 == tile_end;   // this pair holds the tile of the appended token
+    const bool owner = fuse && ntiles > 0 && t1 == tile_end;   // this warp holds the tile of the appended token
     // With launch overlap the previous kernel may still be appending: rows at or above early_end wait for it.  The
     // row a fused append writes is never loaded early either.
     uint32_t early_end = end > p.overlap_tail ? end - p.overlap_tail : 0;
     if (fuse && early_end >= end) early_end = end - 1;
 
-    uint8_t* k_ring = smem + pair * kKStages * L::kKTile;
-    uint8_t* v_ring = smem + L::kOffV + pair * kVStages * L::kKTile;
-    uint8_t* s_ring = smem + L::kOffS + pair * kKStages * 2 * L::kSTile;
-    uint8_t* w_ring = smem + L::kOffW + pair * kSlots * L::kSlotBytes;
-    int16_t* q16 = reinterpret_cast<int16_t*>(smem + L::kOffQ);
+    uint8_t* k_ring = smem + warp * kStages * L::kKTile;
+    uint8_t* v_ring = smem + L::kOffV + warp * kStages * L::kKTile;
+    uint8_t* s_ring = smem + L::kOffS + warp * kStages * 2 * L::kSTile;
+    int8_t* q_hi = reinterpret_cast<int8_t*>(smem + L::kOffQ);
+    int8_t* q_lo = q_hi + 4 * kD;
     float* qmul_s = reinterpret_cast<float*>(smem + L::kOffQmul);
-    const uint32_t bars = smem_u32(smem + L::kOffBar) + pair * L::kBarsPerPair * 8;
-    const uint32_t bar_kfull = bars, bar_vfull = bars + kKStages * 8;
-    const uint32_t bar_wfull = bar_vfull + kVStages * 8, bar_wempty = bar_wfull + kSlots * 8;
-
+    const uint32_t bars = smem_u32(smem + L::kOffBar) + warp * kStages * 8;
     const uint64_t head_row0 = static_cast<uint64_t>(kv_head) * view.capacity;
 
-    // barriers of a pair are initialised by its K-warp before either warp uses them
-    if (is_k_warp && lane == 0) {
-        for (int s = 0; s < L::kBarsPerPair; ++s) mbar_init(bars + s * 8, 1);
+    // the barriers of a warp are its own
+    if (lane == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(bars + s * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    __syncthreads();
+    __syncwarp();
 
-    bool failed = false;
-    // merge area of the pair (reuses its K ring once the main loop is over): m[4], l[4], pad[24], acc[G][128]
-    float* mine = reinterpret_cast<float*>(k_ring);
+    const CUtensorMap* kmap = p.views != nullptr ? &p.views[session].kmap : &kmap_single;
+    const CUtensorMap* vmap = p.views != nullptr ? &p.views[session].vmap : &vmap_single;
+    const uint8_t* ks_plane = static_cast<const uint8_t*>(view.key_scales) + head_row0 * NBLK * 2;
+    const uint8_t* vs_plane = static_cast<const uint8_t*>(view.value_scales) + head_row0 * NBLK * 2;
+    auto issue = [&](int i) {
+        const int stage = i % kStages;
+        const uint32_t pos0 = (t0 + i) * kTile;
+        const uint32_t rows = min(static_cast<uint32_t>(kTile), static_cast<uint32_t>(view.capacity) - pos0);
+        const uint32_t bar = bars + stage * 8;
+        mbar_expect_tx(bar, 2 * L::kKTile + 2 * rows * NBLK * 2);
+        tma_load_2d(smem_u32(k_ring + stage * L::kKTile), kmap, 0, static_cast<int>(head_row0 + pos0), bar);
+        tma_load_2d(smem_u32(v_ring + stage * L::kKTile), vmap, 0, static_cast<int>(head_row0 + pos0), bar);
+        uint8_t* sdst = s_ring + stage * 2 * L::kSTile;
+        bulk_load(smem_u32(sdst), ks_plane + static_cast<size_t>(pos0) * NBLK * 2, rows * NBLK * 2, bar);
+        bulk_load(smem_u32(sdst + L::kSTile), vs_plane + static_cast<size_t>(pos0) * NBLK * 2, rows * NBLK * 2, bar);
+    };
+    // old cache rows do not depend on the preceding kernels: start streaming them before waiting for those
+    int issued = 0;
+    if (lane == 0)
+        while (issued < kStages && issued < ntiles && (t0 + issued + 1) * kTile <= early_end) issue(issued++);
+    pdl_wait();
+    if (owner) {
+        // the new row goes to the cache first; its tile is loaded (by TMA, an asynchronous-proxy read) only afterwards
+        fused_append_row<NBLK>(p, view, kv_head, end - 1, head_row0 + end - 1, lane);
+        __threadfence();
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __syncwarp();
+    }
+    if (lane == 0)
+        while (issued < kStages && issued < ntiles) issue(issued++);
 
-    if (is_k_warp) {
-        // =========================== K-warp: scores, softmax, weights ===========================
-        const CUtensorMap* kmap = p.views != nullptr ? &p.views[session].kmap : &kmap_single;
-        const uint8_t* ks_plane = static_cast<const uint8_t*>(view.key_scales) + head_row0 * NBLK * 2;
-        const uint8_t* vs_plane = static_cast<const uint8_t*>(view.value_scales) + head_row0 * NBLK * 2;
-        auto issue = [&](int i) {
-            const int stage = i % kKStages;
-            const uint32_t pos0 = (t0 + i) * kTile;
-            const uint32_t rows = min(static_cast<uint32_t>(kTile), static_cast<uint32_t>(view.capacity) - pos0);
-            const uint32_t bar = bar_kfull + stage * 8;
-            mbar_expect_tx(bar, L::kKTile + 2 * rows * NBLK * 2);
-            tma_load_2d(smem_u32(k_ring + stage * L::kKTile), kmap, 0, static_cast<int>(head_row0 + pos0), bar);
-            uint8_t* sdst = s_ring + stage * 2 * L::kSTile;
-            bulk_load(smem_u32(sdst), ks_plane + static_cast<size_t>(pos0) * NBLK * 2, rows * NBLK * 2, bar);
-            bulk_load(smem_u32(sdst + L::kSTile), vs_plane + static_cast<size_t>(pos0) * NBLK * 2, rows * NBLK * 2, bar);
-        };
-        // old cache rows do not depend on the preceding kernels: start streaming them before waiting for those
-        int issued = 0;
-        if (lane == 0)
-            while (issued < kKStages && issued < ntiles && (t0 + issued + 1) * kTile <= early_end) issue(issued++);
-        pdl_wait();
-        if (owner) {
-            // the new row goes to the cache first; its tile is loaded (by TMA, an asynchronous-proxy read) only afterwards
-            fused_append_row<NBLK>(p, view, kv_head, end - 1, head_row0 + end - 1, lane);
-            __threadfence();
-            asm volatile("fence.proxy.async;" ::: "memory");
-            // arrive without waiting: the V-warp joins this barrier only before its LAST tile, long after it has
-            // consumed weights this warp still has to produce
-            asm volatile("bar.arrive %0, 64;" ::"r"(2 + pair) : "memory");
-        }
-        if (lane == 0)
-            while (issued < kKStages && issued < ntiles) issue(issued++);
-
-        // quantise Q to int16, one K-warp per head
-        if (pair < G) {
-            const uint32_t head = kv_head * G + pair;
+    // ---- quantise Q to 15 bits (two int8 planes), one warp per head; heads the group does not have are zero ----
+    if (warp < 4) {
+        uint32_t hi4 = 0, lo4 = 0;
+        if (warp < G) {
+            const uint32_t head = kv_head * G + warp;
             const size_t qb = (static_cast<size_t>(session) * p.query_heads + head) * kD + lane * 4;
             float q[4];
             if (Q_F16) {
@@ -276,262 +283,225 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
                 q[0] = raw.x; q[1] = raw.y; q[2] = raw.z; q[3] = raw.w;
             }
             const float amax = warp_max(fmaxf(fmaxf(fabsf(q[0]), fabsf(q[1])), fmaxf(fabsf(q[2]), fabsf(q[3]))));
-            const float inv = amax > 0.0f ? 32767.0f / amax : 0.0f;
-            short4 packed;
-            packed.x = static_cast<short>(__float2int_rn(q[0] * inv));
-            packed.y = static_cast<short>(__float2int_rn(q[1] * inv));
-            packed.z = static_cast<short>(__float2int_rn(q[2] * inv));
-            packed.w = static_cast<short>(__float2int_rn(q[3] * inv));
-            *reinterpret_cast<short4*>(q16 + pair * kD + lane * 4) = packed;
-            // scores are kept in base-2 units: dot * (amax/32767) * softmax_scale * log2(e)
-            if (lane == 0) qmul_s[pair] = (amax / 32767.0f) * p.scale * 1.4426950408889634f;
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(kPairs * 32) : "memory");   // K-warps only
-
-        const int g = lane % G, pl = lane / G;   // head g of position pl (+ PPR * round)
-        int qreg[kD / 2];
+            // q = 128*hi + lo with hi in [-127, 127] and lo in [-64, 63]: |q| <= 16319
+            const float inv = amax > 0.0f ? 16319.0f / amax : 0.0f;
 #pragma unroll
-        for (int i = 0; i < kD / 8; ++i) {
-            const uint4 t = reinterpret_cast<const uint4*>(q16 + g * kD)[i];
-            qreg[4 * i] = static_cast<int>(t.x); qreg[4 * i + 1] = static_cast<int>(t.y);
-            qreg[4 * i + 2] = static_cast<int>(t.z); qreg[4 * i + 3] = static_cast<int>(t.w);
-        }
-        const float qmul = qmul_s[g];
-        float m_run = -INFINITY, l_run = 0.0f;
-        // per-lane byte offsets that do not change from tile to tile
-        // byte offset of logical 16-byte chunk ch of this lane's row in round 0; the 128-byte swizzle stores it
-        // at chunk (ch ^ (row & 7)), and row & 7 == pl & 7 in every round (PPR is a multiple of 8, or pl < 8)
-        uint32_t koff[8];
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) koff[ch] = static_cast<uint32_t>(pl) * kD + (static_cast<uint32_t>(ch ^ (pl & 7)) << 4);
-        const uint32_t s_lane = static_cast<uint32_t>(pl) * NBLK * 2;
-        const uint32_t w_lane = static_cast<uint32_t>(pl * 4 + g) * 4;
-
-        for (int i = 0; i < ntiles; ++i) {
-            const int stage = i % kKStages, slot = i % kSlots;
-            if (!mbar_wait(bar_kfull + stage * 8, (i / kKStages) & 1)) { failed = true; break; }
-            const uint32_t pos0 = (t0 + i) * kTile;
-            const int lo = begin > pos0 ? static_cast<int>(begin - pos0) : 0;
-            const int hi = end - pos0 < static_cast<uint32_t>(kTile) ? static_cast<int>(end - pos0) : kTile;
-            const uint8_t* kt = k_ring + stage * L::kKTile;
-            const uint8_t* kst = s_ring + stage * 2 * L::kSTile + s_lane;
-
-            float s[ROUNDS];
-#ifdef B200KV_SKIP_QK
-#pragma unroll
-            for (int r = 0; r < ROUNDS; ++r) s[r] = static_cast<float>(kt[r * 16] + qreg[r]) * qmul;
-#else
-#pragma unroll
-            for (int r = 0; r < ROUNDS; ++r) {
-                const uint8_t* krow = kt + r * PPR * kD;
-                float ksf[NBLK];
-                if constexpr (NBLK == 4) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(kst + r * PPR * 8);
-                    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-                    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-                    ksf[0] = a.x; ksf[1] = a.y; ksf[2] = b.x; ksf[3] = b.y;
-                } else {
-                    ksf[0] = __half2float(*reinterpret_cast<const __half*>(kst + r * PPR * 2));
-                }
-                float total = 0.0f;
-                int isum0 = 0, isum1 = 0;
-#pragma unroll
-                for (int ch = 0; ch < 8; ++ch) {
-                    const uint4 kw = *reinterpret_cast<const uint4*>(krow + koff[ch]);
-                    isum0 = __dp2a_lo(qreg[8 * ch + 0], static_cast<int>(kw.x), isum0);
-                    isum1 = __dp2a_hi(qreg[8 * ch + 1], static_cast<int>(kw.x), isum1);
-                    isum0 = __dp2a_lo(qreg[8 * ch + 2], static_cast<int>(kw.y), isum0);
-                    isum1 = __dp2a_hi(qreg[8 * ch + 3], static_cast<int>(kw.y), isum1);
-                    isum0 = __dp2a_lo(qreg[8 * ch + 4], static_cast<int>(kw.z), isum0);
-                    isum1 = __dp2a_hi(qreg[8 * ch + 5], static_cast<int>(kw.z), isum1);
-                    isum0 = __dp2a_lo(qreg[8 * ch + 6], static_cast<int>(kw.w), isum0);
-                    isum1 = __dp2a_hi(qreg[8 * ch + 7], static_cast<int>(kw.w), isum1);
-                    if constexpr (NBLK == 4) {
-                        if (ch & 1) {   // a 32-dim block ends every second chunk
-                            total = fmaf(static_cast<float>(isum0 + isum1), ksf[ch >> 1], total);
-                            isum0 = 0; isum1 = 0;
-                        }
-                    }
-                }
-                if constexpr (NBLK == 1) total = static_cast<float>(isum0 + isum1) * ksf[0];
-                const int pos = r * PPR + pl;
-                s[r] = (pos >= lo && pos < hi) ? total * qmul : -INFINITY;
+            for (int i = 0; i < 4; ++i) {
+                const int qi = __float2int_rn(q[i] * inv);
+                const int hi = (qi + 64) >> 7, lo = qi - (hi << 7);
+                hi4 |= static_cast<uint32_t>(hi & 0xff) << (8 * i);
+                lo4 |= static_cast<uint32_t>(lo & 0xff) << (8 * i);
             }
-#endif
-
-            // online softmax, base 2
-            float mt = s[0];
-#pragma unroll
-            for (int r = 1; r < ROUNDS; ++r) mt = fmaxf(mt, s[r]);
-#pragma unroll
-            for (int o = G; o < 32; o <<= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
-            const float m_new = fmaxf(m_run, mt);              // finite: every tile holds a valid position
-            const float alpha = exp2f(m_run - m_new);
-            float w[ROUNDS], lsum = 0.0f;
-#pragma unroll
-            for (int r = 0; r < ROUNDS; ++r) { w[r] = exp2f(s[r] - m_new); lsum += w[r]; }
-            l_run = fmaf(l_run, alpha, lsum);
-            m_run = m_new;
-
-            // effective weights w * value_scale[block] for the V-warp: ew[blk][pos][head]
-            if (!mbar_wait(bar_wempty + slot * 8, ((i / kSlots) & 1) ^ 1)) { failed = true; break; }
-            uint8_t* wt = w_ring + slot * L::kSlotBytes;
-            const uint8_t* vst = kst + L::kSTile;
-#pragma unroll
-            for (int r = 0; r < ROUNDS; ++r) {
-                const bool valid = w[r] > 0.0f;   // masked positions have weight exactly 0; their scales may be stale inf/nan
-                if constexpr (NBLK == 4) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(vst + r * PPR * 8);
-                    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-                    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-                    float* dst = reinterpret_cast<float*>(wt + w_lane + r * PPR * 16);
-                    const float e0 = valid ? w[r] * a.x : 0.0f, e1 = valid ? w[r] * a.y : 0.0f;
-                    const float e2 = valid ? w[r] * b.x : 0.0f, e3 = valid ? w[r] * b.y : 0.0f;
-                    dst[0 * L::kBlkStride / 4] = e0; dst[1 * L::kBlkStride / 4] = e1;
-                    dst[2 * L::kBlkStride / 4] = e2; dst[3 * L::kBlkStride / 4] = e3;
-
-                } else {
-                    const float v = __half2float(*reinterpret_cast<const __half*>(vst + r * PPR * 2));
-                    const float e0 = valid ? w[r] * v : 0.0f;
-                    *reinterpret_cast<float*>(wt + w_lane + r * PPR * 16) = e0;
-                }
-            }
-            if (pl == 0) reinterpret_cast<float*>(wt + NBLK * L::kBlkStride)[g] = alpha;
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(bar_wfull + slot * 8);
-                if (i + kKStages < ntiles) issue(i + kKStages);
-            }
+            // scores are kept in base-2 units: dot * (amax/16319) * softmax_scale * log2(e)
+            if (lane == 0) qmul_s[warp] = (amax / 16319.0f) * p.scale * 1.4426950408889634f;
+        } else if (lane == 0) {
+            qmul_s[warp] = 0.0f;
         }
-#pragma unroll
-        for (int o = G; o < 32; o <<= 1) l_run += __shfl_xor_sync(0xffffffffu, l_run, o);
-        if (failed) { m_run = __int_as_float(0x7fc00000); l_run = m_run; }   // poison the partial
-        if (pl == 0) { mine[g] = m_run; mine[4 + g] = l_run; }
-    } else {
-        // =========================== V-warp: P.V accumulation ============================
-        const int8_t* v_plane = view.value_q8 + head_row0 * kD;
-        auto issue = [&](int i) {
-            const int stage = i % kVStages;
-            const uint32_t pos0 = (t0 + i) * kTile;
-            const uint32_t rows = min(static_cast<uint32_t>(kTile), static_cast<uint32_t>(view.capacity) - pos0);
-            const uint32_t bar = bar_vfull + stage * 8;
-            mbar_expect_tx(bar, rows * kD);
-            bulk_load(smem_u32(v_ring + stage * L::kKTile), v_plane + static_cast<size_t>(pos0) * kD, rows * kD, bar);
-        };
-        int issued = 0;   // kept identical in all lanes: the hand-shake below is warp-wide
-        while (issued < kVStages && issued < ntiles && (t0 + issued + 1) * kTile <= early_end) {
-            if (lane == 0) issue(issued);
-            ++issued;
-        }
-        pdl_wait();
-        while (issued < kVStages && issued < ntiles) {
-            // the tile of a fused append is loaded only after the K-warp has stored the new row
-            if (owner && issued == ntiles - 1) asm volatile("bar.sync %0, 64;" ::"r"(2 + pair) : "memory");
-            if (lane == 0) issue(issued);
-            ++issued;
-        }
-
-        const int r4 = lane >> 3, c = lane & 7;   // positions r4 + 4j, dims [16c, 16c+16)
-        const uint32_t v_lane = static_cast<uint32_t>(r4) * kD + c * 16;
-        const uint32_t w_lane = static_cast<uint32_t>(NBLK == 4 ? (c >> 1) : 0) * L::kBlkStride + r4 * 16;
-        float2 acc[G][8];
-#pragma unroll
-        for (int h = 0; h < G; ++h)
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[h][k] = make_float2(0.0f, 0.0f);
-
-        for (int i = 0; i < ntiles; ++i) {
-            const int stage = i % kVStages, slot = i % kSlots;
-            if (!mbar_wait(bar_vfull + stage * 8, (i / kVStages) & 1)) { failed = true; break; }
-            if (!mbar_wait(bar_wfull + slot * 8, (i / kSlots) & 1)) { failed = true; break; }
-            const uint8_t* vt = v_ring + stage * L::kKTile + v_lane;
-            const uint8_t* wt = w_ring + slot * L::kSlotBytes;
-            {
-                float al[4];
-                *reinterpret_cast<float4*>(al) = *reinterpret_cast<const float4*>(wt + NBLK * L::kBlkStride);
-                bool moved = false;
-#pragma unroll
-                for (int h = 0; h < G; ++h) moved = moved || (al[h] != 1.0f);
-                if (moved) {
-#pragma unroll
-                    for (int h = 0; h < G; ++h) {
-                        const float2 a2 = make_float2(al[h], al[h]);
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) acc[h][k] = __fmul2_rn(acc[h][k], a2);
-                    }
-                }
-            }
-            const uint8_t* wl = wt + w_lane;
-#ifdef B200KV_SKIP_PV
-            acc[0][0].x += static_cast<float>(vt[0]) * wl[0];
-#else
-#pragma unroll kPvUnroll
-            for (int j = 0; j < kTile / 4; ++j) {
-                const uint4 vw = *reinterpret_cast<const uint4*>(vt + j * 4 * kD);
-                float wv[4];
-                *reinterpret_cast<float4*>(wv) = *reinterpret_cast<const float4*>(wl + j * 64);
-                float2 ew[G];
-#pragma unroll
-                for (int h = 0; h < G; ++h) ew[h] = make_float2(wv[h], wv[h]);
-                const uint32_t words[4] = {vw.x ^ 0x80808080u, vw.y ^ 0x80808080u, vw.z ^ 0x80808080u, vw.w ^ 0x80808080u};
-#pragma unroll
-                for (int wi = 0; wi < 4; ++wi) {
-                    const float2 f01 = cvt2(words[wi], 0x7440u, 0x7441u);
-                    const float2 f23 = cvt2(words[wi], 0x7442u, 0x7443u);
-#pragma unroll
-                    for (int h = 0; h < G; ++h) {
-                        acc[h][2 * wi] = __ffma2_rn(ew[h], f01, acc[h][2 * wi]);
-                        acc[h][2 * wi + 1] = __ffma2_rn(ew[h], f23, acc[h][2 * wi + 1]);
-                    }
-                }
-            }
-#endif
-            __syncwarp();   // every lane is done with this stage and this weight slot
-            if (owner && i + kVStages == ntiles - 1) asm volatile("bar.sync %0, 64;" ::"r"(2 + pair) : "memory");
-            if (lane == 0) {
-                mbar_arrive(bar_wempty + slot * 8);
-                if (i + kVStages < ntiles) issue(i + kVStages);
-            }
-        }
-        // sum the 4 position groups
-#pragma unroll
-        for (int h = 0; h < G; ++h)
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                acc[h][k].x += __shfl_xor_sync(0xffffffffu, acc[h][k].x, 8);
-                acc[h][k].y += __shfl_xor_sync(0xffffffffu, acc[h][k].y, 8);
-                acc[h][k].x += __shfl_xor_sync(0xffffffffu, acc[h][k].x, 16);
-                acc[h][k].y += __shfl_xor_sync(0xffffffffu, acc[h][k].y, 16);
-            }
-        if (failed) acc[0][0].x = __int_as_float(0x7fc00000);
-        // the K-warp of this pair is past its last K tile once the last weights have arrived
-        if (r4 == 0) {
-#pragma unroll
-            for (int h = 0; h < G; ++h)
-#pragma unroll
-                for (int k = 0; k < 8; ++k)
-                    *reinterpret_cast<float2*>(mine + 32 + h * kD + c * 16 + 2 * k) = acc[h][k];
-        }
+        reinterpret_cast<uint32_t*>(q_hi + warp * kD)[lane] = hi4;
+        reinterpret_cast<uint32_t*>(q_lo + warp * kD)[lane] = lo4;
     }
     __syncthreads();
 
-    // ---- merge the CTA's pairs: 256 threads = 2 head slots x 128 dims ---------------------------------------
+    // A operand of Q.K^T, per k-step (= one 32-dim block): rows g and g+8 are the hi and lo planes of head g & 3
+    uint32_t qa[4][4];
+    {
+        const int h = g & 3;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            qa[ks][0] = *reinterpret_cast<const uint32_t*>(q_hi + h * kD + 32 * ks + 4 * t);
+            qa[ks][1] = *reinterpret_cast<const uint32_t*>(q_lo + h * kD + 32 * ks + 4 * t);
+            qa[ks][2] = *reinterpret_cast<const uint32_t*>(q_hi + h * kD + 32 * ks + 16 + 4 * t);
+            qa[ks][3] = *reinterpret_cast<const uint32_t*>(q_lo + h * kD + 32 * ks + 16 + 4 * t);
+        }
+    }
+    const float qmul = qmul_s[g & 3];
+    const bool remainder_lane = g >= 4;   // this lane feeds a remainder column of the weight operand
+
+    // P.V accumulators: M-tile mt holds dims 32*(mt>>1) + 4*row + 2*(mt&1) {+0: rows 0-7, +1: rows 8-15};
+    // columns 2t, 2t+1 of this lane: high parts of heads 0..3 (t < 2) or remainders (t >= 2)
+    float acc[8][4];
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[mt][i] = 0.0f;
+    float m_ref = -INFINITY, l_run = 0.0f;
+    bool failed = false;
+
+    // per-lane shared-memory offsets that do not change from tile to tile
+    // ldmatrix: lane supplies the row address of matrix (lane>>3) = 16-byte chunk 4h + (lane>>3) of row (lane&7) [+8 for n-tile 1]
+    const uint32_t ldm_row = static_cast<uint32_t>(lane & 7) * kD;
+    const uint32_t ldm_c0 = static_cast<uint32_t>(((lane >> 3)) ^ (lane & 7)) << 4;         // chunks 0..3
+    const uint32_t ldm_c1 = static_cast<uint32_t>((4 + (lane >> 3)) ^ (lane & 7)) << 4;     // chunks 4..7
+    // V words: positions 2t, 2t+1, 2t+8, 2t+9; the 4 bytes at dims 32*blk + 4g.. live in chunk 2*blk + (g>>2)
+    uint32_t v_off[4][4];
+#pragma unroll
+    for (int pi = 0; pi < 4; ++pi) {
+        const uint32_t pos = 2 * t + (pi & 1) + 8 * (pi >> 1);
+#pragma unroll
+        for (int blk = 0; blk < 4; ++blk)
+            v_off[pi][blk] = pos * kD + ((static_cast<uint32_t>(2 * blk + (g >> 2)) ^ (pos & 7)) << 4) + 4 * (g & 3);
+    }
+
+    for (int i = 0; i < ntiles; ++i) {
+        const int stage = i % kStages;
+        if (!mbar_wait(bars + stage * 8, (i / kStages) & 1)) { failed = true; break; }
+        const uint32_t pos0 = (t0 + i) * kTile;
+        const int lo = begin > pos0 ? static_cast<int>(begin - pos0) : 0;
+        const int hi = end - pos0 < static_cast<uint32_t>(kTile) ? static_cast<int>(end - pos0) : kTile;
+        const uint32_t kt = smem_u32(k_ring + stage * L::kKTile);
+        const uint8_t* vt = v_ring + stage * L::kKTile;
+        const uint8_t* kst = s_ring + stage * 2 * L::kSTile;
+        const uint8_t* vst = kst + L::kSTile;
+
+        // ---- scores of this lane: head g & 3, positions 8j + 2t + {0, 1} -------------------------
+        float s[2][2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            uint32_t kb[8];
+            {
+                uint32_t r[4];
+                ldmatrix_x4(kt + j * 8 * kD + ldm_row + ldm_c0, r);
+                kb[0] = r[0]; kb[1] = r[1]; kb[2] = r[2]; kb[3] = r[3];
+                ldmatrix_x4(kt + j * 8 * kD + ldm_row + ldm_c1, r);
+                kb[4] = r[0]; kb[5] = r[1]; kb[6] = r[2]; kb[7] = r[3];
+            }
+            if constexpr (NBLK == 4) {
+                // scales of positions 8j+2t and 8j+2t+1: 2 x 4 halves, contiguous
+                const uint4 raw = *reinterpret_cast<const uint4*>(kst + (8 * j + 2 * t) * 8);
+                const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+                const float2 a1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.z));
+                const float2 b1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.w));
+                const float ksa[4] = {a0.x, a0.y, a1.x, a1.y}, ksb[4] = {b0.x, b0.y, b1.x, b1.y};
+                float sa = 0.0f, sb = 0.0f;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    int c[4] = {0, 0, 0, 0};
+                    mma_s8(c, qa[ks], kb[2 * ks], kb[2 * ks + 1]);
+                    sa = fmaf(static_cast<float>((c[0] << 7) + c[2]), ksa[ks], sa);
+                    sb = fmaf(static_cast<float>((c[1] << 7) + c[3]), ksb[ks], sb);
+                }
+                s[j][0] = sa; s[j][1] = sb;
+            } else {
+                const __half2 raw = *reinterpret_cast<const __half2*>(kst + (8 * j + 2 * t) * 2);
+                const float2 sc = __half22float2(raw);
+                int c[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) mma_s8(c, qa[ks], kb[2 * ks], kb[2 * ks + 1]);
+                s[j][0] = static_cast<float>((c[0] << 7) + c[2]) * sc.x;
+                s[j][1] = static_cast<float>((c[1] << 7) + c[3]) * sc.y;
+            }
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int pos = 8 * j + 2 * t + e;
+                s[j][e] = (pos >= lo && pos < hi) ? s[j][e] * qmul : -INFINITY;
+            }
+        }
+
+        // ---- online softmax, base 2, lazily updated reference maximum ----------------------------
+        float mt_ = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        mt_ = fmaxf(mt_, __shfl_xor_sync(0xffffffffu, mt_, 1));
+        mt_ = fmaxf(mt_, __shfl_xor_sync(0xffffffffu, mt_, 2));
+        const bool grow = mt_ > m_ref + kRescaleSlack;   // also true for the first tile (m_ref = -inf); NaN scores never grow
+        if (__any_sync(0xffffffffu, grow)) {
+            const float m_new = grow ? mt_ : m_ref;
+            const float alpha = (m_ref == -INFINITY) ? 0.0f : exp2f(m_ref - m_new);   // 1 for heads that did not move
+            l_run *= alpha;
+            m_ref = m_new;
+            // columns 2t, 2t+1 belong to heads (2t)&3, (2t+1)&3, whose factors sit in lanes 4*head
+            const float a0 = __shfl_sync(0xffffffffu, alpha, ((2 * t) & 3) * 4);
+            const float a1 = __shfl_sync(0xffffffffu, alpha, ((2 * t + 1) & 3) * 4);
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) { acc[mt][0] *= a0; acc[mt][1] *= a1; acc[mt][2] *= a0; acc[mt][3] *= a1; }
+        }
+        float w[2][2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                w[j][e] = exp2f(s[j][e] - m_ref);   // masked positions: exp2(-inf) = 0 (m_ref is finite once a tile was seen)
+                l_run += w[j][e];
+            }
+
+        // ---- weight operand: w * value_scale per block, high part or remainder depending on the lane ----
+        uint32_t wb[NBLK][2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            float vs[2][NBLK];
+            if constexpr (NBLK == 4) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(vst + (8 * j + 2 * t) * 8);
+                const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+                const float2 a1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.z));
+                const float2 b1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.w));
+                vs[0][0] = a0.x; vs[0][1] = a0.y; vs[0][2] = a1.x; vs[0][3] = a1.y;
+                vs[1][0] = b0.x; vs[1][1] = b0.y; vs[1][2] = b1.x; vs[1][3] = b1.y;
+            } else {
+                const float2 sc = __half22float2(*reinterpret_cast<const __half2*>(vst + (8 * j + 2 * t) * 2));
+                vs[0][0] = sc.x; vs[1][0] = sc.y;
+            }
+            // masked positions have weight exactly 0; their scales may be stale inf/nan
+            const bool v0 = w[j][0] > 0.0f, v1 = w[j][1] > 0.0f;
+#pragma unroll
+            for (int blk = 0; blk < NBLK; ++blk) {
+                const float e0 = v0 ? w[j][0] * vs[0][blk] : 0.0f;
+                const float e1 = v1 ? w[j][1] * vs[1][blk] : 0.0f;
+                const __half2 h2 = __floats2half2_rn(e0, e1);
+                const float2 back = __half22float2(h2);
+                const uint32_t rem = pack_half2(e0 - back.x, e1 - back.y);
+                wb[blk][j] = remainder_lane ? rem : *reinterpret_cast<const uint32_t*>(&h2);
+            }
+        }
+
+        // ---- P.V: A = V^T of this tile, exact fp16 integers --------------------------------------
+#pragma unroll
+        for (int blk = 0; blk < 4; ++blk) {
+            uint32_t vw[4];
+#pragma unroll
+            for (int pi = 0; pi < 4; ++pi) vw[pi] = *reinterpret_cast<const uint32_t*>(vt + v_off[pi][blk]);
+            const uint32_t b0 = wb[NBLK == 4 ? blk : 0][0], b1 = wb[NBLK == 4 ? blk : 0][1];
+            mma_f16(acc[2 * blk], s8_pair_to_half2<0>(vw[0], vw[1]), s8_pair_to_half2<1>(vw[0], vw[1]),
+                    s8_pair_to_half2<0>(vw[2], vw[3]), s8_pair_to_half2<1>(vw[2], vw[3]), b0, b1);
+            mma_f16(acc[2 * blk + 1], s8_pair_to_half2<2>(vw[0], vw[1]), s8_pair_to_half2<3>(vw[0], vw[1]),
+                    s8_pair_to_half2<2>(vw[2], vw[3]), s8_pair_to_half2<3>(vw[2], vw[3]), b0, b1);
+        }
+
+        __syncwarp();   // every lane is done with this stage
+        if (lane == 0 && i + kStages < ntiles) issue(i + kStages);
+    }
+
+    // ---- the warp's result into its merge area: acc[8 columns][128 dims], m[4], l[4] ----------------------
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (failed) { m_ref = __int_as_float(0x7fc00000); l_run = m_ref; }   // poison the partial
+    float* mine = reinterpret_cast<float*>(k_ring);
+    __syncwarp();
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+        const int dim = 32 * (mt >> 1) + 4 * g + 2 * (mt & 1);
+        *reinterpret_cast<float2*>(mine + (2 * t) * kD + dim) = make_float2(acc[mt][0], acc[mt][2]);
+        *reinterpret_cast<float2*>(mine + (2 * t + 1) * kD + dim) = make_float2(acc[mt][1], acc[mt][3]);
+    }
+    if (t == 0 && g < 4) { mine[8 * kD + g] = m_ref; mine[8 * kD + 4 + g] = l_run; }
+    __syncthreads();
+
+    // ---- merge the CTA's warps: 256 threads = 2 head slots x 128 dims ---------------------------------------
     const int dim = threadIdx.x & (kD - 1);
     for (int h = threadIdx.x >> 7; h < G; h += 2) {
-        float mw[kPairs], M = -INFINITY;
+        float mw[kWarps], M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kPairs; ++w) {
-            const float* src = reinterpret_cast<const float*>(smem + w * kKStages * L::kKTile);
-            mw[w] = src[h];
+        for (int w = 0; w < kWarps; ++w) {
+            const float* src = reinterpret_cast<const float*>(smem + w * L::kWarpArea);
+            mw[w] = src[8 * kD + h];
             M = fmaxf(M, mw[w]);
         }
         float lt = 0.0f, at = 0.0f;
 #pragma unroll
-        for (int w = 0; w < kPairs; ++w) {
-            const float* src = reinterpret_cast<const float*>(smem + w * kKStages * L::kKTile);
+        for (int w = 0; w < kWarps; ++w) {
+            const float* src = reinterpret_cast<const float*>(smem + w * L::kWarpArea);
             const float a = (mw[w] == -INFINITY) ? 0.0f : exp2f(mw[w] - M);   // NaN (poison) propagates
-            lt = fmaf(src[4 + h], a, lt);
-            at = fmaf(src[32 + h * kD + dim], a, at);
+            lt = fmaf(src[8 * kD + 4 + h], a, lt);
+            at = fmaf(src[h * kD + dim] + src[(4 + h) * kD + dim], a, at);
         }
         const uint32_t head = kv_head * G + h;
         const size_t slot_idx = (static_cast<size_t>(session) * p.num_splits + split) * p.query_heads + head;
@@ -557,6 +527,18 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     float* sm = reinterpret_cast<float*>(smem + L::kOffMisc);   // [4][128] m -> a
     float* sl = sm + 4 * 128;                                   // [4][128] l
     float* sg = sl + 4 * 128;                                   // [4] merged max, [4] merged sum
+    // 256 threads = 4 heads x 2 halves of the splits x 32 float4 columns.  The first batch of accumulator loads is
+    // issued together with the loads of (m, l), so the common case (at most 2 x kBatch splits) pays one trip to L2.
+    constexpr int kBatch = 19;
+    const int col = threadIdx.x & 31, part = (threadIdx.x >> 5) & 1, hh = threadIdx.x >> 6;
+    const size_t stride = static_cast<size_t>(p.query_heads) * kD;
+    const float* accp = p.ws_acc + ((static_cast<size_t>(session) * p.num_splits) * p.query_heads + kv_head * G + (hh < G ? hh : 0)) * kD + col * 4;
+    float4 v[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+        const uint32_t sp = part + 2 * u;
+        v[u] = (hh < G && sp < S) ? __ldcg(reinterpret_cast<const float4*>(accp + sp * stride)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
     for (uint32_t idx = threadIdx.x; idx < G * S; idx += blockDim.x) {
         const uint32_t h = idx / S, sp = idx % S;
         const size_t slot_idx = (static_cast<size_t>(session) * p.num_splits + sp) * p.query_heads + kv_head * G + h;
@@ -583,45 +565,45 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
         if (lane == 0) { sg[h] = M; sg[4 + h] = lsum; }
     }
     __syncthreads();
-    // 256 threads = 4 heads x 2 halves of the splits x 32 float4 columns: each thread issues its loads
-    // in batches of 10 -- warps issue in order, so a loop of dependent load/use pairs would pay the L2 latency per step
     {
-        const int col = threadIdx.x & 31, part = (threadIdx.x >> 5) & 1, h = threadIdx.x >> 6;
         float4 tot = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (h < G) {
-            const uint32_t head = kv_head * G + h;
-            const size_t stride = static_cast<size_t>(p.query_heads) * kD;
-            const float* accp = p.ws_acc + ((static_cast<size_t>(session) * p.num_splits) * p.query_heads + head) * kD + col * 4;
-            for (uint32_t sp0 = part; sp0 < S; sp0 += 20) {
-                float4 v[10];
+        if (hh < G) {
 #pragma unroll
-                for (int u = 0; u < 10; ++u) {
+            for (int u = 0; u < kBatch; ++u) {
+                const uint32_t sp = part + 2 * u;
+                const float a = sp < S ? sm[hh * 128 + sp] : 0.0f;
+                tot.x = fmaf(v[u].x, a, tot.x); tot.y = fmaf(v[u].y, a, tot.y);
+                tot.z = fmaf(v[u].z, a, tot.z); tot.w = fmaf(v[u].w, a, tot.w);
+            }
+            for (uint32_t sp0 = part + 2 * kBatch; sp0 < S; sp0 += 2 * kBatch) {   // more splits than one batch covers
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
                     const uint32_t sp = sp0 + 2 * u;
                     v[u] = sp < S ? __ldcg(reinterpret_cast<const float4*>(accp + sp * stride)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 }
 #pragma unroll
-                for (int u = 0; u < 10; ++u) {
+                for (int u = 0; u < kBatch; ++u) {
                     const uint32_t sp = sp0 + 2 * u;
-                    const float a = sp < S ? sm[h * 128 + sp] : 0.0f;
+                    const float a = sp < S ? sm[hh * 128 + sp] : 0.0f;
                     tot.x = fmaf(v[u].x, a, tot.x); tot.y = fmaf(v[u].y, a, tot.y);
                     tot.z = fmaf(v[u].z, a, tot.z); tot.w = fmaf(v[u].w, a, tot.w);
                 }
             }
         }
-        // fold the two halves through shared memory (the pairs' merge areas are free by now)
+        // fold the two halves through shared memory (the warps' merge areas are free by now)
         float4* fold = reinterpret_cast<float4*>(smem);
-        if (part == 1) fold[h * 32 + col] = tot;
+        if (part == 1) fold[hh * 32 + col] = tot;
         __syncthreads();
-        if (part == 0 && h < G) {
-            const float4 o2 = fold[h * 32 + col];
+        if (part == 0 && hh < G) {
+            const float4 o2 = fold[hh * 32 + col];
             tot.x += o2.x; tot.y += o2.y; tot.z += o2.z; tot.w += o2.w;
-            const uint32_t head = kv_head * G + h;
-            const float gsum = sg[4 + h];
+            const uint32_t head = kv_head * G + hh;
+            const float gsum = sg[4 + hh];
             const size_t out_idx = (static_cast<size_t>(session) * p.query_heads + head) * kD + col * 4;
             if (p.fuse.out_m != nullptr) {   // sequence shard: one merged, unnormalised partial
                 *reinterpret_cast<float4*>(p.fuse.out_acc + out_idx) = tot;
                 if (col == 0) {
-                    p.fuse.out_m[static_cast<size_t>(session) * p.query_heads + head] = sg[h];
+                    p.fuse.out_m[static_cast<size_t>(session) * p.query_heads + head] = sg[hh];
                     p.fuse.out_l[static_cast<size_t>(session) * p.query_heads + head] = gsum;
                 }
             } else {
@@ -664,7 +646,7 @@ EncodeFn encoder() {
 }
 
 template <int G, int NBLK, bool Q_F16>
-int launch_one(const DecodeParams& p, const CUtensorMap& kmap, dim3 grid, cudaStream_t stream) {
+int launch_one(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap, dim3 grid, cudaStream_t stream) {
     using L = Smem<NBLK>;
     static std::once_flag once;   // one per kernel instantiation
     static cudaError_t attr_err = cudaSuccess;
@@ -672,13 +654,13 @@ int launch_one(const DecodeParams& p, const CUtensorMap& kmap, dim3 grid, cudaSt
         attr_err = cudaFuncSetAttribute(decode_q8_kernel<G, NBLK, Q_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc);
     });
     if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err, "cudaFuncSetAttribute(decode_q8)"); return B200KV_ERR_CUDA; }
-    B200KV_CUDA_TRY(launch_kernel(decode_q8_kernel<G, NBLK, Q_F16>, grid, dim3(kPairs * 64), L::kAlloc, stream, true, p, kmap));
+    B200KV_CUDA_TRY(launch_kernel(decode_q8_kernel<G, NBLK, Q_F16>, grid, dim3(kWarps * 32), L::kAlloc, stream, true, p, kmap, vmap));
     return B200KV_OK;
 }
 
 template <int G, int NBLK>
-int launch_variant(const DecodeParams& p, const CUtensorMap& kmap, dim3 grid, cudaStream_t stream) {
-    return p.q_is_f16 ? launch_one<G, NBLK, true>(p, kmap, grid, stream) : launch_one<G, NBLK, false>(p, kmap, grid, stream);
+int launch_variant(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap, dim3 grid, cudaStream_t stream) {
+    return p.q_is_f16 ? launch_one<G, NBLK, true>(p, kmap, vmap, grid, stream) : launch_one<G, NBLK, false>(p, kmap, vmap, grid, stream);
 }
 
 }  // namespace
@@ -694,22 +676,30 @@ bool q8_fast_path_ok(const b200kv_view& view, uint32_t query_heads) {
     return encoder() != nullptr;
 }
 
-int encode_k_map(const b200kv_view& view, CUtensorMap* out) {
+namespace {
+int encode_plane_map(int8_t* plane, const b200kv_view& view, CUtensorMap* out) {
     EncodeFn fn = encoder();
     if (fn == nullptr) return B200KV_ERR_UNSUPPORTED;
     const cuuint64_t dims[2] = {kD, static_cast<cuuint64_t>(view.kv_heads) * view.capacity};
     const cuuint64_t strides[1] = {kD};
     const cuuint32_t box[2] = {kD, kTile};
     const cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, view.key_q8, dims, strides, box, elem,
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, plane, dims, strides, box, elem,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? B200KV_OK : B200KV_ERR_UNSUPPORTED;
 }
+}  // namespace
+
+int encode_kv_maps(const b200kv_view& view, CUtensorMap* kmap, CUtensorMap* vmap) {
+    int rc = encode_plane_map(view.key_q8, view, kmap);
+    if (rc == B200KV_OK) rc = encode_plane_map(view.value_q8, view, vmap);
+    return rc;
+}
 
 uint32_t pick_splits_q8(const b200kv_view& geometry, uint32_t query_heads, uint32_t sessions, uint32_t max_length) {
     if (!q8_fast_path_ok(geometry, query_heads)) return 0;
-    // two CTAs of 4 warp pairs per SM; every pair should see at least two tiles
+    // two CTAs of 8 warps per SM; every warp should see at least two tiles
     const uint32_t ctas = 148u * 2u;
     const uint32_t units = geometry.kv_heads * sessions;
     uint32_t s = (ctas + units / 2) / units;   // nearest to one full wave
@@ -719,7 +709,7 @@ uint32_t pick_splits_q8(const b200kv_view& geometry, uint32_t query_heads, uint3
         if (by_length > s) s = by_length;
     }
     const uint32_t tiles = (max_length + kTile - 1) / kTile;
-    uint32_t by_tiles = tiles / (2 * kPairs);
+    uint32_t by_tiles = tiles / (2 * kWarps);
     if (by_tiles == 0) by_tiles = 1;
     if (s > by_tiles) s = by_tiles;
     const uint32_t cap = max_splits_per_session(sessions);
@@ -731,20 +721,21 @@ int launch_decode_q8(const DecodeParams& p_in, const b200kv_view& geometry, uint
     if (!q8_fast_path_ok(geometry, p_in.query_heads)) return B200KV_ERR_UNSUPPORTED;
     DecodeParams p = p_in;
     p.overlap_tail = launch_overlap_tail();
-    CUtensorMap kmap;
+    CUtensorMap kmap, vmap;
     if (p.views == nullptr) {
-        int rc = encode_k_map(geometry, &kmap);
+        int rc = encode_kv_maps(geometry, &kmap, &vmap);
         if (rc != B200KV_OK) return rc;
     } else {
         std::memset(&kmap, 0, sizeof kmap);   // per-session descriptors come from the device table
+        std::memset(&vmap, 0, sizeof vmap);
     }
     const uint32_t g = p.query_heads / geometry.kv_heads;
     const bool blocks = geometry.qblock == 32;
     dim3 grid(p.num_splits, geometry.kv_heads, p.sessions);
     switch (g) {
-        case 1: return blocks ? launch_variant<1, 4>(p, kmap, grid, stream) : launch_variant<1, 1>(p, kmap, grid, stream);
-        case 2: return blocks ? launch_variant<2, 4>(p, kmap, grid, stream) : launch_variant<2, 1>(p, kmap, grid, stream);
-        default: return blocks ? launch_variant<4, 4>(p, kmap, grid, stream) : launch_variant<4, 1>(p, kmap, grid, stream);
+        case 1: return blocks ? launch_variant<1, 4>(p, kmap, vmap, grid, stream) : launch_variant<1, 1>(p, kmap, vmap, grid, stream);
+        case 2: return blocks ? launch_variant<2, 4>(p, kmap, vmap, grid, stream) : launch_variant<2, 1>(p, kmap, vmap, grid, stream);
+        default: return blocks ? launch_variant<4, 4>(p, kmap, vmap, grid, stream) : launch_variant<4, 1>(p, kmap, vmap, grid, stream);
     }
 }
 

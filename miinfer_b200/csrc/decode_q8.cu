@@ -118,6 +118,13 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// c = A * B with a zero accumulator input (no registers to clear)
+__device__ __forceinline__ void mma_s8_zero(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    const int z = 0;
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(z));
+}
 // c += A(16x16 fp16, row) * B(16x8 fp16, col), fp32 accumulators
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -181,7 +188,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
                  const __grid_constant__ CUtensorMap vmap_single) {
     using L = Smem<NBLK>;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1024-aligned, still a shared-space pointer
     __shared__ int s_last;
 
     pdl_launch_dependents();   // the next kernel of the stream may become resident as SMs free up; it orders itself
@@ -240,32 +247,31 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     const CUtensorMap* vmap = p.views != nullptr ? &p.views[session].vmap : &vmap_single;
     const uint8_t* ks_plane = static_cast<const uint8_t*>(view.key_scales) + head_row0 * NBLK * 2;
     const uint8_t* vs_plane = static_cast<const uint8_t*>(view.value_scales) + head_row0 * NBLK * 2;
-    auto issue = [&](int i) {
-        const int stage = i % kStages;
+    const uint32_t k_ring_u = smem_u32(k_ring), v_ring_u = smem_u32(v_ring), s_ring_u = smem_u32(s_ring);
+    const uint32_t capacity = static_cast<uint32_t>(view.capacity);
+    const int row_base = static_cast<int>(head_row0);
+    auto issue = [&](int i, int stage) {
         const uint32_t pos0 = (t0 + i) * kTile;
-        const uint32_t rows = min(static_cast<uint32_t>(kTile), static_cast<uint32_t>(view.capacity) - pos0);
+        const uint32_t sbytes = min(static_cast<uint32_t>(kTile), capacity - pos0) * (NBLK * 2);
         const uint32_t bar = bars + stage * 8;
-        mbar_expect_tx(bar, 2 * L::kKTile + 2 * rows * NBLK * 2);
-        tma_load_2d(smem_u32(k_ring + stage * L::kKTile), kmap, 0, static_cast<int>(head_row0 + pos0), bar);
-        tma_load_2d(smem_u32(v_ring + stage * L::kKTile), vmap, 0, static_cast<int>(head_row0 + pos0), bar);
-        uint8_t* sdst = s_ring + stage * 2 * L::kSTile;
-        bulk_load(smem_u32(sdst), ks_plane + static_cast<size_t>(pos0) * NBLK * 2, rows * NBLK * 2, bar);
-        bulk_load(smem_u32(sdst + L::kSTile), vs_plane + static_cast<size_t>(pos0) * NBLK * 2, rows * NBLK * 2, bar);
+        mbar_expect_tx(bar, 2 * L::kKTile + 2 * sbytes);
+        tma_load_2d(k_ring_u + stage * L::kKTile, kmap, 0, row_base + static_cast<int>(pos0), bar);
+        tma_load_2d(v_ring_u + stage * L::kKTile, vmap, 0, row_base + static_cast<int>(pos0), bar);
+        const uint32_t sdst = s_ring_u + stage * 2 * L::kSTile;
+        bulk_load(sdst, ks_plane + pos0 * (NBLK * 2), sbytes, bar);
+        bulk_load(sdst + L::kSTile, vs_plane + pos0 * (NBLK * 2), sbytes, bar);
     };
     // old cache rows do not depend on the preceding kernels: start streaming them before waiting for those
     int issued = 0;
     if (lane == 0)
-        while (issued < kStages && issued < ntiles && (t0 + issued + 1) * kTile <= early_end) issue(issued++);
+        while (issued < kStages && issued < ntiles && (t0 + issued + 1) * kTile <= early_end) { issue(issued, issued); ++issued; }
     pdl_wait();
-    if (owner) {
-        // the new row goes to the cache first; its tile is loaded (by TMA, an asynchronous-proxy read) only afterwards
-        fused_append_row<NBLK>(p, view, kv_head, end - 1, head_row0 + end - 1, lane);
-        __threadfence();
-        asm volatile("fence.proxy.async;" ::: "memory");
-        __syncwarp();
+    {
+        // the tile that holds the row of a fused append is loaded only after that row has been stored (below)
+        const int limit = owner ? ntiles - 1 : ntiles;
+        if (lane == 0)
+            while (issued < kStages && issued < limit) { issue(issued, issued); ++issued; }
     }
-    if (lane == 0)
-        while (issued < kStages && issued < ntiles) issue(issued++);
 
     // ---- quantise Q to 15 bits (two int8 planes), one warp per head; heads the group does not have are zero ----
     if (warp < 4) {
@@ -301,6 +307,17 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
         reinterpret_cast<uint32_t*>(q_lo + warp * kD)[lane] = lo4;
     }
     __syncthreads();
+
+    if (owner) {
+        // After the barrier, so that only this warp (which was handed fewer tiles) pays for the append.  The new row
+        // goes to the cache first; its tile is loaded (by TMA, an asynchronous-proxy read) only afterwards.
+        fused_append_row<NBLK>(p, view, kv_head, end - 1, head_row0 + end - 1, lane);
+        __threadfence();
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __syncwarp();
+        if (lane == 0)
+            while (issued < kStages && issued < ntiles) { issue(issued, issued); ++issued; }
+    }
 
     // A operand of Q.K^T, per k-step (= one 32-dim block): rows g and g+8 are the hi and lo planes of head g & 3
     uint32_t qa[4][4];
@@ -342,9 +359,10 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
             v_off[pi][blk] = pos * kD + ((static_cast<uint32_t>(2 * blk + (g >> 2)) ^ (pos & 7)) << 4) + 4 * (g & 3);
     }
 
+    int stage = 0;
+    uint32_t phase = 0;
     for (int i = 0; i < ntiles; ++i) {
-        const int stage = i % kStages;
-        if (!mbar_wait(bars + stage * 8, (i / kStages) & 1)) { failed = true; break; }
+        if (!mbar_wait(bars + stage * 8, phase)) { failed = true; break; }
         const uint32_t pos0 = (t0 + i) * kTile;
         const int lo = begin > pos0 ? static_cast<int>(begin - pos0) : 0;
         const int hi = end - pos0 < static_cast<uint32_t>(kTile) ? static_cast<int>(end - pos0) : kTile;
@@ -376,8 +394,8 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
                 float sa = 0.0f, sb = 0.0f;
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    int c[4] = {0, 0, 0, 0};
-                    mma_s8(c, qa[ks], kb[2 * ks], kb[2 * ks + 1]);
+                    int c[4];
+                    mma_s8_zero(c, qa[ks], kb[2 * ks], kb[2 * ks + 1]);
                     sa = fmaf(static_cast<float>((c[0] << 7) + c[2]), ksa[ks], sa);
                     sb = fmaf(static_cast<float>((c[1] << 7) + c[3]), ksb[ks], sb);
                 }
@@ -385,17 +403,25 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
             } else {
                 const __half2 raw = *reinterpret_cast<const __half2*>(kst + (8 * j + 2 * t) * 2);
                 const float2 sc = __half22float2(raw);
-                int c[4] = {0, 0, 0, 0};
+                int c[4];
+                mma_s8_zero(c, qa[0], kb[0], kb[1]);
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) mma_s8(c, qa[ks], kb[2 * ks], kb[2 * ks + 1]);
+                for (int ks = 1; ks < 4; ++ks) mma_s8(c, qa[ks], kb[2 * ks], kb[2 * ks + 1]);
                 s[j][0] = static_cast<float>((c[0] << 7) + c[2]) * sc.x;
                 s[j][1] = static_cast<float>((c[1] << 7) + c[3]) * sc.y;
             }
+            s[j][0] *= qmul;
+            s[j][1] *= qmul;
+        }
+        const bool partial = lo > 0 || hi < kTile;   // only the first and the last tile of a range
+        if (partial) {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int pos = 8 * j + 2 * t + e;
-                s[j][e] = (pos >= lo && pos < hi) ? s[j][e] * qmul : -INFINITY;
-            }
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int pos = 8 * j + 2 * t + e;
+                    if (pos < lo || pos >= hi) s[j][e] = -INFINITY;
+                }
         }
 
         // ---- online softmax, base 2, lazily updated reference maximum ----------------------------
@@ -440,12 +466,17 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
                 const float2 sc = __half22float2(*reinterpret_cast<const __half2*>(vst + (8 * j + 2 * t) * 2));
                 vs[0][0] = sc.x; vs[1][0] = sc.y;
             }
-            // masked positions have weight exactly 0; their scales may be stale inf/nan
-            const bool v0 = w[j][0] > 0.0f, v1 = w[j][1] > 0.0f;
+            if (partial) {   // masked positions have weight exactly 0, but their scales may be stale inf/nan
+#pragma unroll
+                for (int blk = 0; blk < NBLK; ++blk) {
+                    if (!(w[j][0] > 0.0f)) vs[0][blk] = 0.0f;
+                    if (!(w[j][1] > 0.0f)) vs[1][blk] = 0.0f;
+                }
+            }
 #pragma unroll
             for (int blk = 0; blk < NBLK; ++blk) {
-                const float e0 = v0 ? w[j][0] * vs[0][blk] : 0.0f;
-                const float e1 = v1 ? w[j][1] * vs[1][blk] : 0.0f;
+                const float e0 = w[j][0] * vs[0][blk];
+                const float e1 = w[j][1] * vs[1][blk];
                 const __half2 h2 = __floats2half2_rn(e0, e1);
                 const float2 back = __half22float2(h2);
                 const uint32_t rem = pack_half2(e0 - back.x, e1 - back.y);
@@ -467,7 +498,8 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
         }
 
         __syncwarp();   // every lane is done with this stage
-        if (lane == 0 && i + kStages < ntiles) issue(i + kStages);
+        if (lane == 0 && i + kStages < ntiles) issue(i + kStages, stage);
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
     }
 
     // ---- the warp's result into its merge area: acc[8 columns][128 dims], m[4], l[4] ----------------------

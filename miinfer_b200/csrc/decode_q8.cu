@@ -108,6 +108,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -132,14 +136,18 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1,
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Byte `B` of two int8 words (two consecutive positions of one dim) as an exact half2: the bytes land in the
-// mantissas of 0x64xx (= 1024 + u) with their sign bits flipped (u = x + 128), and 1152 is subtracted.
-template <int B>
-__device__ __forceinline__ uint32_t s8_pair_to_half2(uint32_t first, uint32_t second) {
-    constexpr uint32_t sel = B | (B << 4) | ((4 + B) << 8) | ((4 + B) << 12);
-    uint32_t r = __byte_perm(first, second, sel);
-    r = (r & 0x00FF00FFu) ^ 0x64806480u;
+// A transposed 8x8 load of 16-bit elements hands each lane the word [p0.d0, p0.d1, p1.d0, p1.d1]: two
+// consecutive positions p0, p1 of two consecutive dims d0, d1.  These return the two positions of d0 (bytes 0, 2)
+// and of d1 (bytes 1, 3) as exact half2 integers: each byte lands in the mantissa of 0x64xx (= 1024 + u) with its
+// sign bit flipped (u = x + 128), and 1152 is subtracted.
+__device__ __forceinline__ uint32_t s8_even_bytes_to_half2(uint32_t w) {
+    const uint32_t r = (w & 0x00FF00FFu) ^ 0x64806480u;
     const __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&r), __half2half2(__ushort_as_half(0x6480)));   // 0x6480 = 1152
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t s8_odd_bytes_to_half2(uint32_t w) {
+    const uint32_t r = __byte_perm(w, 0x64646464u, 0x4341) ^ 0x00800080u;
+    const __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&r), __half2half2(__ushort_as_half(0x6480)));
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
@@ -334,7 +342,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     const float qmul = qmul_s[g & 3];
     const bool remainder_lane = g >= 4;   // this lane feeds a remainder column of the weight operand
 
-    // P.V accumulators: M-tile mt holds dims 32*(mt>>1) + 4*row + 2*(mt&1) {+0: rows 0-7, +1: rows 8-15};
+    // P.V accumulators: M-tile mt holds dims 16*mt + 2*row {+0: rows 0-7, +1: rows 8-15}, all in block mt >> 1;
     // columns 2t, 2t+1 of this lane: high parts of heads 0..3 (t < 2) or remainders (t >= 2)
     float acc[8][4];
 #pragma unroll
@@ -349,14 +357,13 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     const uint32_t ldm_row = static_cast<uint32_t>(lane & 7) * kD;
     const uint32_t ldm_c0 = static_cast<uint32_t>(((lane >> 3)) ^ (lane & 7)) << 4;         // chunks 0..3
     const uint32_t ldm_c1 = static_cast<uint32_t>((4 + (lane >> 3)) ^ (lane & 7)) << 4;     // chunks 4..7
-    // V words: positions 2t, 2t+1, 2t+8, 2t+9; the 4 bytes at dims 32*blk + 4g.. live in chunk 2*blk + (g>>2)
-    uint32_t v_off[4][4];
+    // V: transposed ldmatrix x4 number c (c = 0..3) fetches the 8x16-byte matrices (rows 0-7, chunk 2c), (rows 8-15,
+    // chunk 2c), (rows 0-7, chunk 2c+1), (rows 8-15, chunk 2c+1); this lane supplies row (lane&7) of matrix (lane>>3)
+    uint32_t v_off[4];
 #pragma unroll
-    for (int pi = 0; pi < 4; ++pi) {
-        const uint32_t pos = 2 * t + (pi & 1) + 8 * (pi >> 1);
-#pragma unroll
-        for (int blk = 0; blk < 4; ++blk)
-            v_off[pi][blk] = pos * kD + ((static_cast<uint32_t>(2 * blk + (g >> 2)) ^ (pos & 7)) << 4) + 4 * (g & 3);
+    for (int c = 0; c < 4; ++c) {
+        const uint32_t mi = lane >> 3, r = lane & 7;
+        v_off[c] = (8 * (mi & 1) + r) * kD + ((static_cast<uint32_t>(2 * c + (mi >> 1)) ^ r) << 4);
     }
 
     int stage = 0;
@@ -367,7 +374,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
         const int lo = begin > pos0 ? static_cast<int>(begin - pos0) : 0;
         const int hi = end - pos0 < static_cast<uint32_t>(kTile) ? static_cast<int>(end - pos0) : kTile;
         const uint32_t kt = smem_u32(k_ring + stage * L::kKTile);
-        const uint8_t* vt = v_ring + stage * L::kKTile;
+        const uint32_t vt = v_ring_u + stage * L::kKTile;
         const uint8_t* kst = s_ring + stage * 2 * L::kSTile;
         const uint8_t* vst = kst + L::kSTile;
 
@@ -486,15 +493,14 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
 
         // ---- P.V: A = V^T of this tile, exact fp16 integers --------------------------------------
 #pragma unroll
-        for (int blk = 0; blk < 4; ++blk) {
+        for (int c = 0; c < 4; ++c) {
             uint32_t vw[4];
-#pragma unroll
-            for (int pi = 0; pi < 4; ++pi) vw[pi] = *reinterpret_cast<const uint32_t*>(vt + v_off[pi][blk]);
-            const uint32_t b0 = wb[NBLK == 4 ? blk : 0][0], b1 = wb[NBLK == 4 ? blk : 0][1];
-            mma_f16(acc[2 * blk], s8_pair_to_half2<0>(vw[0], vw[1]), s8_pair_to_half2<1>(vw[0], vw[1]),
-                    s8_pair_to_half2<0>(vw[2], vw[3]), s8_pair_to_half2<1>(vw[2], vw[3]), b0, b1);
-            mma_f16(acc[2 * blk + 1], s8_pair_to_half2<2>(vw[0], vw[1]), s8_pair_to_half2<3>(vw[0], vw[1]),
-                    s8_pair_to_half2<2>(vw[2], vw[3]), s8_pair_to_half2<3>(vw[2], vw[3]), b0, b1);
+            ldmatrix_x4_trans(vt + v_off[c], vw);
+            const uint32_t b0 = wb[NBLK == 4 ? c : 0][0], b1 = wb[NBLK == 4 ? c : 0][1];
+            mma_f16(acc[2 * c], s8_even_bytes_to_half2(vw[0]), s8_odd_bytes_to_half2(vw[0]),
+                    s8_even_bytes_to_half2(vw[1]), s8_odd_bytes_to_half2(vw[1]), b0, b1);
+            mma_f16(acc[2 * c + 1], s8_even_bytes_to_half2(vw[2]), s8_odd_bytes_to_half2(vw[2]),
+                    s8_even_bytes_to_half2(vw[3]), s8_odd_bytes_to_half2(vw[3]), b0, b1);
         }
 
         __syncwarp();   // every lane is done with this stage
@@ -510,7 +516,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     __syncwarp();
 #pragma unroll
     for (int mt = 0; mt < 8; ++mt) {
-        const int dim = 32 * (mt >> 1) + 4 * g + 2 * (mt & 1);
+        const int dim = 16 * mt + 2 * g;
         *reinterpret_cast<float2*>(mine + (2 * t) * kD + dim) = make_float2(acc[mt][0], acc[mt][2]);
         *reinterpret_cast<float2*>(mine + (2 * t + 1) * kD + dim) = make_float2(acc[mt][1], acc[mt][3]);
     }

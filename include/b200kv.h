@@ -177,9 +177,12 @@ B200KV_API int b200kv_append(const b200kv_view* view, const void* key, const voi
  * `sessions` sessions.  The reference keeps these in file-scope __device__
  * arrays sized for 24 heads (.hip:2104-2113); here the caller owns them.
  * The workspace must be 16-byte aligned and ZERO-FILLED ONCE before its first
- * use (cudaMemset): its head holds the arrival counters of the fused merge,
- * which every launch leaves at zero again.  One workspace serves one launch at
- * a time (launches that overlap on the GPU need separate workspaces). */
+ * use (cudaMemset): its first two thirds hold the tagged partials of the fused
+ * merge (8-byte words {value, tag}; a zero tag means "not written yet"), which
+ * every launch leaves at zero again; the last third holds plain partials.  Pass
+ * the same workspace_bytes for a buffer on every call: the split between the
+ * two parts is derived from it.  One workspace serves one launch at a time
+ * (launches that overlap on the GPU need separate workspaces). */
 B200KV_API size_t b200kv_decode_workspace_bytes(uint32_t query_heads, uint32_t head_dim, uint32_t sessions);
 
 /* Replaces launch_qwen35_tiled_online_attention_quant_dynamic
@@ -214,16 +217,16 @@ B200KV_API int b200kv_decode_step(const b200kv_view* view, const void* key, cons
  * that gave all device memory to its own pool at start-up and forbids driver allocations afterwards, or a
  * sandbox in which allocation calls are not allowed -- and so cannot provide the split-K scratch of
  * b200kv_decode_attn.  Same arguments and results as b200kv_decode_attn, minus the workspace pair; the scratch
- * is a fixed 4 MiB array inside the library (b200kv_decode_static_scratch_bytes), present on every GPU
+ * is a fixed 8 MiB array inside the library (b200kv_decode_static_scratch_bytes), present on every GPU
  * that loads the library until the process exits.
  *   - Limit: b200kv_decode_workspace_bytes(query_heads, head_dim, 1) must not exceed that size (32 query heads
- *     at head_dim 128 and 24 at head_dim 256 fit); larger shapes return B200KV_ERR_WORKSPACE.
+ *     at head_dim 128 and 20 at head_dim 256 fit); larger shapes return B200KV_ERR_WORKSPACE.
  *   - The first call on each device looks up the array's device address (the device must be current); make
  *     that first call before starting any stream capture.
  *   - All calls on a device share the one array: two calls whose kernels overlap on the GPU (different
  *     streams, or launch overlap between them) race on it.  Calls ordered on one stream are safe.
  *   - It calls no cudaMalloc, cudaFree or allocating library routine; it issues one cudaMemsetAsync on
- *     `stream` to clear the arrival counters and then the same kernels as b200kv_decode_attn. */
+ *     `stream` to clear the tagged partials and then the same kernels as b200kv_decode_attn. */
 B200KV_API size_t b200kv_decode_static_scratch_bytes(void);
 B200KV_API int b200kv_decode_attn_static(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
                               float* output, float* gated_output, uint32_t query_heads, float scale,

@@ -197,14 +197,8 @@ static void launch_generic(const DecodeParams& p, uint32_t mode, dim3 grid, cuda
     }
 }
 
-size_t decode_counter_bytes(uint32_t query_heads, uint32_t sessions) {
-    // one uint32 per (session, kv head); kv_heads <= query_heads.  Rounded so the partials stay 256-byte aligned.
-    const size_t raw = static_cast<size_t>(sessions ? sessions : 1) * query_heads * sizeof(uint32_t);
-    return (raw + 255) / 256 * 256;
-}
-
 // Runs stage 1 (streaming kernel if available, else generic) into the workspace.
-// Workspace layout: [counters (zero between launches)] [m] [l] [acc].
+// Workspace layout: [tagged partials of the streaming kernel (zero between launches)] [m] [l] [acc].
 int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, void* workspace,
                       size_t workspace_bytes, uint32_t num_splits_arg, const MergeParams& merge, bool* merged,
                       cudaStream_t stream) {
@@ -219,22 +213,24 @@ int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max
         num_splits = use_fast ? fast : pick_splits_generic(p.query_heads, p.sessions, max_length);
     }
     if (num_splits > cap) num_splits = cap;
-    const size_t counter_bytes = decode_counter_bytes(p.query_heads, p.sessions);
     const size_t slots = static_cast<size_t>(p.sessions) * num_splits * p.query_heads;
-    const size_t need = counter_bytes + slots * (geometry.head_dim + 2u) * sizeof(float);
-    if (workspace == nullptr || workspace_bytes < need) return B200KV_ERR_WORKSPACE;
+    const size_t plain_bytes = slots * (geometry.head_dim + 2u) * sizeof(float);
+    if (workspace == nullptr) return B200KV_ERR_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return B200KV_ERR_INVALID;
+    const size_t plain_offset = workspace_plain_offset(workspace_bytes);
+    if (workspace_bytes - plain_offset < plain_bytes) return B200KV_ERR_WORKSPACE;
     p.num_splits = num_splits;
-    p.ws_m = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + counter_bytes);
+    p.ws_m = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + plain_offset);
     p.ws_l = p.ws_m + slots;
     p.ws_acc = p.ws_l + slots;
     if (use_fast) {
-        p.counters = static_cast<uint32_t*>(workspace);
+        if (plain_offset < 2 * plain_bytes) return B200KV_ERR_WORKSPACE;
+        p.ws_tagged = static_cast<uint64_t*>(workspace);
         p.fuse = merge;
         int rc = launch_decode_q8(p, geometry, max_length, stream);
         if (rc == B200KV_OK) *merged = true;
         if (rc != B200KV_ERR_UNSUPPORTED) return rc;
-        p.counters = nullptr;
+        p.ws_tagged = nullptr;
     }
     dim3 grid(p.query_heads, num_splits, p.sessions);
     if (geometry.head_dim == 128) launch_generic<128>(p, geometry.quant_mode, grid, stream);
@@ -278,7 +274,8 @@ size_t b200kv_view_table_bytes(uint32_t sessions) { return sizeof(SessionEntry) 
 size_t b200kv_decode_workspace_bytes(uint32_t query_heads, uint32_t head_dim, uint32_t sessions) {
     if (sessions == 0) sessions = 1;
     const size_t slots = static_cast<size_t>(sessions) * max_splits_per_session(sessions) * query_heads;
-    return decode_counter_bytes(query_heads, sessions) + slots * (head_dim + 2u) * sizeof(float);
+    // plain partials behind, twice that for the tagged partials of the streaming kernel in front
+    return (slots * (head_dim + 2u) * sizeof(float) + 255) / 256 * 256 * 3;
 }
 
 int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_dtype, const float* gate,

@@ -64,9 +64,9 @@ struct DecodeParams {
     float* ws_m;                             // [sessions][num_splits][query_heads]
     float* ws_l;
     float* ws_acc;                           // [sessions][num_splits][query_heads][d]
-    // Fused merge (streaming kernel only): when `counters` is non-null the last CTA of each
-    // (session, kv head) combines all splits and writes `fuse`'s outputs; the counters must be
-    // zero on entry and are zero again on exit.
+    // Fused merge (streaming kernel only): when `ws_tagged` is non-null the partials go out as tagged 8-byte words
+    // ([sessions][num_splits][query_heads][head_dim + 2]) and designated CTAs combine all splits and write `fuse`'s
+    // outputs; the words must be zero on entry and are zero again on exit.
     // Fused single-token append (streaming kernel, one session): the warp that owns the last tile quantises the new
     // token's K/V row of its kv head and stores it at position end-1 before it loads that tile.
     const void* new_key;                     // [kv_heads*d] of new_is_f16 ? fp16 : fp32, or null = no fused append
@@ -78,7 +78,7 @@ struct DecodeParams {
     float sectioned_step;
     float inv_freq[64];                      // NeoX frequencies for d = 128
     uint32_t overlap_tail;                   // launch overlap: the last n positions of the range are read only after pdl_wait
-    uint32_t* counters;                      // [sessions][kv_heads]
+    uint64_t* ws_tagged;
     MergeParams fuse;
 };
 
@@ -117,7 +117,10 @@ int launch_merge(const MergeParams& p, uint32_t groups, cudaStream_t stream);
 int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, void* workspace,
                       size_t workspace_bytes, uint32_t num_splits_arg, const MergeParams& merge, bool* merged,
                       cudaStream_t stream);
-size_t decode_counter_bytes(uint32_t query_heads, uint32_t sessions);
+// Split of a caller's workspace of `bytes` bytes: tagged partials in front (two thirds, zero between launches),
+// plain [m][l][acc] partials behind.  The split depends only on the size, so launches of different shapes that
+// share one workspace never write plain floats where tagged words are expected.
+inline size_t workspace_plain_offset(size_t bytes) { return bytes / 3 * 2 / 256 * 256; }
 int run_decode(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, void* workspace, size_t workspace_bytes,
                uint32_t num_splits_arg, MergeParams mp, uint32_t groups, cudaStream_t stream);
 

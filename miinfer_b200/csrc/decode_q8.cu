@@ -62,7 +62,7 @@ constexpr int kStages = 3;    // TMA ring depth per warp
 constexpr int kD = 128;
 constexpr uint32_t kSpinLimit = 1u << 20;   // bounded waits: a lost copy ends the kernel with a poisoned partial
 constexpr uint32_t kPositionsPerSplit = 2048;   // batched launches: one split per this many positions of a session
-constexpr int kAppendUnits = 2;    // a fused append is balanced as this many tiles of work
+constexpr int kAppendUnits = 4;    // a fused append is balanced as this many tiles of work
 constexpr float kRescaleSlack = 6.0f;   // log2 units a head's maximum may exceed the reference before a rescale
 
 template <int NBLK>
@@ -73,8 +73,8 @@ struct Smem {
     static constexpr int kOffS = 2 * kOffV;                              // [warp][stage][ks | vs]
     static constexpr int kOffQ = kOffS + kWarps * kStages * 2 * kSTile;  // int8 hi[4][kD], lo[4][kD]
     static constexpr int kOffQmul = kOffQ + 2 * 4 * kD;                  // [4] float
-    static constexpr int kOffMisc = kOffQmul + 16;                       // last-CTA merge scratch: m/l [4][128] floats, totals
-    static constexpr int kOffBar = kOffMisc + (2 * 4 * 128 + 8) * 4;
+    static constexpr int kOffMisc = kOffQmul + 16;                       // merger scratch: m/l [128] floats, totals, fold area
+    static constexpr int kOffBar = kOffMisc + (2 * 128 + 8 + 3 * 64 * 2) * 4;
     static constexpr int kTotal = kOffBar + kWarps * kStages * 8;
     static constexpr int kAlloc = kTotal + 1024;                         // slack to align the base to 1024
     static constexpr int kWarpArea = kStages * kKTile;                   // a warp's K ring doubles as its merge area
@@ -150,6 +150,20 @@ __device__ __forceinline__ uint32_t s8_odd_bytes_to_half2(uint32_t w) {
     const __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&r), __half2half2(__ushort_as_half(0x6480)));
     return *reinterpret_cast<const uint32_t*>(&h);
 }
+// Tagged partials: every float of a split's partial travels as one 8-byte word {value, tag = 1}.  An 8-byte store is
+// indivisible, so a reader that sees the tag also sees the value: no fence and no counter stand between the CTA that
+// produced a partial and the CTA that merges it.  Words are zero between launches; the merger zeroes what it consumed.
+__device__ __forceinline__ void st_tagged(uint64_t* dst, float v) {
+    const uint64_t w = (1ull << 32) | __float_as_uint(v);
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
+}
+__device__ __forceinline__ void ld_tagged2(const uint64_t* src, uint64_t& a, uint64_t& b) {
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(src) : "memory");
+}
+__device__ __forceinline__ bool tagged_ready(uint64_t a, uint64_t b) { return (a >> 32) != 0 && (b >> 32) != 0; }
+constexpr uint32_t kPollLimit = 1u << 17;   // polls of the merger (each a trip to L2) before it gives up and poisons the output
+constexpr int kPartialWords = kD + 2;       // acc[128], m, l
+
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
@@ -166,13 +180,11 @@ __device__ __noinline__ void load_new_row(const void* src, int is_f16, uint32_t 
     }
 }
 
-// Quantises the new K and V rows of `kv_head` and stores them (int8 + fp16 block scales) at cache row `row_index`.
+// Quantises the new K and V rows of `kv_head` (already in registers) and stores them (int8 + fp16 block scales) at
+// cache row `row_index`.
 template <int NBLK>
-__device__ __noinline__ void fused_append_row(const DecodeParams& p, const b200kv_view& view, uint32_t kv_head, uint32_t position,
-                                              uint64_t row_index, int lane) {
-    float k[4], v[4];
-    load_new_row(p.new_key, p.new_is_f16, kv_head, lane, k);
-    load_new_row(p.new_value, p.new_is_f16, kv_head, lane, v);
+__device__ __noinline__ void fused_append_row(const DecodeParams& p, const b200kv_view& view, float (&k)[4], float (&v)[4],
+                                              uint32_t position, uint64_t row_index, int lane) {
     transform_k_row<kD>(k, lane, position, p.k_norm_weight, p.epsilon, p.rope_mode, p.inv_freq, p.sectioned_step);
     int8_t kq[4], vq[4];
     float ksc[4], vsc[4];
@@ -197,7 +209,6 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     using L = Smem<NBLK>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1024-aligned, still a shared-space pointer
-    __shared__ int s_last;
 
     pdl_launch_dependents();   // the next kernel of the stream may become resident as SMs free up; it orders itself
 
@@ -274,6 +285,13 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     if (lane == 0)
         while (issued < kStages && issued < ntiles && (t0 + issued + 1) * kTile <= early_end) { issue(issued, issued); ++issued; }
     pdl_wait();
+    // The new row of a fused append is fetched now, while the memory system is still quiet: once every warp's ring
+    // is streaming, a dependent load waits behind tens of megabytes of queued tile traffic (microseconds).
+    float new_k[4], new_v[4];
+    if (owner) {
+        load_new_row(p.new_key, p.new_is_f16, kv_head, lane, new_k);
+        load_new_row(p.new_value, p.new_is_f16, kv_head, lane, new_v);
+    }
     {
         // the tile that holds the row of a fused append is loaded only after that row has been stored (below)
         const int limit = owner ? ntiles - 1 : ntiles;
@@ -319,7 +337,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     if (owner) {
         // After the barrier, so that only this warp (which was handed fewer tiles) pays for the append.  The new row
         // goes to the cache first; its tile is loaded (by TMA, an asynchronous-proxy read) only afterwards.
-        fused_append_row<NBLK>(p, view, kv_head, end - 1, head_row0 + end - 1, lane);
+        fused_append_row<NBLK>(p, view, new_k, new_v, end - 1, head_row0 + end - 1, lane);
         __threadfence();
         asm volatile("fence.proxy.async;" ::: "memory");
         __syncwarp();
@@ -525,6 +543,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
 
     // ---- merge the CTA's warps: 256 threads = 2 head slots x 128 dims ---------------------------------------
     const int dim = threadIdx.x & (kD - 1);
+    const bool tagged = p.ws_tagged != nullptr;   // fused merge: partials go out as tagged words
     for (int h = threadIdx.x >> 7; h < G; h += 2) {
         float mw[kWarps], M = -INFINITY;
 #pragma unroll
@@ -543,123 +562,124 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
         }
         const uint32_t head = kv_head * G + h;
         const size_t slot_idx = (static_cast<size_t>(session) * p.num_splits + split) * p.query_heads + head;
-        p.ws_acc[slot_idx * kD + dim] = at;
-        if (dim == 0) {
-            p.ws_m[slot_idx] = M * 0.6931471805599453f;   // natural-log units, as the merge kernel expects
-            p.ws_l[slot_idx] = lt;
+        const float m_nat = M * 0.6931471805599453f;   // natural-log units, as the merge expects
+        if (tagged) {
+            uint64_t* dst = p.ws_tagged + slot_idx * kPartialWords;
+            st_tagged(dst + dim, at);
+            if (dim == 0) { st_tagged(dst + kD, m_nat); st_tagged(dst + kD + 1, lt); }
+        } else {
+            p.ws_acc[slot_idx * kD + dim] = at;
+            if (dim == 0) { p.ws_m[slot_idx] = m_nat; p.ws_l[slot_idx] = lt; }
         }
     }
-    if (p.counters == nullptr) return;   // a separate merge kernel follows
+    if (!tagged) return;   // a separate merge kernel follows
 
-    // ---- the last CTA of this (session, kv head) to finish merges all splits -------------------------------------
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const uint32_t prev = atomicAdd(p.counters + session * gridDim.y + kv_head, 1u);
-        s_last = (prev + 1 == num_splits);
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
+    // ---- fused merge: the CTA of split h merges query head h of this kv head (h, h + splits, ... if there are fewer
+    // splits than heads).  It polls the tagged partials of all splits -- normally they are all there by the time it
+    // has finished its own share -- and every other CTA simply leaves.
+    if (split >= static_cast<uint32_t>(G)) return;
     const uint32_t S = num_splits;     // <= kMaxSplitsPerSession == 128; the partial arrays keep the launch-wide stride
-    float* sm = reinterpret_cast<float*>(smem + L::kOffMisc);   // [4][128] m -> a
-    float* sl = sm + 4 * 128;                                   // [4][128] l
-    float* sg = sl + 4 * 128;                                   // [4] merged max, [4] merged sum
-    // 256 threads = 4 heads x 2 halves of the splits x 32 float4 columns.  The first batch of accumulator loads is
-    // issued together with the loads of (m, l), so the common case (at most 2 x kBatch splits) pays one trip to L2.
-    constexpr int kBatch = 19;
-    const int col = threadIdx.x & 31, part = (threadIdx.x >> 5) & 1, hh = threadIdx.x >> 6;
-    const size_t stride = static_cast<size_t>(p.query_heads) * kD;
-    const float* accp = p.ws_acc + ((static_cast<size_t>(session) * p.num_splits) * p.query_heads + kv_head * G + (hh < G ? hh : 0)) * kD + col * 4;
-    float4 v[kBatch];
+    float* sm = reinterpret_cast<float*>(smem + L::kOffMisc);   // [128] m -> rescale factor
+    float* sl = sm + 128;                                       // [128] l
+    float* sg = sl + 128;                                       // merged max, merged sum
+    float2* fold = reinterpret_cast<float2*>(sg + 8);           // [3][64] partial sums of split groups 1..3
+    constexpr int kBatch = 10;   // splits per thread and round: 4 groups x 10 = 40 splits in one trip to L2
+    const int grp = threadIdx.x >> 6, pr = threadIdx.x & 63;    // split group (sp % 4), pair of dims
+    for (uint32_t h = split; h < static_cast<uint32_t>(G); h += S) {
+        const uint32_t head = kv_head * G + h;
+        const size_t stride = static_cast<size_t>(p.query_heads) * kPartialWords;   // words between consecutive splits
+        uint64_t* base = p.ws_tagged + ((static_cast<size_t>(session) * p.num_splits) * p.query_heads + head) * kPartialWords;
+        bool lost = false;
+        float2 tot = make_float2(0.0f, 0.0f);
+        for (uint32_t sp0 = 0; sp0 < S; sp0 += 4 * kBatch) {
+            // Poll in rounds: every round re-issues, back to back, the loads of all words of this thread that have
+            // not shown their tag yet, so that once the last partial has landed one trip to L2 completes the set.
+            uint64_t va[kBatch], vb[kBatch], ma = 0, mb = 0;
+            uint32_t pending = 0;
 #pragma unroll
-    for (int u = 0; u < kBatch; ++u) {
-        const uint32_t sp = part + 2 * u;
-        v[u] = (hh < G && sp < S) ? __ldcg(reinterpret_cast<const float4*>(accp + sp * stride)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    }
-    for (uint32_t idx = threadIdx.x; idx < G * S; idx += blockDim.x) {
-        const uint32_t h = idx / S, sp = idx % S;
-        const size_t slot_idx = (static_cast<size_t>(session) * p.num_splits + sp) * p.query_heads + kv_head * G + h;
-        sm[h * 128 + sp] = __ldcg(p.ws_m + slot_idx);
-        sl[h * 128 + sp] = __ldcg(p.ws_l + slot_idx);
-    }
-    __syncthreads();
-    if (warp < G) {   // one warp per head: global max, rescale factors, merged sum
-        const int h = warp;
-        float M = -INFINITY;
-        for (uint32_t sp = lane; sp < S; sp += 32) {
-            const float m = sm[h * 128 + sp], l = sl[h * 128 + sp];
-            if (!(l <= 0.0f) && m != -INFINITY) M = fmaxf(M, m);   // keeps NaN partials in play
-        }
-        M = warp_max(M);
-        float lsum = 0.0f;
-        for (uint32_t sp = lane; sp < S; sp += 32) {
-            const float m = sm[h * 128 + sp], l = sl[h * 128 + sp];
-            const float a = (!(l <= 0.0f) && m != -INFINITY) ? __expf(m - M) : 0.0f;
-            sm[h * 128 + sp] = a;
-            lsum = fmaf(l, a, lsum);
-        }
-        lsum = warp_sum(lsum);
-        if (lane == 0) { sg[h] = M; sg[4 + h] = lsum; }
-    }
-    __syncthreads();
-    {
-        float4 tot = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (hh < G) {
+            for (int u = 0; u < kBatch; ++u)
+                if (sp0 + grp + 4 * u < S) pending |= 1u << u;
+            const bool polls_ml = sp0 == 0 && threadIdx.x < S;   // (m, l) of split threadIdx.x
+            bool ml_pending = polls_ml;
+            uint64_t* ml_src = base + threadIdx.x * stride + kD;
+            for (uint32_t polls = 0; (pending != 0 || ml_pending) && !lost; ++polls) {
+                if (polls >= kPollLimit) { lost = true; break; }
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u)
+                    if (pending & (1u << u)) ld_tagged2(base + (sp0 + grp + 4 * u) * stride + 2 * pr, va[u], vb[u]);
+                if (ml_pending) ld_tagged2(ml_src, ma, mb);
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u)
+                    if ((pending & (1u << u)) && tagged_ready(va[u], vb[u])) pending &= ~(1u << u);
+                if (ml_pending && tagged_ready(ma, mb)) ml_pending = false;
+            }
+            if (sp0 == 0) {
+                if (polls_ml) {
+                    sm[threadIdx.x] = lost ? __int_as_float(0x7fc00000) : __uint_as_float(static_cast<uint32_t>(ma));
+                    sl[threadIdx.x] = lost ? __int_as_float(0x7fc00000) : __uint_as_float(static_cast<uint32_t>(mb));
+                    asm volatile("st.global.v2.u64 [%0], {%1,%1};" ::"l"(ml_src), "l"(0ull) : "memory");   // consumed
+                }
+                __syncthreads();
+                if (warp == 0) {   // global max, rescale factors, merged sum
+                    float M = -INFINITY;
+                    for (uint32_t sp = lane; sp < S; sp += 32) {
+                        const float m = sm[sp], l = sl[sp];
+                        if (!(l <= 0.0f) && m != -INFINITY) M = fmaxf(M, m);   // keeps NaN partials in play
+                    }
+                    M = warp_max(M);
+                    float lsum = 0.0f;
+                    for (uint32_t sp = lane; sp < S; sp += 32) {
+                        const float m = sm[sp], l = sl[sp];
+                        const float a = (!(l <= 0.0f) && m != -INFINITY) ? __expf(m - M) : 0.0f;
+                        sm[sp] = a;
+                        lsum = fmaf(l, a, lsum);
+                    }
+                    lsum = warp_sum(lsum);
+                    if (lane == 0) { sg[0] = M; sg[1] = lsum; }
+                }
+                __syncthreads();
+            }
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
-                const uint32_t sp = part + 2 * u;
-                const float a = sp < S ? sm[hh * 128 + sp] : 0.0f;
-                tot.x = fmaf(v[u].x, a, tot.x); tot.y = fmaf(v[u].y, a, tot.y);
-                tot.z = fmaf(v[u].z, a, tot.z); tot.w = fmaf(v[u].w, a, tot.w);
-            }
-            for (uint32_t sp0 = part + 2 * kBatch; sp0 < S; sp0 += 2 * kBatch) {   // more splits than one batch covers
-#pragma unroll
-                for (int u = 0; u < kBatch; ++u) {
-                    const uint32_t sp = sp0 + 2 * u;
-                    v[u] = sp < S ? __ldcg(reinterpret_cast<const float4*>(accp + sp * stride)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                }
-#pragma unroll
-                for (int u = 0; u < kBatch; ++u) {
-                    const uint32_t sp = sp0 + 2 * u;
-                    const float a = sp < S ? sm[hh * 128 + sp] : 0.0f;
-                    tot.x = fmaf(v[u].x, a, tot.x); tot.y = fmaf(v[u].y, a, tot.y);
-                    tot.z = fmaf(v[u].z, a, tot.z); tot.w = fmaf(v[u].w, a, tot.w);
+                const uint32_t sp = sp0 + grp + 4 * u;
+                if (sp < S && !(pending & (1u << u))) {
+                    const float a = sm[sp];
+                    tot.x = fmaf(__uint_as_float(static_cast<uint32_t>(va[u])), a, tot.x);
+                    tot.y = fmaf(__uint_as_float(static_cast<uint32_t>(vb[u])), a, tot.y);
+                    asm volatile("st.global.v2.u64 [%0], {%1,%1};" ::"l"(base + sp * stride + 2 * pr), "l"(0ull) : "memory");   // consumed
                 }
             }
         }
-        // fold the two halves through shared memory (the warps' merge areas are free by now)
-        float4* fold = reinterpret_cast<float4*>(smem);
-        if (part == 1) fold[hh * 32 + col] = tot;
+        if (lost) tot.x = tot.y = __int_as_float(0x7fc00000);
+        // fold the 4 split groups through shared memory
+        if (grp > 0) fold[(grp - 1) * 64 + pr] = tot;
         __syncthreads();
-        if (part == 0 && hh < G) {
-            const float4 o2 = fold[hh * 32 + col];
-            tot.x += o2.x; tot.y += o2.y; tot.z += o2.z; tot.w += o2.w;
-            const uint32_t head = kv_head * G + hh;
-            const float gsum = sg[4 + hh];
-            const size_t out_idx = (static_cast<size_t>(session) * p.query_heads + head) * kD + col * 4;
+        if (grp == 0) {
+#pragma unroll
+            for (int k = 0; k < 3; ++k) { const float2 o2 = fold[k * 64 + pr]; tot.x += o2.x; tot.y += o2.y; }
+            const float gsum = sg[1];
+            const size_t out_idx = (static_cast<size_t>(session) * p.query_heads + head) * kD + 2 * pr;
             if (p.fuse.out_m != nullptr) {   // sequence shard: one merged, unnormalised partial
-                *reinterpret_cast<float4*>(p.fuse.out_acc + out_idx) = tot;
-                if (col == 0) {
-                    p.fuse.out_m[static_cast<size_t>(session) * p.query_heads + head] = sg[hh];
+                *reinterpret_cast<float2*>(p.fuse.out_acc + out_idx) = tot;
+                if (pr == 0) {
+                    p.fuse.out_m[static_cast<size_t>(session) * p.query_heads + head] = sg[0];
                     p.fuse.out_l[static_cast<size_t>(session) * p.query_heads + head] = gsum;
                 }
             } else {
                 const float inv = gsum > 0.0f ? 1.0f / gsum : (gsum == gsum ? 0.0f : gsum);
-                float4 o = make_float4(tot.x * inv, tot.y * inv, tot.z * inv, tot.w * inv);
-                if (p.fuse.output != nullptr) *reinterpret_cast<float4*>(p.fuse.output + out_idx) = o;
+                float2 o = make_float2(tot.x * inv, tot.y * inv);
+                if (p.fuse.output != nullptr) *reinterpret_cast<float2*>(p.fuse.output + out_idx) = o;
                 if (p.fuse.gated_output != nullptr) {
                     if (p.fuse.gate != nullptr) {
-                        const float4 gt = *reinterpret_cast<const float4*>(p.fuse.gate + out_idx);
+                        const float2 gt = *reinterpret_cast<const float2*>(p.fuse.gate + out_idx);
                         o.x *= 1.0f / (1.0f + __expf(-gt.x)); o.y *= 1.0f / (1.0f + __expf(-gt.y));
-                        o.z *= 1.0f / (1.0f + __expf(-gt.z)); o.w *= 1.0f / (1.0f + __expf(-gt.w));
                     }
-                    *reinterpret_cast<float4*>(p.fuse.gated_output + out_idx) = o;
+                    *reinterpret_cast<float2*>(p.fuse.gated_output + out_idx) = o;
                 }
             }
         }
+        __syncthreads();   // sm / sg / fold are reused by the next head of this CTA
     }
-    if (threadIdx.x == 0) p.counters[session * gridDim.y + kv_head] = 0;   // leave the workspace ready for the next launch
 }
 
 // ---- host side -----------------------------------------------------------------------------------------

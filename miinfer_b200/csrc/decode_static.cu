@@ -13,9 +13,9 @@
 
 namespace {
 
-// 4 MiB per GPU, held from the moment the library is loaded until the process exits.  Enough for
-// 32 query heads at head_dim 128 (2.1 MB) or 24 heads at head_dim 256 (3.2 MB), one session.
-constexpr size_t kStaticScratchBytes = size_t{4} << 20;
+// 8 MiB per GPU, held from the moment the library is loaded until the process exits.  Enough for
+// 32 query heads at head_dim 128 (6.4 MB) or 20 heads at head_dim 256 (7.9 MB), one session.
+constexpr size_t kStaticScratchBytes = size_t{8} << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
@@ -71,9 +71,10 @@ int b200kv_decode_attn_static(const b200kv_view* view, const void* q, int q_dtyp
     if ((rc = scratch_for_current_device(&scratch)) != B200KV_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-    // Every call shares the array and it keeps what the previous call left.  Only the arrival counters at its
-    // head must start at zero (the partials behind them are fully rewritten before they are read).
-    B200KV_CUDA_TRY(cudaMemsetAsync(scratch, 0, decode_counter_bytes(query_heads, 1), s));
+    // Every call shares the array and it keeps what the previous call left.  The tagged words in its front part
+    // must be zero when a launch starts; launches leave them zero, and clearing them here as well keeps one
+    // failed launch from spoiling the next (the plain partials behind them are rewritten before they are read).
+    B200KV_CUDA_TRY(cudaMemsetAsync(scratch, 0, workspace_plain_offset(kStaticScratchBytes), s));
 
     DecodeParams p{};
     p.view = *view;

@@ -161,7 +161,7 @@ def make_prefill_state(base_position: int, token_count: int, kv_capacity: int = 
 
 def decode_workspace(query_heads: int, head_dim: int, sessions: int = 1, device=None) -> torch.Tensor:
     n = int(lib.b200kv_decode_workspace_bytes(query_heads, head_dim, sessions))
-    return torch.zeros(n, dtype=torch.uint8, device=device or "cuda")   # zero-filled once: arrival counters live at its head
+    return torch.zeros(n, dtype=torch.uint8, device=device or "cuda")   # zero-filled once: the tagged partials in its front part must start at zero
 
 
 def view_table(sessions: int, device=None) -> torch.Tensor:

@@ -46,7 +46,7 @@ def test_version_status_strings_and_host_helpers():
     assert lib.b200kv_cache_bytes(1, 1, 128, 32, 3) == 2 * 136
     assert lib.b200kv_cache_bytes(10, 4, 256, 256, 3) == 2 * 10 * 4 * 258
     assert lib.b200kv_cache_bytes(10, 4, 256, 256, 0) == 2 * 10 * 4 * 512
-    assert lib.b200kv_decode_workspace_bytes(32, 128, 1) == 256 + 128 * 32 * 130 * 4   # arrival counters + partials
+    assert lib.b200kv_decode_workspace_bytes(32, 128, 1) == 3 * 128 * 32 * 130 * 4   # plain partials + twice that for tagged partials
     import kvoracle as ko
 
     toks = [14990, 42, 31415, 2718]

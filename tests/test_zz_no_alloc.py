@@ -16,7 +16,7 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(cuda):
     from miinfer_b200 import kv
     from miinfer_b200._lib import lib
 
-    assert lib.b200kv_decode_static_scratch_bytes() == 4 << 20
+    assert lib.b200kv_decode_static_scratch_bytes() == 8 << 20
     g = torch.Generator(device="cuda")
     g.manual_seed(1234)
     H, Hq, d = 8, 32, 128

@@ -37,8 +37,8 @@ ROW = D + 2 * (D // QB)  # 136 bytes per head-row
 THETA = 1.0e6
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch at 32K context, from the ncu
-# capture summarised in profiles/decode_q8_kernel_32k_context.md (71.45 MB read + 1.28 MB written)
-NCU_TRAFFIC_BYTES_32K = 72_737_792
+# capture summarised in profiles/decode_q8_kernel_32k_context.md (71.61 MB read + 1.74 MB written)
+NCU_TRAFFIC_BYTES_32K = 73_352_704
 
 
 def measured_peak_gbs() -> tuple[float, str]:
@@ -310,7 +310,7 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
         "hbm_frac_whole_step": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES_32K, "peak_kind": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs, burst copy)",
-                     "kernel": "decode_q8_kernel (split-K stage 1 with the merge fused into its last CTA)", "us_per_launch": attn_us,
+                     "kernel": "decode_q8_kernel (split-K stage 1 on warp-level mma, merge fused in)", "us_per_launch": attn_us,
                      "algorithmic_bytes_per_launch": attn_bytes, "frac_of_nominal_8TBs": achieved / 8000.0},
         "e2e": {"value": world * 1000.0 / e2e_ms, "unit": "tokens/s",
                 "h2d_bytes_per_step": int(h_q.numel() * 2 + h_k.numel() * 2 + h_v.numel() * 2),

@@ -233,6 +233,33 @@ B200KV_API int b200kv_decode_attn_static(const b200kv_view* view, const void* q,
                               uint32_t cache_length, const b200kv_decode_state* decode_state,
                               uint32_t num_splits, void* stream);
 
+/* Sequence-sharded decode attention with the cross-GPU merge inside the kernel (no counterpart in the reference,
+ * which is single-GPU; BASELINE config 5).  One process per GPU; this rank attends positions
+ * [range_begin, range_end) of ITS OWN cache shard, stores its per-head partial (m, l, acc) as tagged 8-byte
+ * words into slot [phase][rank] of every rank's exchange buffer (plain peer stores over NVLink, no multicast),
+ * polls its own buffer until the `world` partials of a head are there (bounded: a rank that never shows up turns
+ * the output into NaN instead of hanging the GPU), merges them and zeroes the words again.  Every rank ends
+ * with the same output.  exchange[w]: rank w's buffer as mapped into this process (exchange[rank] = its own),
+ * each of b200kv_exchange_bytes() bytes.  All ranks must launch the same sequence of sharded calls; consecutive
+ * calls on one exchange must alternate phase (0, 1, 0, ...) because a fast rank may already be writing the next
+ * call's words while a slow one still reads this call's.  Streaming-kernel caches only (see
+ * b200kv_decode_kernel_kind); others return B200KV_ERR_UNSUPPORTED and use b200kv_decode_partials + an
+ * all-gather + b200kv_merge_partials_packed.  world <= 8. */
+B200KV_API size_t b200kv_exchange_bytes(uint32_t query_heads, uint32_t head_dim, uint32_t world);
+B200KV_API int b200kv_decode_attn_sharded(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
+                               float* output, float* gated_output, uint32_t query_heads, float scale,
+                               uint32_t range_begin, uint32_t range_end,
+                               void* const* exchange, uint32_t rank, uint32_t world, uint32_t phase,
+                               void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream);
+
+/* Set-up of the exchange buffers (these allocate and are not for the per-token path): create allocates `bytes`
+ * of zeroed device memory on the current device and returns a 64-byte handle that another process on the same
+ * node passes to open to map the buffer; close unmaps it, destroy frees it (after every peer has closed it). */
+B200KV_API int b200kv_exchange_create(size_t bytes, void** buffer, void* handle64);
+B200KV_API int b200kv_exchange_open(const void* handle64, void** peer_buffer);
+B200KV_API int b200kv_exchange_close(void* peer_buffer);
+B200KV_API int b200kv_exchange_destroy(void* buffer);
+
 /* Which stage-1 kernel b200kv_decode_attn picks for this view: 1 = the streaming
  * int8 kernel (int8 K and V, head_dim 128, 1/2/4 query heads per kv head,
  * capacity a multiple of 8), 0 = the generic kernel (every other mode and shape).

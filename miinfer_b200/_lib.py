@@ -51,6 +51,12 @@ SIGNATURES = {
     "b200kv_decode_kernel_kind": (i32, [VP, u32]),
     "b200kv_decode_attn_batched": (i32, [VP, vp, vp, u32, u32, vp, i32, vp, vp, vp, u32, fl, vp, sz, u32, vp]),
     "b200kv_decode_partials": (i32, [VP, vp, i32, u32, fl, u32, u32, vp, vp, vp, vp, sz, u32, vp]),
+    "b200kv_exchange_bytes": (sz, [u32, u32, u32]),
+    "b200kv_decode_attn_sharded": (i32, [VP, vp, i32, vp, vp, vp, u32, fl, u32, u32, C.POINTER(vp), u32, u32, u32, vp, sz, u32, vp]),
+    "b200kv_exchange_create": (i32, [sz, C.POINTER(vp), vp]),
+    "b200kv_exchange_open": (i32, [vp, C.POINTER(vp)]),
+    "b200kv_exchange_close": (i32, [vp]),
+    "b200kv_exchange_destroy": (i32, [vp]),
     "b200kv_merge_partials": (i32, [vp, vp, vp, u32, u32, u32, vp, vp, vp, vp]),
     "b200kv_merge_partials_packed": (i32, [vp, u32, u32, u32, vp, vp, vp, vp]),
     "b200kv_prefill_workspace_bytes": (sz, [u32, u32, u32]),

@@ -466,6 +466,54 @@ int b200kv_decode_partials(const b200kv_view* view, const void* q, int q_dtype, 
     return run_decode(p, *view, range_end - range_begin, workspace, workspace_bytes, num_splits, mp, 1, s);
 }
 
+size_t b200kv_exchange_bytes(uint32_t query_heads, uint32_t head_dim, uint32_t world) {
+    // [2 phases][world][query_heads][head_dim + 2] tagged 8-byte words
+    return static_cast<size_t>(2) * (world ? world : 1) * query_heads * (head_dim + 2u) * sizeof(uint64_t);
+}
+
+int b200kv_decode_attn_sharded(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
+                               float* output, float* gated_output, uint32_t query_heads, float scale,
+                               uint32_t range_begin, uint32_t range_end,
+                               void* const* exchange, uint32_t rank, uint32_t world, uint32_t phase,
+                               void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream) {
+    int rc = validate_view(view);
+    if (rc != B200KV_OK) return rc;
+    if (q == nullptr || (output == nullptr && gated_output == nullptr) || exchange == nullptr) return B200KV_ERR_INVALID;
+    if (q_dtype != B200KV_F16 && q_dtype != B200KV_F32) return B200KV_ERR_INVALID;
+    if ((rc = check_heads(view, query_heads, scale)) != B200KV_OK) return rc;
+    if (range_end > view->capacity || range_begin > range_end) return B200KV_ERR_RANGE;
+    if (world == 0 || world > static_cast<uint32_t>(kMaxExchangeRanks) || rank >= world || phase > 1) return B200KV_ERR_INVALID;
+    for (uint32_t w = 0; w < world; ++w)
+        if (exchange[w] == nullptr || (reinterpret_cast<uintptr_t>(exchange[w]) & 15u) != 0) return B200KV_ERR_INVALID;
+    // the exchange lives inside the streaming kernel; other cache modes use b200kv_decode_partials + a collective
+    if (!q8_fast_path_ok(*view, query_heads) || (num_splits & B200KV_SPLITS_FORCE_GENERIC)) return B200KV_ERR_UNSUPPORTED;
+    if ((rc = ensure_device()) != B200KV_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    DecodeParams p{};
+    p.view = *view;
+    p.cache_length = range_end;
+    p.range_begin = range_begin;
+    p.sessions = 1;
+    p.q = q;
+    p.q_is_f16 = (q_dtype == B200KV_F16);
+    p.query_heads = query_heads;
+    p.scale = scale;
+    MergeParams mp{};
+    mp.query_heads = query_heads;
+    mp.head_dim = view->head_dim;
+    mp.gate = gate;
+    mp.output = output;
+    mp.gated_output = gated_output;
+    for (uint32_t w = 0; w < world; ++w) mp.xchg.peers[w] = static_cast<uint64_t*>(exchange[w]);
+    mp.xchg.rank = rank;
+    mp.xchg.world = world;
+    mp.xchg.phase = phase;
+    // a shard may be empty (range_begin == range_end): the kernel still runs, contributes l = 0 and takes part in the exchange
+    const uint32_t span = range_end - range_begin;
+    return run_decode(p, *view, span ? span : 1, workspace, workspace_bytes, num_splits, mp, 1, s);
+}
+
 int b200kv_merge_partials(const float* part_m, const float* part_l, const float* part_acc,
                           uint32_t num_parts, uint32_t query_heads, uint32_t head_dim,
                           const float* gate, float* output, float* gated_output, void* stream) {

@@ -27,6 +27,18 @@ inline uint32_t max_splits_per_session(uint32_t sessions) {
     return s ? s : 1;
 }
 
+// Cross-GPU step of a sequence-sharded launch (streaming kernel, one session).  Every rank owns an exchange
+// buffer of tagged 8-byte words, [2 phases][world][query_heads][head_dim + 2], zero between launches; peers[w] is
+// rank w's buffer as mapped into this process.  After merging its own splits a rank stores its partial of each
+// head into slot [phase][rank] of EVERY buffer (peer stores over NVLink), then polls slot [phase][*] of its own
+// buffer, merges the `world` partials and zeroes them.  Consecutive launches on one exchange alternate `phase`:
+// a fast rank may already be writing the next launch's words while a slow one still reads this launch's.
+constexpr int kMaxExchangeRanks = 8;
+struct ExchangeParams {
+    uint64_t* peers[kMaxExchangeRanks];
+    uint32_t rank, world, phase;
+};
+
 struct MergeParams {
     const float* part_m;   // [groups][num_parts][query_heads]
     const float* part_l;
@@ -41,6 +53,7 @@ struct MergeParams {
     float* out_m;          // when non-null: emit ONE merged partial per (group, head) instead
     float* out_l;
     float* out_acc;
+    ExchangeParams xchg;   // world == 0: no cross-GPU step
 };
 
 struct DecodeParams {

@@ -161,6 +161,14 @@ __device__ __forceinline__ void ld_tagged2(const uint64_t* src, uint64_t& a, uin
     asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(src) : "memory");
 }
 __device__ __forceinline__ bool tagged_ready(uint64_t a, uint64_t b) { return (a >> 32) != 0 && (b >> 32) != 0; }
+// the same words across GPUs: stores into a peer's memory, loads of words a peer stored into ours
+__device__ __forceinline__ void st_tagged_sys(uint64_t* dst, float v) {
+    const uint64_t w = (1ull << 32) | __float_as_uint(v);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
+}
+__device__ __forceinline__ void ld_tagged2_sys(const uint64_t* src, uint64_t& a, uint64_t& b) {
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(src) : "memory");
+}
 constexpr uint32_t kPollLimit = 1u << 17;   // polls of the merger (each a trip to L2) before it gives up and poisons the output
 constexpr int kPartialWords = kD + 2;       // acc[128], m, l
 
@@ -199,6 +207,75 @@ __device__ __noinline__ void fused_append_row(const DecodeParams& p, const b200k
         static_cast<__half*>(view.key_scales)[row_index * NBLK + lane] = __float2half_rn(ksc[NBLK == 1 ? 0 : lane]);
         static_cast<__half*>(view.value_scales)[row_index * NBLK + lane] = __float2half_rn(vsc[NBLK == 1 ? 0 : lane]);
     }
+}
+
+// Cross-GPU step of a sequence-sharded launch, run by the 64 threads (pair of dims `pr`) that hold the merged
+// partial of `head`: store it into every rank's exchange buffer, wait (bounded) for the partials of all ranks in
+// our own buffer, merge them into (tot, gsum) and zero the words again.
+__device__ __forceinline__ void exchange_partials(const DecodeParams& p, uint32_t head, int pr, float m_local, float2& tot,
+                                               float& gsum, bool lost) {
+    // ---- sequence shard: exchange this rank's partial of the head with every rank and merge them all ----
+    const ExchangeParams& x = p.fuse.xchg;
+    const size_t words_per_rank = static_cast<size_t>(p.query_heads) * kPartialWords;
+    const size_t mine_off = (static_cast<size_t>(x.phase) * x.world + x.rank) * words_per_rank + static_cast<size_t>(head) * kPartialWords;
+    for (uint32_t w = 0; w < x.world; ++w) {
+        uint64_t* dst = x.peers[w] + mine_off;
+        st_tagged_sys(dst + 2 * pr, tot.x);
+        st_tagged_sys(dst + 2 * pr + 1, tot.y);
+        if (pr == 0) { st_tagged_sys(dst + kD, m_local); st_tagged_sys(dst + kD + 1, gsum); }
+    }
+    uint64_t* in = x.peers[x.rank] + static_cast<size_t>(x.phase) * x.world * words_per_rank + static_cast<size_t>(head) * kPartialWords;
+    float fa[kMaxExchangeRanks], fb[kMaxExchangeRanks], fm[kMaxExchangeRanks], fl[kMaxExchangeRanks];
+#pragma unroll
+    for (int w = 0; w < kMaxExchangeRanks; ++w) { fa[w] = fb[w] = 0.0f; fm[w] = -INFINITY; fl[w] = 0.0f; }
+    uint32_t pending = (1u << x.world) - 1u, ml_pending = pending;
+    for (uint32_t polls = 0; (pending | ml_pending) != 0 && !lost; ++polls) {
+        if (polls >= kPollLimit) { lost = true; break; }
+#pragma unroll
+        for (int w = 0; w < kMaxExchangeRanks; ++w) {
+            if (pending & (1u << w)) {
+                uint64_t a, b;
+                ld_tagged2_sys(in + w * words_per_rank + 2 * pr, a, b);
+                if (tagged_ready(a, b)) {
+                    fa[w] = __uint_as_float(static_cast<uint32_t>(a));
+                    fb[w] = __uint_as_float(static_cast<uint32_t>(b));
+                    pending &= ~(1u << w);
+                }
+            }
+            if (ml_pending & (1u << w)) {
+                uint64_t a, b;
+                ld_tagged2_sys(in + w * words_per_rank + kD, a, b);
+                if (tagged_ready(a, b)) {
+                    fm[w] = __uint_as_float(static_cast<uint32_t>(a));
+                    fl[w] = __uint_as_float(static_cast<uint32_t>(b));
+                    ml_pending &= ~(1u << w);
+                }
+            }
+        }
+    }
+    float M2 = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kMaxExchangeRanks; ++w)
+        if (!(fl[w] <= 0.0f) && fm[w] != -INFINITY) M2 = fmaxf(M2, fm[w]);   // ranks beyond `world` keep l = 0
+    float2 t2 = make_float2(0.0f, 0.0f);
+    float l2 = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kMaxExchangeRanks; ++w) {
+        const float a = (!(fl[w] <= 0.0f) && fm[w] != -INFINITY) ? __expf(fm[w] - M2) : 0.0f;
+        l2 = fmaf(fl[w], a, l2);
+        t2.x = fmaf(fa[w], a, t2.x);
+        t2.y = fmaf(fb[w], a, t2.y);
+    }
+    if (lost) { t2.x = t2.y = l2 = __int_as_float(0x7fc00000); }
+    tot = t2;
+    gsum = l2;
+    // consumed: every thread zeroes its accumulator words; (m, l) only after all 64 threads have read them
+    for (uint32_t w = 0; w < x.world; ++w)
+        asm volatile("st.global.v2.u64 [%0], {%1,%1};" ::"l"(in + w * words_per_rank + 2 * pr), "l"(0ull) : "memory");
+    asm volatile("bar.sync 1, 64;" ::: "memory");
+    if (pr == 0)
+        for (uint32_t w = 0; w < x.world; ++w)
+            asm volatile("st.global.v2.u64 [%0], {%1,%1};" ::"l"(in + w * words_per_rank + kD), "l"(0ull) : "memory");
 }
 
 // G query heads per kv head (1, 2 or 4); NBLK scales per row (4 = q8_0 blocks of 32, 1 = one per row).
@@ -657,7 +734,8 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
         if (grp == 0) {
 #pragma unroll
             for (int k = 0; k < 3; ++k) { const float2 o2 = fold[k * 64 + pr]; tot.x += o2.x; tot.y += o2.y; }
-            const float gsum = sg[1];
+            float gsum = sg[1];
+            if (p.fuse.xchg.world > 1) exchange_partials(p, head, pr, sg[0], tot, gsum, lost);
             const size_t out_idx = (static_cast<size_t>(session) * p.query_heads + head) * kD + 2 * pr;
             if (p.fuse.out_m != nullptr) {   // sequence shard: one merged, unnormalised partial
                 *reinterpret_cast<float2*>(p.fuse.out_acc + out_idx) = tot;

@@ -21,7 +21,7 @@ __all__ = [
     "KvCacheQuantMode", "RopeMode", "AttentionKvCacheView", "AttentionLayerKvCacheStorage",
     "launch_kv_store_quant", "launch_decode_attention_quant", "launch_decode_attention_batched", "launch_decode_step",
     "launch_decode_partials", "launch_merge_partials", "launch_merge_partials_packed", "packed_partial", "partial_views", "launch_suffix_attention_quant",
-    "decode_workspace", "prefill_workspace", "view_table", "make_decode_state", "make_prefill_state",
+    "Exchange", "launch_decode_attention_sharded", "decode_workspace", "prefill_workspace", "view_table", "make_decode_state", "make_prefill_state",
     "token_sequence_hash", "save_session", "load_session", "find_matching_session", "decode_kernel_kind", "set_launch_overlap", "B200KvError", "FORCE_GENERIC",
 ]
 
@@ -243,6 +243,73 @@ def launch_decode_partials(view: View, q: torch.Tensor, *, query_heads: int, sca
     check(lib.b200kv_decode_partials(C.byref(view), _ptr(q), _dtype(q), query_heads, scale, range_begin, range_end,
                                      _ptr(part_m), _ptr(part_l), _ptr(part_acc), _ptr(workspace), workspace.numel(),
                                      num_splits, _stream(stream)), "b200kv_decode_partials")
+
+
+class Exchange:
+    """The exchange buffers of sequence-sharded decode on one node: this rank's own buffer plus every peer's,
+    mapped into this process.  `handles` are the 64-byte handles of all ranks in rank order (this rank's own
+    entry comes from `Exchange.create`); see `partition.open_exchange` for the all-gather that collects them."""
+
+    def __init__(self, own_ptr: int, own_handle: bytes, rank: int):
+        self.own_ptr, self.own_handle, self.rank = own_ptr, own_handle, rank
+        self.ptrs: list[int] = []
+        self._table = None
+
+    @staticmethod
+    def create(query_heads: int, head_dim: int, world: int, rank: int) -> "Exchange":
+        ptr = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        check(lib.b200kv_exchange_create(lib.b200kv_exchange_bytes(query_heads, head_dim, world), C.byref(ptr), handle),
+              "b200kv_exchange_create")
+        return Exchange(ptr.value, handle.raw, rank)
+
+    @staticmethod
+    def from_pointers(ptrs: list, rank: int) -> "Exchange":
+        """Exchange over buffers the caller already holds device pointers to (all ranks in one process, tests)."""
+        ex = Exchange(0, b"", rank)
+        ex.ptrs = [int(x) for x in ptrs]
+        ex._table = (C.c_void_p * len(ex.ptrs))(*ex.ptrs)
+        return ex
+
+    def open_peers(self, handles: list) -> None:
+        self.ptrs = []
+        for w, h in enumerate(handles):
+            if w == self.rank:
+                self.ptrs.append(self.own_ptr)
+                continue
+            peer = C.c_void_p()
+            check(lib.b200kv_exchange_open(C.create_string_buffer(bytes(h), 64), C.byref(peer)), "b200kv_exchange_open")
+            self.ptrs.append(peer.value)
+        self._table = (C.c_void_p * len(self.ptrs))(*self.ptrs)
+
+    @property
+    def world(self) -> int:
+        return len(self.ptrs)
+
+    def close(self) -> None:
+        if self.own_ptr:   # peers were mapped by open_peers
+            for w, ptr in enumerate(self.ptrs):
+                if w != self.rank:
+                    lib.b200kv_exchange_close(ptr)
+        self.ptrs = []
+
+    def destroy(self) -> None:
+        self.close()
+        if self.own_ptr:
+            lib.b200kv_exchange_destroy(self.own_ptr)
+            self.own_ptr = 0
+
+
+def launch_decode_attention_sharded(view: View, q: torch.Tensor, exchange: Exchange, *, query_heads: int, scale: float,
+                                    range_begin: int, range_end: int, phase: int, workspace: torch.Tensor,
+                                    output: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                                    gated_output: Optional[torch.Tensor] = None, num_splits: int = 0,
+                                    stream: Optional[torch.cuda.Stream] = None) -> None:
+    """Sequence-sharded decode with the cross-GPU merge inside the kernel (b200kv_decode_attn_sharded)."""
+    check(lib.b200kv_decode_attn_sharded(C.byref(view), _ptr(q), _dtype(q), _ptr(gate), _ptr(output), _ptr(gated_output),
+                                         query_heads, scale, range_begin, range_end, exchange._table, exchange.rank,
+                                         exchange.world, phase, _ptr(workspace), workspace.numel(), num_splits,
+                                         _stream(stream)), "b200kv_decode_attn_sharded")
 
 
 def launch_merge_partials(part_m: torch.Tensor, part_l: torch.Tensor, part_acc: torch.Tensor, *, num_parts: int,

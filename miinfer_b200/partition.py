@@ -79,3 +79,18 @@ def all_gather_partials(dist, packed):
     out = torch.empty((world * packed.shape[0],) + tuple(packed.shape[1:]), dtype=packed.dtype, device=packed.device)
     dist.all_gather_into_tensor(out, packed)   # concatenated along dim 0 (the form every backend accepts)
     return out.view((world,) + tuple(packed.shape))
+
+
+def open_exchange(dist, query_heads: int, head_dim: int):
+    """Set-up of the in-kernel cross-GPU merge of sequence-sharded decode: every rank creates its exchange
+    buffer, the 64-byte handles are all-gathered (host objects, any backend) and every rank maps its peers'
+    buffers.  Returns a `kv.Exchange`; call `.destroy()` after a barrier when done."""
+    from . import kv
+
+    world, rank = dist.get_world_size(), dist.get_rank()
+    ex = kv.Exchange.create(query_heads, head_dim, world, rank)
+    handles = [None] * world
+    dist.all_gather_object(handles, ex.own_handle)
+    ex.open_peers(handles)
+    dist.barrier()
+    return ex

@@ -97,10 +97,12 @@ def run_prefill(args, torch, dist, rank, world, local_rank):
 
 
 def run_seqshard(args, torch, dist, rank, world, local_rank):
-    """One 131072-token session, KV sharded by position over the ranks; per layer each rank reduces its shard to one
-    (m, l, acc) partial per query head, the partials are all-gathered (NCCL) and merged on every rank."""
+    """One 131072-token session, KV sharded by position over the ranks.  Per layer each rank reduces its shard to one
+    (m, l, acc) partial per query head; with `--exchange kernel` (default) the decode kernel itself stores that
+    partial into every peer's exchange buffer over NVLink and merges what it receives, with `--exchange nccl` the
+    partials are all-gathered by NCCL and merged by a second kernel."""
     from miinfer_b200 import kv
-    from miinfer_b200.partition import shard_range
+    from miinfer_b200.partition import open_exchange, shard_range
 
     L, HQ, HKV, D, LAYERS = args.context if args.context != 32768 else 131072, 32, 8, 128, args.layers
     b, e = shard_range(L, rank, world)
@@ -117,12 +119,20 @@ def run_seqshard(args, torch, dist, rank, world, local_rank):
     gathered = kv.packed_partial(HQ, D, world)
     ws = kv.decode_workspace(HQ, D)
     views = [c.view() for c in caches]
-    kv.set_launch_overlap(0)
+    in_kernel = dist is not None and getattr(args, "exchange", "kernel") == "kernel"
+    if in_kernel and LAYERS % 2:
+        raise SystemExit("seqshard --exchange kernel alternates two exchange phases per layer: use an even --layers")
+    exchange = open_exchange(dist, HQ, D) if in_kernel else None
+    kv.set_launch_overlap(0 if (args.no_overlap or (dist is not None and not in_kernel)) else 1)
 
     def step():
         for l in range(LAYERS):
             if dist is None:
                 kv.launch_decode_attention_quant(views[l], q[l], query_heads=HQ, scale=D ** -0.5, cache_length=n, output=out[l], workspace=ws)
+                continue
+            if in_kernel:
+                kv.launch_decode_attention_sharded(views[l], q[l], exchange, query_heads=HQ, scale=D ** -0.5, range_begin=0,
+                                                   range_end=n, phase=l & 1, output=out[l], workspace=ws)
                 continue
             kv.launch_decode_partials(views[l], q[l], query_heads=HQ, scale=D ** -0.5, range_begin=0, range_end=n,
                                       part_m=pm, part_l=pl, part_acc=pa, workspace=ws)
@@ -139,6 +149,10 @@ def run_seqshard(args, torch, dist, rank, world, local_rank):
             step()
     torch.cuda.synchronize()
     ms = _time(torch, dist, stream, graph.replay, args.warmup, args.steps)
+    checksum = float(out.double().abs().sum().item())   # identical on every rank when the exchange is right
+    if exchange is not None:
+        dist.barrier()
+        exchange.destroy()
     bw_peak, _, kind = _peaks()
     bytes_total = LAYERS * L * HKV * 136 * 2
     achieved = bytes_total / (ms * 1e-3) / 1e9
@@ -146,11 +160,13 @@ def run_seqshard(args, torch, dist, rank, world, local_rank):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int8 KV / fp32 accumulate", "data": "synthetic",
             "config": {"workload": f"seqshard: one {L}-token session, {LAYERS} layers, {HQ} Q / {HKV} KV heads, d={D}, q8_0; positions sharded over "
-                                   f"{world} GPU(s); per layer all-gather of {HQ}x({D}+2) fp32 per rank + merge (BASELINE configs[4])",
+                                   f"{world} GPU(s); per layer exchange of {HQ}x({D}+2) fp32 per rank "
+                                   f"({'peer stores + merge inside the decode kernel' if in_kernel else 'NCCL all-gather + merge kernel'}; BASELINE configs[4])",
                        "l2": "inputs larger than L2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": bw_peak * world, "unit": "GB/s", "frac": achieved / (bw_peak * world),
                          "traffic": None, "peak_kind": f"{kind} x {world} GPUs"},
-            "merge_bytes_per_layer_per_rank": HQ * (D + 2) * 4, "gpu_launches": args.steps * LAYERS * (2 if ws is None else 3)}
+            "merge_bytes_per_layer_per_rank": HQ * (D + 2) * 4, "output_checksum": checksum,
+            "gpu_launches": args.steps * LAYERS * (1 if (dist is None or in_kernel) else 3)}
 
 
 def run_batched(args, torch, dist, rank, world, local_rank):

@@ -640,7 +640,25 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
         const uint32_t head = kv_head * G + h;
         const size_t slot_idx = (static_cast<size_t>(session) * p.num_splits + split) * p.query_heads + head;
         const float m_nat = M * 0.6931471805599453f;   // natural-log units, as the merge expects
-        if (tagged) {
+        if (tagged && num_splits == 1 && p.fuse.xchg.world <= 1) {
+            // a single split has nothing to merge with: the result leaves from here (short contexts)
+            const size_t out_idx = (static_cast<size_t>(session) * p.query_heads + head) * kD + dim;
+            if (p.fuse.out_m != nullptr) {
+                p.fuse.out_acc[out_idx] = at;
+                if (dim == 0) {
+                    p.fuse.out_m[static_cast<size_t>(session) * p.query_heads + head] = m_nat;
+                    p.fuse.out_l[static_cast<size_t>(session) * p.query_heads + head] = lt;
+                }
+            } else {
+                const float inv = lt > 0.0f ? 1.0f / lt : (lt == lt ? 0.0f : lt);
+                float o = at * inv;
+                if (p.fuse.output != nullptr) p.fuse.output[out_idx] = o;
+                if (p.fuse.gated_output != nullptr) {
+                    if (p.fuse.gate != nullptr) o *= 1.0f / (1.0f + __expf(-p.fuse.gate[out_idx]));
+                    p.fuse.gated_output[out_idx] = o;
+                }
+            }
+        } else if (tagged) {
             uint64_t* dst = p.ws_tagged + slot_idx * kPartialWords;
             st_tagged(dst + dim, at);
             if (dim == 0) { st_tagged(dst + kD, m_nat); st_tagged(dst + kD + 1, lt); }
@@ -654,7 +672,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     // ---- fused merge: the CTA of split h merges query head h of this kv head (h, h + splits, ... if there are fewer
     // splits than heads).  It polls the tagged partials of all splits -- normally they are all there by the time it
     // has finished its own share -- and every other CTA simply leaves.
-    if (split >= static_cast<uint32_t>(G)) return;
+    if (split >= static_cast<uint32_t>(G) || (num_splits == 1 && p.fuse.xchg.world <= 1)) return;
     const uint32_t S = num_splits;     // <= kMaxSplitsPerSession == 128; the partial arrays keep the launch-wide stride
     float* sm = reinterpret_cast<float*>(smem + L::kOffMisc);   // [128] m -> rescale factor
     float* sl = sm + 128;                                       // [128] l

@@ -150,6 +150,11 @@ def run_seqshard(args, torch, dist, rank, world, local_rank):
     torch.cuda.synchronize()
     ms = _time(torch, dist, stream, graph.replay, args.warmup, args.steps)
     checksum = float(out.double().abs().sum().item())   # identical on every rank when the exchange is right
+    checksum_spread = 0.0
+    if dist is not None:
+        sums = [None] * world
+        dist.all_gather_object(sums, checksum)
+        checksum_spread = (max(sums) - min(sums)) / max(abs(max(sums)), 1e-30)
     if exchange is not None:
         dist.barrier()
         exchange.destroy()
@@ -165,7 +170,7 @@ def run_seqshard(args, torch, dist, rank, world, local_rank):
                        "l2": "inputs larger than L2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": bw_peak * world, "unit": "GB/s", "frac": achieved / (bw_peak * world),
                          "traffic": None, "peak_kind": f"{kind} x {world} GPUs"},
-            "merge_bytes_per_layer_per_rank": HQ * (D + 2) * 4, "output_checksum": checksum,
+            "merge_bytes_per_layer_per_rank": HQ * (D + 2) * 4, "output_checksum": checksum, "output_checksum_spread_over_ranks": checksum_spread,
             "gpu_launches": args.steps * LAYERS * (1 if (dist is None or in_kernel) else 3)}
 
 

@@ -333,6 +333,7 @@ def main() -> None:
     ap.add_argument("--two-launches", action="store_true", help="append and attention as two launches per layer (A/B of the fused step)")
     ap.add_argument("--prefill-kernel", default="tcgen05", choices=["tcgen05", "mma"], help="prefill workload: which attention kernel")
     ap.add_argument("--no-overlap", action="store_true", help="launch every kernel fully serialised (A/B of launch overlap)")
+    ap.add_argument("--default-splits", action="store_true", help="batched workload: leave the split count to the library (A/B of the host-side picker)")
     ap.add_argument("--exchange", default="kernel", choices=["kernel", "nccl"],
                     help="seqshard workload at N>1: cross-GPU merge inside the decode kernel (peer stores) or NCCL all-gather + merge kernel")
     ap.add_argument("--layers", type=int, default=36, help="layers per step (36 = the benchmark; fewer only for ncu captures)")

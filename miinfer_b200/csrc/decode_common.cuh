@@ -73,7 +73,8 @@ struct DecodeParams {
     int q_is_f16;
     uint32_t query_heads;
     float scale;
-    uint32_t num_splits;                     // per session
+    uint32_t num_splits;                     // per session (batched: of the longest session)
+    uint32_t split_positions;                // batched streaming launches: positions per split of a session
     float* ws_m;                             // [sessions][num_splits][query_heads]
     float* ws_l;
     float* ws_acc;                           // [sessions][num_splits][query_heads][d]

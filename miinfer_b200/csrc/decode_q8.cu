@@ -61,7 +61,7 @@ constexpr int kTile = 16;     // positions per tile: one P.V k-step, two Q.K n-t
 constexpr int kStages = 3;    // TMA ring depth per warp
 constexpr int kD = 128;
 constexpr uint32_t kSpinLimit = 1u << 20;   // bounded waits: a lost copy ends the kernel with a poisoned partial
-constexpr uint32_t kPositionsPerSplit = 2048;   // batched launches: one split per this many positions of a session
+constexpr uint32_t kPositionsPerSplit = 2048;   // batched launches, split count left to the library: one split per this many positions
 constexpr int kAppendUnits = 4;    // a fused append is balanced as this many tiles of work
 constexpr float kRescaleSlack = 6.0f;   // log2 units a head's maximum may exceed the reference before a rescale
 
@@ -73,8 +73,8 @@ struct Smem {
     static constexpr int kOffS = 2 * kOffV;                              // [warp][stage][ks | vs]
     static constexpr int kOffQ = kOffS + kWarps * kStages * 2 * kSTile;  // int8 hi[4][kD], lo[4][kD]
     static constexpr int kOffQmul = kOffQ + 2 * 4 * kD;                  // [4] float
-    static constexpr int kOffMisc = kOffQmul + 16;                       // merger scratch: m/l [128] floats, totals, fold area
-    static constexpr int kOffBar = kOffMisc + (2 * 128 + 8 + 3 * 64 * 2) * 4;
+    static constexpr int kOffMisc = kOffQmul + 16;                       // merger scratch: fold area of the split groups
+    static constexpr int kOffBar = kOffMisc + (8 + 3 * 64 * 2) * 4;
     static constexpr int kTotal = kOffBar + kWarps * kStages * 8;
     static constexpr int kAlloc = kTotal + 1024;                         // slack to align the base to 1024
     static constexpr int kWarpArea = kStages * kKTile;                   // a warp's K ring doubles as its merge area
@@ -231,25 +231,25 @@ __device__ __forceinline__ void exchange_partials(const DecodeParams& p, uint32_
     uint32_t pending = (1u << x.world) - 1u, ml_pending = pending;
     for (uint32_t polls = 0; (pending | ml_pending) != 0 && !lost; ++polls) {
         if (polls >= kPollLimit) { lost = true; break; }
+        // all loads first, all checks afterwards: a check between two loads would serialise their trips
+        uint64_t wa[kMaxExchangeRanks], wb[kMaxExchangeRanks], wm[kMaxExchangeRanks], wl[kMaxExchangeRanks];
 #pragma unroll
         for (int w = 0; w < kMaxExchangeRanks; ++w) {
-            if (pending & (1u << w)) {
-                uint64_t a, b;
-                ld_tagged2_sys(in + w * words_per_rank + 2 * pr, a, b);
-                if (tagged_ready(a, b)) {
-                    fa[w] = __uint_as_float(static_cast<uint32_t>(a));
-                    fb[w] = __uint_as_float(static_cast<uint32_t>(b));
-                    pending &= ~(1u << w);
-                }
+            wa[w] = wb[w] = wm[w] = wl[w] = 0;
+            if (pending & (1u << w)) ld_tagged2_sys(in + w * words_per_rank + 2 * pr, wa[w], wb[w]);
+            if (ml_pending & (1u << w)) ld_tagged2_sys(in + w * words_per_rank + kD, wm[w], wl[w]);
+        }
+#pragma unroll
+        for (int w = 0; w < kMaxExchangeRanks; ++w) {
+            if ((pending & (1u << w)) && tagged_ready(wa[w], wb[w])) {
+                fa[w] = __uint_as_float(static_cast<uint32_t>(wa[w]));
+                fb[w] = __uint_as_float(static_cast<uint32_t>(wb[w]));
+                pending &= ~(1u << w);
             }
-            if (ml_pending & (1u << w)) {
-                uint64_t a, b;
-                ld_tagged2_sys(in + w * words_per_rank + kD, a, b);
-                if (tagged_ready(a, b)) {
-                    fm[w] = __uint_as_float(static_cast<uint32_t>(a));
-                    fl[w] = __uint_as_float(static_cast<uint32_t>(b));
-                    ml_pending &= ~(1u << w);
-                }
+            if ((ml_pending & (1u << w)) && tagged_ready(wm[w], wl[w])) {
+                fm[w] = __uint_as_float(static_cast<uint32_t>(wm[w]));
+                fl[w] = __uint_as_float(static_cast<uint32_t>(wl[w]));
+                ml_pending &= ~(1u << w);
             }
         }
     }
@@ -300,7 +300,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     // own length warrants (every CTA of the session derives the same number) and the surplus CTAs leave at once.
     uint32_t num_splits = p.num_splits;
     if (p.lengths != nullptr) {
-        const uint32_t want = (end - begin + kPositionsPerSplit - 1) / kPositionsPerSplit;
+        const uint32_t want = (end - begin + p.split_positions - 1) / p.split_positions;
         num_splits = min(num_splits, max(want, 1u));
         if (split >= num_splits) return;
     }
@@ -674,91 +674,113 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     // has finished its own share -- and every other CTA simply leaves.
     if (split >= static_cast<uint32_t>(G) || (num_splits == 1 && p.fuse.xchg.world <= 1)) return;
     const uint32_t S = num_splits;     // <= kMaxSplitsPerSession == 128; the partial arrays keep the launch-wide stride
-    float* sm = reinterpret_cast<float*>(smem + L::kOffMisc);   // [128] m -> rescale factor
-    float* sl = sm + 128;                                       // [128] l
-    float* sg = sl + 128;                                       // merged max, merged sum
-    float2* fold = reinterpret_cast<float2*>(sg + 8);           // [3][64] partial sums of split groups 1..3
+    float* fold_ml = reinterpret_cast<float*>(smem + L::kOffMisc);   // [3] x {max, sum} of split groups 1..3
+    float2* fold = reinterpret_cast<float2*>(fold_ml + 8);          // [3][64] partial sums of split groups 1..3
     constexpr int kBatch = 10;   // splits per thread and round: 4 groups x 10 = 40 splits in one trip to L2
-    const int grp = threadIdx.x >> 6, pr = threadIdx.x & 63;    // split group (sp % 4), pair of dims
+    // 256 threads = 4 split groups (sp % 4) x 64 pairs of dims.  A group merges its own splits on line (every thread
+    // of a group also reads the group's (m, l) words itself: no staging, no barrier), then the 4 groups are folded.
+    const int grp = threadIdx.x >> 6, pr = threadIdx.x & 63;
     for (uint32_t h = split; h < static_cast<uint32_t>(G); h += S) {
         const uint32_t head = kv_head * G + h;
         const size_t stride = static_cast<size_t>(p.query_heads) * kPartialWords;   // words between consecutive splits
         uint64_t* base = p.ws_tagged + ((static_cast<size_t>(session) * p.num_splits) * p.query_heads + head) * kPartialWords;
         bool lost = false;
         float2 tot = make_float2(0.0f, 0.0f);
+        float Mg = -INFINITY, lg = 0.0f;
         for (uint32_t sp0 = 0; sp0 < S; sp0 += 4 * kBatch) {
             // Poll in rounds: every round re-issues, back to back, the loads of all words of this thread that have
             // not shown their tag yet, so that once the last partial has landed one trip to L2 completes the set.
-            uint64_t va[kBatch], vb[kBatch], ma = 0, mb = 0;
+            float fa[kBatch], fb[kBatch], fm[kBatch], fl[kBatch];
             uint32_t pending = 0;
 #pragma unroll
-            for (int u = 0; u < kBatch; ++u)
+            for (int u = 0; u < kBatch; ++u) {
+                fa[u] = fb[u] = fl[u] = 0.0f;
+                fm[u] = -INFINITY;
                 if (sp0 + grp + 4 * u < S) pending |= 1u << u;
-            const bool polls_ml = sp0 == 0 && threadIdx.x < S;   // (m, l) of split threadIdx.x
-            bool ml_pending = polls_ml;
-            uint64_t* ml_src = base + threadIdx.x * stride + kD;
-            for (uint32_t polls = 0; (pending != 0 || ml_pending) && !lost; ++polls) {
+            }
+            uint32_t ml_pending = pending;
+            for (uint32_t polls = 0; (pending | ml_pending) != 0 && !lost; ++polls) {
                 if (polls >= kPollLimit) { lost = true; break; }
+                // all loads first, all checks afterwards: a check between two loads would serialise their trips
+                uint64_t wa[kBatch], wb[kBatch], wm[kBatch], wl[kBatch];
 #pragma unroll
-                for (int u = 0; u < kBatch; ++u)
-                    if (pending & (1u << u)) ld_tagged2(base + (sp0 + grp + 4 * u) * stride + 2 * pr, va[u], vb[u]);
-                if (ml_pending) ld_tagged2(ml_src, ma, mb);
+                for (int u = 0; u < kBatch; ++u) {
+                    uint64_t* src = base + (sp0 + grp + 4 * u) * stride;
+                    wa[u] = wb[u] = wm[u] = wl[u] = 0;
+                    if (pending & (1u << u)) ld_tagged2(src + 2 * pr, wa[u], wb[u]);
+                    if (ml_pending & (1u << u)) ld_tagged2(src + kD, wm[u], wl[u]);
+                }
 #pragma unroll
-                for (int u = 0; u < kBatch; ++u)
-                    if ((pending & (1u << u)) && tagged_ready(va[u], vb[u])) pending &= ~(1u << u);
-                if (ml_pending && tagged_ready(ma, mb)) ml_pending = false;
-            }
-            if (sp0 == 0) {
-                if (polls_ml) {
-                    sm[threadIdx.x] = lost ? __int_as_float(0x7fc00000) : __uint_as_float(static_cast<uint32_t>(ma));
-                    sl[threadIdx.x] = lost ? __int_as_float(0x7fc00000) : __uint_as_float(static_cast<uint32_t>(mb));
-                    asm volatile("st.global.v2.u64 [%0], {%1,%1};" ::"l"(ml_src), "l"(0ull) : "memory");   // consumed
-                }
-                __syncthreads();
-                if (warp == 0) {   // global max, rescale factors, merged sum
-                    float M = -INFINITY;
-                    for (uint32_t sp = lane; sp < S; sp += 32) {
-                        const float m = sm[sp], l = sl[sp];
-                        if (!(l <= 0.0f) && m != -INFINITY) M = fmaxf(M, m);   // keeps NaN partials in play
+                for (int u = 0; u < kBatch; ++u) {
+                    if ((pending & (1u << u)) && tagged_ready(wa[u], wb[u])) {
+                        fa[u] = __uint_as_float(static_cast<uint32_t>(wa[u]));
+                        fb[u] = __uint_as_float(static_cast<uint32_t>(wb[u]));
+                        pending &= ~(1u << u);
                     }
-                    M = warp_max(M);
-                    float lsum = 0.0f;
-                    for (uint32_t sp = lane; sp < S; sp += 32) {
-                        const float m = sm[sp], l = sl[sp];
-                        const float a = (!(l <= 0.0f) && m != -INFINITY) ? __expf(m - M) : 0.0f;
-                        sm[sp] = a;
-                        lsum = fmaf(l, a, lsum);
+                    if ((ml_pending & (1u << u)) && tagged_ready(wm[u], wl[u])) {
+                        fm[u] = __uint_as_float(static_cast<uint32_t>(wm[u]));
+                        fl[u] = __uint_as_float(static_cast<uint32_t>(wl[u]));
+                        ml_pending &= ~(1u << u);
                     }
-                    lsum = warp_sum(lsum);
-                    if (lane == 0) { sg[0] = M; sg[1] = lsum; }
                 }
-                __syncthreads();
             }
+            float Mr = Mg;
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u)
+                if (!(fl[u] <= 0.0f) && fm[u] != -INFINITY) Mr = fmaxf(Mr, fm[u]);   // keeps NaN partials in play
+            const float keep = (Mg == -INFINITY) ? 0.0f : __expf(Mg - Mr);
+            tot.x *= keep; tot.y *= keep; lg *= keep;
+            Mg = Mr;
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
-                const uint32_t sp = sp0 + grp + 4 * u;
-                if (sp < S && !(pending & (1u << u))) {
-                    const float a = sm[sp];
-                    tot.x = fmaf(__uint_as_float(static_cast<uint32_t>(va[u])), a, tot.x);
-                    tot.y = fmaf(__uint_as_float(static_cast<uint32_t>(vb[u])), a, tot.y);
-                    asm volatile("st.global.v2.u64 [%0], {%1,%1};" ::"l"(base + sp * stride + 2 * pr), "l"(0ull) : "memory");   // consumed
-                }
+                const float a = (!(fl[u] <= 0.0f) && fm[u] != -INFINITY) ? __expf(fm[u] - Mg) : 0.0f;
+                lg = fmaf(fl[u], a, lg);
+                tot.x = fmaf(fa[u], a, tot.x);
+                tot.y = fmaf(fb[u], a, tot.y);
             }
-        }
-        if (lost) tot.x = tot.y = __int_as_float(0x7fc00000);
-        // fold the 4 split groups through shared memory
-        if (grp > 0) fold[(grp - 1) * 64 + pr] = tot;
-        __syncthreads();
-        if (grp == 0) {
+            // consumed: accumulator words by the thread that read them; (m, l) words are read by all 64 threads of
+            // the group, so they are zeroed after the fold barrier below
 #pragma unroll
-            for (int k = 0; k < 3; ++k) { const float2 o2 = fold[k * 64 + pr]; tot.x += o2.x; tot.y += o2.y; }
-            float gsum = sg[1];
-            if (p.fuse.xchg.world > 1) exchange_partials(p, head, pr, sg[0], tot, gsum, lost);
+            for (int u = 0; u < kBatch; ++u)
+                if (sp0 + grp + 4 * u < S)
+                    asm volatile("st.global.v2.u64 [%0], {%1,%1};" ::"l"(base + (sp0 + grp + 4 * u) * stride + 2 * pr), "l"(0ull) : "memory");
+        }
+        if (lost) tot.x = tot.y = lg = __int_as_float(0x7fc00000);
+        // fold the 4 split groups through shared memory
+        if (grp > 0) {
+            fold[(grp - 1) * 64 + pr] = tot;
+            if (pr == 0) { fold_ml[2 * (grp - 1)] = Mg; fold_ml[2 * (grp - 1) + 1] = lg; }
+        }
+        __syncthreads();
+        for (uint32_t sp = threadIdx.x; sp < S; sp += blockDim.x)   // every thread of every group is past its polls
+            asm volatile("st.global.v2.u64 [%0], {%1,%1};" ::"l"(base + sp * stride + kD), "l"(0ull) : "memory");
+        if (grp == 0) {
+            float M = Mg;
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {
+                const float mk = fold_ml[2 * k], lk = fold_ml[2 * k + 1];
+                if (!(lk <= 0.0f) && mk != -INFINITY) M = fmaxf(M, mk);
+            }
+            {
+                const float a0 = (!(lg <= 0.0f) && Mg != -INFINITY) ? __expf(Mg - M) : 0.0f;
+                tot.x *= a0; tot.y *= a0; lg *= a0;
+            }
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {
+                const float mk = fold_ml[2 * k], lk = fold_ml[2 * k + 1];
+                const float a = (!(lk <= 0.0f) && mk != -INFINITY) ? __expf(mk - M) : 0.0f;
+                const float2 o2 = fold[k * 64 + pr];
+                tot.x = fmaf(o2.x, a, tot.x); tot.y = fmaf(o2.y, a, tot.y);
+                lg = fmaf(lk, a, lg);
+            }
+            float gsum = lg;
+            const float m_merged = M;
+            if (p.fuse.xchg.world > 1) exchange_partials(p, head, pr, m_merged, tot, gsum, lost);
             const size_t out_idx = (static_cast<size_t>(session) * p.query_heads + head) * kD + 2 * pr;
             if (p.fuse.out_m != nullptr) {   // sequence shard: one merged, unnormalised partial
                 *reinterpret_cast<float2*>(p.fuse.out_acc + out_idx) = tot;
                 if (pr == 0) {
-                    p.fuse.out_m[static_cast<size_t>(session) * p.query_heads + head] = sg[0];
+                    p.fuse.out_m[static_cast<size_t>(session) * p.query_heads + head] = m_merged;
                     p.fuse.out_l[static_cast<size_t>(session) * p.query_heads + head] = gsum;
                 }
             } else {
@@ -774,7 +796,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
                 }
             }
         }
-        __syncthreads();   // sm / sg / fold are reused by the next head of this CTA
+        __syncthreads();   // the fold area is reused by the next head of this CTA
     }
 }
 
@@ -871,10 +893,15 @@ uint32_t pick_splits_q8(const b200kv_view& geometry, uint32_t query_heads, uint3
     return s ? s : 1;
 }
 
-int launch_decode_q8(const DecodeParams& p_in, const b200kv_view& geometry, uint32_t /*max_length*/, cudaStream_t stream) {
+int launch_decode_q8(const DecodeParams& p_in, const b200kv_view& geometry, uint32_t max_length, cudaStream_t stream) {
     if (!q8_fast_path_ok(geometry, p_in.query_heads)) return B200KV_ERR_UNSUPPORTED;
     DecodeParams p = p_in;
     p.overlap_tail = launch_overlap_tail();
+    // Batched launches: the split count is that of the longest session; a session gets one split per
+    // `split_positions` of its own length (a multiple of the 128 positions one round of the 8 warps covers).
+    const uint32_t per_split = (max_length + p.num_splits - 1) / (p.num_splits ? p.num_splits : 1);
+    p.split_positions = (per_split + 127u) / 128u * 128u;
+    if (p.split_positions < 256u) p.split_positions = 256u;
     CUtensorMap kmap, vmap;
     if (p.views == nullptr) {
         int rc = encode_kv_maps(geometry, &kmap, &vmap);

@@ -94,3 +94,32 @@ def open_exchange(dist, query_heads: int, head_dim: int):
     ex.open_peers(handles)
     dist.barrier()
     return ex
+
+
+def pick_batched_splits(lengths, kv_heads: int, cta_slots: int = 296, max_splits: int = 128) -> int:
+    """Split count (of the longest session) for one batched decode launch over sessions of these lengths.
+    A launch runs one CTA per (split, kv head, session) and `cta_slots` CTAs at a time (two per SM); the
+    kernel gives a session one split per ceil(max_length / splits) positions (rounded up to 128).  The cost of
+    a choice is waves x (positions per split + the fixed cost of a CTA, about 384 positions' worth: prologue,
+    merge of its warps, tagged partial); among equally cheap choices the finer one wins (it balances better).
+    The library's own default (one split per 2048 positions) ignores the wave count."""
+    lengths = [int(x) for x in lengths if int(x) > 0]
+    if not lengths:
+        return 1
+    longest = max(lengths)
+    budget = max(1, min(max_splits, 1024 // max(1, len(lengths))))     # the library's split-slot budget
+    # with many waves the tail of the last one is small and the library's granularity measured best
+    default_splits = min(budget, max(1, -(-longest // 2048)))
+    default_per = -(-(-(-longest // default_splits)) // 128) * 128
+    if sum(-(-n // default_per) for n in lengths) * kv_heads >= 5 * cta_slots:
+        return default_splits
+    best, best_cost, best_per = 1, None, None
+    for splits in range(1, budget + 1):
+        per = max(256, -(-(-(-longest // splits)) // 128) * 128)
+        if -(-longest // per) > splits:      # rounding pushed the longest session over its split count
+            continue
+        ctas = sum(-(-n // per) for n in lengths) * kv_heads
+        cost = -(-ctas // cta_slots) * (per + 384)
+        if best_cost is None or cost < best_cost or (cost == best_cost and per < best_per):
+            best, best_cost, best_per = splits, cost, per
+    return best

@@ -178,7 +178,7 @@ def run_batched(args, torch, dist, rank, world, local_rank):
     """64 sessions with context lengths uniform in [512, 16384] (seeded), one decode step each per layer in ONE launch,
     plus 16 sessions restored from a shared 4096-token prefix snapshot; sessions are bin-packed over the ranks."""
     from miinfer_b200 import kv
-    from miinfer_b200.partition import partition_sessions
+    from miinfer_b200.partition import partition_sessions, pick_batched_splits
 
     HQ, HKV, D, LAYERS = 32, 8, 128, min(args.layers, 4)
     rng = np.random.default_rng(42)
@@ -210,14 +210,17 @@ def run_batched(args, torch, dist, rank, world, local_rank):
                 if i >= 64:
                     caches[l][j].clone_prefix_from(proto[l], 4096)
     restore_ms = _time(torch, dist, stream, restore, 1, 3) if restored or dist is not None else 0.0
+    # the host knows this step's lengths: pick the split count that fills whole waves of CTAs (0 = library default)
+    splits = 0 if getattr(args, "default_splits", False) else pick_batched_splits(lengths, HKV)
+    kv.set_launch_overlap(0 if args.no_overlap else 1)
     for l in range(LAYERS):   # fills the device view tables once
         kv.launch_decode_attention_batched([c.view() for c in caches[l]], tables[l], lens, max(lengths), q[l], query_heads=HQ,
-                                           scale=D ** -0.5, output=out[l], workspace=ws)
+                                           scale=D ** -0.5, output=out[l], workspace=ws, num_splits=splits)
 
     def step():
         for l in range(LAYERS):
             kv.launch_decode_attention_batched(None, tables[l], lens, max(lengths), q[l], query_heads=HQ, scale=D ** -0.5,
-                                               output=out[l], workspace=ws)
+                                               output=out[l], workspace=ws, num_splits=splits)
 
     ms = _time(torch, dist, stream, step, args.warmup, args.steps)
     bw_peak, _, kind = _peaks()
@@ -230,7 +233,7 @@ def run_batched(args, torch, dist, rank, world, local_rank):
                                    f"q8_0; sessions bin-packed over {world} GPU(s) (BASELINE configs[3])", "l2": "inputs larger than L2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": bw_peak * world, "unit": "GB/s", "frac": achieved / (bw_peak * world),
                          "traffic": None, "peak_kind": f"{kind} x {world} GPUs"},
-            "restore_ms_16_sessions": restore_ms, "restore_bytes": LAYERS * 16 * 4096 * HKV * 136 * 2, "gpu_launches": args.steps * LAYERS}
+            "splits_of_longest_session": splits, "restore_ms_16_sessions": restore_ms, "restore_bytes": LAYERS * 16 * 4096 * HKV * 136 * 2, "gpu_launches": args.steps * LAYERS}
 
 
 def run(args, torch, dist, rank, world, local_rank):

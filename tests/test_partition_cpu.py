@@ -81,3 +81,26 @@ def test_sequence_sharded_merge_over_gloo(tmp_path, world):
     mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         assert float((tmp_path / f"rank{r}.txt").read_text()) <= 2e-6
+
+
+def test_pick_batched_splits_fills_waves_and_respects_budgets():
+    from miinfer_b200.partition import pick_batched_splits
+
+    rng = np.random.default_rng(42)
+    lengths = [int(x) for x in rng.integers(512, 16385, size=10)]
+
+    def plan(splits, lens):
+        per = max(256, -(-(-(-max(lens) // splits)) // 128) * 128)
+        return per, sum(-(-n // per) for n in lens) * 8
+
+    s = pick_batched_splits(lengths, 8)
+    per, ctas = plan(s, lengths)
+    per_default, ctas_default = plan(-(-max(lengths) // 2048), lengths)
+    # never worse than the library default under the same cost model, and the longest session fits its split count
+    assert -(-ctas // 296) * (per + 384) <= -(-ctas_default // 296) * (per_default + 384)
+    assert -(-max(lengths) // per) <= s
+    # a single short session needs one split; many sessions are capped by the split-slot budget (1024 slots)
+    assert pick_batched_splits([100], 8) == 1
+    assert pick_batched_splits([16384] * 256, 8) <= 4
+    assert pick_batched_splits([], 8) == 1
+    assert pick_batched_splits([0, 0], 8) == 1

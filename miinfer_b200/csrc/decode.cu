@@ -13,6 +13,8 @@
 
 #include <cmath>
 #include <cstring>
+#include <mutex>
+#include <unordered_map>
 #include <vector>
 
 namespace b200kv {
@@ -252,6 +254,27 @@ int run_decode(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length
     return launch_merge(mp, groups, stream);
 }
 
+// What b200kv_decode_attn_batched staged into a device view table, kept on the host so that later calls with
+// views == NULL need no device-to-host copy (which would stall the stream once per layer and step).
+struct TableRecord { b200kv_view geometry; bool fast; uint32_t sessions; };
+static std::mutex g_tables_mutex;
+static std::unordered_map<const void*, TableRecord> g_tables;
+
+static void remember_table(const void* table, const b200kv_view& geometry, bool fast, uint32_t sessions) {
+    std::lock_guard<std::mutex> lock(g_tables_mutex);
+    if (g_tables.size() > 4096) g_tables.clear();   // tables come and go with their sessions; forgetting only costs a fetch
+    g_tables[table] = TableRecord{geometry, fast, sessions};
+}
+
+static bool recall_table(const void* table, uint32_t sessions, b200kv_view* geometry, bool* fast) {
+    std::lock_guard<std::mutex> lock(g_tables_mutex);
+    const auto it = g_tables.find(table);
+    if (it == g_tables.end() || it->second.sessions != sessions) return false;
+    *geometry = it->second.geometry;
+    *fast = it->second.fast;
+    return true;
+}
+
 static int check_heads(const b200kv_view* view, uint32_t query_heads, float scale) {
     if (query_heads == 0 || query_heads % view->kv_heads != 0 || !std::isfinite(scale)) return B200KV_ERR_INVALID;
     if (query_heads / view->kv_heads > 8) return B200KV_ERR_UNSUPPORTED;
@@ -402,8 +425,11 @@ int b200kv_decode_attn_batched(const b200kv_view* views, void* view_table, const
         geometry_fast = fast_ok;
         B200KV_CUDA_TRY(cudaMemcpyAsync(view_table, staged.data(), sizeof(SessionEntry) * sessions, cudaMemcpyHostToDevice, s));
         B200KV_CUDA_TRY(cudaStreamSynchronize(s));
+        remember_table(view_table, geometry, geometry_fast, sessions);
+    } else if (recall_table(view_table, sessions, &geometry, &geometry_fast)) {
+        // the table was filled by an earlier call of this process: nothing to fetch, the launch stays asynchronous
     } else {
-        // the table already holds the entries of an earlier call: fetch the geometry of entry 0
+        // a table this process has no record of: fetch the geometry of entry 0 (synchronises the stream)
         SessionEntry first;
         B200KV_CUDA_TRY(cudaMemcpyAsync(&first, view_table, sizeof first, cudaMemcpyDeviceToHost, s));
         B200KV_CUDA_TRY(cudaStreamSynchronize(s));

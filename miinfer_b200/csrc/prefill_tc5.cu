@@ -33,8 +33,10 @@ namespace {
 
 constexpr int kBM = 128;          // query rows per CTA
 constexpr int kBN = 64;           // positions per KV tile
-constexpr int kSoftmaxThreads = 128;
-constexpr int kThreads = kSoftmaxThreads + 64;   // + warp 4: TMA producer, warp 5: MMA issuer / TMEM owner
+constexpr int kSoftmaxThreads = 256;              // two threads per query row: columns [0, 32) and [32, 64) of every S tile
+constexpr int kTmaWarp = kSoftmaxThreads / 32;     // TMA producer
+constexpr int kMmaWarp = kTmaWarp + 1;             // MMA issuer / TMEM owner
+constexpr int kThreads = kSoftmaxThreads + 64;
 constexpr uint32_t kSpin = 1u << 20;
 constexpr float kRescaleThreshold = 8.0f;        // log2 units
 
@@ -140,7 +142,8 @@ struct Layout {
     static constexpr int kOffP = kOffV + 2 * kTileBytes;   // [row][128 B] fp16 P tile
     static constexpr int kOffBar = kOffP + kBM * 128;
     static constexpr int kNumBars = 12;   // k_full[2] k_empty[2] v_full[2] v_empty[2] s_full[2] s_empty[2] -> 12, p_full, p_empty -> 14
-    static constexpr int kTotal = kOffBar + 16 * 8 + 16;
+    static constexpr int kOffXch = kOffBar + 16 * 8 + 16;   // [2 parities][128 rows][2 halves] x {value, sequence}
+    static constexpr int kTotal = kOffXch + 2 * kBM * 2 * 8;
     static constexpr int kAlloc = kTotal + 1024;
     static constexpr uint32_t kTmemCols = 512;
     static constexpr uint32_t kColS = 0, kColO = 128;
@@ -187,7 +190,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
         for (int i = 0; i < 14; ++i) mbar_init(bar(i), (i == S_EMPTY || i == S_EMPTY + 1 || i == P_FULL) ? kSoftmaxThreads : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
+    for (int i = tid; i < 2 * kBM * 2 * 2; i += kThreads) reinterpret_cast<uint32_t*>(smem + L::kOffXch)[i] = 0;
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(L::kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -221,7 +225,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
 
     bool failed = false;
 
-    if (warp == 4) {
+    if (warp == kTmaWarp) {
         // =============================== TMA producer ===============================
         if (lane == 0) {
             const int row_base = static_cast<int>(kv_head * p.scratch_rows);
@@ -238,7 +242,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
                     tma_load_2d(sbase + L::kOffV + st * L::kTileBytes + s * (kBN * 128), &p.vmap, s * 64, row_base + j * kBN, bar(V_FULL + st));
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // =============================== MMA issuer ===============================
         if (lane == 0 && ntiles > 0) {
             constexpr uint32_t idesc_s = umma_idesc(kBM, kBN, 0, 0);
@@ -278,8 +282,12 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
         }
     } else {
         // =============================== softmax rows ===============================
-        const int r = tid;                                   // row of this thread == its TMEM lane
-        const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+        // Two threads per row: warps 0-3 take columns [0, 32) of every S tile, warps 4-7 columns [32, 64) (a warp
+        // reaches the 32 TMEM lanes of its number modulo 4).  The pair agrees on the row maximum through a small
+        // exchange area in shared memory (8-byte {value, sequence} words, polled with a bound, double-buffered by
+        // tile parity); each keeps its own partial row sum until the epilogue.
+        const int r = tid & (kBM - 1), hsel = tid >> 7;      // row of this thread == its TMEM lane; column half
+        const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t gr = row0 + r;
         uint32_t len = 0;
         if (gr < total_rows) {
@@ -287,33 +295,40 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
             const uint64_t l64 = static_cast<uint64_t>(base) + token + 1u;
             len = (token < count && l64 <= p.capacity) ? static_cast<uint32_t>(l64) : 0u;
         }
+        volatile unsigned long long* xch = reinterpret_cast<volatile unsigned long long*>(smem + L::kOffXch);
+        auto exchange = [&](int parity, uint32_t seq, float mine, float* theirs) -> bool {
+            xch[(parity * kBM + r) * 2 + hsel] = (static_cast<unsigned long long>(seq) << 32) | __float_as_uint(mine);
+            for (uint32_t spin = 0; spin < kSpin; ++spin) {
+                const unsigned long long w = xch[(parity * kBM + r) * 2 + (hsel ^ 1)];
+                if (static_cast<uint32_t>(w >> 32) == seq) { *theirs = __uint_as_float(static_cast<uint32_t>(w)); return true; }
+            }
+            return false;
+        };
+        constexpr int kHalf = kBN / 2;
         float m_ref = -INFINITY, l_sum = 0.0f;
         for (int j = 0; j < ntiles; ++j) {
             const int st = j & 1;
             if (!mbar_wait(bar(S_FULL + st), static_cast<uint32_t>((j >> 1) & 1))) { failed = true; break; }
             tc_fence_after();
-            float s[kBN];
-            {
-                float t[32];
-                tmem_ld32(tmem_base + lane_addr + L::kColS + st * kBN, t);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) s[i] = t[i];
-                tmem_ld32(tmem_base + lane_addr + L::kColS + st * kBN + 32, t);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) s[32 + i] = t[i];
-            }
+            float s[kHalf];
+            tmem_ld32(tmem_base + lane_addr + L::kColS + st * kBN + hsel * kHalf, s);
             tc_fence_before();
-            mbar_arrive(bar(S_EMPTY + st));   // this row's copy of S is in registers
-            const uint32_t pos0 = static_cast<uint32_t>(j) * kBN;
+            mbar_arrive(bar(S_EMPTY + st));   // this thread's part of S is in registers
+            const uint32_t pos0 = static_cast<uint32_t>(j) * kBN + hsel * kHalf;
             // Raw scores stay unscaled; the softmax scale is folded into the exponent: p = 2^(s*c - m*c).
             // Only the tiles that straddle this row's causal length need the mask.
-            if (pos0 + kBN > len) {
+            if (pos0 + kHalf > len) {
 #pragma unroll
-                for (int i = 0; i < kBN; ++i) s[i] = (pos0 + i < len) ? s[i] : -INFINITY;
+                for (int i = 0; i < kHalf; ++i) s[i] = (pos0 + i < len) ? s[i] : -INFINITY;
             }
             float mt = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < kBN; ++i) mt = fmaxf(mt, s[i]);
+            for (int i = 0; i < kHalf; ++i) mt = fmaxf(mt, s[i]);
+            {
+                float other;
+                if (!exchange(j & 1, static_cast<uint32_t>(j) + 1u, mt, &other)) { failed = true; break; }
+                mt = fmaxf(mt, other);
+            }
             mt *= p.scale_log2;   // scale > 0: the maximum commutes with it
             // lazy rescale: keep the old reference unless the row maximum outgrew it by more than the threshold
             float alpha = 1.0f;
@@ -323,9 +338,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
             }
             const float neg_ref = (m_ref == -INFINITY) ? 0.0f : -m_ref;
             float sum = 0.0f;
-            uint32_t ph[kBN / 2];
+            uint32_t ph[kHalf / 2];
 #pragma unroll
-            for (int i = 0; i < kBN; i += 2) {
+            for (int i = 0; i < kHalf; i += 2) {
                 const float p0 = exp2f(fmaf(s[i], p.scale_log2, neg_ref)), p1 = exp2f(fmaf(s[i + 1], p.scale_log2, neg_ref));
                 const __half2 h = __floats2half2_rn(p0, p1);
                 // the sum uses the rounded values the MMA will multiply, so numerator and denominator stay consistent
@@ -338,9 +353,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
             if (!mbar_wait(bar(P_EMPTY), static_cast<uint32_t>((j & 1) ^ 1))) { failed = true; break; }
             tc_fence_after();
             if (__any_sync(0xffffffffu, alpha != 1.0f) && j > 0) {
-                // rare: rescale this warp's 32 rows of O in TMEM
+                // rare: rescale this warp's 32 rows of O in TMEM, each thread of a pair its half of the columns
 #pragma unroll 1
-                for (int c0 = 0; c0 < D; c0 += 32) {
+                for (int c0 = hsel * (D / 2); c0 < (hsel + 1) * (D / 2); c0 += 32) {
                     float o[32];
                     tmem_ld32(tmem_base + lane_addr + L::kColO + c0, o);
 #pragma unroll
@@ -351,16 +366,20 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
             }
             uint8_t* prow = smem + L::kOffP + r * 128;
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(ph[4 * c], ph[4 * c + 1], ph[4 * c + 2], ph[4 * c + 3]);
+            for (int c = 0; c < 4; ++c)
+                *reinterpret_cast<uint4*>(prow + (((hsel * 4 + c) ^ (r & 7)) << 4)) = make_uint4(ph[4 * c], ph[4 * c + 1], ph[4 * c + 2], ph[4 * c + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
             mbar_arrive(bar(P_FULL));
         }
-        // ---- epilogue: O / sum, gate, store ----
+        // ---- epilogue: O / sum, gate, store; each thread of a pair half of the columns ----
         if (!failed && ntiles > 0 && !mbar_wait(bar(P_EMPTY), static_cast<uint32_t>((ntiles - 1) & 1))) failed = true;
         tc_fence_after();
         {
+            // the row sum is the two partial sums (both threads hold the same reference maximum)
+            float other = 0.0f;
+            if (!failed && !exchange(ntiles & 1, static_cast<uint32_t>(ntiles) + 1u, l_sum, &other)) failed = true;
+            l_sum += other;
             // tcgen05.ld is warp-collective: every lane takes part, rows past the launch only skip the store
             const bool live = gr < total_rows;
             const uint32_t token = live ? gr / G : 0, head = kv_head * G + (live ? gr % G : 0);
@@ -368,7 +387,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
             const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
             const bool have_o = ntiles > 0 && !__any_sync(0xffffffffu, failed);
 #pragma unroll 1
-            for (int c0 = 0; c0 < D; c0 += 32) {
+            for (int c0 = hsel * (D / 2); c0 < (hsel + 1) * (D / 2); c0 += 32) {
                 float o[32];
                 if (have_o) {
                     tmem_ld32(tmem_base + lane_addr + L::kColO + c0, o);
@@ -396,7 +415,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
     // ---- teardown: every role arrives here, with or without a timeout; TMEM is always released ----
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::kTmemCols) : "memory");
     }

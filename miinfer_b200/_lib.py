@@ -61,6 +61,7 @@ SIGNATURES = {
     "b200kv_merge_partials_packed": (i32, [vp, u32, u32, u32, vp, vp, vp, vp]),
     "b200kv_prefill_workspace_bytes": (sz, [u32, u32, u32]),
     "b200kv_prefill_scratch_bytes": (sz, [u64, u32, u32]),
+    "b200kv_prefill_split_bytes": (sz, [u32, u32, u32, u32]),
     "b200kv_prefill_attn": (i32, [VP, vp, i32, vp, vp, u32, u32, u32, fl, vp, vp, sz, vp]),
     "b200kv_snapshot_bytes": (sz, [VP, u64]),
     "b200kv_snapshot_save": (i32, [VP, u64, vp, vp]),

@@ -15,6 +15,7 @@
 
 namespace b200kv {
 size_t prefill_tc5_workspace_bytes(uint32_t rows, uint32_t kv_heads, uint32_t head_dim);
+size_t prefill_tc5_split_bytes(uint32_t token_count, uint32_t query_heads, uint32_t kv_heads, uint32_t head_dim, uint32_t splits);
 int launch_prefill_tc5(const b200kv_view& view, const void* q, int q_is_f16, const float* gate, float* out,
                        uint32_t token_count, uint32_t base_position, const b200kv_prefill_state* prefill_state,
                        uint32_t query_heads, float scale, void* workspace, size_t workspace_bytes, cudaStream_t stream);
@@ -31,6 +32,10 @@ size_t b200kv_prefill_workspace_bytes(uint32_t, uint32_t, uint32_t) { return 0; 
 
 size_t b200kv_prefill_scratch_bytes(uint64_t rows, uint32_t kv_heads, uint32_t head_dim) {
     return prefill_tc5_workspace_bytes(static_cast<uint32_t>(rows), kv_heads, head_dim);
+}
+
+size_t b200kv_prefill_split_bytes(uint32_t token_count, uint32_t query_heads, uint32_t kv_heads, uint32_t head_dim) {
+    return prefill_tc5_split_bytes(token_count, query_heads, kv_heads, head_dim, 4) + 2048;   // up to 4 splits, alignment slack
 }
 
 int b200kv_prefill_attn(const b200kv_view* view, const void* q, int q_dtype, const float* gate,

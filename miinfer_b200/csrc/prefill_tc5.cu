@@ -52,6 +52,12 @@ struct Tc5Params {
     uint64_t capacity;           // cache capacity (causal ranges past it give zero rows)
     uint32_t scratch_rows;       // rows per kv head in the fp16 scratch
     float scale_log2;
+    // KV split: blockIdx.z walks tiles [ntiles*z/S, ntiles*(z+1)/S) of its rows and leaves an unnormalised partial
+    // (O, reference maximum, sum) for prefill_merge_kernel.  kv_splits == 1: the kernel writes the output itself.
+    uint32_t kv_splits;
+    uint32_t rows_padded;        // query rows per kv head, rounded up to the row tile
+    float* part_o;               // [split][kv_head][rows_padded][D]
+    float2* part_ml;             // [split][kv_head][rows_padded] {maximum in log2 units, sum}
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -183,7 +189,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
         if (t_max >= t_first) kv_end = base + static_cast<uint32_t>(t_max) + 1u;
     }
     if (kv_end > p.scratch_rows) kv_end = p.scratch_rows;   // never read past what the pre-pass wrote
-    const int ntiles = static_cast<int>((kv_end + kBN - 1) / kBN);
+    const int ntiles_all = static_cast<int>((kv_end + kBN - 1) / kBN);
+    const int split = static_cast<int>(blockIdx.z), nsplit = static_cast<int>(p.kv_splits);
+    const int tile0 = static_cast<int>(static_cast<long long>(ntiles_all) * split / nsplit);
+    const int ntiles = static_cast<int>(static_cast<long long>(ntiles_all) * (split + 1) / nsplit) - tile0;   // tiles of this CTA
 
     // ---- set-up: barriers, TMEM, Q tile -----------------------------------------------------------------
     if (tid == 0) {
@@ -235,11 +244,11 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
                 if (!mbar_wait(bar(K_EMPTY + st), ph ^ 1)) { failed = true; break; }
                 mbar_expect_tx(bar(K_FULL + st), L::kTileBytes);
                 for (int s = 0; s < L::kSlabs; ++s)
-                    tma_load_2d(sbase + L::kOffK + st * L::kTileBytes + s * (kBN * 128), &p.kmap, s * 64, row_base + j * kBN, bar(K_FULL + st));
+                    tma_load_2d(sbase + L::kOffK + st * L::kTileBytes + s * (kBN * 128), &p.kmap, s * 64, row_base + (tile0 + j) * kBN, bar(K_FULL + st));
                 if (!mbar_wait(bar(V_EMPTY + st), ph ^ 1)) { failed = true; break; }
                 mbar_expect_tx(bar(V_FULL + st), L::kTileBytes);
                 for (int s = 0; s < L::kSlabs; ++s)
-                    tma_load_2d(sbase + L::kOffV + st * L::kTileBytes + s * (kBN * 128), &p.vmap, s * 64, row_base + j * kBN, bar(V_FULL + st));
+                    tma_load_2d(sbase + L::kOffV + st * L::kTileBytes + s * (kBN * 128), &p.vmap, s * 64, row_base + (tile0 + j) * kBN, bar(V_FULL + st));
             }
         }
     } else if (warp == kMmaWarp) {
@@ -314,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
             tmem_ld32(tmem_base + lane_addr + L::kColS + st * kBN + hsel * kHalf, s);
             tc_fence_before();
             mbar_arrive(bar(S_EMPTY + st));   // this thread's part of S is in registers
-            const uint32_t pos0 = static_cast<uint32_t>(j) * kBN + hsel * kHalf;
+            const uint32_t pos0 = static_cast<uint32_t>(tile0 + j) * kBN + hsel * kHalf;
             // Raw scores stay unscaled; the softmax scale is folded into the exponent: p = 2^(s*c - m*c).
             // Only the tiles that straddle this row's causal length need the mask.
             if (pos0 + kHalf > len) {
@@ -386,6 +395,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
             const size_t off = (static_cast<size_t>(token) * p.query_heads + head) * D;
             const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
             const bool have_o = ntiles > 0 && !__any_sync(0xffffffffu, failed);
+            const bool partial = nsplit > 1;
+            const size_t prow_idx = (static_cast<size_t>(split) * p.kv_heads + kv_head) * p.rows_padded + row0 + r;
+            if (partial && live && hsel == 0)   // a poisoned or empty partial is recognised by its sum
+                p.part_ml[prow_idx] = make_float2(m_ref, failed ? __int_as_float(0x7fc00000) : (len == 0 ? 0.0f : l_sum));
 #pragma unroll 1
             for (int c0 = hsel * (D / 2); c0 < (hsel + 1) * (D / 2); c0 += 32) {
                 float o[32];
@@ -396,6 +409,12 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
                     for (int i = 0; i < 32; ++i) o[i] = failed ? __int_as_float(0x7fc00000) : 0.0f;
                 }
                 if (!live) continue;
+                if (partial) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4*>(p.part_o + prow_idx * D + c0 + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+                    continue;
+                }
 #pragma unroll
                 for (int i = 0; i < 32; i += 4) {
                     float4 v = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
@@ -419,6 +438,49 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::kTmemCols) : "memory");
     }
+}
+
+// ---- merge of the KV splits: out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), gate -------------------------------
+struct PrefillMergeParams {
+    const float* part_o;
+    const float2* part_ml;
+    const float* gate;
+    float* out;
+    uint32_t kv_splits, kv_heads, query_heads, rows_padded, total_rows;   // total_rows = token_count * G per kv head
+};
+
+template <int D>
+__global__ void __launch_bounds__(256) prefill_merge_kernel(const __grid_constant__ PrefillMergeParams p) {
+    constexpr int VPR = D / 4;   // float4 per row
+    const uint32_t kv_head = blockIdx.y, G = p.query_heads / p.kv_heads;
+    const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<size_t>(p.total_rows) * VPR) return;
+    const uint32_t gr = static_cast<uint32_t>(idx / VPR), c = static_cast<uint32_t>(idx % VPR) * 4;
+    float m[4], l[4], M = -INFINITY;
+    for (uint32_t s = 0; s < p.kv_splits; ++s) {
+        const float2 ml = p.part_ml[(static_cast<size_t>(s) * p.kv_heads + kv_head) * p.rows_padded + gr];
+        m[s] = ml.x; l[s] = ml.y;
+        if (!(ml.y <= 0.0f) && ml.x != -INFINITY) M = fmaxf(M, ml.x);   // keeps NaN partials in play
+    }
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float lsum = 0.0f;
+    for (uint32_t s = 0; s < p.kv_splits; ++s) {
+        if (l[s] <= 0.0f || m[s] == -INFINITY) continue;   // empty split: its O was never written
+        const float w = exp2f(m[s] - M);
+        const float4 o = *reinterpret_cast<const float4*>(p.part_o + ((static_cast<size_t>(s) * p.kv_heads + kv_head) * p.rows_padded + gr) * D + c);
+        acc.x = fmaf(o.x, w, acc.x); acc.y = fmaf(o.y, w, acc.y); acc.z = fmaf(o.z, w, acc.z); acc.w = fmaf(o.w, w, acc.w);
+        lsum = fmaf(l[s], w, lsum);
+    }
+    const float inv = lsum > 0.0f ? 1.0f / lsum : (lsum == lsum ? 0.0f : lsum);
+    float4 v = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    const uint32_t token = gr / G, head = kv_head * G + gr % G;
+    const size_t off = (static_cast<size_t>(token) * p.query_heads + head) * D + c;
+    if (p.gate != nullptr) {
+        const float4 g = *reinterpret_cast<const float4*>(p.gate + off);
+        v.x *= 1.0f / (1.0f + __expf(-g.x)); v.y *= 1.0f / (1.0f + __expf(-g.y));
+        v.z *= 1.0f / (1.0f + __expf(-g.z)); v.w *= 1.0f / (1.0f + __expf(-g.w));
+    }
+    *reinterpret_cast<float4*>(p.out + off) = v;
 }
 
 // ---- pre-pass: dequantise [0, rows) of every kv head to fp16 ---------------------------------------------------------
@@ -511,8 +573,23 @@ int launch_tc5(const b200kv_view& view, Tc5Params& p, __half* k_scratch, __half*
     }
     const uint32_t G = p.query_heads / p.kv_heads;
     const uint32_t row_tiles = (p.token_count * G + kBM - 1) / kBM;
-    prefill_tc5_kernel<D><<<dim3(row_tiles, p.kv_heads), kThreads, L::kAlloc, stream>>>(p);
+    prefill_tc5_kernel<D><<<dim3(row_tiles, p.kv_heads, p.kv_splits), kThreads, L::kAlloc, stream>>>(p);
     B200KV_CUDA_TRY(cudaGetLastError());
+    if (p.kv_splits > 1) {
+        PrefillMergeParams mp{};
+        mp.part_o = p.part_o;
+        mp.part_ml = p.part_ml;
+        mp.gate = p.gate;
+        mp.out = p.out;
+        mp.kv_splits = p.kv_splits;
+        mp.kv_heads = p.kv_heads;
+        mp.query_heads = p.query_heads;
+        mp.rows_padded = p.rows_padded;
+        mp.total_rows = p.token_count * G;
+        const size_t work = static_cast<size_t>(mp.total_rows) * (D / 4);
+        prefill_merge_kernel<D><<<dim3(static_cast<unsigned>((work + 255) / 256), p.kv_heads), 256, 0, stream>>>(mp);
+        B200KV_CUDA_TRY(cudaGetLastError());
+    }
     return B200KV_OK;
 }
 
@@ -521,6 +598,28 @@ int launch_tc5(const b200kv_view& view, Tc5Params& p, __half* k_scratch, __half*
 size_t prefill_tc5_workspace_bytes(uint32_t rows, uint32_t kv_heads, uint32_t head_dim) {
     const size_t r = (static_cast<size_t>(rows) + kBN - 1) / kBN * kBN;
     return 2 * r * kv_heads * head_dim * sizeof(__half) + 1024;   // K and V planes, 1 KB to align the base
+}
+
+constexpr uint32_t kMaxKvSplits = 4;
+
+// Extra workspace that lets a launch split the KV range of every row tile over several CTAs (partials of `splits` splits).
+size_t prefill_tc5_split_bytes(uint32_t token_count, uint32_t query_heads, uint32_t kv_heads, uint32_t head_dim, uint32_t splits) {
+    if (kv_heads == 0 || query_heads % kv_heads != 0) return 0;
+    const size_t rows_padded = (static_cast<size_t>(token_count) * (query_heads / kv_heads) + kBM - 1) / kBM * kBM;
+    return static_cast<size_t>(splits) * kv_heads * rows_padded * (head_dim + 2) * sizeof(float);
+}
+
+// How many KV splits fill the SMs best: one CTA per SM, `units` row-tile CTAs per split.
+static uint32_t pick_kv_splits(uint32_t units, uint32_t min_tiles) {
+    const uint32_t sms = 148;
+    uint32_t best = 1;
+    double best_eff = static_cast<double>(units) / ((units + sms - 1) / sms * sms);
+    for (uint32_t s = 2; s <= kMaxKvSplits; ++s) {
+        if (min_tiles < 8 * s) break;   // every split should still walk a few tiles
+        const double eff = static_cast<double>(units) * s / ((units * s + sms - 1) / sms * sms);
+        if (eff > best_eff * 1.15) { best = s; best_eff = eff; }   // a split costs a partial round trip: only for a clear gain
+    }
+    return best;
 }
 
 // Returns B200KV_ERR_UNSUPPORTED when this path cannot run (no workspace, no TMA encoder); the caller then uses the
@@ -554,6 +653,24 @@ int launch_prefill_tc5(const b200kv_view& view, const void* q, int q_is_f16, con
     p.capacity = view.capacity;
     p.scratch_rows = scratch_rows;
     p.scale_log2 = scale * 1.4426950408889634f;
+    // KV split when the row tiles alone leave SMs idle and the caller's workspace has room for the partials
+    p.kv_splits = 1;
+    {
+        const uint32_t G = query_heads / view.kv_heads;
+        const uint32_t row_tiles = (token_count * G + kBM - 1) / kBM;
+        const uint32_t min_tiles = static_cast<uint32_t>((static_cast<uint64_t>(prefill_state ? 0 : base_position) + kBN - 1) / kBN);
+        uint32_t want = pick_kv_splits(row_tiles * view.kv_heads, min_tiles);
+        const size_t scratch = prefill_tc5_workspace_bytes(static_cast<uint32_t>(rows), view.kv_heads, view.head_dim);
+        while (want > 1 && workspace_bytes < scratch + 1024 + prefill_tc5_split_bytes(token_count, query_heads, view.kv_heads, view.head_dim, want)) --want;
+        if (want > 1) {
+            p.kv_splits = want;
+            p.rows_padded = row_tiles * kBM;
+            uint8_t* part = reinterpret_cast<uint8_t*>(v_scratch + static_cast<size_t>(view.kv_heads) * scratch_rows * view.head_dim);
+            part = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(part) + 1023) & ~static_cast<uintptr_t>(1023));
+            p.part_o = reinterpret_cast<float*>(part);
+            p.part_ml = reinterpret_cast<float2*>(p.part_o + static_cast<size_t>(want) * view.kv_heads * p.rows_padded * view.head_dim);
+        }
+    }
     return view.head_dim == 128 ? launch_tc5<128>(view, p, k_scratch, v_scratch, static_cast<uint32_t>(rows), stream)
                                 : launch_tc5<256>(view, p, k_scratch, v_scratch, static_cast<uint32_t>(rows), stream);
 }

@@ -169,9 +169,13 @@ def view_table(sessions: int, device=None) -> torch.Tensor:
     return torch.zeros(int(lib.b200kv_view_table_bytes(sessions)), dtype=torch.uint8, device=device or "cuda")
 
 
-def prefill_workspace(rows: int, kv_heads: int, head_dim: int, device=None) -> torch.Tensor:
-    """Scratch that lets launch_suffix_attention_quant run the tcgen05 kernel: `rows` = base_position + token_count."""
+def prefill_workspace(rows: int, kv_heads: int, head_dim: int, device=None, *, token_count: int = 0,
+                      query_heads: int = 0) -> torch.Tensor:
+    """Scratch that lets launch_suffix_attention_quant run the tcgen05 kernel: `rows` = base_position + token_count.
+    With token_count and query_heads given it also has room for the partials of a KV-split launch."""
     n = int(lib.b200kv_prefill_scratch_bytes(rows, kv_heads, head_dim))
+    if token_count and query_heads:
+        n += int(lib.b200kv_prefill_split_bytes(token_count, query_heads, kv_heads, head_dim))
     return torch.zeros(n, dtype=torch.uint8, device=device or "cuda")
 
 

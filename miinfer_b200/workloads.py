@@ -74,7 +74,8 @@ def run_prefill(args, torch, dist, rank, world, local_rank):
     out = torch.zeros(LAYERS, T, hq, D, device="cuda")
     views = [c.view() for c in caches]
     # the fp16 scratch of the visible prefix selects the tcgen05 kernel; --prefill-kernel mma runs the mma.sync one
-    ws = None if args.prefill_kernel == "mma" else kv.prefill_workspace(P + T, hkv, D)
+    # (with room for KV-split partials: the chunk's row tiles alone do not fill the SMs)
+    ws = None if args.prefill_kernel == "mma" else kv.prefill_workspace(P + T, hkv, D, token_count=T, query_heads=hq)
 
     def step():
         for l in range(LAYERS):

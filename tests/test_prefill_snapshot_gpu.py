@@ -202,3 +202,25 @@ def test_session_file_save_find_load_gives_identical_decode(cuda, tmp_path):
     too_small = [kv.AttentionLayerKvCacheStorage(512, kv.KvCacheQuantMode.kQ8Q8, kv_heads=H, head_dim=d, qblock=32) for _ in range(layers)]
     with pytest.raises(kv.B200KvError):
         kv.load_session(found[0], "qwen3-8b", "q4_0", too_small)
+
+
+@pytest.mark.parametrize("P,T,H,Hq,d", [(2048, 128, 4, 24, 256), (1500, 200, 8, 32, 128)])
+def test_suffix_attention_with_the_kv_range_split_over_ctas(cuda, P, T, H, Hq, d):
+    """Few row tiles, long prefix: with room for partials in the workspace the tcgen05 launch splits every row
+    tile's KV range over several CTAs and merges the partials; the result must match the unsplit launch and the oracle."""
+    rng = np.random.default_rng(P + T)
+    host = filled(rng, P + T, H, d, 32, 3, cap=P + T + 64, std=0.5)
+    st = upload(host)
+    q = (rng.standard_normal((T, Hq, d)) * 0.5).astype(np.float32)
+    gate = (rng.standard_normal((T, Hq, d)) * 0.5).astype(np.float32)
+    ref = host.suffix_ref(q, gate, P, d ** -0.5)
+    plain = torch.full((T, Hq, d), float("nan"), device="cuda")
+    kv.launch_suffix_attention_quant(st.view(), to_dev(q), to_dev(gate), plain, kv.prefill_workspace(P + T, H, d), T, P,
+                                     query_heads=Hq, scale=d ** -0.5)
+    split = torch.full((T, Hq, d), float("nan"), device="cuda")
+    ws = kv.prefill_workspace(P + T, H, d, token_count=T, query_heads=Hq)
+    assert ws.numel() > kv.prefill_workspace(P + T, H, d).numel()
+    kv.launch_suffix_attention_quant(st.view(), to_dev(q), to_dev(gate), split, ws, T, P, query_heads=Hq, scale=d ** -0.5)
+    torch.cuda.synchronize()
+    assert np.max(np.abs(split.cpu().numpy() - ref)) <= TOL
+    assert float((split - plain).abs().max()) <= 1e-4     # same tiles, merged in a different order

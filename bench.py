@@ -8,9 +8,9 @@ context (32 Q / 8 KV heads, d=128, q8_0 K/V, batch 1): per layer one fused
 append (fp16 K/V, NeoX RoPE) and one split-K GQA decode attention.  One "step"
 is one decode step over all 36 layers; `value` is decode tokens/s with the
 caches resident in HBM.  With N GPUs every rank decodes its own session (weak
-scaling, no data-path collective).  Other workloads (for tables in DESIGN.md):
-`seqshard` (one 128K-token session sharded by sequence over the ranks, NCCL
-all-gather of the per-rank partials + merge), `batched` (64 sessions of mixed
+scaling, no data-path collective).  Other workloads:
+`seqshard` (one 128K-token session sharded by sequence over the ranks; the per-rank
+partials are exchanged and merged inside the decode kernel, or by NCCL with --exchange nccl), `batched` (64 sessions of mixed
 length), `prefill` (512-token suffix over an 8K prefix, d=256).
 
 The `--impl reference` arm times the CPU restatement of the reference path

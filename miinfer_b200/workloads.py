@@ -1,4 +1,4 @@
-"""Secondary bench workloads (tables in DESIGN.md): suffix prefill (BASELINE config 3), batched
+"""Secondary bench workloads: suffix prefill (BASELINE config 3), batched
 serving (config 4) and sequence-sharded long-context decode (config 5).  bench.py dispatches here
 for --workload prefill|batched|seqshard; the default decode32k workload lives in bench.py."""
 from __future__ import annotations

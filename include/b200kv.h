@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define B200KV_VERSION 100 /* 0.1.0 */
+#define B200KV_VERSION 200 /* 0.2.0 */
 
 #if defined(__GNUC__)
 #define B200KV_API __attribute__((visibility("default")))
@@ -54,6 +54,13 @@ typedef enum b200kv_status {
     B200KV_ERR_IO = -8,          /* session file: open/read/write failed */
     B200KV_ERR_MISMATCH = -9     /* session file does not match the requested prefix */
 } b200kv_status;
+
+/* Bits a kernel ORs into the status word registered with b200kv_set_status_word when one of its bounded waits
+ * runs out (the launch then ends, its outputs are NaN, and the host learns why from this word). */
+#define B200KV_STATUS_COPY_TIMEOUT 1u   /* a tile copy (TMA) never completed */
+#define B200KV_STATUS_SPLIT_TIMEOUT 2u  /* the in-launch merge never saw the partial of one of its splits */
+#define B200KV_STATUS_PEER_TIMEOUT 4u   /* the cross-GPU merge never saw the partial of one of its peers */
+#define B200KV_STATUS_PIPE_TIMEOUT 8u   /* a tensor-core pipeline stage (MMA completion) never signalled */
 
 /* KvCacheQuantMode, include/miinfer/prefill_v2/kv_cache.hpp:16-21 (same values). */
 typedef enum b200kv_quant_mode {
@@ -109,6 +116,14 @@ typedef struct b200kv_prefill_state {
     uint32_t pad_[12];
 } b200kv_prefill_state;
 
+/* One block of the Q8_1 activation format the reference's projections consume: Q8_1Block,
+ * include/miinfer/q4_q8_gemv.hpp:23-27 (36 bytes: fp16 d, fp16 s = d * sum(qs), 32 int8). */
+typedef struct b200kv_q8_1_block {
+    uint16_t d;    /* fp16 bits */
+    uint16_t s;    /* fp16 bits */
+    int8_t qs[32];
+} b200kv_q8_1_block;
+
 /* ---- library / device ------------------------------------------------------ */
 
 B200KV_API int b200kv_version(void);
@@ -134,6 +149,20 @@ B200KV_API int b200kv_device_check(int device);
  * an ordinary kernel between two launches acts as a full barrier.  0 turns the
  * overlap off again. */
 B200KV_API int b200kv_set_launch_overlap(uint32_t tail_positions);
+
+/* Registers a 4-byte-aligned DEVICE word (on the current device; NULL = none, the default) into which every later
+ * launch of this library on that device ORs a B200KV_STATUS_* bit when one of its bounded waits runs out.  The
+ * reference aborts the process on any device error (include/miinfer/hip_check.hpp:11-24); here a lost copy or a
+ * peer that never delivers ends the launch with NaN outputs and this word says which wait it was.  The word is
+ * sticky: the caller zeroes it.  After a non-zero status the tagged words of the workspace (and, for a sharded
+ * launch, of the exchange buffers of ALL ranks, behind a barrier) must be cleared before they are used again:
+ * b200kv_workspace_reset, or a plain memset. */
+B200KV_API int b200kv_set_status_word(uint32_t* device_word);
+/* Zero-fills a decode workspace (or an exchange buffer) asynchronously on `stream`. */
+B200KV_API int b200kv_workspace_reset(void* workspace, size_t workspace_bytes, void* stream);
+/* Which streaming kernel serves int8 caches (process-wide; for A/B measurement and tests): 0 = the tcgen05 kernel
+ * where it applies (default), 1 = the warp-level mma kernel everywhere.  No counterpart in the reference. */
+B200KV_API int b200kv_set_decode_kernel(int choice);
 
 /* ---- cache storage ---------------------------------------------------------
  * Replaces class AttentionLayerKvCacheStorage (kv_cache.hpp:49-122,
@@ -171,6 +200,27 @@ B200KV_API int b200kv_append(const b200kv_view* view, const void* key, const voi
                   const b200kv_prefill_state* prefill_state, const b200kv_decode_state* decode_state,
                   void* stream);
 
+/* ---- the query side and the step state (the operators either side of the KV path in a step) ---------------- */
+
+/* Replaces launch_qwen35_decoupled_q_split_norm_rope_batch (include/miinfer/qwen3_gpu_primitives.hpp:869-881; kernel
+ * gfx906/kernels/qwen3_primitives.hip:994-1045) and launch_qwen35_fused_q_split_norm_rope_dynamic (hpp:934-938;
+ * kernel .hip:661-717).  qfull: the query projection's output [token][heads][q (head_dim) | gate (head_dim)] of
+ * in_dtype.  Writes query [token][heads][head_dim] of out_dtype = RoPE(RMSNorm(q) * q_norm_weight) at position
+ * base_position + token, and gate (fp32, same shape; may be NULL).  q_norm_weight may be NULL (no norm).  A
+ * non-NULL prefill_state (base_position, token_count) or decode_state (position; one token) is read on the device
+ * as in b200kv_append.  The norm and the RoPE are the append kernel's, bit for bit, so a query and the key
+ * appended at the same position are rotated identically. */
+B200KV_API int b200kv_q_split_norm_rope(const void* qfull, int in_dtype, const float* q_norm_weight, void* query, int out_dtype,
+                             float* gate, uint32_t token_count, uint32_t base_position, uint32_t heads, uint32_t head_dim,
+                             int rope_mode, float theta, float epsilon, const b200kv_prefill_state* prefill_state,
+                             const b200kv_decode_state* decode_state, void* stream);
+
+/* Replaces launch_qwen35_decode_state_advance (qwen3_gpu_primitives.hpp:1248-1250; kernel .hip:4417-4428): on the
+ * device, record state->current_token at token_output[state->generated] (if below `capacity`), set state->stop on
+ * an end-of-text token (151643, 151645) or when max_generated is reached, and advance position and generated by
+ * one -- so that a captured decode graph replays at the next position without the host touching the state. */
+B200KV_API int b200kv_decode_state_advance(b200kv_decode_state* state, uint32_t* token_output, uint32_t capacity, void* stream);
+
 /* ---- decode attention ------------------------------------------------------- */
 
 /* Workspace bytes for the split-K partials of one decode launch over
@@ -193,9 +243,12 @@ B200KV_API size_t b200kv_decode_workspace_bytes(uint32_t query_heads, uint32_t h
  * gated_output (= output * sigmoid(gate), gate fp32 [query_heads][head_dim]) are
  * fp32 [query_heads][head_dim]; at least one must be non-NULL; gate may be NULL
  * (then gated_output == output).  num_splits 0 = choose for the device.
- * The reference's gated_output_q8 (Q8_1 re-quantised output) is not provided. */
+ * gated_output_q8 (may be NULL): the gated output re-quantised to Q8_1 blocks of 32 for the projection that
+ * follows, [query_heads * head_dim / 32] blocks, as the reference's stage 2 does (.hip:2354-2383: d = amax/127,
+ * q = roundf(x/d) clamped to +-127, s = d * sum(q), d and s stored as fp16).  Unlike the reference it is also
+ * produced when gate is NULL (from the ungated output). */
 B200KV_API int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
-                       float* output, float* gated_output, uint32_t query_heads, float scale,
+                       float* output, float* gated_output, b200kv_q8_1_block* gated_output_q8, uint32_t query_heads, float scale,
                        uint32_t cache_length, const b200kv_decode_state* decode_state,
                        void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream);
 
@@ -209,7 +262,7 @@ B200KV_API int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_
 B200KV_API int b200kv_decode_step(const b200kv_view* view, const void* key, const void* value, int kv_dtype,
                        const float* k_norm_weight, int rope_mode, float theta, float epsilon,
                        const void* q, int q_dtype, const float* gate, float* output, float* gated_output,
-                       uint32_t query_heads, float scale, uint32_t position, const b200kv_decode_state* decode_state,
+                       b200kv_q8_1_block* gated_output_q8, uint32_t query_heads, float scale, uint32_t position, const b200kv_decode_state* decode_state,
                        void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream);
 
 /* Decode attention without a caller-supplied workspace and without any allocation (no counterpart in the
@@ -225,8 +278,9 @@ B200KV_API int b200kv_decode_step(const b200kv_view* view, const void* key, cons
  *     that first call before starting any stream capture.
  *   - All calls on a device share the one array: two calls whose kernels overlap on the GPU (different
  *     streams, or launch overlap between them) race on it.  Calls ordered on one stream are safe.
- *   - It calls no cudaMalloc, cudaFree or allocating library routine; it issues one cudaMemsetAsync on
- *     `stream` to clear the tagged partials and then the same kernels as b200kv_decode_attn. */
+ *   - It calls no cudaMalloc, cudaFree or allocating library routine, and adds no work to the stream beyond
+ *     the kernels b200kv_decode_attn launches (the array needs no clearing between calls: launches zero the
+ *     words they consumed, and words left by a launch that gave up carry a tag no later launch accepts). */
 B200KV_API size_t b200kv_decode_static_scratch_bytes(void);
 B200KV_API int b200kv_decode_attn_static(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
                               float* output, float* gated_output, uint32_t query_heads, float scale,
@@ -240,9 +294,14 @@ B200KV_API int b200kv_decode_attn_static(const b200kv_view* view, const void* q,
  * polls its own buffer until the `world` partials of a head are there (bounded: a rank that never shows up turns
  * the output into NaN instead of hanging the GPU), merges them and zeroes the words again.  Every rank ends
  * with the same output.  exchange[w]: rank w's buffer as mapped into this process (exchange[rank] = its own),
- * each of b200kv_exchange_bytes() bytes.  All ranks must launch the same sequence of sharded calls; consecutive
- * calls on one exchange must alternate phase (0, 1, 0, ...) because a fast rank may already be writing the next
- * call's words while a slow one still reads this call's.  Streaming-kernel caches only (see
+ * each of b200kv_exchange_bytes() bytes.  All ranks must launch the same sequence of sharded calls.  `phase` is
+ * the call's number on this exchange: any 32-bit value below 0xffffffff that all ranks agree on and that differs
+ * from the previous call's by an odd amount (0, 1, 2, ... is the natural choice; a captured graph may repeat its
+ * own numbers on every replay).  Its lowest bit selects one of two slots -- a fast rank may already be writing the
+ * next call's words while a slow one still reads this call's -- and phase + 1 tags every word, so that words a
+ * late rank stores after its peers gave up are not taken for a later call's.  If any rank's status word shows
+ * B200KV_STATUS_PEER_TIMEOUT, clear the exchange buffers on all ranks behind a barrier before going on.
+ * Streaming-kernel caches only (see
  * b200kv_decode_kernel_kind); others return B200KV_ERR_UNSUPPORTED and use b200kv_decode_partials + an
  * all-gather + b200kv_merge_partials_packed.  world <= 8. */
 B200KV_API size_t b200kv_exchange_bytes(uint32_t query_heads, uint32_t head_dim, uint32_t world);

@@ -36,15 +36,20 @@ SIGNATURES = {
     "b200kv_last_cuda_error": (C.c_char_p, []),
     "b200kv_device_check": (i32, [i32]),
     "b200kv_set_launch_overlap": (i32, [u32]),
+    "b200kv_set_status_word": (i32, [vp]),
+    "b200kv_workspace_reset": (i32, [vp, sz, vp]),
+    "b200kv_set_decode_kernel": (i32, [i32]),
     "b200kv_cache_bytes": (sz, [u64, u32, u32, u32, u32]),
     "b200kv_cache_create": (i32, [C.POINTER(vp), u64, u32, u32, u32, u32]),
     "b200kv_cache_destroy": (i32, [vp]),
     "b200kv_cache_reset": (i32, [vp, vp]),
     "b200kv_cache_view": (i32, [vp, VP]),
     "b200kv_append": (i32, [VP, vp, vp, i32, vp, i32, fl, fl, u32, u32, vp, vp, vp]),
+    "b200kv_q_split_norm_rope": (i32, [vp, i32, vp, vp, i32, vp, u32, u32, u32, u32, i32, fl, fl, vp, vp, vp]),
+    "b200kv_decode_state_advance": (i32, [vp, vp, u32, vp]),
     "b200kv_decode_workspace_bytes": (sz, [u32, u32, u32]),
-    "b200kv_decode_attn": (i32, [VP, vp, i32, vp, vp, vp, u32, fl, u32, vp, vp, sz, u32, vp]),
-    "b200kv_decode_step": (i32, [VP, vp, vp, i32, vp, i32, fl, fl, vp, i32, vp, vp, vp, u32, fl, u32, vp, vp, sz, u32, vp]),
+    "b200kv_decode_attn": (i32, [VP, vp, i32, vp, vp, vp, vp, u32, fl, u32, vp, vp, sz, u32, vp]),
+    "b200kv_decode_step": (i32, [VP, vp, vp, i32, vp, i32, fl, fl, vp, i32, vp, vp, vp, vp, u32, fl, u32, vp, vp, sz, u32, vp]),
     "b200kv_decode_static_scratch_bytes": (sz, []),
     "b200kv_decode_attn_static": (i32, [VP, vp, i32, vp, vp, vp, u32, fl, u32, vp, u32, vp]),
     "b200kv_view_table_bytes": (sz, [u32]),

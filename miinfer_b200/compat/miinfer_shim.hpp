@@ -71,18 +71,21 @@ inline void launch_qwen35_decoupled_k_norm_rope_kv_store_batch_quant(
                        "launch_qwen35_decoupled_k_norm_rope_kv_store_batch_quant");
 }
 
-// qwen3_gpu_primitives.hpp:719-739 (gated_output_q8 is not provided)
+// Q8_1Block (include/miinfer/q4_q8_gemv.hpp:23-27): the 36-byte activation block the projections consume
+using Q8_1Block = b200kv_q8_1_block;
+
+// qwen3_gpu_primitives.hpp:719-739
 inline void launch_qwen35_tiled_online_attention_quant_dynamic(
     const float* q, const __half* key_cache_f16, const __half* value_cache_f16, const int8_t* key_cache_q8, const __half* key_scales,
     const int8_t* value_cache_q8, const __half* value_scales, const DeviceDecodeState* decode_state, std::uint32_t cache_capacity,
     float* output, const float* gate, float* gated_output, std::uint32_t query_heads, std::uint32_t kv_heads, std::uint32_t head_dim,
-    float scale, bool is_k_q8, bool is_v_q8, cudaStream_t stream = nullptr) {
+    float scale, bool is_k_q8, bool is_v_q8, cudaStream_t stream = nullptr, Q8_1Block* gated_output_q8 = nullptr) {
     if (decode_state == nullptr) shim_detail::check(B200KV_ERR_INVALID, "launch_qwen35_tiled_online_attention_quant_dynamic");
     const b200kv_view v = shim_detail::make_view(key_cache_f16, value_cache_f16, key_cache_q8, key_scales, value_cache_q8,
                                                  value_scales, cache_capacity, kv_heads, head_dim, kv_qblock(), is_k_q8, is_v_q8);
     const auto& ws = shim_detail::decode_workspace();
-    shim_detail::check(b200kv_decode_attn(&v, q, B200KV_F32, gate, output, gated_output, query_heads, scale, 0, decode_state, ws.ptr,
-                                          ws.bytes, 0, stream),
+    shim_detail::check(b200kv_decode_attn(&v, q, B200KV_F32, gate, output, gated_output, gated_output_q8, query_heads, scale, 0,
+                                          decode_state, ws.ptr, ws.bytes, 0, stream),
                        "launch_qwen35_tiled_online_attention_quant_dynamic");
 }
 

@@ -165,10 +165,28 @@ __global__ void merge_kernel(const __grid_constant__ MergeParams p) {
     }
     const float o = gsum > 0.0f ? total / gsum : (gsum == gsum ? 0.0f : gsum);
     if (p.output != nullptr) p.output[out_idx] = o;
-    if (p.gated_output != nullptr) {
+    if (p.gated_output != nullptr || p.gated_output_q8 != nullptr) {
         float g = o;
         if (p.gate != nullptr) g = o * (1.0f / (1.0f + __expf(-p.gate[out_idx])));
-        p.gated_output[out_idx] = g;
+        if (p.gated_output != nullptr) p.gated_output[out_idx] = g;
+        if (p.gated_output_q8 != nullptr) {
+            // Q8_1 block of 32 consecutive dims = one warp (gfx906/kernels/qwen3_primitives.hip:2354-2383);
+            // IEEE operations so that a host restatement reproduces the bits
+            const float amax = warp_max(fabsf(g));
+            const float dq = __fdiv_rn(amax, 127.0f);
+            const float id = dq != 0.0f ? __fdiv_rn(1.0f, dq) : 0.0f;
+            const int q = max(-127, min(127, static_cast<int>(roundf(__fmul_rn(g, id)))));
+            int qs = q;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) qs += __shfl_xor_sync(0xffffffffu, qs, off);
+            b200kv_q8_1_block* dst = p.gated_output_q8 + out_idx / 32;
+            dst->qs[dim & 31] = static_cast<int8_t>(q);
+            if ((dim & 31) == 0) {
+                const __half dh = __float2half_rn(dq), sh = __float2half_rn(__fmul_rn(static_cast<float>(qs), dq));
+                dst->d = *reinterpret_cast<const uint16_t*>(&dh);
+                dst->s = *reinterpret_cast<const uint16_t*>(&sh);
+            }
+        }
     }
 }
 
@@ -225,12 +243,19 @@ int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max
     p.ws_m = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + plain_offset);
     p.ws_l = p.ws_m + slots;
     p.ws_acc = p.ws_l + slots;
+    p.status = current_status_word();
     if (use_fast) {
         if (plain_offset < 2 * plain_bytes) return B200KV_ERR_WORKSPACE;
-        p.ws_tagged = static_cast<uint64_t*>(workspace);
+        // The in-launch merge; a lone split that has to produce Q8_1 blocks goes through the merge kernel instead
+        // (a block of 32 outputs is quantised by 16 cooperating threads, which the single-split shortcut has not).
+        const bool fuse_merge = !(num_splits == 1 && merge.gated_output_q8 != nullptr && merge.xchg.world <= 1);
+        p.ws_tagged = fuse_merge ? static_cast<uint64_t*>(workspace) : nullptr;
+        p.tag = next_launch_tag();
         p.fuse = merge;
-        int rc = launch_decode_q8(p, geometry, max_length, stream);
-        if (rc == B200KV_OK) *merged = true;
+        int rc = B200KV_ERR_UNSUPPORTED;
+        if (streaming_kernel_choice() == 0) rc = launch_decode_tc5(p, geometry, max_length, stream);
+        if (rc == B200KV_ERR_UNSUPPORTED) rc = launch_decode_q8(p, geometry, max_length, stream);
+        if (rc == B200KV_OK) *merged = fuse_merge;
         if (rc != B200KV_ERR_UNSUPPORTED) return rc;
         p.ws_tagged = nullptr;
     }
@@ -258,17 +283,24 @@ int run_decode(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length
 // views == NULL need no device-to-host copy (which would stall the stream once per layer and step).
 struct TableRecord { b200kv_view geometry; bool fast; uint32_t sessions; };
 static std::mutex g_tables_mutex;
-static std::unordered_map<const void*, TableRecord> g_tables;
+static std::unordered_map<uint64_t, TableRecord> g_tables;   // keyed by (device, address): addresses repeat across devices
+
+static uint64_t table_key(const void* table) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) (void)cudaGetLastError();
+    // device pointers use at most 57 bits; the ordinal goes on top
+    return (static_cast<uint64_t>(device & 0x7f) << 57) ^ static_cast<uint64_t>(reinterpret_cast<uintptr_t>(table));
+}
 
 static void remember_table(const void* table, const b200kv_view& geometry, bool fast, uint32_t sessions) {
     std::lock_guard<std::mutex> lock(g_tables_mutex);
     if (g_tables.size() > 4096) g_tables.clear();   // tables come and go with their sessions; forgetting only costs a fetch
-    g_tables[table] = TableRecord{geometry, fast, sessions};
+    g_tables[table_key(table)] = TableRecord{geometry, fast, sessions};
 }
 
 static bool recall_table(const void* table, uint32_t sessions, b200kv_view* geometry, bool* fast) {
     std::lock_guard<std::mutex> lock(g_tables_mutex);
-    const auto it = g_tables.find(table);
+    const auto it = g_tables.find(table_key(table));
     if (it == g_tables.end() || it->second.sessions != sessions) return false;
     *geometry = it->second.geometry;
     *fast = it->second.fast;
@@ -302,12 +334,13 @@ size_t b200kv_decode_workspace_bytes(uint32_t query_heads, uint32_t head_dim, ui
 }
 
 int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
-                       float* output, float* gated_output, uint32_t query_heads, float scale,
+                       float* output, float* gated_output, b200kv_q8_1_block* gated_output_q8, uint32_t query_heads, float scale,
                        uint32_t cache_length, const b200kv_decode_state* decode_state,
                        void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream) {
     int rc = validate_view(view);
     if (rc != B200KV_OK) return rc;
-    if (q == nullptr || (output == nullptr && gated_output == nullptr)) return B200KV_ERR_INVALID;
+    // at least one output, as the reference launcher demands (gfx906/kernels/qwen3_primitives.hip:7509-7512)
+    if (q == nullptr || (output == nullptr && gated_output == nullptr && gated_output_q8 == nullptr)) return B200KV_ERR_INVALID;
     if (q_dtype != B200KV_F16 && q_dtype != B200KV_F32) return B200KV_ERR_INVALID;
     if ((rc = check_heads(view, query_heads, scale)) != B200KV_OK) return rc;
     if (decode_state == nullptr && cache_length > view->capacity) return B200KV_ERR_RANGE;
@@ -331,17 +364,19 @@ int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_dtype, cons
     mp.gate = gate;
     mp.output = output;
     mp.gated_output = gated_output;
+    mp.gated_output_q8 = gated_output_q8;
     return run_decode(p, *view, max_length, workspace, workspace_bytes, num_splits, mp, 1, s);
 }
 
 int b200kv_decode_step(const b200kv_view* view, const void* key, const void* value, int kv_dtype,
                        const float* k_norm_weight, int rope_mode, float theta, float epsilon,
                        const void* q, int q_dtype, const float* gate, float* output, float* gated_output,
-                       uint32_t query_heads, float scale, uint32_t position, const b200kv_decode_state* decode_state,
-                       void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream) {
+                       b200kv_q8_1_block* gated_output_q8, uint32_t query_heads, float scale, uint32_t position,
+                       const b200kv_decode_state* decode_state, void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream) {
     int rc = validate_view(view);
     if (rc != B200KV_OK) return rc;
-    if (key == nullptr || value == nullptr || q == nullptr || (output == nullptr && gated_output == nullptr)) return B200KV_ERR_INVALID;
+    if (key == nullptr || value == nullptr || q == nullptr || (output == nullptr && gated_output == nullptr && gated_output_q8 == nullptr))
+        return B200KV_ERR_INVALID;
     if ((kv_dtype != B200KV_F16 && kv_dtype != B200KV_F32) || (q_dtype != B200KV_F16 && q_dtype != B200KV_F32)) return B200KV_ERR_INVALID;
     if (rope_mode < B200KV_ROPE_NONE || rope_mode > B200KV_ROPE_SECTIONED64) return B200KV_ERR_INVALID;
     if (!std::isfinite(theta) || !std::isfinite(epsilon) || (rope_mode != B200KV_ROPE_NONE && !(theta > 0.0f))) return B200KV_ERR_INVALID;
@@ -352,8 +387,8 @@ int b200kv_decode_step(const b200kv_view* view, const void* key, const void* val
         // no fused kernel for this cache: the two launches the fused one stands for
         rc = b200kv_append(view, key, value, kv_dtype, k_norm_weight, rope_mode, theta, epsilon, 1, position, nullptr, decode_state, stream);
         if (rc != B200KV_OK) return rc;
-        return b200kv_decode_attn(view, q, q_dtype, gate, output, gated_output, query_heads, scale, position + 1, decode_state,
-                                  workspace, workspace_bytes, num_splits, stream);
+        return b200kv_decode_attn(view, q, q_dtype, gate, output, gated_output, gated_output_q8, query_heads, scale, position + 1,
+                                  decode_state, workspace, workspace_bytes, num_splits, stream);
     }
     if ((rc = ensure_device()) != B200KV_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -385,6 +420,7 @@ int b200kv_decode_step(const b200kv_view* view, const void* key, const void* val
     mp.gate = gate;
     mp.output = output;
     mp.gated_output = gated_output;
+    mp.gated_output_q8 = gated_output_q8;
     return run_decode(p, *view, max_length, workspace, workspace_bytes, num_splits, mp, 1, s);
 }
 
@@ -418,10 +454,12 @@ int b200kv_decode_attn_batched(const b200kv_view* views, void* view_table, const
         for (uint32_t i = 0; i < sessions; ++i) {
             std::memset(&staged[i], 0, sizeof(SessionEntry));
             staged[i].view = views[i];
-            if (!q8_fast_path_ok(views[i], query_heads) || encode_kv_maps(views[i], &staged[i].kmap, &staged[i].vmap) != B200KV_OK) fast_ok = false;
+            if (!q8_fast_path_ok(views[i], query_heads) || encode_kv_maps(views[i], 16, &staged[i].kmap, &staged[i].vmap) != B200KV_OK ||
+                encode_kv_maps(views[i], 128, &staged[i].kmap128, &staged[i].vmap128) != B200KV_OK)
+                fast_ok = false;
         }
         if (!fast_ok)
-            for (uint32_t i = 0; i < sessions; ++i) std::memset(&staged[i].kmap, 0, 2 * sizeof(CUtensorMap));
+            for (uint32_t i = 0; i < sessions; ++i) std::memset(&staged[i].kmap, 0, 4 * sizeof(CUtensorMap));
         geometry_fast = fast_ok;
         B200KV_CUDA_TRY(cudaMemcpyAsync(view_table, staged.data(), sizeof(SessionEntry) * sessions, cudaMemcpyHostToDevice, s));
         B200KV_CUDA_TRY(cudaStreamSynchronize(s));
@@ -493,7 +531,7 @@ int b200kv_decode_partials(const b200kv_view* view, const void* q, int q_dtype, 
 }
 
 size_t b200kv_exchange_bytes(uint32_t query_heads, uint32_t head_dim, uint32_t world) {
-    // [2 phases][world][query_heads][head_dim + 2] tagged 8-byte words
+    // [2 slots][world][query_heads][head_dim + 2] tagged 8-byte words
     return static_cast<size_t>(2) * (world ? world : 1) * query_heads * (head_dim + 2u) * sizeof(uint64_t);
 }
 
@@ -508,7 +546,7 @@ int b200kv_decode_attn_sharded(const b200kv_view* view, const void* q, int q_dty
     if (q_dtype != B200KV_F16 && q_dtype != B200KV_F32) return B200KV_ERR_INVALID;
     if ((rc = check_heads(view, query_heads, scale)) != B200KV_OK) return rc;
     if (range_end > view->capacity || range_begin > range_end) return B200KV_ERR_RANGE;
-    if (world == 0 || world > static_cast<uint32_t>(kMaxExchangeRanks) || rank >= world || phase > 1) return B200KV_ERR_INVALID;
+    if (world == 0 || world > static_cast<uint32_t>(kMaxExchangeRanks) || rank >= world || phase == 0xffffffffu) return B200KV_ERR_INVALID;
     for (uint32_t w = 0; w < world; ++w)
         if (exchange[w] == nullptr || (reinterpret_cast<uintptr_t>(exchange[w]) & 15u) != 0) return B200KV_ERR_INVALID;
     // the exchange lives inside the streaming kernel; other cache modes use b200kv_decode_partials + a collective
@@ -535,6 +573,7 @@ int b200kv_decode_attn_sharded(const b200kv_view* view, const void* q, int q_dty
     mp.xchg.rank = rank;
     mp.xchg.world = world;
     mp.xchg.phase = phase;
+    mp.xchg.tag = phase + 1u;   // never 0
     // a shard may be empty (range_begin == range_end): the kernel still runs, contributes l = 0 and takes part in the exchange
     const uint32_t span = range_end - range_begin;
     return run_decode(p, *view, span ? span : 1, workspace, workspace_bytes, num_splits, mp, 1, s);

@@ -8,14 +8,17 @@
 namespace b200kv {
 
 // One session of a batched launch as it sits in the device-side view table: the
-// TMA descriptors of its int8 K and V planes followed by its view.
+// TMA descriptors of its int8 K and V planes (tiles of 16 positions for the warp-level mma kernel, of 128 for the
+// tcgen05 kernel) followed by its view.
 struct alignas(128) SessionEntry {
     CUtensorMap kmap;
     CUtensorMap vmap;
+    CUtensorMap kmap128;
+    CUtensorMap vmap128;
     b200kv_view view;
     uint8_t pad[128 - sizeof(b200kv_view)];
 };
-static_assert(sizeof(SessionEntry) == 384, "table entry layout");
+static_assert(sizeof(SessionEntry) == 640, "table entry layout");
 
 // Upper bound on split slots per launch: slots = sessions * splits_per_session.
 constexpr uint32_t kMaxSplitsPerSession = 128;
@@ -33,10 +36,12 @@ inline uint32_t max_splits_per_session(uint32_t sessions) {
 // head into slot [phase][rank] of EVERY buffer (peer stores over NVLink), then polls slot [phase][*] of its own
 // buffer, merges the `world` partials and zeroes them.  Consecutive launches on one exchange alternate `phase`:
 // a fast rank may already be writing the next launch's words while a slow one still reads this launch's.
+// Every word carries the call's tag (phase + 1, never 0) in its upper half: words of any other call, e.g. those a
+// rank stored after its peers had given up waiting for it, read as "not there yet".
 constexpr int kMaxExchangeRanks = 8;
 struct ExchangeParams {
     uint64_t* peers[kMaxExchangeRanks];
-    uint32_t rank, world, phase;
+    uint32_t rank, world, phase, tag;
 };
 
 struct MergeParams {
@@ -50,6 +55,7 @@ struct MergeParams {
     const float* gate;     // [groups][query_heads][d] or null
     float* output;         // normalised, or null
     float* gated_output;   // normalised * sigmoid(gate), or null
+    b200kv_q8_1_block* gated_output_q8;   // the gated output re-quantised to Q8_1 blocks of 32, or null
     float* out_m;          // when non-null: emit ONE merged partial per (group, head) instead
     float* out_l;
     float* out_acc;
@@ -93,8 +99,17 @@ struct DecodeParams {
     float inv_freq[64];                      // NeoX frequencies for d = 128
     uint32_t overlap_tail;                   // launch overlap: the last n positions of the range are read only after pdl_wait
     uint64_t* ws_tagged;
+    uint32_t tag;                            // tag of this launch's words in ws_tagged (never 0; differs from the previous launch's)
+    uint32_t* status;                        // device word that collects B200KV_STATUS_* bits of waits that ran out, or null
     MergeParams fuse;
 };
+
+// Tag for the tagged words of one launch: a process-wide counter that skips 0.
+uint32_t next_launch_tag();
+// The device status word registered with b200kv_set_status_word for the current device (null if none).
+uint32_t* current_status_word();
+// Which streaming kernel serves int8 caches: 0 = the tcgen05 kernel where it applies, 1 = the warp-level mma kernel.
+int streaming_kernel_choice();
 
 // The scanned range [begin, end) of one session, resolved on the device the way
 // the reference resolves its DeviceDecodeState (position + 1 entries,
@@ -141,10 +156,12 @@ int run_decode(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length
 // Fast path for int8 K and V (decode_q8.cu).  Returns B200KV_ERR_UNSUPPORTED when
 // the geometry has no specialised kernel, so the caller can use the generic one.
 int launch_decode_q8(const DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, cudaStream_t stream);
+// The same launch on the tcgen05 kernel (decode_tc5.cu); B200KV_ERR_UNSUPPORTED where it does not apply.
+int launch_decode_tc5(const DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, cudaStream_t stream);
 uint32_t pick_splits_q8(const b200kv_view& geometry, uint32_t query_heads, uint32_t sessions, uint32_t max_length);
 // TMA descriptors of a view's int8 K and V planes (rows of head_dim bytes, 128-byte swizzle).
 // B200KV_ERR_UNSUPPORTED when the view cannot take the streaming kernel (then the generic kernel is used).
-int encode_kv_maps(const b200kv_view& view, CUtensorMap* kmap, CUtensorMap* vmap);
+int encode_kv_maps(const b200kv_view& view, uint32_t tile_positions, CUtensorMap* kmap, CUtensorMap* vmap);
 bool q8_fast_path_ok(const b200kv_view& view, uint32_t query_heads);
 
 }  // namespace b200kv

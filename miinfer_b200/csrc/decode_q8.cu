@@ -46,8 +46,7 @@
 //    query head); the last CTA of a kv head to finish merges all splits.
 //  * Every wait is bounded: a copy that never arrives poisons the partial with
 //    NaN instead of hanging the GPU.
-#include "append_row.cuh"
-#include "decode_common.cuh"
+#include "decode_tail.cuh"
 
 #include <cstring>
 #include <mutex>
@@ -150,132 +149,9 @@ __device__ __forceinline__ uint32_t s8_odd_bytes_to_half2(uint32_t w) {
     const __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&r), __half2half2(__ushort_as_half(0x6480)));
     return *reinterpret_cast<const uint32_t*>(&h);
 }
-// Tagged partials: every float of a split's partial travels as one 8-byte word {value, tag = 1}.  An 8-byte store is
-// indivisible, so a reader that sees the tag also sees the value: no fence and no counter stand between the CTA that
-// produced a partial and the CTA that merges it.  Words are zero between launches; the merger zeroes what it consumed.
-__device__ __forceinline__ void st_tagged(uint64_t* dst, float v) {
-    const uint64_t w = (1ull << 32) | __float_as_uint(v);
-    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
-}
-__device__ __forceinline__ void ld_tagged2(const uint64_t* src, uint64_t& a, uint64_t& b) {
-    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(src) : "memory");
-}
-__device__ __forceinline__ bool tagged_ready(uint64_t a, uint64_t b) { return (a >> 32) != 0 && (b >> 32) != 0; }
-// the same words across GPUs: stores into a peer's memory, loads of words a peer stored into ours
-__device__ __forceinline__ void st_tagged_sys(uint64_t* dst, float v) {
-    const uint64_t w = (1ull << 32) | __float_as_uint(v);
-    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
-}
-__device__ __forceinline__ void ld_tagged2_sys(const uint64_t* src, uint64_t& a, uint64_t& b) {
-    asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(src) : "memory");
-}
-constexpr uint32_t kPollLimit = 1u << 17;   // polls of the merger (each a trip to L2) before it gives up and poisons the output
-constexpr int kPartialWords = kD + 2;       // acc[128], m, l
-
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
-}
-
-// ---- fused single-token append -----------------------------------------------------------------------------
-// Kept out of line so the rarely-taken path does not widen the register allocation of the streaming loops.
-// Loads the new row of `kv_head` (lane L: elements L, L+32, L+64, L+96).
-__device__ __noinline__ void load_new_row(const void* src, int is_f16, uint32_t kv_head, int lane, float (&x)[4]) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const size_t i = static_cast<size_t>(kv_head) * kD + lane + 32 * j;
-        x[j] = is_f16 ? __half2float(static_cast<const __half*>(src)[i]) : static_cast<const float*>(src)[i];
-    }
-}
-
-// Quantises the new K and V rows of `kv_head` (already in registers) and stores them (int8 + fp16 block scales) at
-// cache row `row_index`.
-template <int NBLK>
-__device__ __noinline__ void fused_append_row(const DecodeParams& p, const b200kv_view& view, float (&k)[4], float (&v)[4],
-                                              uint32_t position, uint64_t row_index, int lane) {
-    transform_k_row<kD>(k, lane, position, p.k_norm_weight, p.epsilon, p.rope_mode, p.inv_freq, p.sectioned_step);
-    int8_t kq[4], vq[4];
-    float ksc[4], vsc[4];
-    quantize_row<4>(k, NBLK == 1, kq, ksc);
-    quantize_row<4>(v, NBLK == 1, vq, vsc);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        view.key_q8[row_index * kD + lane + 32 * j] = kq[j];
-        view.value_q8[row_index * kD + lane + 32 * j] = vq[j];
-    }
-    if (lane < NBLK) {
-        static_cast<__half*>(view.key_scales)[row_index * NBLK + lane] = __float2half_rn(ksc[NBLK == 1 ? 0 : lane]);
-        static_cast<__half*>(view.value_scales)[row_index * NBLK + lane] = __float2half_rn(vsc[NBLK == 1 ? 0 : lane]);
-    }
-}
-
-// Cross-GPU step of a sequence-sharded launch, run by the 64 threads (pair of dims `pr`) that hold the merged
-// partial of `head`: store it into every rank's exchange buffer, wait (bounded) for the partials of all ranks in
-// our own buffer, merge them into (tot, gsum) and zero the words again.
-__device__ __forceinline__ void exchange_partials(const DecodeParams& p, uint32_t head, int pr, float m_local, float2& tot,
-                                               float& gsum, bool lost) {
-    // ---- sequence shard: exchange this rank's partial of the head with every rank and merge them all ----
-    const ExchangeParams& x = p.fuse.xchg;
-    const size_t words_per_rank = static_cast<size_t>(p.query_heads) * kPartialWords;
-    const size_t mine_off = (static_cast<size_t>(x.phase) * x.world + x.rank) * words_per_rank + static_cast<size_t>(head) * kPartialWords;
-    for (uint32_t w = 0; w < x.world; ++w) {
-        uint64_t* dst = x.peers[w] + mine_off;
-        st_tagged_sys(dst + 2 * pr, tot.x);
-        st_tagged_sys(dst + 2 * pr + 1, tot.y);
-        if (pr == 0) { st_tagged_sys(dst + kD, m_local); st_tagged_sys(dst + kD + 1, gsum); }
-    }
-    uint64_t* in = x.peers[x.rank] + static_cast<size_t>(x.phase) * x.world * words_per_rank + static_cast<size_t>(head) * kPartialWords;
-    float fa[kMaxExchangeRanks], fb[kMaxExchangeRanks], fm[kMaxExchangeRanks], fl[kMaxExchangeRanks];
-#pragma unroll
-    for (int w = 0; w < kMaxExchangeRanks; ++w) { fa[w] = fb[w] = 0.0f; fm[w] = -INFINITY; fl[w] = 0.0f; }
-    uint32_t pending = (1u << x.world) - 1u, ml_pending = pending;
-    for (uint32_t polls = 0; (pending | ml_pending) != 0 && !lost; ++polls) {
-        if (polls >= kPollLimit) { lost = true; break; }
-        // all loads first, all checks afterwards: a check between two loads would serialise their trips
-        uint64_t wa[kMaxExchangeRanks], wb[kMaxExchangeRanks], wm[kMaxExchangeRanks], wl[kMaxExchangeRanks];
-#pragma unroll
-        for (int w = 0; w < kMaxExchangeRanks; ++w) {
-            wa[w] = wb[w] = wm[w] = wl[w] = 0;
-            if (pending & (1u << w)) ld_tagged2_sys(in + w * words_per_rank + 2 * pr, wa[w], wb[w]);
-            if (ml_pending & (1u << w)) ld_tagged2_sys(in + w * words_per_rank + kD, wm[w], wl[w]);
-        }
-#pragma unroll
-        for (int w = 0; w < kMaxExchangeRanks; ++w) {
-            if ((pending & (1u << w)) && tagged_ready(wa[w], wb[w])) {
-                fa[w] = __uint_as_float(static_cast<uint32_t>(wa[w]));
-                fb[w] = __uint_as_float(static_cast<uint32_t>(wb[w]));
-                pending &= ~(1u << w);
-            }
-            if ((ml_pending & (1u << w)) && tagged_ready(wm[w], wl[w])) {
-                fm[w] = __uint_as_float(static_cast<uint32_t>(wm[w]));
-                fl[w] = __uint_as_float(static_cast<uint32_t>(wl[w]));
-                ml_pending &= ~(1u << w);
-            }
-        }
-    }
-    float M2 = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kMaxExchangeRanks; ++w)
-        if (!(fl[w] <= 0.0f) && fm[w] != -INFINITY) M2 = fmaxf(M2, fm[w]);   // ranks beyond `world` keep l = 0
-    float2 t2 = make_float2(0.0f, 0.0f);
-    float l2 = 0.0f;
-#pragma unroll
-    for (int w = 0; w < kMaxExchangeRanks; ++w) {
-        const float a = (!(fl[w] <= 0.0f) && fm[w] != -INFINITY) ? __expf(fm[w] - M2) : 0.0f;
-        l2 = fmaf(fl[w], a, l2);
-        t2.x = fmaf(fa[w], a, t2.x);
-        t2.y = fmaf(fb[w], a, t2.y);
-    }
-    if (lost) { t2.x = t2.y = l2 = __int_as_float(0x7fc00000); }
-    tot = t2;
-    gsum = l2;
-    // consumed: every thread zeroes its accumulator words; (m, l) only after all 64 threads have read them
-    for (uint32_t w = 0; w < x.world; ++w)
-        asm volatile("st.global.v2.u64 [%0], {%1,%1};" ::"l"(in + w * words_per_rank + 2 * pr), "l"(0ull) : "memory");
-    asm volatile("bar.sync 1, 64;" ::: "memory");
-    if (pr == 0)
-        for (uint32_t w = 0; w < x.world; ++w)
-            asm volatile("st.global.v2.u64 [%0], {%1,%1};" ::"l"(in + w * words_per_rank + kD), "l"(0ull) : "memory");
 }
 
 // G query heads per kv head (1, 2 or 4); NBLK scales per row (4 = q8_0 blocks of 32, 1 = one per row).
@@ -366,8 +242,8 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     // is streaming, a dependent load waits behind tens of megabytes of queued tile traffic (microseconds).
     float new_k[4], new_v[4];
     if (owner) {
-        load_new_row(p.new_key, p.new_is_f16, kv_head, lane, new_k);
-        load_new_row(p.new_value, p.new_is_f16, kv_head, lane, new_v);
+        tail::load_new_row(p.new_key, p.new_is_f16, kv_head, lane, new_k);
+        tail::load_new_row(p.new_value, p.new_is_f16, kv_head, lane, new_v);
     }
     {
         // the tile that holds the row of a fused append is loaded only after that row has been stored (below)
@@ -414,7 +290,7 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
     if (owner) {
         // After the barrier, so that only this warp (which was handed fewer tiles) pays for the append.  The new row
         // goes to the cache first; its tile is loaded (by TMA, an asynchronous-proxy read) only afterwards.
-        fused_append_row<NBLK>(p, view, new_k, new_v, end - 1, head_row0 + end - 1, lane);
+        tail::fused_append_row<NBLK>(p, view, new_k, new_v, end - 1, head_row0 + end - 1, lane);
         __threadfence();
         asm volatile("fence.proxy.async;" ::: "memory");
         __syncwarp();
@@ -620,7 +496,6 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
 
     // ---- merge the CTA's warps: 256 threads = 2 head slots x 128 dims ---------------------------------------
     const int dim = threadIdx.x & (kD - 1);
-    const bool tagged = p.ws_tagged != nullptr;   // fused merge: partials go out as tagged words
     for (int h = threadIdx.x >> 7; h < G; h += 2) {
         float mw[kWarps], M = -INFINITY;
 #pragma unroll
@@ -638,166 +513,13 @@ decode_q8_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__
             at = fmaf(src[h * kD + dim] + src[(4 + h) * kD + dim], a, at);
         }
         const uint32_t head = kv_head * G + h;
-        const size_t slot_idx = (static_cast<size_t>(session) * p.num_splits + split) * p.query_heads + head;
         const float m_nat = M * 0.6931471805599453f;   // natural-log units, as the merge expects
-        if (tagged && num_splits == 1 && p.fuse.xchg.world <= 1) {
-            // a single split has nothing to merge with: the result leaves from here (short contexts)
-            const size_t out_idx = (static_cast<size_t>(session) * p.query_heads + head) * kD + dim;
-            if (p.fuse.out_m != nullptr) {
-                p.fuse.out_acc[out_idx] = at;
-                if (dim == 0) {
-                    p.fuse.out_m[static_cast<size_t>(session) * p.query_heads + head] = m_nat;
-                    p.fuse.out_l[static_cast<size_t>(session) * p.query_heads + head] = lt;
-                }
-            } else {
-                const float inv = lt > 0.0f ? 1.0f / lt : (lt == lt ? 0.0f : lt);
-                float o = at * inv;
-                if (p.fuse.output != nullptr) p.fuse.output[out_idx] = o;
-                if (p.fuse.gated_output != nullptr) {
-                    if (p.fuse.gate != nullptr) o *= 1.0f / (1.0f + __expf(-p.fuse.gate[out_idx]));
-                    p.fuse.gated_output[out_idx] = o;
-                }
-            }
-        } else if (tagged) {
-            uint64_t* dst = p.ws_tagged + slot_idx * kPartialWords;
-            st_tagged(dst + dim, at);
-            if (dim == 0) { st_tagged(dst + kD, m_nat); st_tagged(dst + kD + 1, lt); }
-        } else {
-            p.ws_acc[slot_idx * kD + dim] = at;
-            if (dim == 0) { p.ws_m[slot_idx] = m_nat; p.ws_l[slot_idx] = lt; }
-        }
+        tail::emit_partial(p, session, split, num_splits, head, dim, at, m_nat, lt);
     }
-    if (!tagged) return;   // a separate merge kernel follows
-
-    // ---- fused merge: the CTA of split h merges query head h of this kv head (h, h + splits, ... if there are fewer
-    // splits than heads).  It polls the tagged partials of all splits -- normally they are all there by the time it
-    // has finished its own share -- and every other CTA simply leaves.
-    if (split >= static_cast<uint32_t>(G) || (num_splits == 1 && p.fuse.xchg.world <= 1)) return;
-    const uint32_t S = num_splits;     // <= kMaxSplitsPerSession == 128; the partial arrays keep the launch-wide stride
-    float* fold_ml = reinterpret_cast<float*>(smem + L::kOffMisc);   // [3] x {max, sum} of split groups 1..3
-    float2* fold = reinterpret_cast<float2*>(fold_ml + 8);          // [3][64] partial sums of split groups 1..3
-    constexpr int kBatch = 10;   // splits per thread and round: 4 groups x 10 = 40 splits in one trip to L2
-    // 256 threads = 4 split groups (sp % 4) x 64 pairs of dims.  A group merges its own splits on line (every thread
-    // of a group also reads the group's (m, l) words itself: no staging, no barrier), then the 4 groups are folded.
-    const int grp = threadIdx.x >> 6, pr = threadIdx.x & 63;
-    for (uint32_t h = split; h < static_cast<uint32_t>(G); h += S) {
-        const uint32_t head = kv_head * G + h;
-        const size_t stride = static_cast<size_t>(p.query_heads) * kPartialWords;   // words between consecutive splits
-        uint64_t* base = p.ws_tagged + ((static_cast<size_t>(session) * p.num_splits) * p.query_heads + head) * kPartialWords;
-        bool lost = false;
-        float2 tot = make_float2(0.0f, 0.0f);
-        float Mg = -INFINITY, lg = 0.0f;
-        for (uint32_t sp0 = 0; sp0 < S; sp0 += 4 * kBatch) {
-            // Poll in rounds: every round re-issues, back to back, the loads of all words of this thread that have
-            // not shown their tag yet, so that once the last partial has landed one trip to L2 completes the set.
-            float fa[kBatch], fb[kBatch], fm[kBatch], fl[kBatch];
-            uint32_t pending = 0;
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                fa[u] = fb[u] = fl[u] = 0.0f;
-                fm[u] = -INFINITY;
-                if (sp0 + grp + 4 * u < S) pending |= 1u << u;
-            }
-            uint32_t ml_pending = pending;
-            for (uint32_t polls = 0; (pending | ml_pending) != 0 && !lost; ++polls) {
-                if (polls >= kPollLimit) { lost = true; break; }
-                // all loads first, all checks afterwards: a check between two loads would serialise their trips
-                uint64_t wa[kBatch], wb[kBatch], wm[kBatch], wl[kBatch];
-#pragma unroll
-                for (int u = 0; u < kBatch; ++u) {
-                    uint64_t* src = base + (sp0 + grp + 4 * u) * stride;
-                    wa[u] = wb[u] = wm[u] = wl[u] = 0;
-                    if (pending & (1u << u)) ld_tagged2(src + 2 * pr, wa[u], wb[u]);
-                    if (ml_pending & (1u << u)) ld_tagged2(src + kD, wm[u], wl[u]);
-                }
-#pragma unroll
-                for (int u = 0; u < kBatch; ++u) {
-                    if ((pending & (1u << u)) && tagged_ready(wa[u], wb[u])) {
-                        fa[u] = __uint_as_float(static_cast<uint32_t>(wa[u]));
-                        fb[u] = __uint_as_float(static_cast<uint32_t>(wb[u]));
-                        pending &= ~(1u << u);
-                    }
-                    if ((ml_pending & (1u << u)) && tagged_ready(wm[u], wl[u])) {
-                        fm[u] = __uint_as_float(static_cast<uint32_t>(wm[u]));
-                        fl[u] = __uint_as_float(static_cast<uint32_t>(wl[u]));
-                        ml_pending &= ~(1u << u);
-                    }
-                }
-            }
-            float Mr = Mg;
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u)
-                if (!(fl[u] <= 0.0f) && fm[u] != -INFINITY) Mr = fmaxf(Mr, fm[u]);   // keeps NaN partials in play
-            const float keep = (Mg == -INFINITY) ? 0.0f : __expf(Mg - Mr);
-            tot.x *= keep; tot.y *= keep; lg *= keep;
-            Mg = Mr;
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const float a = (!(fl[u] <= 0.0f) && fm[u] != -INFINITY) ? __expf(fm[u] - Mg) : 0.0f;
-                lg = fmaf(fl[u], a, lg);
-                tot.x = fmaf(fa[u], a, tot.x);
-                tot.y = fmaf(fb[u], a, tot.y);
-            }
-            // consumed: accumulator words by the thread that read them; (m, l) words are read by all 64 threads of
-            // the group, so they are zeroed after the fold barrier below
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u)
-                if (sp0 + grp + 4 * u < S)
-                    asm volatile("st.global.v2.u64 [%0], {%1,%1};" ::"l"(base + (sp0 + grp + 4 * u) * stride + 2 * pr), "l"(0ull) : "memory");
-        }
-        if (lost) tot.x = tot.y = lg = __int_as_float(0x7fc00000);
-        // fold the 4 split groups through shared memory
-        if (grp > 0) {
-            fold[(grp - 1) * 64 + pr] = tot;
-            if (pr == 0) { fold_ml[2 * (grp - 1)] = Mg; fold_ml[2 * (grp - 1) + 1] = lg; }
-        }
-        __syncthreads();
-        for (uint32_t sp = threadIdx.x; sp < S; sp += blockDim.x)   // every thread of every group is past its polls
-            asm volatile("st.global.v2.u64 [%0], {%1,%1};" ::"l"(base + sp * stride + kD), "l"(0ull) : "memory");
-        if (grp == 0) {
-            float M = Mg;
-#pragma unroll
-            for (int k = 0; k < 3; ++k) {
-                const float mk = fold_ml[2 * k], lk = fold_ml[2 * k + 1];
-                if (!(lk <= 0.0f) && mk != -INFINITY) M = fmaxf(M, mk);
-            }
-            {
-                const float a0 = (!(lg <= 0.0f) && Mg != -INFINITY) ? __expf(Mg - M) : 0.0f;
-                tot.x *= a0; tot.y *= a0; lg *= a0;
-            }
-#pragma unroll
-            for (int k = 0; k < 3; ++k) {
-                const float mk = fold_ml[2 * k], lk = fold_ml[2 * k + 1];
-                const float a = (!(lk <= 0.0f) && mk != -INFINITY) ? __expf(mk - M) : 0.0f;
-                const float2 o2 = fold[k * 64 + pr];
-                tot.x = fmaf(o2.x, a, tot.x); tot.y = fmaf(o2.y, a, tot.y);
-                lg = fmaf(lk, a, lg);
-            }
-            float gsum = lg;
-            const float m_merged = M;
-            if (p.fuse.xchg.world > 1) exchange_partials(p, head, pr, m_merged, tot, gsum, lost);
-            const size_t out_idx = (static_cast<size_t>(session) * p.query_heads + head) * kD + 2 * pr;
-            if (p.fuse.out_m != nullptr) {   // sequence shard: one merged, unnormalised partial
-                *reinterpret_cast<float2*>(p.fuse.out_acc + out_idx) = tot;
-                if (pr == 0) {
-                    p.fuse.out_m[static_cast<size_t>(session) * p.query_heads + head] = m_merged;
-                    p.fuse.out_l[static_cast<size_t>(session) * p.query_heads + head] = gsum;
-                }
-            } else {
-                const float inv = gsum > 0.0f ? 1.0f / gsum : (gsum == gsum ? 0.0f : gsum);
-                float2 o = make_float2(tot.x * inv, tot.y * inv);
-                if (p.fuse.output != nullptr) *reinterpret_cast<float2*>(p.fuse.output + out_idx) = o;
-                if (p.fuse.gated_output != nullptr) {
-                    if (p.fuse.gate != nullptr) {
-                        const float2 gt = *reinterpret_cast<const float2*>(p.fuse.gate + out_idx);
-                        o.x *= 1.0f / (1.0f + __expf(-gt.x)); o.y *= 1.0f / (1.0f + __expf(-gt.y));
-                    }
-                    *reinterpret_cast<float2*>(p.fuse.gated_output + out_idx) = o;
-                }
-            }
-        }
-        __syncthreads();   // the fold area is reused by the next head of this CTA
-    }
+    if (failed) tail::report(p, B200KV_STATUS_COPY_TIMEOUT);
+    if (p.ws_tagged == nullptr) return;   // a separate merge kernel follows
+    // the CTA of split h merges query head h of this kv head once all splits' tagged partials have landed
+    tail::fused_merge(p, session, kv_head, split, num_splits, G, reinterpret_cast<float*>(smem + L::kOffMisc));
 }
 
 // ---- host side -----------------------------------------------------------------------------------------
@@ -824,11 +546,8 @@ EncodeFn encoder() {
 template <int G, int NBLK, bool Q_F16>
 int launch_one(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap, dim3 grid, cudaStream_t stream) {
     using L = Smem<NBLK>;
-    static std::once_flag once;   // one per kernel instantiation
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(decode_q8_kernel<G, NBLK, Q_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc);
-    });
+    static std::atomic<uint64_t> done{0};   // one per kernel instantiation: devices that have opted in
+    const cudaError_t attr_err = opt_in_dynamic_smem(reinterpret_cast<const void*>(decode_q8_kernel<G, NBLK, Q_F16>), L::kAlloc, done);
     if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err, "cudaFuncSetAttribute(decode_q8)"); return B200KV_ERR_CUDA; }
     B200KV_CUDA_TRY(launch_kernel(decode_q8_kernel<G, NBLK, Q_F16>, grid, dim3(kWarps * 32), L::kAlloc, stream, true, p, kmap, vmap));
     return B200KV_OK;
@@ -853,12 +572,12 @@ bool q8_fast_path_ok(const b200kv_view& view, uint32_t query_heads) {
 }
 
 namespace {
-int encode_plane_map(int8_t* plane, const b200kv_view& view, CUtensorMap* out) {
+int encode_plane_map(int8_t* plane, const b200kv_view& view, uint32_t tile_positions, CUtensorMap* out) {
     EncodeFn fn = encoder();
     if (fn == nullptr) return B200KV_ERR_UNSUPPORTED;
     const cuuint64_t dims[2] = {kD, static_cast<cuuint64_t>(view.kv_heads) * view.capacity};
     const cuuint64_t strides[1] = {kD};
-    const cuuint32_t box[2] = {kD, kTile};
+    const cuuint32_t box[2] = {kD, tile_positions};
     const cuuint32_t elem[2] = {1, 1};
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, plane, dims, strides, box, elem,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -867,9 +586,9 @@ int encode_plane_map(int8_t* plane, const b200kv_view& view, CUtensorMap* out) {
 }
 }  // namespace
 
-int encode_kv_maps(const b200kv_view& view, CUtensorMap* kmap, CUtensorMap* vmap) {
-    int rc = encode_plane_map(view.key_q8, view, kmap);
-    if (rc == B200KV_OK) rc = encode_plane_map(view.value_q8, view, vmap);
+int encode_kv_maps(const b200kv_view& view, uint32_t tile_positions, CUtensorMap* kmap, CUtensorMap* vmap) {
+    int rc = encode_plane_map(view.key_q8, view, tile_positions, kmap);
+    if (rc == B200KV_OK) rc = encode_plane_map(view.value_q8, view, tile_positions, vmap);
     return rc;
 }
 
@@ -904,7 +623,7 @@ int launch_decode_q8(const DecodeParams& p_in, const b200kv_view& geometry, uint
     if (p.split_positions < 256u) p.split_positions = 256u;
     CUtensorMap kmap, vmap;
     if (p.views == nullptr) {
-        int rc = encode_kv_maps(geometry, &kmap, &vmap);
+        int rc = encode_kv_maps(geometry, kTile, &kmap, &vmap);
         if (rc != B200KV_OK) return rc;
     } else {
         std::memset(&kmap, 0, sizeof kmap);   // per-session descriptors come from the device table

@@ -71,10 +71,10 @@ int b200kv_decode_attn_static(const b200kv_view* view, const void* q, int q_dtyp
     if ((rc = scratch_for_current_device(&scratch)) != B200KV_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-    // Every call shares the array and it keeps what the previous call left.  The tagged words in its front part
-    // must be zero when a launch starts; launches leave them zero, and clearing them here as well keeps one
-    // failed launch from spoiling the next (the plain partials behind them are rewritten before they are read).
-    B200KV_CUDA_TRY(cudaMemsetAsync(scratch, 0, workspace_plain_offset(kStaticScratchBytes), s));
+    // Every call shares the array and it keeps what the previous call left.  Nothing has to be cleared here: the
+    // array starts out zero (static storage), every launch zeroes the tagged words it consumed, and words that a
+    // launch which gave up left behind carry that launch's tag, which no later launch accepts; the plain
+    // partials behind the tagged part are rewritten before they are read.
 
     DecodeParams p{};
     p.view = *view;

@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 
@@ -51,6 +52,10 @@ cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     }
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
+
+// Kernels that need more than 48 KB of dynamic shared memory opt in once PER DEVICE (the attribute belongs to the
+// device's context): `done_mask` is the kernel's own bit set of the device ordinals already done.
+cudaError_t opt_in_dynamic_smem(const void* kernel, int bytes, std::atomic<uint64_t>& done_mask);
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

@@ -1,9 +1,10 @@
 // Library plumbing: status strings, device guard, view validation and the
 // owning cache storage object (the counterpart of MIInfer's
 // AttentionLayerKvCacheStorage, src/prefill_v2/kv_cache.cpp:10-130).
-#include "kv_common.cuh"
+#include "decode_common.cuh"
 
 #include <atomic>
+#include <mutex>
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -14,6 +15,38 @@ static thread_local char g_last_error[256] = "";
 static std::atomic<uint32_t> g_overlap_tail{0};
 
 uint32_t launch_overlap_tail() { return g_overlap_tail.load(std::memory_order_relaxed); }
+
+static std::atomic<uint32_t> g_launch_tag{0};
+uint32_t next_launch_tag() {
+    uint32_t t = g_launch_tag.fetch_add(1, std::memory_order_relaxed) + 1;
+    if (t == 0) t = g_launch_tag.fetch_add(1, std::memory_order_relaxed) + 1;   // the counter wrapped: 0 means "no word"
+    return t;
+}
+
+constexpr int kMaxDevices = 64;
+static std::atomic<uint32_t*> g_status_word[kMaxDevices] = {};
+uint32_t* current_status_word() {
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    return g_status_word[device].load(std::memory_order_relaxed);
+}
+
+static std::atomic<int> g_streaming_kernel{0};
+int streaming_kernel_choice() { return g_streaming_kernel.load(std::memory_order_relaxed); }
+
+cudaError_t opt_in_dynamic_smem(const void* kernel, int bytes, std::atomic<uint64_t>& done_mask) {
+    int device = -1;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) return err;
+    const bool tracked = device >= 0 && device < 64;
+    if (tracked && (done_mask.load(std::memory_order_acquire) >> device) & 1ull) return cudaSuccess;
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (err == cudaSuccess && tracked) done_mask.fetch_or(1ull << device, std::memory_order_release);
+    return err;
+}
 
 void set_last_cuda_error(cudaError_t err, const char* where) {
     std::snprintf(g_last_error, sizeof g_last_error, "%s: %s (%s)", cudaGetErrorName(err),
@@ -69,6 +102,31 @@ int b200kv_version(void) { return B200KV_VERSION; }
 
 int b200kv_set_launch_overlap(uint32_t tail_positions) {
     g_overlap_tail.store(tail_positions, std::memory_order_relaxed);
+    return B200KV_OK;
+}
+
+int b200kv_set_status_word(uint32_t* device_word) {
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
+        (void)cudaGetLastError();
+        return B200KV_ERR_DEVICE;
+    }
+    if ((reinterpret_cast<uintptr_t>(device_word) & 3u) != 0) return B200KV_ERR_INVALID;
+    g_status_word[device].store(device_word, std::memory_order_relaxed);
+    return B200KV_OK;
+}
+
+int b200kv_set_decode_kernel(int choice) {
+    if (choice < 0 || choice > 1) return B200KV_ERR_INVALID;
+    g_streaming_kernel.store(choice, std::memory_order_relaxed);
+    return B200KV_OK;
+}
+
+int b200kv_workspace_reset(void* workspace, size_t workspace_bytes, void* stream) {
+    if (workspace == nullptr) return B200KV_ERR_INVALID;
+    int rc = ensure_device();
+    if (rc != B200KV_OK) return rc;
+    B200KV_CUDA_TRY(cudaMemsetAsync(workspace, 0, workspace_bytes, static_cast<cudaStream_t>(stream)));
     return B200KV_OK;
 }
 

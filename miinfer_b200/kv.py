@@ -22,6 +22,7 @@ __all__ = [
     "launch_kv_store_quant", "launch_decode_attention_quant", "launch_decode_attention_batched", "launch_decode_step",
     "launch_decode_partials", "launch_merge_partials", "launch_merge_partials_packed", "packed_partial", "partial_views", "launch_suffix_attention_quant",
     "Exchange", "launch_decode_attention_sharded", "decode_workspace", "prefill_workspace", "view_table", "make_decode_state", "make_prefill_state",
+    "launch_q_split_norm_rope", "launch_decode_state_advance", "q8_1_blocks", "exchange_words", "set_status_word", "workspace_reset", "set_decode_kernel",
     "token_sequence_hash", "save_session", "load_session", "find_matching_session", "decode_kernel_kind", "set_launch_overlap", "B200KvError", "FORCE_GENERIC",
 ]
 
@@ -195,13 +196,32 @@ def launch_kv_store_quant(view: View, key: torch.Tensor, value: torch.Tensor, k_
                             _stream(stream)), "b200kv_append")
 
 
+def launch_q_split_norm_rope(qfull: torch.Tensor, q_norm_weight: Optional[torch.Tensor], query: torch.Tensor,
+                             gate: Optional[torch.Tensor], token_count: int, base_position: int, *, heads: int, head_dim: int,
+                             rope_mode: RopeMode = RopeMode.SECTIONED64, theta: float = 1.0e6, epsilon: float = 1.0e-6,
+                             prefill_state: Optional[torch.Tensor] = None, decode_state: Optional[torch.Tensor] = None,
+                             stream: Optional[torch.cuda.Stream] = None) -> None:
+    """launch_qwen35_decoupled_q_split_norm_rope_batch / launch_qwen35_fused_q_split_norm_rope_dynamic
+    (qwen3_gpu_primitives.hpp:869-881, 934-938): qfull [token][heads][q | gate] -> query, gate [token][heads][d]."""
+    check(lib.b200kv_q_split_norm_rope(_ptr(qfull), _dtype(qfull), _ptr(q_norm_weight), _ptr(query), _dtype(query), _ptr(gate),
+                                       token_count, base_position, heads, head_dim, int(rope_mode), theta, epsilon,
+                                       _ptr(prefill_state), _ptr(decode_state), _stream(stream)), "b200kv_q_split_norm_rope")
+
+
+def launch_decode_state_advance(state: torch.Tensor, token_output: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> None:
+    """launch_qwen35_decode_state_advance (qwen3_gpu_primitives.hpp:1248-1250): device-side position/generated advance."""
+    check(lib.b200kv_decode_state_advance(_ptr(state), _ptr(token_output), token_output.numel(), _stream(stream)),
+          "b200kv_decode_state_advance")
+
+
 def launch_decode_attention_quant(view: View, q: torch.Tensor, *, query_heads: int, scale: float,
                                   cache_length: int = 0, decode_state: Optional[torch.Tensor] = None,
                                   output: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                                  gated_output: Optional[torch.Tensor] = None, workspace: torch.Tensor,
-                                  num_splits: int = 0, stream: Optional[torch.cuda.Stream] = None) -> None:
-    """launch_qwen35_tiled_online_attention_quant_dynamic (qwen3_gpu_primitives.hpp:719-739)."""
-    check(lib.b200kv_decode_attn(C.byref(view), _ptr(q), _dtype(q), _ptr(gate), _ptr(output), _ptr(gated_output),
+                                  gated_output: Optional[torch.Tensor] = None, gated_output_q8: Optional[torch.Tensor] = None,
+                                  workspace: torch.Tensor, num_splits: int = 0, stream: Optional[torch.cuda.Stream] = None) -> None:
+    """launch_qwen35_tiled_online_attention_quant_dynamic (qwen3_gpu_primitives.hpp:719-739).
+    gated_output_q8: uint8 tensor of query_heads * head_dim / 32 Q8_1 blocks (36 bytes each), see `q8_1_blocks`."""
+    check(lib.b200kv_decode_attn(C.byref(view), _ptr(q), _dtype(q), _ptr(gate), _ptr(output), _ptr(gated_output), _ptr(gated_output_q8),
                                  query_heads, scale, cache_length, _ptr(decode_state), _ptr(workspace),
                                  workspace.numel(), num_splits, _stream(stream)), "b200kv_decode_attn")
 
@@ -210,14 +230,15 @@ def launch_decode_step(view: View, key: torch.Tensor, value: torch.Tensor, q: to
                        position: int = 0, decode_state: Optional[torch.Tensor] = None, k_norm_weight: Optional[torch.Tensor] = None,
                        rope_mode: RopeMode = RopeMode.NEOX_FULL, theta: float = 1.0e6, epsilon: float = 1.0e-6,
                        output: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                       gated_output: Optional[torch.Tensor] = None, workspace: torch.Tensor, num_splits: int = 0,
-                       stream: Optional[torch.cuda.Stream] = None) -> None:
+                       gated_output: Optional[torch.Tensor] = None, gated_output_q8: Optional[torch.Tensor] = None,
+                       workspace: torch.Tensor, num_splits: int = 0, stream: Optional[torch.cuda.Stream] = None) -> None:
     """Append one token and attend in one launch (b200kv_decode_step): the fused form of the store + decode-attention
     call pair of src/prefill_v2/attention_layer.cpp:599-632."""
     if key.dtype != value.dtype:
         raise ValueError("key and value must share a dtype")
     check(lib.b200kv_decode_step(C.byref(view), _ptr(key), _ptr(value), _dtype(key), _ptr(k_norm_weight), int(rope_mode), theta,
-                                 epsilon, _ptr(q), _dtype(q), _ptr(gate), _ptr(output), _ptr(gated_output), query_heads, scale,
+                                 epsilon, _ptr(q), _dtype(q), _ptr(gate), _ptr(output), _ptr(gated_output), _ptr(gated_output_q8),
+                                 query_heads, scale,
                                  position, _ptr(decode_state), _ptr(workspace), workspace.numel(), num_splits, _stream(stream)),
           "b200kv_decode_step")
 
@@ -353,6 +374,36 @@ def launch_suffix_attention_quant(view: View, q: torch.Tensor, gate: Optional[to
     check(lib.b200kv_prefill_attn(C.byref(view), _ptr(q), _dtype(q), _ptr(gate), _ptr(gated_output), token_count,
                                   base_position, query_heads, scale, _ptr(prefill_state), _ptr(workspace),
                                   0 if workspace is None else workspace.numel(), _stream(stream)), "b200kv_prefill_attn")
+
+
+def q8_1_blocks(query_heads: int, head_dim: int, device=None) -> torch.Tensor:
+    """Room for the Q8_1 form of one decode output: query_heads * head_dim / 32 blocks of 36 bytes
+    (fp16 d, fp16 s, 32 int8; Q8_1Block, include/miinfer/q4_q8_gemv.hpp:23-27)."""
+    return torch.zeros(query_heads * head_dim // 32, 36, dtype=torch.uint8, device=device or "cuda")
+
+
+def exchange_words(values: torch.Tensor, phase: int) -> torch.Tensor:
+    """fp32 values as the 8-byte words of call number `phase` of a sequence-sharded exchange: the value in the low
+    half, the call's tag (phase + 1) in the high half.  Tests use it to play a peer's part."""
+    bits = values.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    return bits | ((int(phase) + 1) << 32)
+
+
+def set_status_word(word: Optional[torch.Tensor]) -> None:
+    """b200kv_set_status_word: register a device int32 word (or None) that collects the timeout bits of later launches."""
+    check(lib.b200kv_set_status_word(None if word is None else word.data_ptr()), "b200kv_set_status_word")
+
+
+STATUS_COPY_TIMEOUT, STATUS_SPLIT_TIMEOUT, STATUS_PEER_TIMEOUT, STATUS_PIPE_TIMEOUT = 1, 2, 4, 8
+
+
+def workspace_reset(workspace: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> None:
+    check(lib.b200kv_workspace_reset(_ptr(workspace), workspace.numel() * workspace.element_size(), _stream(stream)), "b200kv_workspace_reset")
+
+
+def set_decode_kernel(choice: int) -> None:
+    """b200kv_set_decode_kernel: 0 = tcgen05 streaming kernel where it applies (default), 1 = warp-level mma kernel."""
+    check(lib.b200kv_set_decode_kernel(int(choice)), "b200kv_set_decode_kernel")
 
 
 def set_launch_overlap(tail_positions: int) -> None:

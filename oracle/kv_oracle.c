@@ -534,6 +534,70 @@ KVO_API void kvo_merge_partials(const float* part_m, const float* part_l, const 
     }
 }
 
+/* Re-quantisation of a decode output row to Q8_1 blocks of 32 for the projection that follows, as the
+ * reference's stage 2 does it (qwen3_splitk_stage2_kernel, .hip:2354-2383): scale = amax / 127,
+ * q = roundf(x * (1 / scale)) clamped to [-127, 127] (half away from zero, unlike the cache quantizer),
+ * d = fp16(scale), s = fp16((float)sum(q) * scale).  Block layout: Q8_1Block,
+ * include/miinfer/q4_q8_gemv.hpp:23-27 (fp16 d, fp16 s, 32 int8 = 36 bytes).  x: fp32 [count], count % 32 == 0. */
+KVO_API void kvo_quantize_q8_1(const float* x, size_t count, uint8_t* blocks) {
+    for (size_t b = 0; b < count / 32; ++b) {
+        const float* v = x + b * 32;
+        float amax = 0.0f;
+        for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        const float scale = amax / 127.0f;
+        const float inv = scale != 0.0f ? 1.0f / scale : 0.0f;
+        int sum = 0;
+        int8_t* qs = (int8_t*)(blocks + b * 36 + 4);
+        for (int i = 0; i < 32; ++i) {
+            int q = (int)roundf(v[i] * inv);
+            q = q < -127 ? -127 : (q > 127 ? 127 : q);
+            qs[i] = (int8_t)q;
+            sum += q;
+        }
+        const uint16_t d = kvo_float_to_half_rn(scale), sh = kvo_float_to_half_rn((float)sum * scale);
+        memcpy(blocks + b * 36, &d, 2);
+        memcpy(blocks + b * 36 + 2, &sh, 2);
+    }
+}
+
+/* Query side of an attention layer: de-interleave the projection output [token][heads][q (d) | gate (d)],
+ * RMSNorm * weight on q (same binary-tree sum of squares as the store kernel), RoPE at base_position + token,
+ * write q and gate as [token][heads][d].  Follows qwen35_decoupled_q_split_norm_rope_batch_kernel
+ * (.hip:994-1045) and its single-token twin qwen35_fused_q_split_norm_rope_kernel (.hip:661-717); the norm, the
+ * RoPE and the deviations (1/sqrtf, pinned trig) are exactly those of kvo_append, so Q and K are rotated by
+ * identical bits.  q_norm_weight may be NULL (no norm), rope_mode as kvo_append. */
+KVO_API void kvo_q_split_norm_rope(const float* qfull, const float* q_norm_weight, float* query_rope, float* gate,
+                                   uint32_t token_count, uint32_t base_position, uint32_t heads, uint32_t head_dim,
+                                   int rope_mode, float theta, float epsilon, int trig_mode) {
+    const uint32_t d = head_dim;
+    float* scratch = (float*)malloc(sizeof(float) * d);
+    for (uint32_t t = 0; t < token_count; ++t)
+        for (uint32_t h = 0; h < heads; ++h) {
+            const float* src = qfull + ((size_t)t * heads + h) * 2 * d;
+            float* row = query_rope + ((size_t)t * heads + h) * d;
+            if (gate) memcpy(gate + ((size_t)t * heads + h) * d, src + d, sizeof(float) * d);
+            if (q_norm_weight) {
+                float ss = kvo_tree_sum_squares(src, d, scratch);
+                float r = 1.0f / sqrtf(ss / (float)d + epsilon);
+                for (uint32_t i = 0; i < d; ++i) row[i] = src[i] * r * q_norm_weight[i];
+            } else {
+                memcpy(row, src, sizeof(float) * d);
+            }
+            kvo_rope_row(row, d, base_position + t, theta, rope_mode, trig_mode);
+        }
+    free(scratch);
+}
+
+/* Device-side step bookkeeping of a replayed decode graph: qwen35_decode_state_advance_kernel, .hip:4417-4428.
+ * state: the 16 words of a DeviceDecodeState {current_token, position, generated, stop, max_generated, ...}. */
+KVO_API void kvo_decode_state_advance(uint32_t* state, uint32_t* token_output, uint32_t capacity) {
+    const uint32_t generated = state[2];
+    if (generated < capacity) token_output[generated] = state[0];
+    state[3] = (state[3] || state[0] == 151643u || state[0] == 151645u || generated + 1 >= state[4]) ? 1u : 0u;
+    state[1] += 1;
+    state[2] = generated + 1;
+}
+
 /* Split-K decode end to end in kernel order (stage 1 + stage 2). */
 KVO_API void kvo_decode_attn_splitk(const kvo_view* view, const float* q, const float* gate, float* out,
                                     float* gated_out, uint32_t query_heads, float scale, uint64_t length,

@@ -50,3 +50,21 @@ def assert_planes_equal(st: kv.AttentionLayerKvCacheStorage, host: ko.HostCache,
 def to_dev(a: np.ndarray, dtype=None) -> torch.Tensor:
     t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
     return t if dtype is None else t.to(dtype)
+
+
+def attention_error(got: np.ndarray, ref: np.ndarray):
+    """(max-abs, relative L2) of an attention output against the oracle's."""
+    diff = got.astype(np.float64) - ref.astype(np.float64)
+    return float(np.max(np.abs(diff))), float(np.linalg.norm(diff) / max(np.linalg.norm(ref.astype(np.float64)), 1e-30))
+
+
+def assert_attention_close(got: np.ndarray, ref: np.ndarray, what: str, tol_abs: float = 2.0e-3, tol_rel: float = 1.0e-3):
+    """Two gates: the absolute one the path's specification states (max-abs 2e-3 against the fp32-accumulated
+    reference) and a relative one (relative L2), because at long contexts the outputs themselves are of the order
+    of 1e-2 and the absolute gate alone would pass a visibly wrong result.  The measured errors are printed."""
+    assert np.isfinite(got).all(), f"{what}: non-finite output"
+    max_abs, rel_l2 = attention_error(got, ref)
+    print(f"[parity] {what}: max_abs {max_abs:.3e} rel_l2 {rel_l2:.3e} (output std {float(np.std(ref)):.3e})")
+    assert max_abs <= tol_abs, f"{what}: max-abs error {max_abs:.3e} > {tol_abs}"
+    assert rel_l2 <= tol_rel, f"{what}: relative L2 error {rel_l2:.3e} > {tol_rel}"
+    return max_abs, rel_l2

@@ -71,6 +71,9 @@ _o.kvo_upload_raw.restype = i32
 _o.kvo_upload_raw.argtypes = [VP, u64, vp]
 _o.kvo_token_sequence_hash.restype = u64
 _o.kvo_token_sequence_hash.argtypes = [vp, sz]
+_o.kvo_quantize_q8_1.argtypes = [vp, sz, vp]
+_o.kvo_q_split_norm_rope.argtypes = [vp, vp, vp, vp, u32, u32, u32, u32, i32, fl, fl, i32]
+_o.kvo_decode_state_advance.argtypes = [vp, vp, u32]
 _o.kvo_num_threads.restype = i32
 _o.kvo_set_num_threads.argtypes = [i32]
 
@@ -225,6 +228,31 @@ def merge_partials(m, l, acc, gate=None):
     g = None if gate is None else np.ascontiguousarray(gate, np.float32)
     _o.kvo_merge_partials(_p(m), _p(l), _p(acc), parts, hq, d, _p(g), _p(out), _p(gated))
     return out, gated
+
+
+def quantize_q8_1(x: np.ndarray) -> np.ndarray:
+    """Q8_1 blocks (36 bytes each) of an fp32 array whose size is a multiple of 32."""
+    x = np.ascontiguousarray(x, np.float32)
+    blocks = np.zeros((x.size // 32, 36), np.uint8)
+    _o.kvo_quantize_q8_1(_p(x), x.size, _p(blocks))
+    return blocks
+
+
+def q_split_norm_rope(qfull: np.ndarray, weight, base_position: int, *, rope_mode: int, theta=1.0e6, epsilon=1.0e-6, trig_mode=1):
+    """qfull fp32 [token][heads][2*d] -> (query [token][heads][d], gate [token][heads][d])."""
+    qfull = np.ascontiguousarray(qfull, np.float32)
+    t, h, d2 = qfull.shape
+    d = d2 // 2
+    q = np.empty((t, h, d), np.float32)
+    g = np.empty((t, h, d), np.float32)
+    w = None if weight is None else np.ascontiguousarray(weight, np.float32)
+    _o.kvo_q_split_norm_rope(_p(qfull), _p(w), _p(q), _p(g), t, base_position, h, d, rope_mode, theta, epsilon, trig_mode)
+    return q, g
+
+
+def decode_state_advance(state: np.ndarray, token_output: np.ndarray) -> None:
+    assert state.dtype == np.uint32 and token_output.dtype == np.uint32
+    _o.kvo_decode_state_advance(_p(state), _p(token_output), token_output.size)
 
 
 def token_sequence_hash(tokens) -> int:

@@ -15,10 +15,10 @@ TOL = 2.0e-3
 H, HQ, D = 8, 32, 128
 
 
-def _tagged(values: torch.Tensor) -> torch.Tensor:
-    """fp32 values as the 8-byte words {value, tag = 1} of the exchange format."""
-    bits = values.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
-    return bits | (1 << 32)
+def _tagged(values: torch.Tensor, phase: int) -> torch.Tensor:
+    """fp32 values as the 8-byte words {value, tag = phase + 1} of the exchange format."""
+    from miinfer_b200 import kv
+    return kv.exchange_words(values, phase)
 
 
 def _setup(n, seed):
@@ -54,7 +54,7 @@ def test_world_of_one_equals_plain_decode(cuda):
     assert int(buf.abs().sum()) == 0
 
 
-@pytest.mark.parametrize("n,cut,phase", [(4096, 2048, 0), (5000, 1777, 1), (2500, 2500, 0)])
+@pytest.mark.parametrize("n,cut,phase", [(4096, 2048, 0), (5000, 1777, 1), (2500, 2500, 0), (4096, 1024, 36)])
 def test_two_ranks_with_the_peer_partial_already_delivered(cuda, n, cut, phase):
     kv, host, st, q16, q = _setup(n, 23 + phase)
     ws = kv.decode_workspace(HQ, D)
@@ -68,10 +68,11 @@ def test_two_ranks_with_the_peer_partial_already_delivered(cuda, n, cut, phase):
     words_per_rank = HQ * (D + 2)
     own = torch.zeros(2 * 2 * words_per_rank, dtype=torch.int64, device="cuda")     # [phase][src rank][head][d + 2]
     peer = torch.zeros_like(own)                                                      # what rank 1 would receive
-    slot = own[(phase * 2 + 1) * words_per_rank:(phase * 2 + 2) * words_per_rank].view(HQ, D + 2)
-    slot[:, :D] = _tagged(pa.view(HQ, D))
-    slot[:, D] = _tagged(pm)
-    slot[:, D + 1] = _tagged(pl)
+    slot_index = phase & 1      # the call number's lowest bit selects the slot, the number itself tags the words
+    slot = own[(slot_index * 2 + 1) * words_per_rank:(slot_index * 2 + 2) * words_per_rank].view(HQ, D + 2)
+    slot[:, :D] = _tagged(pa.view(HQ, D), phase)
+    slot[:, D] = _tagged(pm, phase)
+    slot[:, D + 1] = _tagged(pl, phase)
     ex = kv.Exchange.from_pointers([own.data_ptr(), peer.data_ptr()], 0)
     out = torch.full((HQ, D), float("nan"), device="cuda")
     gate = torch.randn(HQ, D, device="cuda")
@@ -86,22 +87,45 @@ def test_two_ranks_with_the_peer_partial_already_delivered(cuda, n, cut, phase):
     assert np.max(np.abs(out.cpu().numpy() - want)) <= TOL
     # consumed words are zero again; rank 0's partial went to the peer's buffer, slot [phase][0], fully tagged
     assert int(own.abs().sum()) == 0
-    sent = peer[(phase * 2) * words_per_rank:(phase * 2 + 1) * words_per_rank]
-    assert bool(((sent >> 32) == 1).all())
-    other = torch.cat([peer[:(phase * 2) * words_per_rank], peer[(phase * 2 + 1) * words_per_rank:]])
+    sent = peer[(slot_index * 2) * words_per_rank:(slot_index * 2 + 1) * words_per_rank]
+    assert bool(((sent >> 32) == phase + 1).all())
+    other = torch.cat([peer[:(slot_index * 2) * words_per_rank], peer[(slot_index * 2 + 1) * words_per_rank:]])
     assert int(other.abs().sum()) == 0
 
 
-def test_a_peer_that_never_delivers_poisons_the_output_and_returns(cuda):
-    """The wait for a peer is bounded: with nothing in the peer's slot the kernel gives up and writes NaN."""
+@pytest.mark.parametrize("stale", [False, True])
+def test_a_peer_that_never_delivers_poisons_the_output_and_sets_the_status_word(cuda, stale):
+    """The wait for a peer is bounded: with nothing in the peer's slot -- or only the words of an EARLIER call,
+    as a rank that arrives after its peers gave up would leave them -- the kernel gives up, writes NaN and
+    reports the timeout in the registered status word.  After clearing, the next call works again."""
     kv, host, st, q16, q = _setup(1024, 5)
     ws = kv.decode_workspace(HQ, D)
     words_per_rank = HQ * (D + 2)
     own = torch.zeros(2 * 2 * words_per_rank, dtype=torch.int64, device="cuda")
     peer = torch.zeros_like(own)
+    if stale:   # call 4's words sit in slot 0 where call 6 looks: same slot, other tag
+        own[words_per_rank:2 * words_per_rank] = _tagged(torch.ones(words_per_rank, device="cuda"), 4)
     ex = kv.Exchange.from_pointers([own.data_ptr(), peer.data_ptr()], 0)
     out = torch.zeros(HQ, D, device="cuda")
-    kv.launch_decode_attention_sharded(st.view(), q, ex, query_heads=HQ, scale=D ** -0.5, range_begin=0, range_end=1024,
-                                       phase=0, output=out, workspace=ws)
-    torch.cuda.synchronize()
-    assert bool(torch.isnan(out).all())
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kv.set_status_word(status)
+    try:
+        kv.launch_decode_attention_sharded(st.view(), q, ex, query_heads=HQ, scale=D ** -0.5, range_begin=0, range_end=1024,
+                                           phase=6, output=out, workspace=ws)
+        torch.cuda.synchronize()
+        assert bool(torch.isnan(out).all())
+        assert int(status.item()) & kv.STATUS_PEER_TIMEOUT
+        # recovery as documented: zero the status word, clear the workspace and the exchange buffers, go on
+        status.zero_(); own.zero_(); peer.zero_()
+        kv.workspace_reset(ws)
+        want = _reference(kv, st, q, 1024, ws)
+        pm = torch.full((HQ,), float("-inf"), device="cuda"); pl = torch.zeros(HQ, device="cuda"); pa = torch.zeros(HQ, D, device="cuda")
+        slot = own[(1 * 2 + 1) * words_per_rank:(1 * 2 + 2) * words_per_rank].view(HQ, D + 2)   # call 7 -> slot 1; the peer's shard is empty
+        slot[:, :D] = _tagged(pa, 7); slot[:, D] = _tagged(pm, 7); slot[:, D + 1] = _tagged(pl, 7)
+        kv.launch_decode_attention_sharded(st.view(), q, ex, query_heads=HQ, scale=D ** -0.5, range_begin=0, range_end=1024,
+                                           phase=7, output=out, workspace=ws)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert float((out - want).abs().max()) <= 2e-5
+    finally:
+        kv.set_status_word(None)

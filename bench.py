@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the quantized-KV decode path (BASELINE.json metric).
+"""Benchmark of the quantized-KV decode path: q8_0-KV decode attention throughput at 32K context.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
@@ -12,6 +12,12 @@ scaling, no data-path collective).  Other workloads:
 `seqshard` (one 128K-token session sharded by sequence over the ranks; the per-rank
 partials are exchanged and merged inside the decode kernel, or by NCCL with --exchange nccl), `batched` (64 sessions of mixed
 length), `prefill` (512-token suffix over an 8K prefix, d=256).
+
+The default run also measures, as sub-records of the same JSON line, the suffix-prefill
+workload (`prefill`) and -- with N > 1 GPUs -- the sharded workloads (`seqshard`, `batched`)
+together with their own 1-GPU times; `--no-extras` leaves them out.  After the timed region the
+output of one layer is compared with the CPU oracle on the cache as it then lies (`check`),
+and the step graph is replayed for two seconds with the SM clock sampled (`sustained`).
 
 The `--impl reference` arm times the CPU restatement of the reference path
 (oracle/) on the host cores; the reference itself has no CPU implementation of
@@ -36,8 +42,8 @@ LAYERS, HQ, HKV, D, QB = 36, 32, 8, 128, 32
 ROW = D + 2 * (D // QB)  # 136 bytes per head-row
 THETA = 1.0e6
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch at 32K context, from the ncu
-# capture summarised in profiles/decode_q8_kernel_32k_context.md (71.61 MB read + 1.74 MB written)
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch at 32K context, from an ncu capture of
+# this kernel on a 2-layer run of the same launch size (71.61 MB read + 1.74 MB written)
 NCU_TRAFFIC_BYTES_32K = 73_352_704
 
 
@@ -58,7 +64,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "25"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             pass
@@ -155,7 +161,7 @@ def run_reference_arm(args) -> None:
 
 
 def workload_config(name: str, context: int, n_gpus: int) -> dict:
-    return {"workload": f"{name}: {LAYERS}-layer Qwen3-8B-shaped KV decode step (BASELINE configs[1] at 32K context): "
+    return {"workload": f"{name}: {LAYERS}-layer Qwen3-8B-shaped KV decode step at {context} context: "
                         f"per layer fused append + split-K GQA attention, {HQ} Q / {HKV} KV heads, d={D}, q8_0 K/V "
                         f"(32 int8 + fp16 scale), batch 1 per GPU",
             "context": context, "layers": LAYERS, "sessions_per_gpu": 1, "parallelism": f"session-parallel x{n_gpus}",
@@ -183,7 +189,7 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
     from miinfer_b200 import kv
 
     ctx = args.context
-    cap = (ctx + args.warmup + 2 * args.steps + 128 + 63) // 64 * 64
+    cap = (ctx + args.warmup + 2 * args.steps + 256 + 63) // 64 * 64
     dev = torch.device("cuda", local_rank)
     caches = [kv.AttentionLayerKvCacheStorage(cap, kv.KvCacheQuantMode.kQ8Q8, kv_heads=HKV, head_dim=D, qblock=QB, device=dev)
               for _ in range(LAYERS)]
@@ -200,21 +206,27 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
     state = kv.make_decode_state(ctx - 1, device=dev)   # position of the token being appended; length = position + 1
     scale = D ** -0.5
 
+    def nxt(l):
+        """The cache attended next: the following layer's (the first layer's of the next step after the last)."""
+        return None if args.no_next_hint else views[(l + 1) % LAYERS]
+
     def layer_pass():
         for l in range(LAYERS):
             if args.two_launches:   # the reference's call pair: store kernel, then decode attention
                 kv.launch_kv_store_quant(views[l], k_new[l], v_new[l], None, 1, 0, rope_mode=kv.RopeMode.NEOX_FULL,
                                          theta=THETA, decode_state=state)
                 kv.launch_decode_attention_quant(views[l], q[l], query_heads=HQ, scale=scale, decode_state=state,
-                                                 output=out[l], workspace=ws)
+                                                 output=out[l], workspace=ws, next_view=nxt(l))
             else:                   # the same work as one launch (append fused into the streaming kernel)
                 kv.launch_decode_step(views[l], k_new[l], v_new[l], q[l], query_heads=HQ, scale=scale, decode_state=state,
-                                      rope_mode=kv.RopeMode.NEOX_FULL, theta=THETA, output=out[l], workspace=ws)
+                                      rope_mode=kv.RopeMode.NEOX_FULL, theta=THETA, output=out[l], workspace=ws, next_view=nxt(l))
+
+    attn_state = kv.make_decode_state(ctx - 2, device=dev)   # attention alone scans the rows that are there: position + 1 of them
 
     def attention_only_pass():
         for l in range(LAYERS):
-            kv.launch_decode_attention_quant(views[l], q[l], query_heads=HQ, scale=scale, decode_state=state,
-                                             output=out[l], workspace=ws)
+            kv.launch_decode_attention_quant(views[l], q[l], query_heads=HQ, scale=scale, decode_state=attn_state,
+                                             output=out[l], workspace=ws, next_view=nxt(l))
 
     # consecutive layers' kernels may overlap their ramp-up and tail (programmatic dependent launch);
     # one trailing cache row -- the token appended by the preceding kernel -- is guarded
@@ -257,6 +269,7 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
 
     # ---- dominant kernel: decode attention alone (one launch per layer), for the roofline -----
     with torch.cuda.stream(stream):
+        attn_state[1] = state[1] - 1       # the rows appended so far
         for _ in range(3):
             attn_graph.replay()
         a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -265,7 +278,7 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
             attn_graph.replay()
         a1.record(stream)
     torch.cuda.synchronize()
-    length_now = int(state[1].item())   # context length the attention-only replays scanned
+    length_now = int(attn_state[1].item()) + 1   # context length the attention-only replays scanned
     attn_us = 1000.0 * a0.elapsed_time(a1) / (args.steps * LAYERS)
     attn_bytes = length_now * HKV * ROW * 2 + HQ * D * 2 + HQ * D * 4
 
@@ -292,6 +305,50 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
     barrier()
     e2e_ms = t0.elapsed_time(t1) / e2e_steps
 
+    # ---- the same step graph replayed for two seconds, SM clock sampled over the window --------------------
+    sustained = None
+    if not args.no_sustained:
+        chunk = max(1, min(args.steps + args.warmup, 64))      # replays between rewinds of the position (the cache has room for these)
+        first_position = ctx - 1
+        s_sampler = ClockSampler(local_rank)
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        replays = 0
+        t_wall = time.perf_counter()
+        with torch.cuda.stream(stream):
+            s0.record(stream)
+            while time.perf_counter() - t_wall < 2.0:
+                state[1] = first_position                      # rewind: the same rows are rewritten with the same bits
+                for _ in range(chunk):
+                    graph.replay()
+                replays += chunk
+                stream.synchronize()
+            s1.record(stream)
+        torch.cuda.synchronize()
+        s_clocks = s_sampler.stop()
+        s_ms = s0.elapsed_time(s1) / replays
+        sustained = {"seconds": s0.elapsed_time(s1) / 1000.0, "steps": replays, "ms_per_step": s_ms, "tokens_per_s": 1000.0 / s_ms,
+                     "sm_mhz_median": s_clocks.get("sm_mhz"), "sm_max_mhz": s_clocks.get("sm_max_mhz"), "clock_samples": s_clocks.get("samples"),
+                     "reasons": s_clocks.get("reasons"),
+                     "ms_times_median_mhz": None if s_clocks.get("sm_mhz") is None else s_ms * s_clocks["sm_mhz"],
+                     "note": "includes one host synchronisation and one position rewind per %d replays" % chunk}
+
+    # ---- the output against the CPU oracle, on the cache as it now lies on the device (layer 0) ----------------
+    check = None
+    if rank == 0 and not args.no_check:
+        from miinfer_b200 import workloads as wl
+
+        ko = wl._oracle()
+        ko.set_threads(os.cpu_count() or 1)
+        with torch.cuda.stream(stream):
+            attn_state[1] = state[1] - 1
+            kv.launch_decode_attention_quant(views[0], q[0], query_heads=HQ, scale=scale, decode_state=attn_state, output=out[0], workspace=ws)
+        torch.cuda.synchronize()
+        rows = int(attn_state[1].item()) + 1
+        host = wl.host_cache_from_planes(ko, wl.planes_of(torch, caches[0], rows), rows, HKV, D)
+        ref, _ = host.decode_ref(q[0].float().cpu().numpy(), scale, rows)
+        check = wl.error_record(out[0].cpu().numpy(), ref, layer=0, context=rows,
+                                rows_appended_by_the_fused_step=rows - (ctx - 1))
+
     ms = torch.tensor([ms_total / args.steps, e2e_ms, attn_us], device=dev, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -310,14 +367,16 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
         "hbm_frac_whole_step": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES_32K, "peak_kind": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs, burst copy)",
-                     "kernel": "decode_q8_kernel (split-K stage 1 on warp-level mma, merge fused in)", "us_per_launch": attn_us,
+                     "kernel": ("decode_q8_kernel (split-K stage 1 on warp-level mma, merge fused in)" if args.decode_kernel == "mma" else
+                                "decode_tc5_kernel (split-K stage 1 on tcgen05 int8 MMA from TMA tiles, merge fused in)"), "us_per_launch": attn_us,
                      "algorithmic_bytes_per_launch": attn_bytes, "frac_of_nominal_8TBs": achieved / 8000.0},
         "e2e": {"value": world * 1000.0 / e2e_ms, "unit": "tokens/s",
                 "h2d_bytes_per_step": int(h_q.numel() * 2 + h_k.numel() * 2 + h_v.numel() * 2),
                 "d2h_bytes_per_step": int(h_out.numel() * 4), "ms_per_step": e2e_ms},
         "gpu_launches": args.steps * LAYERS * (2 if args.two_launches else 1),   # per layer: fused append+attention+merge
-        "clocks": clocks,
+        "clocks": clocks, "check": check, "sustained": sustained,
     }
+    del caches, views
     return line
 
 
@@ -330,12 +389,19 @@ def main() -> None:
     ap.add_argument("--workload", default="decode32k")
     ap.add_argument("--context", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-next-hint", action="store_true", help="do not tell a layer's launch which cache is attended next (A/B of the L2 prefetch hint)")
+    ap.add_argument("--no-check", action="store_true", help="skip the comparison of one layer's output with the CPU oracle")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the two-second replay window")
+    ap.add_argument("--no-extras", action="store_true", help="skip the sub-records (prefill; with N > 1 also seqshard and batched)")
+    ap.add_argument("--seq-context", type=int, default=131072, help="seqshard workload: context length of the one session")
     ap.add_argument("--two-launches", action="store_true", help="append and attention as two launches per layer (A/B of the fused step)")
     ap.add_argument("--prefill-kernel", default="tcgen05", choices=["tcgen05", "mma"], help="prefill workload: which attention kernel")
     ap.add_argument("--no-overlap", action="store_true", help="launch every kernel fully serialised (A/B of launch overlap)")
     ap.add_argument("--default-splits", action="store_true", help="batched workload: leave the split count to the library (A/B of the host-side picker)")
-    ap.add_argument("--exchange", default="kernel", choices=["kernel", "nccl"],
+    ap.add_argument("--exchange", default="kernel", choices=["kernel", "nccl", "nccl-c"],
                     help="seqshard workload at N>1: cross-GPU merge inside the decode kernel (peer stores) or NCCL all-gather + merge kernel")
+    ap.add_argument("--decode-kernel", default="tcgen05", choices=["tcgen05", "mma"],
+                    help="which streaming decode kernel serves the int8 caches (A/B): tcgen05 (default) or warp-level mma")
     ap.add_argument("--layers", type=int, default=36, help="layers per step (36 = the benchmark; fewer only for ncu captures)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
@@ -363,11 +429,23 @@ def main() -> None:
         dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         dist = dist_mod
 
+    from miinfer_b200 import kv as _kv
+
+    _kv.set_decode_kernel({"tcgen05": 0, "mma": 1}[args.decode_kernel])
+    args.cpu_threads = os.cpu_count() or 1
+    from miinfer_b200 import workloads
+
     if args.workload == "decode32k":
         line = run_decode32k(args, torch, dist, rank, world, local_rank)
-    else:
-        from miinfer_b200 import workloads
+        if not args.no_extras and args.layers == 36:
+            import gc
 
+            gc.collect()
+            torch.cuda.empty_cache()
+            sub = workloads.extras(args, torch, dist, rank, world, local_rank)
+            if rank == 0 and line is not None:
+                line.update(sub)
+    else:
         line = workloads.run(args, torch, dist, rank, world, local_rank)
     if rank == 0 and line is not None:
         if world == 1 and not args.no_cpu_baseline:

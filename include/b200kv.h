@@ -160,6 +160,13 @@ B200KV_API int b200kv_set_launch_overlap(uint32_t tail_positions);
 B200KV_API int b200kv_set_status_word(uint32_t* device_word);
 /* Zero-fills a decode workspace (or an exchange buffer) asynchronously on `stream`. */
 B200KV_API int b200kv_workspace_reset(void* workspace, size_t workspace_bytes, void* stream);
+/* Tracing (the reference times its stages with event pairs in *_profiled twins of its layer functions,
+ * src/prefill_v2/attention_layer.cpp:391-549): registers a DEVICE buffer of 8-byte words on the current device (NULL =
+ * off, the default) into which every CTA of session 0 of a later tcgen05 decode launch writes 8 nanosecond time
+ * stamps (%globaltimer) at [(kv_head * splits + split) * 8]: CTA start, dependency wait over, set-up done, first score
+ * tile seen, tile loop over, last sums folded, partial written, merge done (0 where a CTA has no such step).  Launches
+ * whose grid does not fit the buffer are not traced. */
+B200KV_API int b200kv_set_timeline_buffer(uint64_t* device_words, uint32_t capacity_words);
 /* Which streaming kernel serves int8 caches (process-wide; for A/B measurement and tests): 0 = the tcgen05 kernel
  * where it applies (default), 1 = the warp-level mma kernel everywhere.  No counterpart in the reference. */
 B200KV_API int b200kv_set_decode_kernel(int choice);
@@ -246,10 +253,16 @@ B200KV_API size_t b200kv_decode_workspace_bytes(uint32_t query_heads, uint32_t h
  * gated_output_q8 (may be NULL): the gated output re-quantised to Q8_1 blocks of 32 for the projection that
  * follows, [query_heads * head_dim / 32] blocks, as the reference's stage 2 does (.hip:2354-2383: d = amax/127,
  * q = roundf(x/d) clamped to +-127, s = d * sum(q), d and s stored as fp16).  Unlike the reference it is also
- * produced when gate is NULL (from the ungated output). */
+ * produced when gate is NULL (from the ungated output).
+ * next_view (may be NULL; no counterpart in the reference): a hint -- the cache the caller will attend next on this
+ * stream, normally the next layer's.  While the tcgen05 kernel streams its own tiles it pulls that cache's tiles towards
+ * L2 (those the next launch will not already have fetched itself when it is released), which keeps HBM busy through
+ * the phases in which a launch cannot stream: the merge at its end and the set-up of the next one.  Used only for
+ * single-session launches on caches of the same shape and only while the prefetched part stays well inside L2
+ * (contexts up to about 40K positions at 8 kv heads); it never changes a result. */
 B200KV_API int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
                        float* output, float* gated_output, b200kv_q8_1_block* gated_output_q8, uint32_t query_heads, float scale,
-                       uint32_t cache_length, const b200kv_decode_state* decode_state,
+                       uint32_t cache_length, const b200kv_decode_state* decode_state, const b200kv_view* next_view,
                        void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream);
 
 /* One decode step of a layer in ONE launch: append the new token's K/V row at `position` (or at
@@ -263,7 +276,7 @@ B200KV_API int b200kv_decode_step(const b200kv_view* view, const void* key, cons
                        const float* k_norm_weight, int rope_mode, float theta, float epsilon,
                        const void* q, int q_dtype, const float* gate, float* output, float* gated_output,
                        b200kv_q8_1_block* gated_output_q8, uint32_t query_heads, float scale, uint32_t position, const b200kv_decode_state* decode_state,
-                       void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream);
+                       const b200kv_view* next_view, void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream);
 
 /* Decode attention without a caller-supplied workspace and without any allocation (no counterpart in the
  * reference).  For hosts that cannot allocate device memory once they are running -- a serving process
@@ -288,7 +301,7 @@ B200KV_API int b200kv_decode_attn_static(const b200kv_view* view, const void* q,
                               uint32_t num_splits, void* stream);
 
 /* Sequence-sharded decode attention with the cross-GPU merge inside the kernel (no counterpart in the reference,
- * which is single-GPU; BASELINE config 5).  One process per GPU; this rank attends positions
+ * which is single-GPU; the long-context workload: one 131072-token session over 1/2/4/8 GPUs).  One process per GPU; this rank attends positions
  * [range_begin, range_end) of ITS OWN cache shard, stores its per-head partial (m, l, acc) as tagged 8-byte
  * words into slot [phase][rank] of every rank's exchange buffer (plain peer stores over NVLink, no multicast),
  * polls its own buffer until the `world` partials of a head are there (bounded: a rank that never shows up turns
@@ -370,6 +383,22 @@ B200KV_API int b200kv_merge_partials(const float* part_m, const float* part_l, c
 B200KV_API int b200kv_merge_partials_packed(const float* packed, uint32_t num_parts, uint32_t query_heads, uint32_t head_dim,
                                  const float* gate, float* output, float* gated_output, void* stream);
 
+/* Sequence-sharded decode over NCCL from a C or C++ host (no counterpart in the reference): per layer, every rank
+ * runs b200kv_decode_partials on its shard with the pointers b200kv_dist_partial hands out, then b200kv_dist_merge
+ * all-gathers the packed partials (query_heads * (head_dim + 2) fp32 per rank) on `stream` and merges them; every
+ * rank ends with the same output.  For every cache mode and shape; int8 caches at head_dim 128 have the faster
+ * in-kernel exchange, b200kv_decode_attn_sharded.  init takes either an existing ncclComm_t (nccl_comm != NULL; rank
+ * and world are read from it) or a 128-byte NCCL unique id created by b200kv_dist_unique_id on one rank and passed
+ * to the others by the host's own means.  NCCL is looked up at run time (B200KV_ERR_UNSUPPORTED if there is none).
+ * These allocate and are collective: set-up calls, not for the per-token path -- except b200kv_dist_merge. */
+typedef struct b200kv_dist b200kv_dist;
+B200KV_API int b200kv_dist_unique_id(void* id128);
+B200KV_API int b200kv_dist_init(b200kv_dist** out, void* nccl_comm, const void* id128, uint32_t rank, uint32_t world,
+                     uint32_t query_heads, uint32_t head_dim);
+B200KV_API int b200kv_dist_partial(b200kv_dist* dist, float** part_m, float** part_l, float** part_acc);
+B200KV_API int b200kv_dist_merge(b200kv_dist* dist, const float* gate, float* output, float* gated_output, void* stream);
+B200KV_API int b200kv_dist_destroy(b200kv_dist* dist);
+
 /* ---- suffix / prefill attention -------------------------------------------- */
 
 /* Minimum workspace of b200kv_prefill_attn: 0 (`workspace` may be NULL; the reference needs 32*T*heads*(2+d)
@@ -416,6 +445,13 @@ B200KV_API int b200kv_snapshot_restore(const b200kv_view* view, uint64_t tokens,
  * in-VRAM counterpart of copy_session_checkpoint/restore_session_checkpoint,
  * tools/miinfer_cli.cpp:1248-1317. */
 B200KV_API int b200kv_snapshot_clone(const b200kv_view* dst, const b200kv_view* src, uint64_t tokens, void* stream);
+
+/* download_key / download_value, src/prefill_v2/kv_cache.cpp:132-212: the first `tokens` positions of one side as
+ * fp32 [kv_head][tokens][head_dim] in HOST memory, dequantised (int8 value x the fp16 scale of its block; fp16 values
+ * widened).  Blocking; for inspection and tests, not the per-token path.  tokens > capacity -> B200KV_ERR_RANGE
+ * (the reference throws). */
+B200KV_API int b200kv_download_key(const b200kv_view* view, uint64_t tokens, float* host_dst, void* stream);
+B200KV_API int b200kv_download_value(const b200kv_view* view, uint64_t tokens, float* host_dst, void* stream);
 
 /* ---- prefix identity and the on-disk session (host side) -------------------- */
 
@@ -484,6 +520,76 @@ B200KV_API int b200kv_session_write(const char* path, const char* model_id, cons
 B200KV_API int b200kv_session_read(const char* path, const char* model_id, const char* quantization, uint32_t layers, uint32_t kv_heads,
                         uint32_t head_dim, uint32_t qblock, uint32_t quant_mode, uint32_t* tokens_out, uint32_t tokens_capacity,
                         uint32_t* prefix_length_out, void* kv_payload_out, uint64_t payload_capacity);
+
+/* ---- in-VRAM snapshot pool and the prefix-reuse policy (host side; these allocate: not for the per-token path) ---- */
+
+/* A store of prefix snapshots in device memory with longest-prefix lookup: the multi-snapshot machinery of the
+ * reference's first engine, tools/miinfer_cli.cpp:1043-1317 (SessionCheckpoint, a compressed radix tree over the
+ * token ids, least-recently-used eviction) for the KV part.  max_entries 0 = 8 and max_bytes 0 = 3 GiB, the
+ * reference's budget (tools/miinfer_cli.cpp:62-63); granularity = only prefixes whose length is a multiple of it
+ * are captured (the reference: 512, the prefill tile, :1185; 0 or 1 = any length).  model_id / quantization
+ * identify what the snapshots belong to: lookups for another identity find nothing (:1073-1079). */
+typedef struct b200kv_pool b200kv_pool;
+typedef struct b200kv_pool_counters {
+    uint32_t entries;
+    uint64_t bytes;
+    uint64_t hits, misses, captures, evictions, skipped;
+} b200kv_pool_counters;
+B200KV_API int b200kv_pool_create(b200kv_pool** out, const char* model_id, const char* quantization, uint32_t max_entries,
+                       uint64_t max_bytes, uint32_t granularity);
+B200KV_API int b200kv_pool_destroy(b200kv_pool* pool);
+/* capture_session_checkpoint (:1184-1228): keep the first prefix_length positions of every layer under `tokens`
+ * (device-to-device, on `stream`); an entry with the same tokens is refreshed; the oldest entries are evicted to stay
+ * within the budget.  *captured (may be NULL) = 0 when the capture was skipped (granularity, larger than the whole
+ * budget, or no device memory left), which is not an error. */
+B200KV_API int b200kv_pool_capture(b200kv_pool* pool, const uint32_t* tokens, uint32_t prefix_length, const b200kv_view* layer_views,
+                        uint32_t layers, void* stream, int* captured);
+/* The same bookkeeping without a payload, for a host that keeps the snapshot bytes elsewhere: `bytes` is what the
+ * entry counts against the budget. */
+B200KV_API int b200kv_pool_capture_index_only(b200kv_pool* pool, const uint32_t* tokens, uint32_t prefix_length, uint64_t bytes, int* captured);
+/* longest_session_checkpoint (:1126-1148): length of the longest stored sequence that is a prefix of `prompt` and
+ * strictly shorter than it (0 = none); *common_length (may be NULL) = how many leading prompt tokens the index shares
+ * with any stored sequence.  A hit marks the entry as used. */
+B200KV_API int b200kv_pool_lookup(b200kv_pool* pool, const char* model_id, const char* quantization, const uint32_t* prompt,
+                       uint32_t prompt_length, uint32_t* matched_length, uint32_t* common_length);
+/* restore_session_checkpoint (:1290-1317): look up as above and copy the entry's positions into the caches. */
+B200KV_API int b200kv_pool_restore(b200kv_pool* pool, const uint32_t* prompt, uint32_t prompt_length, const b200kv_view* layer_views,
+                        uint32_t layers, void* stream, uint32_t* matched_length);
+B200KV_API int b200kv_pool_stats(b200kv_pool* pool, b200kv_pool_counters* out);
+
+/* The prefix-reuse fields of GenerateOptions and the reuse telemetry of GenerateStats,
+ * include/miinfer/prefill_v2/model.hpp:27-68. */
+typedef struct b200kv_reuse_options {
+    int enable_prefix_reuse;
+    int cache_prefix_after;
+    uint32_t cache_prefix_len;           /* 0 = the whole prompt */
+    const char* persistent_session_dir;  /* NULL or "" = no files */
+} b200kv_reuse_options;
+typedef enum b200kv_reuse_source { B200KV_REUSE_NONE = 0, B200KV_REUSE_RESIDENT = 1, B200KV_REUSE_POOL = 2, B200KV_REUSE_DISK = 3 } b200kv_reuse_source;
+typedef struct b200kv_reuse_stats {
+    int reuse_hit;
+    int source;                          /* b200kv_reuse_source */
+    uint32_t prefix_tokens_reused;
+    uint32_t suffix_tokens_dispatched;
+    uint32_t gqa_kv_reused_tokens;
+    double restore_ms;
+} b200kv_reuse_stats;
+/* The reuse branch at the start of PrefillV2Model::generate (src/prefill_v2/model.cpp:751-775): decide how much of
+ * `prompt` need not be prefilled and bring that prefix into the caches.  Tried in this order: the prefix already
+ * resident in the caches (resident_* describe it; an exact match strictly shorter than the prompt; nothing is
+ * copied), the pool (may be NULL; no counterpart in that function), the session directory.  With layers == 0 only the
+ * decision is taken (no device work).  The caller prefills prompt[stats->prefix_tokens_reused:]. */
+B200KV_API int b200kv_reuse_begin(const b200kv_reuse_options* options, const char* model_id, const char* quantization,
+                       const char* resident_model_id, const char* resident_quantization, uint32_t resident_layout_version,
+                       const uint32_t* resident_tokens, uint32_t resident_length, b200kv_pool* pool, const uint32_t* prompt,
+                       uint32_t prompt_length, const b200kv_view* layer_views, uint32_t layers, void* stream, b200kv_reuse_stats* stats);
+/* The step after prefill (model.cpp:868-887): with cache_prefix_after, *cached_length = the prefix the caller now
+ * treats as resident (cache_prefix_len, or the whole prompt); it is captured into the pool (if any) and, when a
+ * session directory is set and the prefix has at least 256 tokens and no file yet, saved there (a failed write is
+ * not an error; *wrote_file says whether one was written). */
+B200KV_API int b200kv_reuse_commit(const b200kv_reuse_options* options, const char* model_id, const char* quantization, b200kv_pool* pool,
+                        const uint32_t* prompt, uint32_t prompt_length, const b200kv_view* layer_views, uint32_t layers, void* stream,
+                        uint32_t* cached_length, int* wrote_file);
 
 #ifdef __cplusplus
 }

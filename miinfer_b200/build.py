@@ -67,7 +67,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if verbose:
         print(log)
     cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB_PATH),
-           *[str(obj) for obj, _ in results], "-Xlinker", "--exclude-libs=ALL"]
+           *[str(obj) for obj, _ in results], "-Xlinker", "--exclude-libs=ALL", "-ldl"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")

@@ -22,6 +22,7 @@
 #include <stdexcept>
 #include <string>
 #include <utility>
+#include <vector>
 
 #include "b200kv.h"
 
@@ -85,7 +86,7 @@ inline void launch_qwen35_tiled_online_attention_quant_dynamic(
                                                  value_scales, cache_capacity, kv_heads, head_dim, kv_qblock(), is_k_q8, is_v_q8);
     const auto& ws = shim_detail::decode_workspace();
     shim_detail::check(b200kv_decode_attn(&v, q, B200KV_F32, gate, output, gated_output, gated_output_q8, query_heads, scale, 0,
-                                          decode_state, ws.ptr, ws.bytes, 0, stream),
+                                          decode_state, nullptr, ws.ptr, ws.bytes, 0, stream),
                        "launch_qwen35_tiled_online_attention_quant_dynamic");
 }
 
@@ -108,6 +109,32 @@ inline void launch_qwen35_splitk_suffix_attention_quant(
                                                              : 0,
                                            stream),
                        "launch_qwen35_splitk_suffix_attention_quant");
+}
+
+// qwen3_gpu_primitives.hpp:869-881: the query side of a prefill chunk (sectioned RoPE on the first 64 dims)
+inline void launch_qwen35_decoupled_q_split_norm_rope_batch(
+    const float* qfull, const float* q_norm_weight, float* query_rope, float* gate, std::uint32_t token_count, std::uint32_t base_position,
+    std::uint32_t heads, std::uint32_t head_dim, float theta, float epsilon, cudaStream_t stream = nullptr,
+    const DevicePrefillState* prefill_state = nullptr) {
+    shim_detail::check(b200kv_q_split_norm_rope(qfull, B200KV_F32, q_norm_weight, query_rope, B200KV_F32, gate, token_count, base_position, heads,
+                                                head_dim, B200KV_ROPE_SECTIONED64, theta, epsilon, prefill_state, nullptr, stream),
+                       "launch_qwen35_decoupled_q_split_norm_rope_batch");
+}
+
+// qwen3_gpu_primitives.hpp:934-938: the query side of a decode step, position read from the device state
+inline void launch_qwen35_fused_q_split_norm_rope_dynamic(
+    const float* qfull, const float* q_norm_weight, float* query_rope, float* gate, std::uint32_t heads, std::uint32_t head_dim,
+    const DeviceDecodeState* decode_state, float theta, float epsilon, cudaStream_t stream = nullptr) {
+    if (decode_state == nullptr) shim_detail::check(B200KV_ERR_INVALID, "launch_qwen35_fused_q_split_norm_rope_dynamic");
+    shim_detail::check(b200kv_q_split_norm_rope(qfull, B200KV_F32, q_norm_weight, query_rope, B200KV_F32, gate, 1, 0, heads, head_dim,
+                                                B200KV_ROPE_SECTIONED64, theta, epsilon, nullptr, decode_state, stream),
+                       "launch_qwen35_fused_q_split_norm_rope_dynamic");
+}
+
+// qwen3_gpu_primitives.hpp:1248-1250
+inline void launch_qwen35_decode_state_advance(DeviceDecodeState* state, std::uint32_t* token_output, std::uint32_t capacity,
+                                               cudaStream_t stream = nullptr) {
+    shim_detail::check(b200kv_decode_state_advance(state, token_output, capacity, stream), "launch_qwen35_decode_state_advance");
 }
 
 namespace prefill_v2 {
@@ -159,6 +186,17 @@ public:
         if (tokens > view_.capacity) throw std::runtime_error("AttentionLayerKvCacheStorage::upload_raw: tokens exceeds capacity");
         shim_detail::check(b200kv_snapshot_restore(&view_, tokens, host_src, stream), "upload_raw");
         if (stream == nullptr) cudaStreamSynchronize(nullptr);
+    }
+    // kv_cache.cpp:132-212: dequantising downloads to fp32 host vectors [kv_head][tokens][head_dim]
+    void download_key(std::vector<float>& host_key, std::size_t tokens) const {
+        if (tokens > view_.capacity) throw std::runtime_error("AttentionLayerKvCacheStorage: tokens exceeds capacity");
+        host_key.resize(static_cast<std::size_t>(view_.kv_heads) * tokens * view_.head_dim);
+        shim_detail::check(b200kv_download_key(&view_, tokens, host_key.data(), nullptr), "download_key");
+    }
+    void download_value(std::vector<float>& host_value, std::size_t tokens) const {
+        if (tokens > view_.capacity) throw std::runtime_error("AttentionLayerKvCacheStorage: tokens exceeds capacity");
+        host_value.resize(static_cast<std::size_t>(view_.kv_heads) * tokens * view_.head_dim);
+        shim_detail::check(b200kv_download_value(&view_, tokens, host_value.data(), nullptr), "download_value");
     }
     [[nodiscard]] AttentionKvCacheView view() const noexcept {
         AttentionKvCacheView v;

@@ -244,6 +244,7 @@ int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max
     p.ws_l = p.ws_m + slots;
     p.ws_acc = p.ws_l + slots;
     p.status = current_status_word();
+    p.timeline = current_timeline_buffer(num_splits * geometry.kv_heads);
     if (use_fast) {
         if (plain_offset < 2 * plain_bytes) return B200KV_ERR_WORKSPACE;
         // The in-launch merge; a lone split that has to produce Q8_1 blocks goes through the merge kernel instead
@@ -253,7 +254,7 @@ int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max
         p.tag = next_launch_tag();
         p.fuse = merge;
         int rc = B200KV_ERR_UNSUPPORTED;
-        if (streaming_kernel_choice() == 0) rc = launch_decode_tc5(p, geometry, max_length, stream);
+        if (streaming_kernel_choice() != 1) rc = launch_decode_tc5(p, geometry, max_length, stream);
         if (rc == B200KV_ERR_UNSUPPORTED) rc = launch_decode_q8(p, geometry, max_length, stream);
         if (rc == B200KV_OK) *merged = fuse_merge;
         if (rc != B200KV_ERR_UNSUPPORTED) return rc;
@@ -329,13 +330,13 @@ size_t b200kv_view_table_bytes(uint32_t sessions) { return sizeof(SessionEntry) 
 size_t b200kv_decode_workspace_bytes(uint32_t query_heads, uint32_t head_dim, uint32_t sessions) {
     if (sessions == 0) sessions = 1;
     const size_t slots = static_cast<size_t>(sessions) * max_splits_per_session(sessions) * query_heads;
-    // plain partials behind, twice that for the tagged partials of the streaming kernel in front
+    // plain partials behind, twice that for the tagged partials of the streaming kernels in front
     return (slots * (head_dim + 2u) * sizeof(float) + 255) / 256 * 256 * 3;
 }
 
 int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
                        float* output, float* gated_output, b200kv_q8_1_block* gated_output_q8, uint32_t query_heads, float scale,
-                       uint32_t cache_length, const b200kv_decode_state* decode_state,
+                       uint32_t cache_length, const b200kv_decode_state* decode_state, const b200kv_view* next_view,
                        void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream) {
     int rc = validate_view(view);
     if (rc != B200KV_OK) return rc;
@@ -356,6 +357,7 @@ int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_dtype, cons
     p.q_is_f16 = (q_dtype == B200KV_F16);
     p.query_heads = query_heads;
     p.scale = scale;
+    p.next_view = (next_view != nullptr && validate_view(next_view) == B200KV_OK) ? next_view : nullptr;   // a hint: a bad one is ignored
     // with a device-side length the launch is sized for the whole cache
     const uint32_t max_length = decode_state ? static_cast<uint32_t>(view->capacity) : cache_length;
     MergeParams mp{};
@@ -372,7 +374,8 @@ int b200kv_decode_step(const b200kv_view* view, const void* key, const void* val
                        const float* k_norm_weight, int rope_mode, float theta, float epsilon,
                        const void* q, int q_dtype, const float* gate, float* output, float* gated_output,
                        b200kv_q8_1_block* gated_output_q8, uint32_t query_heads, float scale, uint32_t position,
-                       const b200kv_decode_state* decode_state, void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream) {
+                       const b200kv_decode_state* decode_state, const b200kv_view* next_view, void* workspace, size_t workspace_bytes,
+                       uint32_t num_splits, void* stream) {
     int rc = validate_view(view);
     if (rc != B200KV_OK) return rc;
     if (key == nullptr || value == nullptr || q == nullptr || (output == nullptr && gated_output == nullptr && gated_output_q8 == nullptr))
@@ -388,7 +391,7 @@ int b200kv_decode_step(const b200kv_view* view, const void* key, const void* val
         rc = b200kv_append(view, key, value, kv_dtype, k_norm_weight, rope_mode, theta, epsilon, 1, position, nullptr, decode_state, stream);
         if (rc != B200KV_OK) return rc;
         return b200kv_decode_attn(view, q, q_dtype, gate, output, gated_output, gated_output_q8, query_heads, scale, position + 1,
-                                  decode_state, workspace, workspace_bytes, num_splits, stream);
+                                  decode_state, next_view, workspace, workspace_bytes, num_splits, stream);
     }
     if ((rc = ensure_device()) != B200KV_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -401,6 +404,7 @@ int b200kv_decode_step(const b200kv_view* view, const void* key, const void* val
     p.q_is_f16 = (q_dtype == B200KV_F16);
     p.query_heads = query_heads;
     p.scale = scale;
+    p.next_view = (next_view != nullptr && validate_view(next_view) == B200KV_OK) ? next_view : nullptr;
     p.new_key = key;
     p.new_value = value;
     p.new_is_f16 = (kv_dtype == B200KV_F16);

@@ -98,14 +98,24 @@ struct DecodeParams {
     float sectioned_step;
     float inv_freq[64];                      // NeoX frequencies for d = 128
     uint32_t overlap_tail;                   // launch overlap: the last n positions of the range are read only after pdl_wait
+    // Hint: the cache the caller attends next (normally the next layer's), whose tiles the tcgen05 kernel pulls towards L2
+    // while it streams its own.  next_view is the host-side argument; the launch resolves it into the fields below.
+    const b200kv_view* next_view;
+    uint32_t next_rows;                      // rows of the next cache worth prefetching (0 = no hint)
+    uint64_t next_capacity;
+    const uint8_t* next_key_scales;
+    const uint8_t* next_value_scales;
     uint64_t* ws_tagged;
     uint32_t tag;                            // tag of this launch's words in ws_tagged (never 0; differs from the previous launch's)
     uint32_t* status;                        // device word that collects B200KV_STATUS_* bits of waits that ran out, or null
+    uint64_t* timeline;                      // device buffer for per-CTA time stamps (tcgen05 decode kernel), or null
     MergeParams fuse;
 };
 
 // Tag for the tagged words of one launch: a process-wide counter that skips 0.
 uint32_t next_launch_tag();
+// The device buffer registered with b200kv_set_timeline_buffer for the current device (null if none).
+uint64_t* current_timeline_buffer(uint32_t ctas);
 // The device status word registered with b200kv_set_status_word for the current device (null if none).
 uint32_t* current_status_word();
 // Which streaming kernel serves int8 caches: 0 = the tcgen05 kernel where it applies, 1 = the warp-level mma kernel.
@@ -146,9 +156,8 @@ int launch_merge(const MergeParams& p, uint32_t groups, cudaStream_t stream);
 int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, void* workspace,
                       size_t workspace_bytes, uint32_t num_splits_arg, const MergeParams& merge, bool* merged,
                       cudaStream_t stream);
-// Split of a caller's workspace of `bytes` bytes: tagged partials in front (two thirds, zero between launches),
-// plain [m][l][acc] partials behind.  The split depends only on the size, so launches of different shapes that
-// share one workspace never write plain floats where tagged words are expected.
+// Split of a caller's workspace of `bytes` bytes: tagged partials in front (two thirds), plain [m][l][acc] partials
+// behind.  The split depends only on the size.
 inline size_t workspace_plain_offset(size_t bytes) { return bytes / 3 * 2 / 256 * 256; }
 int run_decode(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, void* workspace, size_t workspace_bytes,
                uint32_t num_splits_arg, MergeParams mp, uint32_t groups, cudaStream_t stream);

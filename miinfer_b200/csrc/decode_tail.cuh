@@ -239,15 +239,23 @@ __device__ __forceinline__ void write_merged(const MergeParams& f, uint32_t sess
 
 // ---- fused merge: the CTA of split h merges query head h of its kv head (h, h + splits, ... if there are fewer
 // splits than heads).  It polls the tagged partials of all splits -- normally they are all there by the time it
-// has finished its own share -- and every other CTA simply leaves.  Called by ALL 256 threads of the CTA (the CTAs
-// that have nothing to merge return at once); uses named barriers 1 (64 threads) and 2 (256 threads).
-// fold_area: (8 + 3 * 64 * 2) floats of shared memory nothing else uses any more.
+// has finished its own share -- and every other CTA simply leaves.  (Electing instead the CTAs that arrive last, with
+// an atomic counter behind the partial stores, measured slower: the atomic's round trip and the merger reading its
+// own partial back through L2 cost more than the polls they save.)  Called by ALL 256 threads of the CTA after they
+// have issued their emit_partial stores (the CTAs that have nothing to merge return at once); uses named barriers
+// 1 (64 threads) and 2 (256 threads).  fold_area: (8 + 3 * 64 * 2) floats of shared memory nothing else uses any more.
 __device__ __forceinline__ void fused_merge(const DecodeParams& p, uint32_t session, uint32_t kv_head, uint32_t split,
                                             uint32_t num_splits, int G, float* fold_area) {
     constexpr int kD = 128;
     constexpr int kPartialWords = kD + 2;
-    if (split >= static_cast<uint32_t>(G) || merge_not_needed(p, num_splits)) return;
+    if (merge_not_needed(p, num_splits)) return;
     const uint32_t S = num_splits;     // <= kMaxSplitsPerSession == 128; the partial arrays keep the launch-wide stride
+    const uint32_t rank = split;
+    if (rank >= static_cast<uint32_t>(G)) return;
+    uint64_t* tl = (p.timeline != nullptr && session == 0 && threadIdx.x == 0) ? p.timeline + (static_cast<size_t>(kv_head) * gridDim.x + split) * 16 : nullptr;
+    auto now = [] { uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
+    if (tl) tl[8] = now();
+    uint32_t rounds = 0;
     const uint32_t tag = p.tag;
     float* fold_ml = fold_area;                                   // [3] x {max, sum} of split groups 1..3
     float2* fold = reinterpret_cast<float2*>(fold_ml + 8);        // [3][64] partial sums of split groups 1..3
@@ -255,7 +263,7 @@ __device__ __forceinline__ void fused_merge(const DecodeParams& p, uint32_t sess
     // 256 threads = 4 split groups (sp % 4) x 64 pairs of dims.  A group merges its own splits on line (every thread
     // of a group also reads the group's (m, l) words itself: no staging, no barrier), then the 4 groups are folded.
     const int grp = threadIdx.x >> 6, pr = threadIdx.x & 63;
-    for (uint32_t h = split; h < static_cast<uint32_t>(G); h += S) {
+    for (uint32_t h = rank; h < static_cast<uint32_t>(G); h += S) {
         const uint32_t head = kv_head * G + h;
         const size_t stride = static_cast<size_t>(p.query_heads) * kPartialWords;   // words between consecutive splits
         uint64_t* base = p.ws_tagged + ((static_cast<size_t>(session) * p.num_splits) * p.query_heads + head) * kPartialWords;
@@ -275,6 +283,7 @@ __device__ __forceinline__ void fused_merge(const DecodeParams& p, uint32_t sess
             }
             uint32_t ml_pending = pending;
             for (uint32_t polls = 0; (pending | ml_pending) != 0 && !lost; ++polls) {
+                ++rounds;
                 if (polls >= kPollLimit) { lost = true; report(p, B200KV_STATUS_SPLIT_TIMEOUT); break; }
                 // all loads first, all checks afterwards: a check between two loads would serialise their trips
                 uint64_t wa[kBatch], wb[kBatch], wm[kBatch], wl[kBatch];
@@ -320,6 +329,7 @@ __device__ __forceinline__ void fused_merge(const DecodeParams& p, uint32_t sess
                 if (sp0 + grp + 4 * u < S) zero2(base + (sp0 + grp + 4 * u) * stride + 2 * pr);
         }
         if (lost) tot.x = tot.y = lg = __int_as_float(0x7fc00000);
+        if (tl) { tl[9] = now(); tl[12] = rounds; }
         // fold the 4 split groups through shared memory
         if (grp > 0) {
             fold[(grp - 1) * 64 + pr] = tot;
@@ -349,8 +359,10 @@ __device__ __forceinline__ void fused_merge(const DecodeParams& p, uint32_t sess
             }
             float gsum = lg;
             const float m_merged = M;
+            if (tl) tl[10] = now();
             if (p.fuse.xchg.world > 1) exchange_partials(p, head, pr, m_merged, tot, gsum, lost);
             write_merged(p.fuse, session, head, pr, tot, gsum, m_merged);
+            if (tl) tl[11] = now();
         }
         asm volatile("bar.sync 2, 256;" ::: "memory");   // the fold area is reused by the next head of this CTA
     }

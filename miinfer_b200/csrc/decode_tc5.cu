@@ -13,18 +13,20 @@
 //  * S^T = K . Q^T: the K tile as it lies is the A operand (M = 128 positions, K-major), Q is quantised once per
 //    launch to 15 bits per head (q = 128 hi + lo, two int8 planes = 8 of the 16 rows of the B operand).  One MMA
 //    per q8_0 block of 32 dims (kind::i8 has K = 32), each into its own 16 TMEM columns, so the per-block key
-//    scales can be applied to exact int32 sums: 128 threads (one per position = TMEM lane) read their 32 sums with
-//    tcgen05.ld and finish the scores in fp32.
+//    scales can be applied to exact int32 sums: 256 threads (two per position = TMEM lane, each with two of the four
+//    query heads) read their sums with tcgen05.ld and finish the scores in fp32.
 //  * Online softmax in base 2: the tile maximum per head is found with redux.sync inside each warp and one exchange
-//    through shared memory between the four warps; the running maximum is uniform across the CTA.
+//    through shared memory between the four warps of a head group; the running maximum is uniform across the group.
 //  * O^T += V^T . P: the V tile as it lies is the A operand again, this time MN-major (M = 128 dims, K = positions),
-//    and P is written by the 128 threads as unsigned 16-bit fixed point in two uint8 planes, pre-multiplied by the
-//    value scale of each block: P[(block, plane, head)][position] = 32 B-operand rows, so that one MMA chain yields,
+//    and P is written as unsigned 16-bit fixed point in two uint8 planes, pre-multiplied by the value scale of each
+//    block: P[position][(group, block, plane, head)] = 32 B-operand columns, MN-major too, so that a thread stores
+//    its 16 bytes of a position with one store and one MMA chain yields,
 //    for every dim, the sums of all four blocks' weightings, of which the thread of that dim keeps its own block's
 //    (the other three quarters are the price of per-block value scales: tensor throughput is not what bounds this
 //    kernel).  The fixed-point scale is per tile, head and block (tile maximum of the weights x tile maximum of the
 //    value scales / 65535), so the int32 sums are exact and every tile is folded into fp32 accumulators in
-//    registers (4 per thread) as soon as its MMA chain has completed; rescaling at a new maximum costs 12 multiplies.
+//    registers (2 per thread) once its MMA chain has completed; P and the sums are double-buffered, so the softmax
+//    threads never wait for the chain of the tile they have just handed over.
 //  * The CTA's partial leaves as tagged words and the CTA of split h merges head h (decode_tail.cuh), as in decode_q8.cu.
 //  * Every wait is bounded.  A wait that runs out sets a status bit, poisons the partial with NaN and lets the CTA
 //    finish in the normal way (all later waits are skipped, barriers are still attended, TMEM is freed).
@@ -40,14 +42,21 @@ namespace {
 constexpr int kD = 128;
 constexpr int kTileM = 128;            // positions per tile = rows of the S MMA = TMEM lanes
 constexpr int kStages = 3;
-constexpr int kThreads = 256;          // warps 0-3: softmax threads (TMEM lanes 0-127); 4: TMA producer (+ fused append);
-constexpr int kProducerWarp = 4;       // 5: MMA issuer and TMEM owner; 6-7 only take part in the merge
-constexpr int kMmaWarp = 5;
+// Warps 0-3: softmax threads, one per position of a tile (TMEM lane = position = tid).  Warp 4: TMA producer.  Warp 5:
+// issuer of the S = K.Q^T MMAs and TMEM owner.  Warp 6: issuer of the P.V MMAs.  Warp 7: the fused single-token
+// append.  Two issuers, so that each sleeps on its own barriers instead of one thread polling both (a polling warp
+// takes issue slots from the softmax warps).  (Two softmax threads per position, each with two of the four heads,
+// measured no faster: in steady state the loop runs at the memory system's pace either way.)
+constexpr int kThreads = 256;
+constexpr int kConsumers = 128;
+constexpr int kProducerWarp = 4, kMmaWarp = 5, kPvWarp = 6, kAppendWarp = 7;
 constexpr uint32_t kSpin = 1u << 20;
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColS = 0;          // two S buffers of 4 blocks x 16 columns
-constexpr uint32_t kColO = 128;        // 32 columns: (block, plane, head)
+constexpr uint32_t kColO = 128;        // two O buffers of 32 columns: (block, plane, head)
 constexpr float kPMax = 65535.0f;
+constexpr int kEarlyTiles = 2;         // ring stages filled before the launch is released (3 measured no better: the early
+                                       // copies of a launch compete with the merge of the one before it)
 
 template <int NBLK>
 struct Smem {
@@ -55,20 +64,20 @@ struct Smem {
     static constexpr int kSTile = kTileM * NBLK * 2;                  // 1024 (q8_0) or 256 (row scale)
     static constexpr int kOffK = 0;
     static constexpr int kOffV = kStages * kKTile;
-    static constexpr int kOffP = 2 * kStages * kKTile;                // [32 rows][128 B], K-major, swizzled
-    static constexpr int kOffQ = kOffP + 32 * 128;                    // [16 rows][128 B]
-    static constexpr int kOffS = kOffQ + 16 * 128;                    // [stage][ks | vs]
-    static constexpr int kOffXch = kOffS + kStages * 2 * kSTile;      // [2][4 warps][8] words: tile maxima
+    static constexpr int kOffP = 2 * kStages * kKTile;                // 2 x [128 positions][32 B], MN-major, 32-byte swizzle
+    static constexpr int kOffQ = kOffP + 2 * kTileM * 32;             // [8 rows][128 B]: the Q planes (rows 8-15 of the 16-row operand: see below)
+    static constexpr int kOffS = kOffQ + 8 * 128;                     // [stage][ks | vs]
+    static constexpr int kOffXch = kOffS + kStages * 2 * kSTile;      // [2 parities][4 warps][8] words: tile maxima
     static constexpr int kOffL = kOffXch + 2 * 4 * 8 * 4;             // [4 warps][4] row sums
     static constexpr int kOffQmul = kOffL + 64;                       // [4]
-    static constexpr int kOffFold = kOffQmul + 16;                    // merger scratch (decode_tail.cuh)
-    static constexpr int kOffBar = kOffFold + (8 + 3 * 64 * 2) * 4;
-    static constexpr int kNumBars = 2 * kStages + 6;                  // full[3] empty[3] s_full[2] s_empty[2] p_full p_empty
+    static constexpr int kOffBar = kOffQmul + 16;
+    static constexpr int kNumBars = 2 * kStages + 9;                  // full[3] empty[3] s_full[2] s_empty[2] p_full[2] p_empty[2] row
     static constexpr int kOffMisc = kOffBar + kNumBars * 8;           // tmem slot, fail flag
     static constexpr int kTotal = kOffMisc + 16;
     static constexpr int kAlloc = kTotal + 1024;                      // slack to align the base to 1024
 };
 static_assert(Smem<4>::kAlloc <= 115712, "two CTAs per SM");
+static_assert(2 * kTileM * 32 >= (8 + 3 * 64 * 2) * 4, "the merger's scratch fits where P was");
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
@@ -82,13 +91,6 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Non-blocking probe (try_wait may park the thread for a while; the MMA issuer polls several barriers in turn).
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
 // Bounded wait: false if the phase did not complete within the spin limit.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t spin = 0; spin < kSpin; ++spin)
@@ -99,27 +101,37 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+// Pull a tile (or a plain byte range) into L2 without a destination in shared memory.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_prefetch(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 
 // Shared-memory matrix descriptor (sm_100 format): start address, leading/stride byte offsets (all >> 4),
-// descriptor version 1, 128-byte swizzle.  K-major operands: rows of 128 bytes, 8-row groups `sbo` apart.
-// MN-major operands: 128 contiguous bytes along M/N, rows of k 128 bytes apart, 8-k groups `sbo` apart.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// descriptor version 1, swizzle mode.  K-major operands: rows of 128 bytes, 8-row groups `sbo` apart.
+// MN-major operands: one swizzle span (128 or 32 bytes) contiguous along M/N, consecutive k one span apart, groups of
+// 8 k `sbo` apart, further spans along M/N `lbo` apart.
+// `layout`: 2 = 128-byte swizzle, 6 = 32-byte swizzle.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
     d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
+    d |= static_cast<uint64_t>(layout) << 61;
     return d;
 }
 // Instruction descriptor for kind::i8: int32 accumulate; operand formats (1 = signed, 0 = unsigned) and majors
 // (0 = K-major, 1 = MN-major).
-__host__ __device__ constexpr uint32_t umma_idesc_i8(uint32_t m, uint32_t n, uint32_t a_signed, uint32_t b_signed, uint32_t a_mn_major) {
-    return (2u << 4) | (a_signed << 7) | (b_signed << 10) | (a_mn_major << 15) | ((n >> 3) << 17) | ((m >> 4) << 24);
+__host__ __device__ constexpr uint32_t umma_idesc_i8(uint32_t m, uint32_t n, uint32_t a_signed, uint32_t b_signed, uint32_t a_mn_major,
+                                                     uint32_t b_mn_major = 0) {
+    return (2u << 4) | (a_signed << 7) | (b_signed << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p; }"
@@ -136,6 +148,11 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&r)[8]) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(taddr));
 }
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Order-preserving map of fp32 to int32 (for redux.sync.max) and back.
@@ -146,7 +163,8 @@ __device__ __forceinline__ float unordered(int i) { return __int_as_float(i ^ ((
 template <int NBLK, bool Q_F16>
 __global__ void __launch_bounds__(kThreads, 2)
 decode_tc5_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ CUtensorMap kmap_single,
-                  const __grid_constant__ CUtensorMap vmap_single) {
+                  const __grid_constant__ CUtensorMap vmap_single, const __grid_constant__ CUtensorMap kmap_next,
+                  const __grid_constant__ CUtensorMap vmap_next) {
     using L = Smem<NBLK>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1024-aligned, still a shared-space pointer
@@ -156,6 +174,11 @@ decode_tc5_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t split = blockIdx.x, kv_head = blockIdx.y, session = blockIdx.z;
+    // optional per-CTA time stamps (b200kv_set_timeline_buffer): 8 words per CTA -- start, dependency wait over, set-up
+    // barrier passed, first S tile seen, loop end, last sums folded, partial emitted, merge done
+    const bool TL = p.timeline != nullptr && session == 0;
+    uint64_t* tl = TL ? p.timeline + (static_cast<size_t>(kv_head) * gridDim.x + split) * 16 : nullptr;
+    if (TL && tid == 0) tl[0] = global_ns();
     const b200kv_view& view = session_view(p, session);
     uint32_t begin, end;
     resolve_range(p, session, view, &begin, &end);
@@ -188,7 +211,9 @@ decode_tc5_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
     auto bar_empty = [&](int s) { return bar0 + (kStages + s) * 8; };
     auto bar_s_full = [&](int b) { return bar0 + (2 * kStages + b) * 8; };
     auto bar_s_empty = [&](int b) { return bar0 + (2 * kStages + 2 + b) * 8; };
-    const uint32_t bar_p_full = bar0 + (2 * kStages + 4) * 8, bar_p_empty = bar0 + (2 * kStages + 5) * 8;
+    auto bar_p_full = [&](int b) { return bar0 + (2 * kStages + 4 + b) * 8; };
+    auto bar_p_empty = [&](int b) { return bar0 + (2 * kStages + 6 + b) * 8; };
+    const uint32_t bar_row = bar0 + (2 * kStages + 8) * 8;   // the appended row is in the cache
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
     uint32_t* fail_flag = tmem_slot + 1;
 
@@ -214,41 +239,64 @@ decode_tc5_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
         bulk_load(sdst + L::kSTile, vs_plane + static_cast<size_t>(pos0) * (NBLK * 2), sbytes, bar);
     };
 
+    // Tile i of the NEXT cache the caller will attend (p.next: normally the next layer's) towards L2.  A launch is
+    // released only when the one before it has completed, and then spends about 2.5 us on Q and on its first tile
+    // before a ring stage frees up; with the merge and hand-over at its end, HBM idles for a third of a launch's time
+    // at 32K positions.  Pulling the next launch's tiles -- those its rings will not already hold -- into L2 while this
+    // launch streams fills those gaps: the next launch then finds them in L2.  (Prefetching a launch's OWN later tiles
+    // at its start measured slower: the bulk requests delay the loads and stores of the previous launch's merge.)
+    const bool hint = p.next_rows > 0;
+    const int next_row_base = static_cast<int>(static_cast<uint64_t>(kv_head) * p.next_capacity);
+    auto prefetch_next = [&](int i) {
+        const uint32_t pos0 = (t0 + i) * kTileM;
+        if (pos0 >= p.next_rows) return;
+        const uint32_t sbytes = min(static_cast<uint32_t>(kTileM), static_cast<uint32_t>(p.next_capacity) - pos0) * (NBLK * 2);
+        tma_prefetch_2d(&kmap_next, 0, next_row_base + static_cast<int>(pos0));
+        tma_prefetch_2d(&vmap_next, 0, next_row_base + static_cast<int>(pos0));
+        bulk_prefetch(p.next_key_scales + (static_cast<size_t>(kv_head) * p.next_capacity + pos0) * (NBLK * 2), sbytes);
+        bulk_prefetch(p.next_value_scales + (static_cast<size_t>(kv_head) * p.next_capacity + pos0) * (NBLK * 2), sbytes);
+    };
+
     // ---- set-up ---------------------------------------------------------------------------------------------
     int issued = 0;
     if (warp == kProducerWarp) {
         if (lane == 0) {
             for (int s = 0; s < kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
-            for (int b = 0; b < 2; ++b) { mbar_init(bar_s_full(b), 1); mbar_init(bar_s_empty(b), 128); }
-            mbar_init(bar_p_full, 128);
-            mbar_init(bar_p_empty, 1);
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(bar_s_full(b), 1); mbar_init(bar_s_empty(b), kConsumers);
+                mbar_init(bar_p_full(b), kConsumers); mbar_init(bar_p_empty(b), 1);
+            }
+            mbar_init(bar_row, 1);
             *fail_flag = 0;
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             // old cache rows do not depend on the preceding kernels: start streaming them before waiting for those
-            while (issued < kStages && issued < ntiles && (t0 + issued + 1) * kTileM <= early_end) { issue(issued); ++issued; }
+            while (issued < kEarlyTiles && issued < ntiles && (t0 + issued + 1) * kTileM <= early_end) { issue(issued); ++issued; }
         }
-        issued = __shfl_sync(0xffffffffu, issued, 0);
     } else if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     pdl_wait();
-    if (warp == kProducerWarp && owner) {
-        // The new row of a fused append: fetched, transformed, quantised and stored by this warp now, while the
-        // memory system is still quiet; its tile is loaded (by TMA, an asynchronous-proxy read) only afterwards.
-        float new_k[4], new_v[4];
+    if (TL && tid == 0) tl[1] = global_ns();
+    // The new row of a fused append is fetched now, while the memory system is still quiet (once the rings stream, a
+    // dependent load waits behind megabytes of queued tile traffic); its own warp transforms and stores it after the
+    // set-up barrier, while the other warps are already at work on the tiles before it.
+    float new_k[4], new_v[4];
+    const bool appends = warp == kAppendWarp && owner;
+    if (appends) {
         tail::load_new_row(p.new_key, p.new_is_f16, kv_head, lane, new_k);
         tail::load_new_row(p.new_value, p.new_is_f16, kv_head, lane, new_v);
-        tail::fused_append_row<NBLK>(p, view, new_k, new_v, end - 1, head_row0 + end - 1, lane);
-        __threadfence();
-        asm volatile("fence.proxy.async;" ::: "memory");
-        __syncwarp();
     }
-    if (warp == kProducerWarp && lane == 0)
-        while (issued < kStages && issued < ntiles) { issue(issued); ++issued; }
+    if (warp == kProducerWarp && lane == 0) {
+        const int limit = owner ? ntiles - 1 : ntiles;   // the tile that holds the appended row is loaded only after the row is stored
+        while (issued < kStages && issued < limit) { issue(issued); ++issued; }
+    }
 
-    // ---- Q: 15 bits per head as two int8 planes, rows h (hi) and 4 + h (lo) of the B operand of S^T = K . Q^T ----
+    // ---- Q: 15 bits per head as two int8 planes.  Rows of the B operand of S^T = K . Q^T:
+    //      [hi h0 .. hi h3, lo h0 .. lo h3].  The operand has 16 rows (the smallest N next to
+    //      M = 128 that every kind::i8 shape table lists); rows 8-15 are whatever follows in shared memory (the scale
+    //      tiles): they only produce columns 8-15 of S, which nobody reads, and integer sums of arbitrary bytes are harmless ----
     if (warp < 4) {
         uint32_t hi4 = 0, lo4 = 0;
         float qm = 0.0f;
@@ -282,99 +330,111 @@ decode_tc5_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
         const int n_hi = warp, n_lo = 4 + warp;
         *reinterpret_cast<uint32_t*>(smem + L::kOffQ + n_hi * 128 + ((((lane >> 2) ^ (n_hi & 7))) << 4) + (lane & 3) * 4) = hi4;
         *reinterpret_cast<uint32_t*>(smem + L::kOffQ + n_lo * 128 + ((((lane >> 2) ^ (n_lo & 7))) << 4) + (lane & 3) * 4) = lo4;
-    } else if (warp >= 6) {
-        // rows 8-15 of the Q operand are zero
-        reinterpret_cast<uint4*>(smem + L::kOffQ + 8 * 128)[tid - 192] = make_uint4(0, 0, 0, 0);
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // Q was written by ordinary stores, the MMA reads it through the async proxy
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (TL && tid == 0) tl[2] = global_ns();
 
-    // what the softmax threads hand to the epilogue
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // this thread's dim (= tid), heads 0..3, relative to m_run
-    float m_run[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-    float l_run[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // sums over this thread's positions only
     bool failed = false;
 
     if (warp == kProducerWarp) {
         // =============================== TMA producer ===============================
         if (lane == 0) {
+            if (hint)
+                for (int i = kEarlyTiles; i < issued - 1; ++i) prefetch_next(i);
             for (int i = issued; i < ntiles; ++i) {
                 // stage i % kStages is free once the P.V of tile i - kStages has completed
-                if (!mbar_wait(bar_empty(i % kStages), static_cast<uint32_t>((i / kStages - 1) & 1))) { failed = true; break; }
+                if (i >= kStages && !mbar_wait(bar_empty(i % kStages), static_cast<uint32_t>((i / kStages - 1) & 1))) { failed = true; break; }
+                if (owner && i == ntiles - 1 && !mbar_wait(bar_row, 0)) { failed = true; break; }
                 issue(i);
+                if (hint && i - 1 >= kEarlyTiles) prefetch_next(i - 1);   // the next launch fills its first kEarlyTiles stages itself
             }
+            if (hint && ntiles - 1 >= kEarlyTiles) prefetch_next(ntiles - 1);
+        }
+    } else if (warp == kAppendWarp) {
+        // =============================== fused append of the new token's row ===============================
+        if (appends) {
+            tail::fused_append_row<NBLK>(p, view, new_k, new_v, end - 1, head_row0 + end - 1, lane);
+            __threadfence();
+            asm volatile("fence.proxy.async;" ::: "memory");   // the row goes to the cache first; its tile is read by TMA (async proxy) afterwards
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_row);
         }
     } else if (warp == kMmaWarp) {
-        // =============================== MMA issuer ===============================
-        if (lane == 0 && ntiles > 0) {
+        // =============================== issuer of S^T = K . Q^T ===============================
+        if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc_i8(kTileM, 16, 1, 1, 0);   // K (signed) x Q planes (signed), both K-major
-            constexpr uint32_t idesc_o = umma_idesc_i8(kD, 32, 1, 0, 1);       // V^T (signed, MN-major) x P planes (unsigned, K-major)
-            int ns = 0, np = 0;   // next S and next P.V to issue
-            uint32_t idle = 0;
-            while (np < ntiles) {
-                bool progressed = false;
-                if (ns < ntiles && ns <= np + 1) {
-                    const int stage = ns % kStages, buf = ns & 1;
-                    if (mbar_test(bar_full(stage), static_cast<uint32_t>((ns / kStages) & 1)) &&
-                        mbar_test(bar_s_empty(buf), static_cast<uint32_t>(((ns >> 1) & 1) ^ 1))) {
-                        tc_fence_after();
-                        const uint32_t kt = sbase + L::kOffK + stage * L::kKTile;
+            for (int i = 0; i < ntiles; ++i) {
+                const int stage = i % kStages, buf = i & 1;
+                if (!mbar_wait(bar_s_empty(buf), static_cast<uint32_t>(((i >> 1) & 1) ^ 1))) { failed = true; break; }   // S buffer read out (tile i - 2)
+                if (!mbar_wait(bar_full(stage), static_cast<uint32_t>((i / kStages) & 1))) { failed = true; break; }     // tile landed
+                tc_fence_after();
+                const uint32_t kt = sbase + L::kOffK + stage * L::kKTile;
 #pragma unroll
-                        for (int b = 0; b < 4; ++b)   // one q8_0 block of 32 dims per MMA, each into its own 16 columns
-                            umma_i8(tmem_base + kColS + buf * 64 + b * 16, umma_desc(kt + 32 * b, 16, 1024),
-                                    umma_desc(sbase + L::kOffQ + 32 * b, 16, 1024), idesc_s, 0);
-                        umma_commit(bar_s_full(buf));
-                        ++ns;
-                        progressed = true;
-                    }
-                }
-                if (np < ns && mbar_test(bar_p_full, static_cast<uint32_t>(np & 1))) {
-                    tc_fence_after();
-                    const int stage = np % kStages;
-                    const uint32_t vt = sbase + L::kOffV + stage * L::kKTile;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)   // 32 positions per MMA
-                        umma_i8(tmem_base + kColO, umma_desc(vt + j * (32 * kD), kTileM * kD, 1024),
-                                umma_desc(sbase + L::kOffP + 32 * j, 16, 1024), idesc_o, j > 0);
-                    umma_commit(bar_p_empty);           // P tile free, the tile's sums complete
-                    umma_commit(bar_empty(stage));      // ring stage may be refilled
-                    ++np;
-                    progressed = true;
-                }
-                if (progressed) idle = 0;
-                else if (++idle >= 16u * kSpin) { failed = true; break; }   // a probe is much shorter than a try_wait
+                for (int b = 0; b < 4; ++b)   // one q8_0 block of 32 dims per MMA, each into its own 16 columns
+                    umma_i8(tmem_base + kColS + buf * 64 + b * 16, umma_desc(kt + 32 * b, 16, 1024, 2),
+                            umma_desc(sbase + L::kOffQ + 32 * b, 16, 1024, 2), idesc_s, 0);
+                umma_commit(bar_s_full(buf));
             }
         }
-    } else if (warp < 4) {
+    } else if (warp == kPvWarp) {
+        // =============================== issuer of O^T = V^T . P ===============================
+        if (lane == 0) {
+            constexpr uint32_t idesc_o = umma_idesc_i8(kD, 32, 1, 0, 1, 1);    // V^T (signed, MN-major) x P planes (unsigned, MN-major)
+            for (int i = 0; i < ntiles; ++i) {
+                const int stage = i % kStages, buf = i & 1;
+                if (!mbar_wait(bar_p_full(buf), static_cast<uint32_t>((i >> 1) & 1))) { failed = true; break; }
+                if (!mbar_wait(bar_full(stage), static_cast<uint32_t>((i / kStages) & 1))) { failed = true; break; }   // long complete: the V tile's landing, observed by this thread
+                tc_fence_after();
+                const uint32_t vt = sbase + L::kOffV + stage * L::kKTile;
+                const uint32_t pt = sbase + L::kOffP + buf * (kTileM * 32);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)   // 32 positions per MMA
+                    umma_i8(tmem_base + kColO + buf * 32, umma_desc(vt + j * (32 * kD), kTileM * kD, 1024, 2),
+                            umma_desc(pt + j * (32 * 32), 32, 256, 6), idesc_o, j > 0);
+                umma_commit(bar_p_empty(buf));      // P buffer free, the tile's sums complete
+                umma_commit(bar_empty(stage));      // ring stage may be refilled
+            }
+        }
+    }
+
+    // what the softmax threads hand to the epilogue: this thread's dim (= tid), heads 0..3, relative to m_run
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float m_run[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+
+    if (warp < 4) {
         // =============================== softmax threads: one per position of a tile ===============================
         const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
         float qmul[4];
 #pragma unroll
         for (int h = 0; h < 4; ++h) qmul[h] = reinterpret_cast<const float*>(smem + L::kOffQmul)[h];
-        // P rows n = 8*block + 4*plane + head; this thread's byte of row n sits in chunk (tid >> 4) ^ (n & 7)
-        uint32_t p_addr[8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r) p_addr[r] = sbase + L::kOffP + r * 128 + ((((tid >> 4) ^ r)) << 4) + (tid & 15);
+        // P is the MN-major B operand: this position's 32 bytes (column n = 8*block + 4*plane + head) form one row of
+        // 32 bytes, 32-byte swizzle: 16-byte chunk c of row r sits at 32 r + ((c ^ ((r >> 2) & 1)) << 4)
+        const uint32_t p_row = static_cast<uint32_t>(tid) * 32u;
+        const uint32_t p_flip = static_cast<uint32_t>((tid >> 2) & 1) << 4;
         int* xch = reinterpret_cast<int*>(smem + L::kOffXch);
-        float pend[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // fixed-point scale of the P.V sums still in flight (own block), relative to m_run
+        float l_run[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // sums over this thread's positions only
+        // per O buffer: fixed-point scale of the sums in flight (own block), relative to m_run
+        float pend_a[4] = {0.0f, 0.0f, 0.0f, 0.0f}, pend_b[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         auto wait = [&](uint32_t bar, uint32_t parity) { if (!failed && !mbar_wait(bar, parity)) failed = true; };
-        auto fold_o = [&]() {   // the completed sums of the previous tile: own block's 8 columns -> fp32 accumulators
+        auto fold_o = [&](int buf) {   // the completed sums of a tile: own block's 8 columns -> fp32 accumulators
             int o[8];
             tc_fence_after();
-            tmem_ld8(tmem_base + lane_addr + kColO + warp * 8, o);
+            tmem_ld8(tmem_base + lane_addr + kColO + buf * 32 + warp * 8, o);
             tmem_ld_wait();
             tc_fence_before();
 #pragma unroll
-            for (int h = 0; h < 4; ++h) acc[h] = fmaf(static_cast<float>(o[h] * 256 + o[4 + h]), pend[h], acc[h]);
+            for (int h = 0; h < 4; ++h) acc[h] = fmaf(static_cast<float>(o[h] * 256 + o[4 + h]), buf ? pend_b[h] : pend_a[h], acc[h]);
         };
 
         for (int i = 0; i < ntiles; ++i) {
             const int stage = i % kStages, buf = i & 1;
             wait(bar_full(stage), static_cast<uint32_t>((i / kStages) & 1));      // the scale tiles of this stage (async-proxy writes)
             wait(bar_s_full(buf), static_cast<uint32_t>((i >> 1) & 1));
+            if (TL && i == 0 && tid == 0) tl[3] = global_ns();
             tc_fence_after();
             int sv[4][8];   // per block: hi sums of heads 0-3, lo sums of heads 0-3
 #pragma unroll
@@ -459,43 +519,53 @@ decode_tc5_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
             for (int h = 0; h < 4; ++h) {
                 const float m_new = fmaxf(m_run[h], m_tile[h]);
                 const float alpha = (m_run[h] == -INFINITY) ? 0.0f : exp2f(m_run[h] - m_new);
-                acc[h] *= alpha; l_run[h] *= alpha; pend[h] *= alpha;
+                acc[h] *= alpha; l_run[h] *= alpha; pend_a[h] *= alpha; pend_b[h] *= alpha;
                 m_run[h] = m_new;
                 const float w = (s[h] == -INFINITY) ? 0.0f : exp2f(s[h] - m_new);
                 l_run[h] += w;
                 const float wmax = (m_tile[h] == -INFINITY) ? 0.0f : exp2f(m_tile[h] - m_new);
-                wn[h] = wmax > 0.0f ? w * __frcp_rn(wmax) : 0.0f;
+                wn[h] = wmax > 0.0f ? __fdividef(w, wmax) : 0.0f;
                 nscale[h] = wmax * vs_own * (1.0f / kPMax);
             }
-            uint32_t pq[4][4];   // [block][head]: w * value_scale as 16-bit fixed point
+            // [block]: w * value_scale as 16-bit fixed point, then the planes: hi bytes of heads 0-3, lo bytes of heads 0-3
+            uint32_t p_hi[4], p_lo[4];
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-                const float wv = (valid && vs_max[b] > 0.0f) ? vs[b] * (kPMax * __frcp_rn(vs_max[b])) : 0.0f;
+                const float wv = (valid && vs_max[b] > 0.0f) ? vs[b] * __fdividef(kPMax, vs_max[b]) : 0.0f;
+                uint32_t pq[4];
 #pragma unroll
-                for (int h = 0; h < 4; ++h) pq[b][h] = min(__float2uint_rn(wn[h] * wv), 65535u);
+                for (int h = 0; h < 4; ++h) pq[h] = min(__float2uint_rn(wn[h] * wv), 65535u);
+                const uint32_t p01 = pq[0] | (pq[1] << 16), p23 = pq[2] | (pq[3] << 16);
+                p_hi[b] = __byte_perm(p01, p23, 0x7531);
+                p_lo[b] = __byte_perm(p01, p23, 0x6420);
             }
-            // ---- the previous tile's P.V has completed: fold its sums, then P is free for this tile ----
-            if (i > 0) {
-                wait(bar_p_empty, static_cast<uint32_t>((i - 1) & 1));
-                fold_o();
+            // ---- P and O buffer `buf` were last used by tile i - 2: its P.V has completed; fold its sums first ----
+            if (i >= 2) {
+                wait(bar_p_empty(buf), static_cast<uint32_t>(((i >> 1) - 1) & 1));
+                fold_o(buf);
             }
 #pragma unroll
-            for (int h = 0; h < 4; ++h) pend[h] = nscale[h];
-#pragma unroll
-            for (int b = 0; b < 4; ++b)
-#pragma unroll
-                for (int h = 0; h < 4; ++h) {
-                    asm volatile("st.shared.u8 [%0], %1;" ::"r"(p_addr[h] + b * 1024), "r"(pq[b][h] >> 8) : "memory");      // plane 0: high byte
-                    asm volatile("st.shared.u8 [%0], %1;" ::"r"(p_addr[4 + h] + b * 1024), "r"(pq[b][h]) : "memory");       // plane 1: low byte
-                }
+            for (int h = 0; h < 4; ++h) { if (buf) pend_b[h] = nscale[h]; else pend_a[h] = nscale[h]; }
+            const uint32_t pt = sbase + L::kOffP + buf * (kTileM * 32) + p_row;
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(pt + p_flip), "r"(p_hi[0]), "r"(p_lo[0]), "r"(p_hi[1]), "r"(p_lo[1]) : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(pt + (p_flip ^ 16u)), "r"(p_hi[2]), "r"(p_lo[2]), "r"(p_hi[3]), "r"(p_lo[3]) : "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(bar_p_full);
+            mbar_arrive(bar_p_full(buf));
         }
-        if (ntiles > 0) {
-            wait(bar_p_empty, static_cast<uint32_t>((ntiles - 1) & 1));
-            fold_o();
+        if (TL && tid == 0) tl[4] = global_ns();
+        // the last two tiles' sums
+        if (ntiles >= 2) {
+            const int buf = (ntiles - 2) & 1;
+            wait(bar_p_empty(buf), static_cast<uint32_t>(((ntiles - 2) >> 1) & 1));
+            fold_o(buf);
         }
-        // ---- row sums over the CTA ----
+        if (ntiles >= 1) {
+            const int buf = (ntiles - 1) & 1;
+            wait(bar_p_empty(buf), static_cast<uint32_t>(((ntiles - 1) >> 1) & 1));
+            fold_o(buf);
+        }
+        if (TL && tid == 0) tl[5] = global_ns();
+        // ---- row sums over the CTA, then the CTA's partial leaves at once: thread = dim holds all four heads ----
 #pragma unroll
         for (int h = 0; h < 4; ++h) l_run[h] = warp_sum(l_run[h]);
         if (lane == 0) {
@@ -509,6 +579,7 @@ decode_tc5_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
             const float4 a = *reinterpret_cast<const float4*>(smem + L::kOffL + w * 16);
             lt[0] += a.x; lt[1] += a.y; lt[2] += a.z; lt[3] += a.w;
         }
+        // a wait that ran out anywhere in the pipeline ends in a wait of these threads running out
         const bool poisoned = *reinterpret_cast<volatile uint32_t*>(fail_flag) != 0;
         if (poisoned && tid == 0) tail::report(p, B200KV_STATUS_PIPE_TIMEOUT);
 #pragma unroll
@@ -518,6 +589,7 @@ decode_tc5_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
             if (poisoned) { at = __int_as_float(0x7fc00000); mh = at; lh = at; }
             tail::emit_partial(p, session, split, num_splits, kv_head * G + h, tid, at, mh, lh);
         }
+        if (TL && tid == 0) tl[6] = global_ns();
     }
 
     // ---- teardown: every role arrives here, with or without a timeout; TMEM is always released ----
@@ -528,19 +600,22 @@ decode_tc5_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
     if (p.ws_tagged == nullptr) return;   // a separate merge kernel follows
-    // the CTA of split h merges query head h of this kv head once all splits' tagged partials have landed
-    tail::fused_merge(p, session, kv_head, split, num_splits, G, reinterpret_cast<float*>(smem + L::kOffFold));
+    // the CTA of split h merges query head h of this kv head once all splits' tagged partials have landed (256 threads;
+    // the merger's scratch takes the place of the P buffers, which every MMA has long consumed)
+    tail::fused_merge(p, session, kv_head, split, num_splits, G, reinterpret_cast<float*>(smem + L::kOffP));
+    if (TL && tid == 0) tl[7] = global_ns();
 }
 
 // ---- host side -----------------------------------------------------------------------------------------
 
 template <int NBLK, bool Q_F16>
-int launch_one(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap, dim3 grid, cudaStream_t stream) {
+int launch_one(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap, const CUtensorMap& kmap_next, const CUtensorMap& vmap_next,
+               dim3 grid, cudaStream_t stream) {
     using L = Smem<NBLK>;
     static std::atomic<uint64_t> done{0};   // one per kernel instantiation: devices that have opted in
     const cudaError_t attr_err = opt_in_dynamic_smem(reinterpret_cast<const void*>(decode_tc5_kernel<NBLK, Q_F16>), L::kAlloc, done);
     if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err, "cudaFuncSetAttribute(decode_tc5)"); return B200KV_ERR_CUDA; }
-    B200KV_CUDA_TRY(launch_kernel(decode_tc5_kernel<NBLK, Q_F16>, grid, dim3(kThreads), L::kAlloc, stream, true, p, kmap, vmap));
+    B200KV_CUDA_TRY(launch_kernel(decode_tc5_kernel<NBLK, Q_F16>, grid, dim3(kThreads), L::kAlloc, stream, true, p, kmap, vmap, kmap_next, vmap_next));
     return B200KV_OK;
 }
 
@@ -563,10 +638,28 @@ int launch_decode_tc5(const DecodeParams& p_in, const b200kv_view& geometry, uin
         std::memset(&kmap, 0, sizeof kmap);   // per-session descriptors come from the device table
         std::memset(&vmap, 0, sizeof vmap);
     }
+    // The cache attended next (a hint): only where it has this cache's shape, for single-session launches, and where
+    // what would be prefetched stays well inside L2 next to this launch's own tiles.
+    CUtensorMap kmap_next, vmap_next;
+    std::memset(&kmap_next, 0, sizeof kmap_next);
+    std::memset(&vmap_next, 0, sizeof vmap_next);
+    p.next_rows = 0;
+    if (p_in.next_view != nullptr && p.views == nullptr && p.sessions == 1) {
+        const b200kv_view& nv = *p_in.next_view;
+        const uint64_t bytes = static_cast<uint64_t>(max_length) * nv.kv_heads * (2 * kD + 4 * (kD / nv.qblock));
+        if (q8_fast_path_ok(nv, p.query_heads) && nv.kv_heads == geometry.kv_heads && nv.qblock == geometry.qblock && bytes <= (48ull << 20) * 2 &&
+            encode_kv_maps(nv, kTileM, &kmap_next, &vmap_next) == B200KV_OK) {
+            p.next_rows = max_length < nv.capacity ? max_length : static_cast<uint32_t>(nv.capacity);
+            p.next_capacity = nv.capacity;
+            p.next_key_scales = static_cast<const uint8_t*>(nv.key_scales);
+            p.next_value_scales = static_cast<const uint8_t*>(nv.value_scales);
+        }
+    }
+    p.next_view = nullptr;
     const bool blocks = geometry.qblock == 32;
     dim3 grid(p.num_splits, geometry.kv_heads, p.sessions);
-    if (blocks) return p.q_is_f16 ? launch_one<4, true>(p, kmap, vmap, grid, stream) : launch_one<4, false>(p, kmap, vmap, grid, stream);
-    return p.q_is_f16 ? launch_one<1, true>(p, kmap, vmap, grid, stream) : launch_one<1, false>(p, kmap, vmap, grid, stream);
+    if (blocks) return p.q_is_f16 ? launch_one<4, true>(p, kmap, vmap, kmap_next, vmap_next, grid, stream) : launch_one<4, false>(p, kmap, vmap, kmap_next, vmap_next, grid, stream);
+    return p.q_is_f16 ? launch_one<1, true>(p, kmap, vmap, kmap_next, vmap_next, grid, stream) : launch_one<1, false>(p, kmap, vmap, kmap_next, vmap_next, grid, stream);
 }
 
 }  // namespace b200kv

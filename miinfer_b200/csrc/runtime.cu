@@ -34,6 +34,18 @@ uint32_t* current_status_word() {
     return g_status_word[device].load(std::memory_order_relaxed);
 }
 
+static std::atomic<uint64_t*> g_timeline[kMaxDevices] = {};
+static std::atomic<uint32_t> g_timeline_words[kMaxDevices] = {};
+uint64_t* current_timeline_buffer(uint32_t ctas) {
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    uint64_t* buf = g_timeline[device].load(std::memory_order_relaxed);
+    return (buf != nullptr && static_cast<uint64_t>(ctas) * 16 <= g_timeline_words[device].load(std::memory_order_relaxed)) ? buf : nullptr;
+}
+
 static std::atomic<int> g_streaming_kernel{0};
 int streaming_kernel_choice() { return g_streaming_kernel.load(std::memory_order_relaxed); }
 
@@ -113,6 +125,18 @@ int b200kv_set_status_word(uint32_t* device_word) {
     }
     if ((reinterpret_cast<uintptr_t>(device_word) & 3u) != 0) return B200KV_ERR_INVALID;
     g_status_word[device].store(device_word, std::memory_order_relaxed);
+    return B200KV_OK;
+}
+
+int b200kv_set_timeline_buffer(uint64_t* device_words, uint32_t capacity_words) {
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
+        (void)cudaGetLastError();
+        return B200KV_ERR_DEVICE;
+    }
+    if ((reinterpret_cast<uintptr_t>(device_words) & 7u) != 0) return B200KV_ERR_INVALID;
+    g_timeline[device].store(device_words, std::memory_order_relaxed);
+    g_timeline_words[device].store(device_words ? capacity_words : 0, std::memory_order_relaxed);
     return B200KV_OK;
 }
 

@@ -18,6 +18,8 @@
 #include <cstdio>
 #include <cstring>
 #include <filesystem>
+#include <new>
+#include <stdexcept>
 #include <string>
 #include <string_view>
 #include <vector>
@@ -60,12 +62,36 @@ bool same_geometry(const b200kv_view* views, uint32_t layers) {
     return true;
 }
 
-// Reads and checks header + tokens; leaves the file positioned at the (empty) GDN section.
+uint64_t file_size(std::FILE* f) {
+    struct stat st;
+    return (f != nullptr && fstat(fileno(f), &st) == 0 && st.st_size > 0) ? static_cast<uint64_t>(st.st_size) : 0;
+}
+
+// Runs an entry point's body; nothing may leave an extern "C" function as an exception.  A size taken from a damaged
+// file that cannot be allocated is a format error, anything else the file system's.
+template <typename F>
+int guarded(F&& body) {
+    try {
+        return body();
+    } catch (const std::bad_alloc&) {
+        return B200KV_ERR_FORMAT;
+    } catch (const std::length_error&) {
+        return B200KV_ERR_FORMAT;
+    } catch (const std::exception&) {
+        return B200KV_ERR_IO;
+    }
+}
+
+// Reads and checks header + tokens; leaves the file positioned at the (empty) GDN section.  Every length the header
+// states is checked against the size of the file before anything is allocated from it.
 int read_front(File& in, b200kv_session_header* hdr, std::vector<uint32_t>* tokens) {
+    const uint64_t size = file_size(in.f);
     if (!in.read(hdr, sizeof *hdr)) return B200KV_ERR_FORMAT;
     if (std::memcmp(hdr->magic, "MISS", 4) != 0 || hdr->version != kSessionVersion) return B200KV_ERR_FORMAT;
     if (hdr->tokens_bytes != static_cast<uint64_t>(hdr->prefix_length) * sizeof(uint32_t) || hdr->prefix_length == 0) return B200KV_ERR_FORMAT;
     if (hdr->prefix_length > (1u << 28)) return B200KV_ERR_FORMAT;
+    if (hdr->tokens_bytes > size || hdr->kv_bytes > size || sizeof *hdr + hdr->tokens_bytes + hdr->kv_bytes + sizeof(Trailer) != size)
+        return B200KV_ERR_FORMAT;
     tokens->resize(hdr->prefix_length);
     if (!in.read(tokens->data(), hdr->tokens_bytes)) return B200KV_ERR_FORMAT;
     if (b200kv_token_sequence_hash(tokens->data(), tokens->size()) != hdr->token_hash) return B200KV_ERR_FORMAT;   // :198
@@ -98,6 +124,7 @@ int b200kv_prefix_match(const char* cached_model_id, const char* cached_quantiza
 int b200kv_session_write(const char* path, const char* model_id, const char* quantization, const uint32_t* tokens,
                          uint32_t prefix_length, const void* kv_payload, uint64_t layer_bytes, uint32_t layers,
                          uint32_t kv_heads, uint32_t head_dim, uint32_t qblock, uint32_t quant_mode) {
+    return guarded([&]() -> int {
     if (path == nullptr || tokens == nullptr || prefix_length == 0) return B200KV_ERR_INVALID;   // the reference refuses an empty prefix (:40-42)
     if (layers != 0 && kv_payload == nullptr) return B200KV_ERR_INVALID;
     b200kv_session_header h;
@@ -138,9 +165,11 @@ int b200kv_session_write(const char* path, const char* model_id, const char* qua
     }
     std::filesystem::rename(tmp, final_path, ec);
     return ec ? B200KV_ERR_IO : B200KV_OK;
+    });
 }
 
 int b200kv_session_inspect(const char* path, b200kv_session_header* header, uint32_t* tokens_out, uint32_t tokens_capacity) {
+    return guarded([&]() -> int {
     if (path == nullptr || header == nullptr) return B200KV_ERR_INVALID;
     File in(path, "rb");
     if (in.f == nullptr) return B200KV_ERR_IO;
@@ -152,11 +181,13 @@ int b200kv_session_inspect(const char* path, b200kv_session_header* header, uint
         std::memcpy(tokens_out, tokens.data(), tokens.size() * sizeof(uint32_t));
     }
     return B200KV_OK;
+    });
 }
 
 int b200kv_session_read(const char* path, const char* model_id, const char* quantization, uint32_t layers, uint32_t kv_heads,
                         uint32_t head_dim, uint32_t qblock, uint32_t quant_mode, uint32_t* tokens_out, uint32_t tokens_capacity,
                         uint32_t* prefix_length_out, void* kv_payload_out, uint64_t payload_capacity) {
+    return guarded([&]() -> int {
     if (path == nullptr) return B200KV_ERR_INVALID;
     File in(path, "rb");
     if (in.f == nullptr) return B200KV_ERR_IO;
@@ -182,16 +213,20 @@ int b200kv_session_read(const char* path, const char* model_id, const char* quan
     }
     if (prefix_length_out != nullptr) *prefix_length_out = h.prefix_length;
     return B200KV_OK;
+    });
 }
 
 int b200kv_session_find(const char* session_dir, const char* model_id, const char* quantization, const uint32_t* prompt,
                         uint32_t prompt_length, char* path_out, size_t path_bytes, uint32_t* prefix_length_out) {
+    return guarded([&]() -> int {
     if (session_dir == nullptr || prompt == nullptr || path_out == nullptr) return B200KV_ERR_INVALID;
     std::error_code ec;
     if (!std::filesystem::is_directory(session_dir, ec)) return B200KV_ERR_MISMATCH;
     uint32_t best = 0;
     std::string best_path;
-    for (const auto& entry : std::filesystem::directory_iterator(session_dir, ec)) {
+    std::filesystem::directory_iterator it(session_dir, ec), last;
+    for (; !ec && it != last; it.increment(ec)) {
+        const std::filesystem::directory_entry& entry = *it;
         if (!entry.is_regular_file(ec) || entry.path().extension() != ".miinfer") continue;
         b200kv_session_header h;
         std::vector<uint32_t> tokens;
@@ -207,10 +242,12 @@ int b200kv_session_find(const char* session_dir, const char* model_id, const cha
     std::memcpy(path_out, best_path.c_str(), best_path.size() + 1);
     if (prefix_length_out != nullptr) *prefix_length_out = best;
     return B200KV_OK;
+    });
 }
 
 int b200kv_session_save(const char* path, const char* model_id, const char* quantization, const uint32_t* tokens,
                         uint32_t prefix_length, const b200kv_view* layer_views, uint32_t layers, void* stream) {
+    return guarded([&]() -> int {
     if (layer_views == nullptr || layers == 0 || prefix_length == 0) return B200KV_ERR_INVALID;
     for (uint32_t i = 0; i < layers; ++i) {
         int rc = b200kv::validate_view(&layer_views[i]);
@@ -227,10 +264,12 @@ int b200kv_session_save(const char* path, const char* model_id, const char* quan
     B200KV_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));   // the reference syncs here too (:112-114)
     return b200kv_session_write(path, model_id, quantization, tokens, prefix_length, payload.data(), layer_bytes, layers,
                                 layer_views[0].kv_heads, layer_views[0].head_dim, layer_views[0].qblock, layer_views[0].quant_mode);
+    });
 }
 
 int b200kv_session_load(const char* path, const char* model_id, const char* quantization, const b200kv_view* layer_views,
                         uint32_t layers, uint32_t* tokens_out, uint32_t tokens_capacity, uint32_t* prefix_length_out, void* stream) {
+    return guarded([&]() -> int {
     if (layer_views == nullptr || layers == 0) return B200KV_ERR_INVALID;
     for (uint32_t i = 0; i < layers; ++i) {
         int rc = b200kv::validate_view(&layer_views[i]);
@@ -242,6 +281,10 @@ int b200kv_session_load(const char* path, const char* model_id, const char* quan
     if (rc != B200KV_OK) return rc;
     for (uint32_t i = 0; i < layers; ++i)
         if (h.prefix_length > layer_views[i].capacity) return B200KV_ERR_RANGE;
+    // the payload must be exactly what these caches hold for that many positions: checked before it sizes a buffer
+    if (h.gqa_layers != layers) return B200KV_ERR_MISMATCH;
+    if (h.kv_bytes != static_cast<uint64_t>(b200kv_snapshot_bytes(&layer_views[0], h.prefix_length)) * layers)
+        return h.kv_quant_mode != layer_views[0].quant_mode ? B200KV_ERR_MISMATCH : B200KV_ERR_FORMAT;
     std::vector<uint8_t> payload(h.kv_bytes);
     uint32_t prefix = 0;
     rc = b200kv_session_read(path, model_id, quantization, layers, layer_views[0].kv_heads, layer_views[0].head_dim, layer_views[0].qblock,
@@ -256,6 +299,7 @@ int b200kv_session_load(const char* path, const char* model_id, const char* quan
     B200KV_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));   // the staging buffer dies with this call
     if (prefix_length_out != nullptr) *prefix_length_out = prefix;
     return B200KV_OK;
+    });
 }
 
 }  // extern "C"

@@ -152,3 +152,60 @@ int b200kv_snapshot_clone(const b200kv_view* dst, const b200kv_view* src, uint64
 }
 
 }  // extern "C"
+
+// ---- dequantising download (inspection and tests) ----------------------------------------------------------------
+// AttentionLayerKvCacheStorage::download_key / download_value, src/prefill_v2/kv_cache.cpp:132-212: the first `tokens`
+// positions of one side as fp32 [kv_head][tokens][head_dim] in HOST memory, int8 values multiplied by their fp16
+// scale (here: the scale of their block), fp16 values widened.  Like the reference's it is a blocking host routine
+// (it stages the raw planes in host memory and converts there); it is not part of the per-token path.
+#include <vector>
+
+namespace {
+int download_side(const b200kv_view* view, uint64_t tokens, float* host_dst, bool key, cudaStream_t stream) {
+    using namespace b200kv;
+    int rc = validate_view(view);
+    if (rc != B200KV_OK) return rc;
+    if (host_dst == nullptr && tokens > 0) return B200KV_ERR_INVALID;
+    if (tokens > view->capacity) return B200KV_ERR_RANGE;   // the reference throws (kv_cache.cpp:133-135)
+    if (tokens == 0) return B200KV_OK;
+    if ((rc = ensure_device()) != B200KV_OK) return rc;
+    const uint32_t H = view->kv_heads, d = view->head_dim, nblk = d / view->qblock;
+    const bool q8 = key ? is_k_q8(view->quant_mode) : is_v_q8(view->quant_mode);
+    try {
+        if (q8) {
+            std::vector<int8_t> q(static_cast<size_t>(H) * tokens * d);
+            std::vector<uint16_t> sc(static_cast<size_t>(H) * tokens * nblk);
+            const int8_t* src_q = key ? view->key_q8 : view->value_q8;
+            const uint8_t* src_s = static_cast<const uint8_t*>(key ? view->key_scales : view->value_scales);
+            B200KV_CUDA_TRY(cudaMemcpy2DAsync(q.data(), tokens * d, src_q, view->capacity * d, tokens * d, H, cudaMemcpyDeviceToHost, stream));
+            B200KV_CUDA_TRY(cudaMemcpy2DAsync(sc.data(), tokens * nblk * 2, src_s, view->capacity * nblk * 2, tokens * nblk * 2, H,
+                                              cudaMemcpyDeviceToHost, stream));
+            B200KV_CUDA_TRY(cudaStreamSynchronize(stream));
+            for (size_t row = 0; row < static_cast<size_t>(H) * tokens; ++row)
+                for (uint32_t b = 0; b < nblk; ++b) {
+                    const float scale = __half2float(__ushort_as_half(sc[row * nblk + b]));
+                    for (uint32_t i = 0; i < view->qblock; ++i) {
+                        const size_t idx = row * d + b * view->qblock + i;
+                        host_dst[idx] = static_cast<float>(q[idx]) * scale;
+                    }
+                }
+        } else {
+            std::vector<uint16_t> h(static_cast<size_t>(H) * tokens * d);
+            const void* src = key ? view->key_f16 : view->value_f16;
+            B200KV_CUDA_TRY(cudaMemcpy2DAsync(h.data(), tokens * d * 2, src, view->capacity * d * 2, tokens * d * 2, H, cudaMemcpyDeviceToHost, stream));
+            B200KV_CUDA_TRY(cudaStreamSynchronize(stream));
+            for (size_t i = 0; i < h.size(); ++i) host_dst[i] = __half2float(__ushort_as_half(h[i]));
+        }
+    } catch (const std::exception&) {
+        return B200KV_ERR_CUDA;
+    }
+    return B200KV_OK;
+}
+}  // namespace
+
+extern "C" int b200kv_download_key(const b200kv_view* view, uint64_t tokens, float* host_dst, void* stream) {
+    return download_side(view, tokens, host_dst, true, static_cast<cudaStream_t>(stream));
+}
+extern "C" int b200kv_download_value(const b200kv_view* view, uint64_t tokens, float* host_dst, void* stream) {
+    return download_side(view, tokens, host_dst, false, static_cast<cudaStream_t>(stream));
+}

@@ -15,14 +15,14 @@ from typing import Optional
 
 import torch
 
-from ._lib import B200KvError, View, check, lib
+from ._lib import B200KvError, PoolCounters, ReuseOptions, ReuseStats, View, check, lib
 
 __all__ = [
     "KvCacheQuantMode", "RopeMode", "AttentionKvCacheView", "AttentionLayerKvCacheStorage",
     "launch_kv_store_quant", "launch_decode_attention_quant", "launch_decode_attention_batched", "launch_decode_step",
     "launch_decode_partials", "launch_merge_partials", "launch_merge_partials_packed", "packed_partial", "partial_views", "launch_suffix_attention_quant",
     "Exchange", "launch_decode_attention_sharded", "decode_workspace", "prefill_workspace", "view_table", "make_decode_state", "make_prefill_state",
-    "launch_q_split_norm_rope", "launch_decode_state_advance", "q8_1_blocks", "exchange_words", "set_status_word", "workspace_reset", "set_decode_kernel",
+    "SnapshotPool", "ReusableContext", "DistMerge", "launch_q_split_norm_rope", "launch_decode_state_advance", "q8_1_blocks", "exchange_words", "set_status_word", "workspace_reset", "set_decode_kernel",
     "token_sequence_hash", "save_session", "load_session", "find_matching_session", "decode_kernel_kind", "set_launch_overlap", "B200KvError", "FORCE_GENERIC",
 ]
 
@@ -139,6 +139,24 @@ class AttentionLayerKvCacheStorage:
         v = self.view()
         check(lib.b200kv_snapshot_restore(C.byref(v), tokens, src.data_ptr(), _stream(stream)), "b200kv_snapshot_restore")
 
+    def download_key(self, tokens: int):
+        """kv_cache.cpp:132-170: the first `tokens` positions of K as a float32 numpy array [kv_head][tokens][head_dim], dequantised."""
+        return self._download(tokens, lib.b200kv_download_key)
+
+    def download_value(self, tokens: int):
+        """kv_cache.cpp:172-212."""
+        return self._download(tokens, lib.b200kv_download_value)
+
+    def _download(self, tokens: int, fn):
+        import numpy as np
+
+        if tokens > self.capacity:
+            raise RuntimeError("AttentionLayerKvCacheStorage: tokens exceeds capacity")   # kv_cache.cpp:133-135
+        out = np.empty((self.kv_heads, tokens, self.head_dim), np.float32)
+        v = self.view()
+        check(fn(C.byref(v), tokens, out.ctypes.data, _stream(None)), "b200kv_download")
+        return out
+
     def clone_prefix_from(self, other: "AttentionLayerKvCacheStorage", tokens: int,
                           stream: Optional[torch.cuda.Stream] = None) -> None:
         """Device-to-device copy of the first `tokens` positions (tools/miinfer_cli.cpp:1248-1317)."""
@@ -218,11 +236,14 @@ def launch_decode_attention_quant(view: View, q: torch.Tensor, *, query_heads: i
                                   cache_length: int = 0, decode_state: Optional[torch.Tensor] = None,
                                   output: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
                                   gated_output: Optional[torch.Tensor] = None, gated_output_q8: Optional[torch.Tensor] = None,
-                                  workspace: torch.Tensor, num_splits: int = 0, stream: Optional[torch.cuda.Stream] = None) -> None:
+                                  next_view: Optional[View] = None, workspace: torch.Tensor, num_splits: int = 0,
+                                  stream: Optional[torch.cuda.Stream] = None) -> None:
     """launch_qwen35_tiled_online_attention_quant_dynamic (qwen3_gpu_primitives.hpp:719-739).
-    gated_output_q8: uint8 tensor of query_heads * head_dim / 32 Q8_1 blocks (36 bytes each), see `q8_1_blocks`."""
+    gated_output_q8: uint8 tensor of query_heads * head_dim / 32 Q8_1 blocks (36 bytes each), see `q8_1_blocks`.
+    next_view: hint -- the cache attended next on this stream (the next layer's); its tiles are pulled towards L2."""
     check(lib.b200kv_decode_attn(C.byref(view), _ptr(q), _dtype(q), _ptr(gate), _ptr(output), _ptr(gated_output), _ptr(gated_output_q8),
-                                 query_heads, scale, cache_length, _ptr(decode_state), _ptr(workspace),
+                                 query_heads, scale, cache_length, _ptr(decode_state), None if next_view is None else C.byref(next_view),
+                                 _ptr(workspace),
                                  workspace.numel(), num_splits, _stream(stream)), "b200kv_decode_attn")
 
 
@@ -231,15 +252,17 @@ def launch_decode_step(view: View, key: torch.Tensor, value: torch.Tensor, q: to
                        rope_mode: RopeMode = RopeMode.NEOX_FULL, theta: float = 1.0e6, epsilon: float = 1.0e-6,
                        output: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
                        gated_output: Optional[torch.Tensor] = None, gated_output_q8: Optional[torch.Tensor] = None,
-                       workspace: torch.Tensor, num_splits: int = 0, stream: Optional[torch.cuda.Stream] = None) -> None:
+                       next_view: Optional[View] = None, workspace: torch.Tensor, num_splits: int = 0,
+                       stream: Optional[torch.cuda.Stream] = None) -> None:
     """Append one token and attend in one launch (b200kv_decode_step): the fused form of the store + decode-attention
-    call pair of src/prefill_v2/attention_layer.cpp:599-632."""
+    call pair of src/prefill_v2/attention_layer.cpp:599-632.  next_view: see launch_decode_attention_quant."""
     if key.dtype != value.dtype:
         raise ValueError("key and value must share a dtype")
     check(lib.b200kv_decode_step(C.byref(view), _ptr(key), _ptr(value), _dtype(key), _ptr(k_norm_weight), int(rope_mode), theta,
                                  epsilon, _ptr(q), _dtype(q), _ptr(gate), _ptr(output), _ptr(gated_output), _ptr(gated_output_q8),
                                  query_heads, scale,
-                                 position, _ptr(decode_state), _ptr(workspace), workspace.numel(), num_splits, _stream(stream)),
+                                 position, _ptr(decode_state), None if next_view is None else C.byref(next_view), _ptr(workspace),
+                                 workspace.numel(), num_splits, _stream(stream)),
           "b200kv_decode_step")
 
 
@@ -335,6 +358,42 @@ def launch_decode_attention_sharded(view: View, q: torch.Tensor, exchange: Excha
                                          query_heads, scale, range_begin, range_end, exchange._table, exchange.rank,
                                          exchange.world, phase, _ptr(workspace), workspace.numel(), num_splits,
                                          _stream(stream)), "b200kv_decode_attn_sharded")
+
+
+class DistMerge:
+    """b200kv_dist_*: the NCCL form of the cross-GPU merge for a C or C++ host.  `unique_id()` on one rank, passed
+    to the others (any transport), then every rank constructs a DistMerge; per layer: launch_decode_partials with
+    `self.partial` and `merge(output=...)`."""
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        check(lib.b200kv_dist_unique_id(buf), "b200kv_dist_unique_id")
+        return buf.raw
+
+    def __init__(self, unique_id: bytes, rank: int, world: int, query_heads: int, head_dim: int):
+        self._h = C.c_void_p()
+        check(lib.b200kv_dist_init(C.byref(self._h), None, C.create_string_buffer(unique_id, 128), rank, world, query_heads, head_dim),
+              "b200kv_dist_init")
+        m, l, a = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        check(lib.b200kv_dist_partial(self._h, C.byref(m), C.byref(l), C.byref(a)), "b200kv_dist_partial")
+        self.partial_ptrs = (m.value, l.value, a.value)
+        self.query_heads, self.head_dim = query_heads, head_dim
+
+    def decode_partials(self, view: View, q: torch.Tensor, *, scale: float, range_begin: int, range_end: int, workspace: torch.Tensor,
+                        num_splits: int = 0, stream: Optional[torch.cuda.Stream] = None) -> None:
+        m, l, a = self.partial_ptrs
+        check(lib.b200kv_decode_partials(C.byref(view), _ptr(q), _dtype(q), self.query_heads, scale, range_begin, range_end, m, l, a,
+                                         _ptr(workspace), workspace.numel(), num_splits, _stream(stream)), "b200kv_decode_partials")
+
+    def merge(self, *, output: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+              gated_output: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None) -> None:
+        check(lib.b200kv_dist_merge(self._h, _ptr(gate), _ptr(output), _ptr(gated_output), _stream(stream)), "b200kv_dist_merge")
+
+    def destroy(self) -> None:
+        if self._h:
+            lib.b200kv_dist_destroy(self._h)
+            self._h = C.c_void_p()
 
 
 def launch_merge_partials(part_m: torch.Tensor, part_l: torch.Tensor, part_acc: torch.Tensor, *, num_parts: int,
@@ -449,6 +508,107 @@ def find_matching_session(session_dir: str, model_id: str, quantization: str, pr
     n = C.c_uint32()
     rc = lib.b200kv_session_find(session_dir.encode(), model_id.encode(), quantization.encode(), p, len(prompt), out, 4096, C.byref(n))
     return (out.value.decode(), n.value) if rc == 0 else None
+
+
+def _tokens(tokens):
+    return (C.c_uint32 * len(tokens))(*tokens)
+
+
+class SnapshotPool:
+    """In-VRAM store of prefix snapshots with longest-prefix lookup (b200kv_pool_*): the KV part of the first
+    engine's session checkpoints, tools/miinfer_cli.cpp:1043-1317 (radix tree over token ids, least-recently-used
+    eviction, 8 entries / 3 GiB by default, captures only at multiples of `granularity` tokens)."""
+
+    def __init__(self, model_id: str = "", quantization: str = "", *, max_entries: int = 8, max_bytes: int = 3 << 30, granularity: int = 512):
+        self._h = C.c_void_p()
+        self.model_id, self.quantization = model_id, quantization
+        check(lib.b200kv_pool_create(C.byref(self._h), model_id.encode(), quantization.encode(), max_entries, max_bytes, granularity),
+              "b200kv_pool_create")
+
+    def close(self) -> None:
+        if self._h:
+            lib.b200kv_pool_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def capture(self, tokens, storages=None, *, index_only_bytes: Optional[int] = None, stream: Optional[torch.cuda.Stream] = None) -> bool:
+        """Keep the first len(tokens) positions of every layer (or, with index_only_bytes, only the bookkeeping)."""
+        done = C.c_int()
+        if index_only_bytes is not None:
+            check(lib.b200kv_pool_capture_index_only(self._h, _tokens(tokens), len(tokens), index_only_bytes, C.byref(done)),
+                  "b200kv_pool_capture_index_only")
+        else:
+            check(lib.b200kv_pool_capture(self._h, _tokens(tokens), len(tokens), _views(storages), len(storages), _stream(stream), C.byref(done)),
+                  "b200kv_pool_capture")
+        return bool(done.value)
+
+    def lookup(self, prompt, model_id: Optional[str] = None, quantization: Optional[str] = None):
+        """(matched_length, common_length) of the longest stored proper prefix of `prompt`."""
+        m, c = C.c_uint32(), C.c_uint32()
+        check(lib.b200kv_pool_lookup(self._h, None if model_id is None else model_id.encode(),
+                                     None if quantization is None else quantization.encode(), _tokens(prompt), len(prompt), C.byref(m), C.byref(c)),
+              "b200kv_pool_lookup")
+        return m.value, c.value
+
+    def restore(self, prompt, storages, stream: Optional[torch.cuda.Stream] = None) -> int:
+        """Copy the longest stored proper prefix of `prompt` into the caches; returns its length (0 = none)."""
+        m = C.c_uint32()
+        check(lib.b200kv_pool_restore(self._h, _tokens(prompt), len(prompt), _views(storages), len(storages), _stream(stream), C.byref(m)),
+              "b200kv_pool_restore")
+        return m.value
+
+    def stats(self) -> dict:
+        c = PoolCounters()
+        check(lib.b200kv_pool_stats(self._h, C.byref(c)), "b200kv_pool_stats")
+        return {n: getattr(c, n) for n, _ in PoolCounters._fields_}
+
+
+class ReusableContext:
+    """Prefix reuse around one set of layer caches: what PrefillV2Model::generate does with its ReusableContext and
+    session directory (src/prefill_v2/model.cpp:751-775, 868-887).  `begin(prompt)` decides how much of the prompt is
+    already covered -- the prefix resident in the caches, a pool snapshot, a session file, in that order -- and brings
+    it into the caches; the caller prefills the rest and calls `commit(prompt)`."""
+
+    LAYOUT_VERSION = 20260925
+
+    def __init__(self, model_id: str, quantization: str, storages, *, pool: Optional[SnapshotPool] = None, enable_prefix_reuse: bool = True,
+                 cache_prefix_after: bool = True, cache_prefix_len: int = 0, persistent_session_dir: str = ""):
+        self.model_id, self.quantization, self.storages, self.pool = model_id, quantization, list(storages or []), pool
+        self._dir = persistent_session_dir.encode()
+        self.options = ReuseOptions(int(enable_prefix_reuse), int(cache_prefix_after), cache_prefix_len, self._dir)
+        self.resident_tokens: list[int] = []
+
+    def has_valid_prefix(self) -> bool:
+        return len(self.resident_tokens) > 0
+
+    def begin(self, prompt, stream: Optional[torch.cuda.Stream] = None) -> dict:
+        stats = ReuseStats()
+        views = _views(self.storages) if self.storages else None
+        check(lib.b200kv_reuse_begin(C.byref(self.options), self.model_id.encode(), self.quantization.encode(), self.model_id.encode(),
+                                     self.quantization.encode(), self.LAYOUT_VERSION, _tokens(self.resident_tokens), len(self.resident_tokens),
+                                     self.pool._h if self.pool is not None else None, _tokens(prompt), len(prompt), views, len(self.storages),
+                                     _stream(stream) if self.storages else None, C.byref(stats)), "b200kv_reuse_begin")
+        out = {n: getattr(stats, n) for n, _ in ReuseStats._fields_}
+        if stats.reuse_hit and stats.source != 1:
+            self.resident_tokens = list(prompt[:stats.prefix_tokens_reused])
+        elif not stats.reuse_hit:
+            self.resident_tokens = []      # the caches are about to be overwritten from position 0
+        return out
+
+    def commit(self, prompt, stream: Optional[torch.cuda.Stream] = None) -> dict:
+        cached, wrote = C.c_uint32(), C.c_int()
+        views = _views(self.storages) if self.storages else None
+        check(lib.b200kv_reuse_commit(C.byref(self.options), self.model_id.encode(), self.quantization.encode(),
+                                      self.pool._h if self.pool is not None else None, _tokens(prompt), len(prompt), views, len(self.storages),
+                                      _stream(stream) if self.storages else None, C.byref(cached), C.byref(wrote)), "b200kv_reuse_commit")
+        if cached.value:
+            self.resident_tokens = list(prompt[:cached.value])
+        return {"cached_length": cached.value, "wrote_file": bool(wrote.value)}
 
 
 def token_sequence_hash(tokens) -> int:

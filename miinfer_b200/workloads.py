@@ -1,10 +1,16 @@
-"""Secondary bench workloads: suffix prefill (BASELINE config 3), batched
-serving (config 4) and sequence-sharded long-context decode (config 5).  bench.py dispatches here
-for --workload prefill|batched|seqshard; the default decode32k workload lives in bench.py."""
+"""Secondary bench workloads: suffix prefill (a 512-token chunk over an 8192-token q8_0 prefix), batched serving
+(64 sessions of mixed length plus 16 restored from a shared prefix snapshot) and sequence-sharded long-context
+decode (one 131072-token session over the ranks).  bench.py dispatches here for --workload prefill|batched|seqshard,
+and calls `extras` to attach them as sub-records to its default line.  Every workload function can be run with
+`dist=None, world=1` inside a multi-rank job (rank 0 does that to measure a workload's own 1-GPU time), and every
+one ends with a comparison of one layer's output against the CPU oracle evaluated on the cache planes as they lie on
+the device (`check`): test infrastructure used as the checker, outside every timed region."""
 from __future__ import annotations
 
 import json
+import sys
 from pathlib import Path
+from types import SimpleNamespace
 
 import numpy as np
 
@@ -17,6 +23,41 @@ def _peaks():
         d = json.loads(f.read_text())
         return float(d["hbm_gbs"]), float(d["bf16_tflops_sustained"]), "measured"
     return 6650.0, 1400.0, "fallback"
+
+
+def _oracle():
+    tests = str(ROOT / "tests")
+    if tests not in sys.path:
+        sys.path.insert(0, tests)
+    import kvoracle as ko
+
+    return ko
+
+
+def host_cache_from_planes(ko, planes: dict, capacity: int, kv_heads: int, head_dim: int, qblock: int = 32):
+    """An oracle-side cache over numpy copies of device planes (int8 K/V, fp16 scales as uint16)."""
+    host = ko.HostCache(capacity, kv_heads, head_dim, qblock, 3)
+    host.key_q8[...] = planes["key_q8"]
+    host.value_q8[...] = planes["value_q8"]
+    host.key_scales[...] = planes["key_scales"]
+    host.value_scales[...] = planes["value_scales"]
+    return host
+
+
+def planes_of(torch, storage, rows: int) -> dict:
+    """The first `rows` positions of a Q8/Q8 storage object's planes as numpy arrays."""
+    return {"key_q8": storage.key_cache_q8[:, :rows].cpu().numpy(), "value_q8": storage.value_cache_q8[:, :rows].cpu().numpy(),
+            "key_scales": storage.key_scales[:, :rows].contiguous().view(torch.int16).cpu().numpy().view(np.uint16),
+            "value_scales": storage.value_scales[:, :rows].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)}
+
+
+def error_record(got: np.ndarray, ref: np.ndarray, **extra) -> dict:
+    diff = got.astype(np.float64) - ref.astype(np.float64)
+    rec = {"max_abs": float(np.max(np.abs(diff))), "rel_l2": float(np.linalg.norm(diff) / max(np.linalg.norm(ref.astype(np.float64)), 1e-30)),
+           "against": "CPU oracle (two-pass fp32 softmax) on the device's cache planes", "tolerance_max_abs": 2.0e-3}
+    rec["ok"] = bool(np.isfinite(got).all() and rec["max_abs"] <= 2.0e-3)
+    rec.update(extra)
+    return rec
 
 
 def _fill(kv, torch, st, tokens, seed, chunk=8192):
@@ -84,17 +125,25 @@ def run_prefill(args, torch, dist, rank, world, local_rank):
 
     stream = torch.cuda.Stream()
     ms = _time(torch, dist, stream, step, args.warmup, args.steps)
+    check = None
+    if rank == 0 and not args.no_check:
+        ko = _oracle()
+        ko.set_threads(args.cpu_threads)
+        host = host_cache_from_planes(ko, planes_of(torch, caches[0], P + T), P + T, hkv, D)
+        tokens = 64     # the last 64 query tokens of the chunk see the longest ranges; the oracle costs ~14 ms per token
+        ref = host.suffix_ref(q[0, T - tokens:].float().cpu().numpy(), gate[0, T - tokens:].cpu().numpy(), P + T - tokens, D ** -0.5)
+        check = error_record(out[0, T - tokens:].cpu().numpy(), ref, layer=0, tokens=f"last {tokens} of {T}")
     flops = 4.0 * D * HQ * (T * P + T * (T + 1) / 2) * LAYERS   # QK^T and PV over the causal ranges, all heads
     _, tf_peak, kind = _peaks()
     achieved = flops / (ms * 1e-3) / 1e12
     return {"metric": "suffix_prefill_tflops_512_over_8192", "value": achieved, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int8 KV dequantised to fp16, fp32 accumulate", "data": "synthetic",
-            "config": {"workload": f"prefill: {T}-token chunk over {P}-token q8_0 prefix, {HQ} Q / {HKV} KV heads, d={D}, {LAYERS} layers "
-                                   f"(BASELINE configs[2]); kv heads split over {world} GPU(s); kernel {args.prefill_kernel}", "l2": "L2 flushed implicitly: 16 layer caches of 19 MB rotate"},
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak,
-                         "traffic": None, "peak_kind": f"{kind} (bf16_tflops_sustained)"},
-            "gpu_launches": args.steps * LAYERS * (2 if ws is None else 3)}
+            "config": {"workload": f"prefill: {T}-token chunk over {P}-token q8_0 prefix, {HQ} Q / {HKV} KV heads, d={D}, {LAYERS} layers; "
+                                   f"kv heads split over {world} GPU(s); kernel {args.prefill_kernel}", "l2": "L2 flushed implicitly: 16 layer caches of 19 MB rotate"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf_peak * world, "unit": "TFLOP/s", "frac": achieved / (tf_peak * world),
+                         "traffic": None, "peak_kind": f"{kind} (bf16_tflops_sustained) x {world} GPUs"},
+            "check": check, "gpu_launches": args.steps * LAYERS * (2 if ws is None else 4)}
 
 
 def run_seqshard(args, torch, dist, rank, world, local_rank):
@@ -105,7 +154,7 @@ def run_seqshard(args, torch, dist, rank, world, local_rank):
     from miinfer_b200 import kv
     from miinfer_b200.partition import open_exchange, shard_range
 
-    L, HQ, HKV, D, LAYERS = args.context if args.context != 32768 else 131072, 32, 8, 128, args.layers
+    L, HQ, HKV, D, LAYERS = args.seq_context, 32, 8, 128, args.layers
     b, e = shard_range(L, rank, world)
     n = e - b
     cap = (n + 64 + 63) // 64 * 64
@@ -121,10 +170,16 @@ def run_seqshard(args, torch, dist, rank, world, local_rank):
     ws = kv.decode_workspace(HQ, D)
     views = [c.view() for c in caches]
     in_kernel = dist is not None and getattr(args, "exchange", "kernel") == "kernel"
-    if in_kernel and LAYERS % 2:
-        raise SystemExit("seqshard --exchange kernel alternates two exchange phases per layer: use an even --layers")
+    nccl_c = dist is not None and getattr(args, "exchange", "kernel") == "nccl-c"
     exchange = open_exchange(dist, HQ, D) if in_kernel else None
+    dm = None
+    if nccl_c:   # the library's own NCCL communicator (b200kv_dist_*), its unique id handed round through torch.distributed
+        ids = [kv.DistMerge.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        dm = kv.DistMerge(ids[0], rank, world, HQ, D)
     kv.set_launch_overlap(0 if (args.no_overlap or (dist is not None and not in_kernel)) else 1)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kv.set_status_word(status)
 
     def step():
         for l in range(LAYERS):
@@ -132,14 +187,22 @@ def run_seqshard(args, torch, dist, rank, world, local_rank):
                 kv.launch_decode_attention_quant(views[l], q[l], query_heads=HQ, scale=D ** -0.5, cache_length=n, output=out[l], workspace=ws)
                 continue
             if in_kernel:
+                # the call number on this exchange: consecutive layers alternate the slot, and the step's second half
+                # continues the count so that a replayed graph never meets its own previous words in the same slot
                 kv.launch_decode_attention_sharded(views[l], q[l], exchange, query_heads=HQ, scale=D ** -0.5, range_begin=0,
-                                                   range_end=n, phase=l & 1, output=out[l], workspace=ws)
+                                                   range_end=n, phase=l, output=out[l], workspace=ws)
+                continue
+            if nccl_c:
+                dm.decode_partials(views[l], q[l], scale=D ** -0.5, range_begin=0, range_end=n, workspace=ws)
+                dm.merge(output=out[l])
                 continue
             kv.launch_decode_partials(views[l], q[l], query_heads=HQ, scale=D ** -0.5, range_begin=0, range_end=n,
                                       part_m=pm, part_l=pl, part_acc=pa, workspace=ws)
             dist.all_gather_into_tensor(gathered.view(-1), mine.view(-1))     # 16.6 KB per rank: the one exchange step
             kv.launch_merge_partials_packed(gathered, num_parts=world, query_heads=HQ, head_dim=D, output=out[l])
 
+    if in_kernel and LAYERS % 2:
+        raise SystemExit("seqshard --exchange kernel alternates two exchange slots per layer: use an even --layers")
     # the whole decode step (kernels and collectives) is captured once and replayed: the exchange is latency-bound
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
@@ -150,15 +213,52 @@ def run_seqshard(args, torch, dist, rank, world, local_rank):
             step()
     torch.cuda.synchronize()
     ms = _time(torch, dist, stream, graph.replay, args.warmup, args.steps)
+    kv.set_status_word(None)
+    kv.set_launch_overlap(0)
     checksum = float(out.double().abs().sum().item())   # identical on every rank when the exchange is right
     checksum_spread = 0.0
+    check = None
     if dist is not None:
         sums = [None] * world
         dist.all_gather_object(sums, checksum)
         checksum_spread = (max(sums) - min(sums)) / max(abs(max(sums)), 1e-30)
+    if not args.no_check:
+        # layer 0 against the oracle over the WHOLE context: every rank's shard of layer 0 is gathered to rank 0
+        p = planes_of(torch, caches[0], n)
+        flat = torch.cat([torch.from_numpy(p[k].reshape(-1).view(np.uint8)) for k in ("key_q8", "value_q8", "key_scales", "value_scales")]).cuda()
+        if dist is not None:
+            sizes = [None] * world
+            dist.all_gather_object(sizes, int(n))
+            if len(set(sizes)) != 1:
+                flat = None     # ragged shards: the gather below assumes equal ones
+            else:
+                allp = torch.empty(world * flat.numel(), dtype=torch.uint8, device="cuda")
+                dist.all_gather_into_tensor(allp, flat)
+                flat = allp
+        if rank == 0 and flat is not None:
+            ko = _oracle()
+            ko.set_threads(args.cpu_threads)
+            host = ko.HostCache(L, HKV, D, 32, 3)
+            per = flat.numel() // world
+            for r in range(world):
+                rb, re_ = shard_range(L, r, world)
+                m = re_ - rb
+                blob = flat[r * per:(r + 1) * per].cpu().numpy()
+                o = 0
+                for name, width, dt in (("key_q8", D, np.int8), ("value_q8", D, np.int8), ("key_scales", 8, np.uint16), ("value_scales", 8, np.uint16)):
+                    nbytes = HKV * m * width
+                    arr = blob[o:o + nbytes].view(dt).reshape(HKV, m, -1)
+                    getattr(host, name)[:, rb:re_] = arr
+                    o += nbytes
+            ref, _ = host.decode_ref(q[0].float().cpu().numpy(), D ** -0.5, L)
+            check = error_record(out[0].cpu().numpy(), ref, layer=0, context=L,
+                                 exchange=("in-kernel peer stores" if in_kernel else "NCCL all-gather") if dist is not None else "none (1 GPU)")
     if exchange is not None:
         dist.barrier()
         exchange.destroy()
+    if dm is not None:
+        dist.barrier()
+        dm.destroy()
     bw_peak, _, kind = _peaks()
     bytes_total = LAYERS * L * HKV * 136 * 2
     achieved = bytes_total / (ms * 1e-3) / 1e9
@@ -167,17 +267,19 @@ def run_seqshard(args, torch, dist, rank, world, local_rank):
             "dtype": "int8 KV / fp32 accumulate", "data": "synthetic",
             "config": {"workload": f"seqshard: one {L}-token session, {LAYERS} layers, {HQ} Q / {HKV} KV heads, d={D}, q8_0; positions sharded over "
                                    f"{world} GPU(s); per layer exchange of {HQ}x({D}+2) fp32 per rank "
-                                   f"({'peer stores + merge inside the decode kernel' if in_kernel else 'NCCL all-gather + merge kernel'}; BASELINE configs[4])",
+                                   f"({'peer stores + merge inside the decode kernel' if in_kernel else ('NCCL all-gather + merge kernel through the C entry points' if nccl_c else 'NCCL all-gather + merge kernel')})",
                        "l2": "inputs larger than L2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": bw_peak * world, "unit": "GB/s", "frac": achieved / (bw_peak * world),
                          "traffic": None, "peak_kind": f"{kind} x {world} GPUs"},
             "merge_bytes_per_layer_per_rank": HQ * (D + 2) * 4, "output_checksum": checksum, "output_checksum_spread_over_ranks": checksum_spread,
+            "status_word": int(status.item()), "check": check,
             "gpu_launches": args.steps * LAYERS * (1 if (dist is None or in_kernel) else 3)}
 
 
 def run_batched(args, torch, dist, rank, world, local_rank):
     """64 sessions with context lengths uniform in [512, 16384] (seeded), one decode step each per layer in ONE launch,
-    plus 16 sessions restored from a shared 4096-token prefix snapshot; sessions are bin-packed over the ranks."""
+    plus 16 sessions restored from a shared 4096-token prefix snapshot kept in a snapshot pool; sessions are bin-packed
+    over the ranks."""
     from miinfer_b200 import kv
     from miinfer_b200.partition import partition_sessions, pick_batched_splits
 
@@ -195,6 +297,10 @@ def run_batched(args, torch, dist, rank, world, local_rank):
         for j, (i, L) in enumerate(zip(mine, lengths)):
             if i < 64:
                 _fill(kv, torch, caches[l][j], L, 10000 * l + i)
+    # the shared prefix lives in an in-VRAM snapshot pool under its token ids; restored sessions look it up
+    prefix_tokens = [int(t) for t in np.random.default_rng(7).integers(0, 150000, 4096)]
+    pool = kv.SnapshotPool(max_entries=8, max_bytes=3 << 30)
+    pool.capture(prefix_tokens, proto)
     S = len(mine)
     g = torch.Generator(device="cuda"); g.manual_seed(rank)
     q = torch.randn(LAYERS, S, HQ, D, generator=g, device="cuda").half()
@@ -204,12 +310,13 @@ def run_batched(args, torch, dist, rank, world, local_rank):
     tables = [kv.view_table(S) for _ in range(LAYERS)]
     stream = torch.cuda.current_stream()
 
-    # restore of the snapshot sessions: device-to-device clone of the first 4096 positions, timed on its own
+    # restore of the snapshot sessions: longest-prefix lookup in the pool, then a device-to-device clone of the
+    # matched 4096 positions per layer; timed on its own
     def restore():
-        for l in range(LAYERS):
-            for j, i in enumerate(mine):
-                if i >= 64:
-                    caches[l][j].clone_prefix_from(proto[l], 4096)
+        for j, i in enumerate(mine):
+            if i >= 64:
+                matched = pool.restore(prefix_tokens + [1, 2, 3], [caches[l][j] for l in range(LAYERS)])
+                assert matched == 4096
     restore_ms = _time(torch, dist, stream, restore, 1, 3) if restored or dist is not None else 0.0
     # the host knows this step's lengths: pick the split count that fills whole waves of CTAs (0 = library default)
     splits = 0 if getattr(args, "default_splits", False) else pick_batched_splits(lengths, HKV)
@@ -233,6 +340,20 @@ def run_batched(args, torch, dist, rank, world, local_rank):
             step()
     torch.cuda.synchronize()
     ms = _time(torch, dist, gstream, graph.replay, args.warmup, args.steps)
+    kv.set_launch_overlap(0)
+    check = None
+    if rank == 0 and not args.no_check:
+        ko = _oracle()
+        ko.set_threads(args.cpu_threads)
+        worst = {"max_abs": 0.0, "rel_l2": 0.0}
+        picks = [0, S - 1] + ([mine.index(restored[0])] if restored else [])     # the longest, the shortest and a restored session
+        for j in picks:
+            host = host_cache_from_planes(ko, planes_of(torch, caches[0][j], lengths[j]), lengths[j], HKV, D)
+            ref, _ = host.decode_ref(q[0, j].float().cpu().numpy(), D ** -0.5, lengths[j])
+            rec = error_record(out[0, j].cpu().numpy(), ref)
+            worst = {k: max(worst[k], rec[k]) for k in worst}
+        check = {**worst, "ok": bool(worst["max_abs"] <= 2.0e-3), "layer": 0, "sessions_checked": len(picks),
+                 "against": "CPU oracle (two-pass fp32 softmax) on the device's cache planes", "tolerance_max_abs": 2.0e-3}
     bw_peak, _, kind = _peaks()
     bytes_total = LAYERS * sum(lengths_all) * HKV * 136 * 2
     achieved = bytes_total / (ms * 1e-3) / 1e9
@@ -240,10 +361,11 @@ def run_batched(args, torch, dist, rank, world, local_rank):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int8 KV / fp32 accumulate", "data": "synthetic",
             "config": {"workload": f"batched: 64 sessions U[512,16384] + 16 restored from a 4096-token snapshot, {LAYERS} layers, {HQ} Q / {HKV} KV, d={D}, "
-                                   f"q8_0; sessions bin-packed over {world} GPU(s) (BASELINE configs[3])", "l2": "inputs larger than L2"},
+                                   f"q8_0; sessions bin-packed over {world} GPU(s)", "l2": "inputs larger than L2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": bw_peak * world, "unit": "GB/s", "frac": achieved / (bw_peak * world),
                          "traffic": None, "peak_kind": f"{kind} x {world} GPUs"},
-            "splits_of_longest_session": splits, "restore_ms_16_sessions": restore_ms, "restore_bytes": LAYERS * 16 * 4096 * HKV * 136 * 2, "gpu_launches": args.steps * LAYERS}
+            "splits_of_longest_session": splits, "restore_ms_16_sessions": restore_ms, "restore_bytes": LAYERS * 16 * 4096 * HKV * 136 * 2,
+            "check": check, "gpu_launches": args.steps * LAYERS}
 
 
 def run(args, torch, dist, rank, world, local_rank):
@@ -252,3 +374,61 @@ def run(args, torch, dist, rank, world, local_rank):
         raise SystemExit(f"unknown workload {args.workload}")
     line = fn(args, torch, dist, rank, world, local_rank)
     return line if rank == 0 else None
+
+
+def _brief(line: dict, base: dict | None = None) -> dict:
+    keep = {k: line[k] for k in ("metric", "value", "unit", "ms_per_step", "scaling", "n_gpus", "steps", "warmup", "roofline", "check",
+                                 "gpu_launches") if k in line}
+    keep["workload"] = line["config"]["workload"]
+    for k in ("restore_ms_16_sessions", "splits_of_longest_session", "output_checksum_spread_over_ranks", "status_word"):
+        if k in line:
+            keep[k] = line[k]
+    if base is not None:
+        keep["single_gpu_ms_per_step"] = base["ms_per_step"]
+        keep["single_gpu_source"] = "measured in this run on rank 0 alone, same problem, same kernels"
+        keep["speedup_over_single_gpu"] = base["ms_per_step"] / line["ms_per_step"]
+    return keep
+
+
+def extras(args, torch, dist, rank, world, local_rank) -> dict:
+    """Sub-records for bench.py's default line: `prefill` always; with N > 1 GPUs also `seqshard` and `batched`, each
+    next to its own 1-GPU time measured by rank 0 alone on the full problem while the other ranks wait on the host."""
+    sub = SimpleNamespace(**vars(args))
+    sub.steps, sub.warmup = max(3, min(args.steps, 20)), 3
+    out = {}
+
+    def release():
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+
+    def alone(fn):
+        """rank 0 runs `fn` as a 1-GPU job; the others block on the host (a store key, not a GPU-side barrier)."""
+        res = None
+        if rank == 0:
+            res = fn(sub, torch, None, 0, 1, local_rank)
+            release()
+        if dist is not None:
+            store = dist.distributed_c10d._get_default_store()
+            key = f"alone_{fn.__name__}"
+            if rank == 0:
+                store.set(key, "done")
+            else:
+                store.wait([key])
+            dist.barrier()
+        return res
+
+    if world in (1, 2, 4):
+        line = run_prefill(sub, torch, dist, rank, world, local_rank)
+        release()
+        base = alone(run_prefill) if world > 1 else None
+        if rank == 0:
+            out["prefill"] = _brief(line, base)
+    if world > 1:
+        for name, fn in (("seqshard", run_seqshard), ("batched", run_batched)):
+            line = fn(sub, torch, dist, rank, world, local_rank)
+            release()
+            base = alone(fn)
+            if rank == 0:
+                out[name] = _brief(line, base)
+    return out

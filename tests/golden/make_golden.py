@@ -1,7 +1,7 @@
 """Generates the committed golden fixtures.  Run in a container that holds the
-MIInfer source tree (default /root/reference); the tests only read the .npz files.
+MIInfer source tree (--ref PATH, or the MIINFER_REF environment variable); the tests only read the .npz files.
 
-  python tests/golden/make_golden.py [--ref /root/reference]
+  python tests/golden/make_golden.py --ref PATH_TO_MIINFER
 
 1. m4a4_four_position.npz -- the reference's own stored layer-0 traces for the
    KV path (tests/reference/qwen3/m4a4-four-position/, README there lists the
@@ -20,6 +20,7 @@ MIInfer source tree (default /root/reference); the tests only read the .npz file
 from __future__ import annotations
 
 import argparse
+import os
 import ctypes as C
 from pathlib import Path
 
@@ -99,7 +100,8 @@ def host_primitives() -> None:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("MIINFER_REF"), required=os.environ.get("MIINFER_REF") is None,
+                    help="root of the MIInfer source tree")
     args = ap.parse_args()
     four_position(Path(args.ref))
     deeper_layers(Path(args.ref))

@@ -260,7 +260,7 @@ def token_sequence_hash(tokens) -> int:
     return int(_o.kvo_token_sequence_hash(_p(a), a.size))
 
 
-# -- seeded synthetic inputs (BASELINE configs: fp16 N(0,1) activations) ----------
+# -- seeded synthetic inputs (fp16 N(0,1) activations, as the benchmark workloads use) ----------
 def normal_f16(rng: np.random.Generator, shape, std: float = 1.0) -> np.ndarray:
     """fp16 N(0, std) values as a float16 array (exactly representable inputs)."""
     return (rng.standard_normal(shape, dtype=np.float32) * std).astype(np.float16)

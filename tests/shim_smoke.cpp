@@ -58,7 +58,38 @@ int main() {
     }
     bool threw = false;
     try { cache.download_raw(out.data(), kCap + 1); } catch (const std::runtime_error&) { threw = true; }
-    std::printf("shim %s worst=%.3e checksum=%.6f bytes=%zu\n", (worst < 2e-3 && threw) ? "ok" : "MISMATCH", worst, checksum,
-                cache.raw_tokens_bytes(kPrefix));
-    return (worst < 2e-3 && threw) ? 0 : 2;
+    // the operators either side of the KV path, with the reference's names: query-side split / norm / RoPE from the device
+    // state (attention_layer.cpp:589), the Q8_1 form of the gated output for the projection that follows (:659-662), the
+    // step advance (model.cpp:1136-1197), and the dequantising download (kv_cache.cpp:132-170)
+    std::vector<float> qfull(kQ * 2 * kD);
+    for (auto& x : qfull) x = rnd();
+    float *dqfull = dalloc<float>(qfull.size()), *dqr = dalloc<float>(kQ * kD), *dgate1 = dalloc<float>(kQ * kD), *dgated = dalloc<float>(kQ * kD);
+    Q8_1Block* dq8 = dalloc<Q8_1Block>(kQ * kD / 32);
+    std::uint32_t* dtok = dalloc<std::uint32_t>(4);
+    cudaMemcpy(dqfull, qfull.data(), qfull.size() * 4, cudaMemcpyHostToDevice);
+    launch_qwen35_fused_q_split_norm_rope_dynamic(dqfull, dw, dqr, dgate1, kQ, kD, dst, 1.0e6f, 1.0e-6f);
+    launch_qwen35_tiled_online_attention_quant_dynamic(dqr, v.key_cache, v.value_cache, v.key_cache_q8, v.key_scales, v.value_cache_q8,
+        v.value_scales, dst, kCap, nullptr, dgate1, dgated, kQ, kKv, kD, 1.0f / 16.0f, v.is_k_q8(), v.is_v_q8(), nullptr, dq8);
+    launch_qwen35_decode_state_advance(dst, dtok, 4);
+    if (cudaDeviceSynchronize() != cudaSuccess) { std::printf("shim FAILED: %s\n", cudaGetErrorString(cudaGetLastError())); return 1; }
+    std::vector<float> gated(kQ * kD), key_rows;
+    std::vector<Q8_1Block> q8(kQ * kD / 32);
+    DeviceDecodeState after{};
+    cudaMemcpy(gated.data(), dgated, gated.size() * 4, cudaMemcpyDeviceToHost);
+    cudaMemcpy(q8.data(), dq8, q8.size() * sizeof(Q8_1Block), cudaMemcpyDeviceToHost);
+    cudaMemcpy(&after, dst, sizeof after, cudaMemcpyDeviceToHost);
+    cache.download_key(key_rows, kPrefix);
+    // every Q8_1 block reproduces its 32 gated outputs to within half a quantisation step (plus what the fp16 rounding of
+    // the stored scale adds: at most 127 * 2^-11 of a step)
+    double q8_worst = 0.0;
+    for (std::size_t b = 0; b < q8.size(); ++b) {
+        const float d = __half2float(*reinterpret_cast<const __half*>(&q8[b].d));
+        for (int i = 0; i < 32; ++i) q8_worst = std::fmax(q8_worst, std::fabs(static_cast<double>(q8[b].qs[i]) * d - gated[b * 32 + i]) - 0.57 * d);
+    }
+    const bool extras_ok = q8_worst <= 1e-6 && after.position == kPrefix + kChunk && after.generated == 1 &&
+                           key_rows.size() == static_cast<std::size_t>(kKv) * kPrefix * kD && std::isfinite(key_rows[5]);
+    const bool ok = worst < 2e-3 && threw && extras_ok;
+    std::printf("shim %s worst=%.3e checksum=%.6f bytes=%zu q8=%.2e pos=%u\n", ok ? "ok" : "MISMATCH", worst, checksum,
+                cache.raw_tokens_bytes(kPrefix), q8_worst, after.position);
+    return ok ? 0 : 2;
 }

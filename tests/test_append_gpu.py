@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 # (head_dim, kv_heads, qblock, mode, rope_mode, k_norm, dtype)
 CASES = [
-    (128, 8, 32, 3, 1, False, np.float16),    # BASELINE configs 1/2/4/5: q8_0 blocks, NeoX RoPE, fp16 in
+    (128, 8, 32, 3, 1, False, np.float16),    # the Qwen3-8B-shaped workloads: q8_0 blocks, NeoX RoPE, fp16 in
     (256, 4, 32, 3, 2, True, np.float16),     # config 3: sectioned RoPE + K RMSNorm
     (256, 4, 256, 3, 2, True, np.float32),    # the reference's own format: one scale per row, fp32 in
     (256, 4, 256, 1, 2, True, np.float32),    # Q8 K + fp16 V

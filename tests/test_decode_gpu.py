@@ -1,5 +1,5 @@
 """GPU parity: split-K GQA decode attention against the oracle's fp32-accumulated
-two-pass reference, max-abs <= 2e-3 (the tolerance BASELINE.json states),
+two-pass reference, max-abs <= 2e-3 (the tolerance the path's specification states),
 through the C ABI."""
 import numpy as np
 import pytest
@@ -34,7 +34,7 @@ def gpu_decode(st, q, Hq, scale, length, *, gate=None, num_splits=0, decode_stat
 
 # (d, H, Hq, qblock, mode, L)
 SHAPES = [
-    (128, 8, 32, 32, 3, 4097),     # BASELINE config 1
+    (128, 8, 32, 32, 3, 4097),     # single-layer decode step over a 4096-token context
     (128, 8, 32, 32, 3, 1),
     (128, 8, 32, 32, 3, 31),
     (128, 8, 32, 32, 3, 1025),

@@ -23,7 +23,7 @@ def filled(rng, L, H, d, qb, mode, cap=None, std=1.0):
 SUFFIX = [
     (64, 16, 256, 4, 24, 256, 3),     # the reference's own test ladder, tests/qwen3_quant_kv_attention_test.cpp:82-87
     (512, 64, 256, 4, 24, 256, 3),
-    (512, 64, 256, 4, 24, 32, 3),     # same with q8_0 blocks (BASELINE config 3 format)
+    (512, 64, 256, 4, 24, 32, 3),     # same with q8_0 blocks (the suffix-prefill workload's format)
     (100, 33, 256, 4, 24, 256, 1),
     (100, 33, 256, 4, 24, 256, 2),
     (0, 40, 256, 4, 24, 32, 3),       # cold prefill: no prefix at all

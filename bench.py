@@ -206,27 +206,23 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
     state = kv.make_decode_state(ctx - 1, device=dev)   # position of the token being appended; length = position + 1
     scale = D ** -0.5
 
-    def nxt(l):
-        """The cache attended next: the following layer's (the first layer's of the next step after the last)."""
-        return None if args.no_next_hint else views[(l + 1) % LAYERS]
-
     def layer_pass():
         for l in range(LAYERS):
             if args.two_launches:   # the reference's call pair: store kernel, then decode attention
                 kv.launch_kv_store_quant(views[l], k_new[l], v_new[l], None, 1, 0, rope_mode=kv.RopeMode.NEOX_FULL,
                                          theta=THETA, decode_state=state)
                 kv.launch_decode_attention_quant(views[l], q[l], query_heads=HQ, scale=scale, decode_state=state,
-                                                 output=out[l], workspace=ws, next_view=nxt(l))
+                                                 output=out[l], workspace=ws)
             else:                   # the same work as one launch (append fused into the streaming kernel)
                 kv.launch_decode_step(views[l], k_new[l], v_new[l], q[l], query_heads=HQ, scale=scale, decode_state=state,
-                                      rope_mode=kv.RopeMode.NEOX_FULL, theta=THETA, output=out[l], workspace=ws, next_view=nxt(l))
+                                      rope_mode=kv.RopeMode.NEOX_FULL, theta=THETA, output=out[l], workspace=ws)
 
     attn_state = kv.make_decode_state(ctx - 2, device=dev)   # attention alone scans the rows that are there: position + 1 of them
 
     def attention_only_pass():
         for l in range(LAYERS):
             kv.launch_decode_attention_quant(views[l], q[l], query_heads=HQ, scale=scale, decode_state=attn_state,
-                                             output=out[l], workspace=ws, next_view=nxt(l))
+                                             output=out[l], workspace=ws)
 
     # consecutive layers' kernels may overlap their ramp-up and tail (programmatic dependent launch);
     # one trailing cache row -- the token appended by the preceding kernel -- is guarded
@@ -389,7 +385,6 @@ def main() -> None:
     ap.add_argument("--workload", default="decode32k")
     ap.add_argument("--context", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-next-hint", action="store_true", help="do not tell a layer's launch which cache is attended next (A/B of the L2 prefetch hint)")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of one layer's output with the CPU oracle")
     ap.add_argument("--no-sustained", action="store_true", help="skip the two-second replay window")
     ap.add_argument("--no-extras", action="store_true", help="skip the sub-records (prefill; with N > 1 also seqshard and batched)")

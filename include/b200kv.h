@@ -253,16 +253,10 @@ B200KV_API size_t b200kv_decode_workspace_bytes(uint32_t query_heads, uint32_t h
  * gated_output_q8 (may be NULL): the gated output re-quantised to Q8_1 blocks of 32 for the projection that
  * follows, [query_heads * head_dim / 32] blocks, as the reference's stage 2 does (.hip:2354-2383: d = amax/127,
  * q = roundf(x/d) clamped to +-127, s = d * sum(q), d and s stored as fp16).  Unlike the reference it is also
- * produced when gate is NULL (from the ungated output).
- * next_view (may be NULL; no counterpart in the reference): a hint -- the cache the caller will attend next on this
- * stream, normally the next layer's.  While the tcgen05 kernel streams its own tiles it pulls that cache's tiles towards
- * L2 (those the next launch will not already have fetched itself when it is released), which keeps HBM busy through
- * the phases in which a launch cannot stream: the merge at its end and the set-up of the next one.  Used only for
- * single-session launches on caches of the same shape and only while the prefetched part stays well inside L2
- * (contexts up to about 40K positions at 8 kv heads); it never changes a result. */
+ * produced when gate is NULL (from the ungated output). */
 B200KV_API int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
                        float* output, float* gated_output, b200kv_q8_1_block* gated_output_q8, uint32_t query_heads, float scale,
-                       uint32_t cache_length, const b200kv_decode_state* decode_state, const b200kv_view* next_view,
+                       uint32_t cache_length, const b200kv_decode_state* decode_state,
                        void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream);
 
 /* One decode step of a layer in ONE launch: append the new token's K/V row at `position` (or at
@@ -276,7 +270,7 @@ B200KV_API int b200kv_decode_step(const b200kv_view* view, const void* key, cons
                        const float* k_norm_weight, int rope_mode, float theta, float epsilon,
                        const void* q, int q_dtype, const float* gate, float* output, float* gated_output,
                        b200kv_q8_1_block* gated_output_q8, uint32_t query_heads, float scale, uint32_t position, const b200kv_decode_state* decode_state,
-                       const b200kv_view* next_view, void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream);
+                       void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream);
 
 /* Decode attention without a caller-supplied workspace and without any allocation (no counterpart in the
  * reference).  For hosts that cannot allocate device memory once they are running -- a serving process

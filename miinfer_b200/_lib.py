@@ -66,8 +66,8 @@ SIGNATURES = {
     "b200kv_q_split_norm_rope": (i32, [vp, i32, vp, vp, i32, vp, u32, u32, u32, u32, i32, fl, fl, vp, vp, vp]),
     "b200kv_decode_state_advance": (i32, [vp, vp, u32, vp]),
     "b200kv_decode_workspace_bytes": (sz, [u32, u32, u32]),
-    "b200kv_decode_attn": (i32, [VP, vp, i32, vp, vp, vp, vp, u32, fl, u32, vp, VP, vp, sz, u32, vp]),
-    "b200kv_decode_step": (i32, [VP, vp, vp, i32, vp, i32, fl, fl, vp, i32, vp, vp, vp, vp, u32, fl, u32, vp, VP, vp, sz, u32, vp]),
+    "b200kv_decode_attn": (i32, [VP, vp, i32, vp, vp, vp, vp, u32, fl, u32, vp, vp, sz, u32, vp]),
+    "b200kv_decode_step": (i32, [VP, vp, vp, i32, vp, i32, fl, fl, vp, i32, vp, vp, vp, vp, u32, fl, u32, vp, vp, sz, u32, vp]),
     "b200kv_decode_static_scratch_bytes": (sz, []),
     "b200kv_decode_attn_static": (i32, [VP, vp, i32, vp, vp, vp, u32, fl, u32, vp, u32, vp]),
     "b200kv_view_table_bytes": (sz, [u32]),

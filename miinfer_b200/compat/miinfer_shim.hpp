@@ -17,6 +17,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime_api.h>
 
+#include <cmath>
 #include <cstddef>
 #include <cstdint>
 #include <stdexcept>
@@ -86,7 +87,7 @@ inline void launch_qwen35_tiled_online_attention_quant_dynamic(
                                                  value_scales, cache_capacity, kv_heads, head_dim, kv_qblock(), is_k_q8, is_v_q8);
     const auto& ws = shim_detail::decode_workspace();
     shim_detail::check(b200kv_decode_attn(&v, q, B200KV_F32, gate, output, gated_output, gated_output_q8, query_heads, scale, 0,
-                                          decode_state, nullptr, ws.ptr, ws.bytes, 0, stream),
+                                          decode_state, ws.ptr, ws.bytes, 0, stream),
                        "launch_qwen35_tiled_online_attention_quant_dynamic");
 }
 
@@ -217,6 +218,85 @@ public:
 private:
     b200kv_cache* cache_ = nullptr;
     b200kv_view view_{};
+};
+
+
+// Steps 3-5 of PrefillV2AttentionLayer::forward and ::decode (src/prefill_v2/attention_layer.cpp:291-349, 587-656): the
+// query-side split / norm / RoPE, the KV store, and the attention over the cache -- the part of the layer executor that
+// is the KV path.  The projections before (steps 1-2) and after (step 6 on) stay with the caller.  Buffers are the
+// caller's, named as in PrefillV2Workspace (src/prefill_v2/workspace.hpp:15-60).
+struct AttentionKvPathBuffers {
+    const float* attn_qfull = nullptr;       // [token][q_heads][q | gate] from the Q projection
+    const float* attn_k = nullptr;           // [token][kv_heads * head_dim]
+    const float* attn_v = nullptr;
+    float* attn_q_rope = nullptr;            // [token][q_heads][head_dim]
+    float* gate = nullptr;
+    float* attn_gated_output = nullptr;
+    Q8_1Block* attn_gated_output_q8 = nullptr;   // decode only, optional: the input format of the output projection
+    float* splitk_attn_workspace = nullptr;  // optional scratch of the suffix kernel (b200kv_prefill_scratch_bytes)
+    std::size_t splitk_attn_workspace_bytes = 0;
+};
+
+class AttentionLayerKvPath {
+public:
+    AttentionLayerKvPath(const float* d_q_norm, const float* d_k_norm, std::uint32_t q_heads = 24, std::uint32_t kv_heads = 4,
+                         std::uint32_t head_dim = 256, float rope_theta = 1.0e6f, float rms_epsilon = 1.0e-6f)
+        : q_norm_(d_q_norm), k_norm_(d_k_norm), q_heads_(q_heads), kv_heads_(kv_heads), head_dim_(head_dim), theta_(rope_theta), eps_(rms_epsilon) {}
+
+    // attention_layer.cpp:291-349.  The chunk is stored first and attended second; causality inside the chunk is the
+    // per-token length.  The reference picks between three attention kernels here (a query-tiled fp16 kernel, the
+    // split-K suffix kernel when token_count <= 512 behind a prefix or under a device-side state, a cold-prefill fp16
+    // kernel otherwise); this library has one entry point for all of those cases and picks its kernel by the workspace.
+    void forward(const AttentionKvCacheView& kv_cache, const AttentionKvPathBuffers& ws, std::uint32_t token_count, std::uint32_t base_position,
+                 cudaStream_t stream = nullptr, const DevicePrefillState* prefill_state = nullptr) const {
+        launch_qwen35_decoupled_q_split_norm_rope_batch(ws.attn_qfull, q_norm_, ws.attn_q_rope, ws.gate, token_count, base_position, q_heads_,
+                                                        head_dim_, theta_, eps_, stream, prefill_state);
+        store(kv_cache, ws, token_count, base_position, stream, prefill_state, nullptr);
+        const b200kv_view v = raw(kv_cache);
+        shim_detail::check(b200kv_prefill_attn(&v, ws.attn_q_rope, B200KV_F32, ws.gate, ws.attn_gated_output, token_count, base_position, q_heads_,
+                                               scale(), prefill_state, ws.splitk_attn_workspace, ws.splitk_attn_workspace_bytes, stream),
+                           "AttentionLayerKvPath::forward");
+    }
+
+    // attention_layer.cpp:587-656.  With a device-side state (graph replay) the query side, the store and the attention
+    // all read the position on the device; the attention covers positions [0, position], i.e. position + 1 entries
+    // (the reference's host-position branch passes position + 1 as the BASE of a one-token suffix call and so attends
+    // one slot too many, :646; that is not reproduced).
+    void decode(const AttentionKvCacheView& kv_cache, const AttentionKvPathBuffers& ws, std::uint32_t position, cudaStream_t stream = nullptr,
+                const DeviceDecodeState* decode_state = nullptr) const {
+        if (decode_state != nullptr)
+            launch_qwen35_fused_q_split_norm_rope_dynamic(ws.attn_qfull, q_norm_, ws.attn_q_rope, ws.gate, q_heads_, head_dim_, decode_state, theta_,
+                                                          eps_, stream);
+        else
+            launch_qwen35_decoupled_q_split_norm_rope_batch(ws.attn_qfull, q_norm_, ws.attn_q_rope, ws.gate, 1, position, q_heads_, head_dim_, theta_,
+                                                            eps_, stream);
+        const b200kv_view v = raw(kv_cache);
+        const auto& dws = shim_detail::decode_workspace();
+        // store + attention as ONE launch where the cache takes the streaming kernel, as two otherwise (b200kv_decode_step decides)
+        shim_detail::check(b200kv_decode_step(&v, ws.attn_k, ws.attn_v, B200KV_F32, k_norm_, B200KV_ROPE_SECTIONED64, theta_, eps_, ws.attn_q_rope,
+                                              B200KV_F32, ws.gate, nullptr, ws.attn_gated_output, ws.attn_gated_output_q8, q_heads_, scale(), position,
+                                              decode_state, dws.ptr, dws.bytes, 0, stream),
+                           "AttentionLayerKvPath::decode");
+    }
+
+private:
+    void store(const AttentionKvCacheView& c, const AttentionKvPathBuffers& ws, std::uint32_t token_count, std::uint32_t base_position,
+               cudaStream_t stream, const DevicePrefillState* ps, const DeviceDecodeState* ds) const {
+        const b200kv_view v = raw(c);   // launch_qwen35_decoupled_k_norm_rope_kv_store_batch_quant with the view's own scale-block width
+        shim_detail::check(b200kv_append(&v, ws.attn_k, ws.attn_v, B200KV_F32, k_norm_, B200KV_ROPE_SECTIONED64, theta_, eps_, token_count, base_position,
+                                         ps, ds, stream),
+                           "AttentionLayerKvPath::store");
+    }
+    b200kv_view raw(const AttentionKvCacheView& c) const {
+        return shim_detail::make_view(c.key_cache, c.value_cache, c.key_cache_q8, c.key_scales, c.value_cache_q8, c.value_scales,
+                                      static_cast<std::uint32_t>(c.capacity), kv_heads_, head_dim_, static_cast<std::uint32_t>(c.qblock), c.is_k_q8(),
+                                      c.is_v_q8());
+    }
+    float scale() const { return 1.0f / std::sqrt(static_cast<float>(head_dim_)); }
+    const float* q_norm_;
+    const float* k_norm_;
+    std::uint32_t q_heads_, kv_heads_, head_dim_;
+    float theta_, eps_;
 };
 
 }  // namespace prefill_v2

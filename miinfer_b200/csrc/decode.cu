@@ -336,7 +336,7 @@ size_t b200kv_decode_workspace_bytes(uint32_t query_heads, uint32_t head_dim, ui
 
 int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
                        float* output, float* gated_output, b200kv_q8_1_block* gated_output_q8, uint32_t query_heads, float scale,
-                       uint32_t cache_length, const b200kv_decode_state* decode_state, const b200kv_view* next_view,
+                       uint32_t cache_length, const b200kv_decode_state* decode_state,
                        void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream) {
     int rc = validate_view(view);
     if (rc != B200KV_OK) return rc;
@@ -357,7 +357,6 @@ int b200kv_decode_attn(const b200kv_view* view, const void* q, int q_dtype, cons
     p.q_is_f16 = (q_dtype == B200KV_F16);
     p.query_heads = query_heads;
     p.scale = scale;
-    p.next_view = (next_view != nullptr && validate_view(next_view) == B200KV_OK) ? next_view : nullptr;   // a hint: a bad one is ignored
     // with a device-side length the launch is sized for the whole cache
     const uint32_t max_length = decode_state ? static_cast<uint32_t>(view->capacity) : cache_length;
     MergeParams mp{};
@@ -374,8 +373,7 @@ int b200kv_decode_step(const b200kv_view* view, const void* key, const void* val
                        const float* k_norm_weight, int rope_mode, float theta, float epsilon,
                        const void* q, int q_dtype, const float* gate, float* output, float* gated_output,
                        b200kv_q8_1_block* gated_output_q8, uint32_t query_heads, float scale, uint32_t position,
-                       const b200kv_decode_state* decode_state, const b200kv_view* next_view, void* workspace, size_t workspace_bytes,
-                       uint32_t num_splits, void* stream) {
+                       const b200kv_decode_state* decode_state, void* workspace, size_t workspace_bytes, uint32_t num_splits, void* stream) {
     int rc = validate_view(view);
     if (rc != B200KV_OK) return rc;
     if (key == nullptr || value == nullptr || q == nullptr || (output == nullptr && gated_output == nullptr && gated_output_q8 == nullptr))
@@ -391,7 +389,7 @@ int b200kv_decode_step(const b200kv_view* view, const void* key, const void* val
         rc = b200kv_append(view, key, value, kv_dtype, k_norm_weight, rope_mode, theta, epsilon, 1, position, nullptr, decode_state, stream);
         if (rc != B200KV_OK) return rc;
         return b200kv_decode_attn(view, q, q_dtype, gate, output, gated_output, gated_output_q8, query_heads, scale, position + 1,
-                                  decode_state, next_view, workspace, workspace_bytes, num_splits, stream);
+                                  decode_state, workspace, workspace_bytes, num_splits, stream);
     }
     if ((rc = ensure_device()) != B200KV_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -404,7 +402,6 @@ int b200kv_decode_step(const b200kv_view* view, const void* key, const void* val
     p.q_is_f16 = (q_dtype == B200KV_F16);
     p.query_heads = query_heads;
     p.scale = scale;
-    p.next_view = (next_view != nullptr && validate_view(next_view) == B200KV_OK) ? next_view : nullptr;
     p.new_key = key;
     p.new_value = value;
     p.new_is_f16 = (kv_dtype == B200KV_F16);

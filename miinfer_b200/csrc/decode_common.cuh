@@ -98,13 +98,6 @@ struct DecodeParams {
     float sectioned_step;
     float inv_freq[64];                      // NeoX frequencies for d = 128
     uint32_t overlap_tail;                   // launch overlap: the last n positions of the range are read only after pdl_wait
-    // Hint: the cache the caller attends next (normally the next layer's), whose tiles the tcgen05 kernel pulls towards L2
-    // while it streams its own.  next_view is the host-side argument; the launch resolves it into the fields below.
-    const b200kv_view* next_view;
-    uint32_t next_rows;                      // rows of the next cache worth prefetching (0 = no hint)
-    uint64_t next_capacity;
-    const uint8_t* next_key_scales;
-    const uint8_t* next_value_scales;
     uint64_t* ws_tagged;
     uint32_t tag;                            // tag of this launch's words in ws_tagged (never 0; differs from the previous launch's)
     uint32_t* status;                        // device word that collects B200KV_STATUS_* bits of waits that ran out, or null

@@ -252,10 +252,6 @@ __device__ __forceinline__ void fused_merge(const DecodeParams& p, uint32_t sess
     const uint32_t S = num_splits;     // <= kMaxSplitsPerSession == 128; the partial arrays keep the launch-wide stride
     const uint32_t rank = split;
     if (rank >= static_cast<uint32_t>(G)) return;
-    uint64_t* tl = (p.timeline != nullptr && session == 0 && threadIdx.x == 0) ? p.timeline + (static_cast<size_t>(kv_head) * gridDim.x + split) * 16 : nullptr;
-    auto now = [] { uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
-    if (tl) tl[8] = now();
-    uint32_t rounds = 0;
     const uint32_t tag = p.tag;
     float* fold_ml = fold_area;                                   // [3] x {max, sum} of split groups 1..3
     float2* fold = reinterpret_cast<float2*>(fold_ml + 8);        // [3][64] partial sums of split groups 1..3
@@ -283,7 +279,6 @@ __device__ __forceinline__ void fused_merge(const DecodeParams& p, uint32_t sess
             }
             uint32_t ml_pending = pending;
             for (uint32_t polls = 0; (pending | ml_pending) != 0 && !lost; ++polls) {
-                ++rounds;
                 if (polls >= kPollLimit) { lost = true; report(p, B200KV_STATUS_SPLIT_TIMEOUT); break; }
                 // all loads first, all checks afterwards: a check between two loads would serialise their trips
                 uint64_t wa[kBatch], wb[kBatch], wm[kBatch], wl[kBatch];
@@ -329,7 +324,6 @@ __device__ __forceinline__ void fused_merge(const DecodeParams& p, uint32_t sess
                 if (sp0 + grp + 4 * u < S) zero2(base + (sp0 + grp + 4 * u) * stride + 2 * pr);
         }
         if (lost) tot.x = tot.y = lg = __int_as_float(0x7fc00000);
-        if (tl) { tl[9] = now(); tl[12] = rounds; }
         // fold the 4 split groups through shared memory
         if (grp > 0) {
             fold[(grp - 1) * 64 + pr] = tot;
@@ -359,10 +353,8 @@ __device__ __forceinline__ void fused_merge(const DecodeParams& p, uint32_t sess
             }
             float gsum = lg;
             const float m_merged = M;
-            if (tl) tl[10] = now();
             if (p.fuse.xchg.world > 1) exchange_partials(p, head, pr, m_merged, tot, gsum, lost);
             write_merged(p.fuse, session, head, pr, tot, gsum, m_merged);
-            if (tl) tl[11] = now();
         }
         asm volatile("bar.sync 2, 256;" ::: "memory");   // the fold area is reused by the next head of this CTA
     }

@@ -13,20 +13,21 @@
 //  * S^T = K . Q^T: the K tile as it lies is the A operand (M = 128 positions, K-major), Q is quantised once per
 //    launch to 15 bits per head (q = 128 hi + lo, two int8 planes = 8 of the 16 rows of the B operand).  One MMA
 //    per q8_0 block of 32 dims (kind::i8 has K = 32), each into its own 16 TMEM columns, so the per-block key
-//    scales can be applied to exact int32 sums: 256 threads (two per position = TMEM lane, each with two of the four
-//    query heads) read their sums with tcgen05.ld and finish the scores in fp32.
+//    scales can be applied to exact int32 sums: 128 threads (one per position = TMEM lane) read their 32 sums with
+//    tcgen05.ld and finish the scores in fp32.
 //  * Online softmax in base 2: the tile maximum per head is found with redux.sync inside each warp and one exchange
-//    through shared memory between the four warps of a head group; the running maximum is uniform across the group.
+//    through shared memory between the four warps; the running maximum is uniform across the CTA.
 //  * O^T += V^T . P: the V tile as it lies is the A operand again, this time MN-major (M = 128 dims, K = positions),
-//    and P is written as unsigned 16-bit fixed point in two uint8 planes, pre-multiplied by the value scale of each
-//    block: P[position][(group, block, plane, head)] = 32 B-operand columns, MN-major too, so that a thread stores
-//    its 16 bytes of a position with one store and one MMA chain yields,
-//    for every dim, the sums of all four blocks' weightings, of which the thread of that dim keeps its own block's
-//    (the other three quarters are the price of per-block value scales: tensor throughput is not what bounds this
-//    kernel).  The fixed-point scale is per tile, head and block (tile maximum of the weights x tile maximum of the
-//    value scales / 65535), so the int32 sums are exact and every tile is folded into fp32 accumulators in
-//    registers (2 per thread) once its MMA chain has completed; P and the sums are double-buffered, so the softmax
-//    threads never wait for the chain of the tile they have just handed over.
+//    and P is written by the 128 threads as unsigned 16-bit fixed point in two uint8 planes, pre-multiplied by the
+//    value scale of each block: P[position][(block, plane, head)] = 32 B-operand columns, MN-major too (rows of 32
+//    bytes, 32-byte swizzle), so that a thread stores its position's 32 bytes with two 16-byte stores and one MMA
+//    chain yields, for every dim, the sums of all four blocks' weightings, of which the thread of that dim keeps its
+//    own block's (the other three quarters are the price of per-block value scales: tensor throughput is not what
+//    bounds this kernel).  The fixed-point scale is per tile, head and block (tile maximum of the weights x tile
+//    maximum of the value scales / 65535), so the int32 sums are exact and every tile is folded into fp32 accumulators
+//    in registers (4 per thread) once its MMA chain has completed; rescaling at a new maximum costs a dozen multiplies.
+//    P and the sums are double-buffered, so the softmax threads never wait for the chain of the tile they have just
+//    handed over.
 //  * The CTA's partial leaves as tagged words and the CTA of split h merges head h (decode_tail.cuh), as in decode_q8.cu.
 //  * Every wait is bounded.  A wait that runs out sets a status bit, poisons the partial with NaN and lets the CTA
 //    finish in the normal way (all later waits are skipped, barriers are still attended, TMEM is freed).
@@ -56,7 +57,8 @@ constexpr uint32_t kColS = 0;          // two S buffers of 4 blocks x 16 columns
 constexpr uint32_t kColO = 128;        // two O buffers of 32 columns: (block, plane, head)
 constexpr float kPMax = 65535.0f;
 constexpr int kEarlyTiles = 2;         // ring stages filled before the launch is released (3 measured no better: the early
-                                       // copies of a launch compete with the merge of the one before it)
+                                       // copies of a launch compete with the merge of the one before it; pulling later
+                                       // tiles -- its own, or through a hint the next launch's -- towards L2 measured slower)
 
 template <int NBLK>
 struct Smem {
@@ -100,13 +102,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-// Pull a tile (or a plain byte range) into L2 without a destination in shared memory.
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void bulk_prefetch(const void* src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -163,8 +158,7 @@ __device__ __forceinline__ float unordered(int i) { return __int_as_float(i ^ ((
 template <int NBLK, bool Q_F16>
 __global__ void __launch_bounds__(kThreads, 2)
 decode_tc5_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ CUtensorMap kmap_single,
-                  const __grid_constant__ CUtensorMap vmap_single, const __grid_constant__ CUtensorMap kmap_next,
-                  const __grid_constant__ CUtensorMap vmap_next) {
+                  const __grid_constant__ CUtensorMap vmap_single) {
     using L = Smem<NBLK>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1024-aligned, still a shared-space pointer
@@ -177,7 +171,7 @@ decode_tc5_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
     // optional per-CTA time stamps (b200kv_set_timeline_buffer): 8 words per CTA -- start, dependency wait over, set-up
     // barrier passed, first S tile seen, loop end, last sums folded, partial emitted, merge done
     const bool TL = p.timeline != nullptr && session == 0;
-    uint64_t* tl = TL ? p.timeline + (static_cast<size_t>(kv_head) * gridDim.x + split) * 16 : nullptr;
+    uint64_t* tl = TL ? p.timeline + (static_cast<size_t>(kv_head) * gridDim.x + split) * 8 : nullptr;
     if (TL && tid == 0) tl[0] = global_ns();
     const b200kv_view& view = session_view(p, session);
     uint32_t begin, end;
@@ -237,24 +231,6 @@ decode_tc5_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
         const uint32_t sdst = sbase + L::kOffS + stage * 2 * L::kSTile;
         bulk_load(sdst, ks_plane + static_cast<size_t>(pos0) * (NBLK * 2), sbytes, bar);
         bulk_load(sdst + L::kSTile, vs_plane + static_cast<size_t>(pos0) * (NBLK * 2), sbytes, bar);
-    };
-
-    // Tile i of the NEXT cache the caller will attend (p.next: normally the next layer's) towards L2.  A launch is
-    // released only when the one before it has completed, and then spends about 2.5 us on Q and on its first tile
-    // before a ring stage frees up; with the merge and hand-over at its end, HBM idles for a third of a launch's time
-    // at 32K positions.  Pulling the next launch's tiles -- those its rings will not already hold -- into L2 while this
-    // launch streams fills those gaps: the next launch then finds them in L2.  (Prefetching a launch's OWN later tiles
-    // at its start measured slower: the bulk requests delay the loads and stores of the previous launch's merge.)
-    const bool hint = p.next_rows > 0;
-    const int next_row_base = static_cast<int>(static_cast<uint64_t>(kv_head) * p.next_capacity);
-    auto prefetch_next = [&](int i) {
-        const uint32_t pos0 = (t0 + i) * kTileM;
-        if (pos0 >= p.next_rows) return;
-        const uint32_t sbytes = min(static_cast<uint32_t>(kTileM), static_cast<uint32_t>(p.next_capacity) - pos0) * (NBLK * 2);
-        tma_prefetch_2d(&kmap_next, 0, next_row_base + static_cast<int>(pos0));
-        tma_prefetch_2d(&vmap_next, 0, next_row_base + static_cast<int>(pos0));
-        bulk_prefetch(p.next_key_scales + (static_cast<size_t>(kv_head) * p.next_capacity + pos0) * (NBLK * 2), sbytes);
-        bulk_prefetch(p.next_value_scales + (static_cast<size_t>(kv_head) * p.next_capacity + pos0) * (NBLK * 2), sbytes);
     };
 
     // ---- set-up ---------------------------------------------------------------------------------------------
@@ -343,16 +319,12 @@ decode_tc5_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
     if (warp == kProducerWarp) {
         // =============================== TMA producer ===============================
         if (lane == 0) {
-            if (hint)
-                for (int i = kEarlyTiles; i < issued - 1; ++i) prefetch_next(i);
             for (int i = issued; i < ntiles; ++i) {
                 // stage i % kStages is free once the P.V of tile i - kStages has completed
                 if (i >= kStages && !mbar_wait(bar_empty(i % kStages), static_cast<uint32_t>((i / kStages - 1) & 1))) { failed = true; break; }
                 if (owner && i == ntiles - 1 && !mbar_wait(bar_row, 0)) { failed = true; break; }
                 issue(i);
-                if (hint && i - 1 >= kEarlyTiles) prefetch_next(i - 1);   // the next launch fills its first kEarlyTiles stages itself
             }
-            if (hint && ntiles - 1 >= kEarlyTiles) prefetch_next(ntiles - 1);
         }
     } else if (warp == kAppendWarp) {
         // =============================== fused append of the new token's row ===============================
@@ -609,13 +581,12 @@ decode_tc5_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
 // ---- host side -----------------------------------------------------------------------------------------
 
 template <int NBLK, bool Q_F16>
-int launch_one(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap, const CUtensorMap& kmap_next, const CUtensorMap& vmap_next,
-               dim3 grid, cudaStream_t stream) {
+int launch_one(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap, dim3 grid, cudaStream_t stream) {
     using L = Smem<NBLK>;
     static std::atomic<uint64_t> done{0};   // one per kernel instantiation: devices that have opted in
     const cudaError_t attr_err = opt_in_dynamic_smem(reinterpret_cast<const void*>(decode_tc5_kernel<NBLK, Q_F16>), L::kAlloc, done);
     if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err, "cudaFuncSetAttribute(decode_tc5)"); return B200KV_ERR_CUDA; }
-    B200KV_CUDA_TRY(launch_kernel(decode_tc5_kernel<NBLK, Q_F16>, grid, dim3(kThreads), L::kAlloc, stream, true, p, kmap, vmap, kmap_next, vmap_next));
+    B200KV_CUDA_TRY(launch_kernel(decode_tc5_kernel<NBLK, Q_F16>, grid, dim3(kThreads), L::kAlloc, stream, true, p, kmap, vmap));
     return B200KV_OK;
 }
 
@@ -638,28 +609,10 @@ int launch_decode_tc5(const DecodeParams& p_in, const b200kv_view& geometry, uin
         std::memset(&kmap, 0, sizeof kmap);   // per-session descriptors come from the device table
         std::memset(&vmap, 0, sizeof vmap);
     }
-    // The cache attended next (a hint): only where it has this cache's shape, for single-session launches, and where
-    // what would be prefetched stays well inside L2 next to this launch's own tiles.
-    CUtensorMap kmap_next, vmap_next;
-    std::memset(&kmap_next, 0, sizeof kmap_next);
-    std::memset(&vmap_next, 0, sizeof vmap_next);
-    p.next_rows = 0;
-    if (p_in.next_view != nullptr && p.views == nullptr && p.sessions == 1) {
-        const b200kv_view& nv = *p_in.next_view;
-        const uint64_t bytes = static_cast<uint64_t>(max_length) * nv.kv_heads * (2 * kD + 4 * (kD / nv.qblock));
-        if (q8_fast_path_ok(nv, p.query_heads) && nv.kv_heads == geometry.kv_heads && nv.qblock == geometry.qblock && bytes <= (48ull << 20) * 2 &&
-            encode_kv_maps(nv, kTileM, &kmap_next, &vmap_next) == B200KV_OK) {
-            p.next_rows = max_length < nv.capacity ? max_length : static_cast<uint32_t>(nv.capacity);
-            p.next_capacity = nv.capacity;
-            p.next_key_scales = static_cast<const uint8_t*>(nv.key_scales);
-            p.next_value_scales = static_cast<const uint8_t*>(nv.value_scales);
-        }
-    }
-    p.next_view = nullptr;
     const bool blocks = geometry.qblock == 32;
     dim3 grid(p.num_splits, geometry.kv_heads, p.sessions);
-    if (blocks) return p.q_is_f16 ? launch_one<4, true>(p, kmap, vmap, kmap_next, vmap_next, grid, stream) : launch_one<4, false>(p, kmap, vmap, kmap_next, vmap_next, grid, stream);
-    return p.q_is_f16 ? launch_one<1, true>(p, kmap, vmap, kmap_next, vmap_next, grid, stream) : launch_one<1, false>(p, kmap, vmap, kmap_next, vmap_next, grid, stream);
+    if (blocks) return p.q_is_f16 ? launch_one<4, true>(p, kmap, vmap, grid, stream) : launch_one<4, false>(p, kmap, vmap, grid, stream);
+    return p.q_is_f16 ? launch_one<1, true>(p, kmap, vmap, grid, stream) : launch_one<1, false>(p, kmap, vmap, grid, stream);
 }
 
 }  // namespace b200kv

@@ -43,7 +43,7 @@ uint64_t* current_timeline_buffer(uint32_t ctas) {
         return nullptr;
     }
     uint64_t* buf = g_timeline[device].load(std::memory_order_relaxed);
-    return (buf != nullptr && static_cast<uint64_t>(ctas) * 16 <= g_timeline_words[device].load(std::memory_order_relaxed)) ? buf : nullptr;
+    return (buf != nullptr && static_cast<uint64_t>(ctas) * 8 <= g_timeline_words[device].load(std::memory_order_relaxed)) ? buf : nullptr;
 }
 
 static std::atomic<int> g_streaming_kernel{0};

@@ -236,13 +236,12 @@ def launch_decode_attention_quant(view: View, q: torch.Tensor, *, query_heads: i
                                   cache_length: int = 0, decode_state: Optional[torch.Tensor] = None,
                                   output: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
                                   gated_output: Optional[torch.Tensor] = None, gated_output_q8: Optional[torch.Tensor] = None,
-                                  next_view: Optional[View] = None, workspace: torch.Tensor, num_splits: int = 0,
+                                  workspace: torch.Tensor, num_splits: int = 0,
                                   stream: Optional[torch.cuda.Stream] = None) -> None:
     """launch_qwen35_tiled_online_attention_quant_dynamic (qwen3_gpu_primitives.hpp:719-739).
-    gated_output_q8: uint8 tensor of query_heads * head_dim / 32 Q8_1 blocks (36 bytes each), see `q8_1_blocks`.
-    next_view: hint -- the cache attended next on this stream (the next layer's); its tiles are pulled towards L2."""
+    gated_output_q8: uint8 tensor of query_heads * head_dim / 32 Q8_1 blocks (36 bytes each), see `q8_1_blocks`."""
     check(lib.b200kv_decode_attn(C.byref(view), _ptr(q), _dtype(q), _ptr(gate), _ptr(output), _ptr(gated_output), _ptr(gated_output_q8),
-                                 query_heads, scale, cache_length, _ptr(decode_state), None if next_view is None else C.byref(next_view),
+                                 query_heads, scale, cache_length, _ptr(decode_state),
                                  _ptr(workspace),
                                  workspace.numel(), num_splits, _stream(stream)), "b200kv_decode_attn")
 
@@ -252,16 +251,16 @@ def launch_decode_step(view: View, key: torch.Tensor, value: torch.Tensor, q: to
                        rope_mode: RopeMode = RopeMode.NEOX_FULL, theta: float = 1.0e6, epsilon: float = 1.0e-6,
                        output: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
                        gated_output: Optional[torch.Tensor] = None, gated_output_q8: Optional[torch.Tensor] = None,
-                       next_view: Optional[View] = None, workspace: torch.Tensor, num_splits: int = 0,
+                       workspace: torch.Tensor, num_splits: int = 0,
                        stream: Optional[torch.cuda.Stream] = None) -> None:
     """Append one token and attend in one launch (b200kv_decode_step): the fused form of the store + decode-attention
-    call pair of src/prefill_v2/attention_layer.cpp:599-632.  next_view: see launch_decode_attention_quant."""
+    call pair of src/prefill_v2/attention_layer.cpp:599-632."""
     if key.dtype != value.dtype:
         raise ValueError("key and value must share a dtype")
     check(lib.b200kv_decode_step(C.byref(view), _ptr(key), _ptr(value), _dtype(key), _ptr(k_norm_weight), int(rope_mode), theta,
                                  epsilon, _ptr(q), _dtype(q), _ptr(gate), _ptr(output), _ptr(gated_output), _ptr(gated_output_q8),
                                  query_heads, scale,
-                                 position, _ptr(decode_state), None if next_view is None else C.byref(next_view), _ptr(workspace),
+                                 position, _ptr(decode_state), _ptr(workspace),
                                  workspace.numel(), num_splits, _stream(stream)),
           "b200kv_decode_step")
 

@@ -88,8 +88,31 @@ int main() {
     }
     const bool extras_ok = q8_worst <= 1e-6 && after.position == kPrefix + kChunk && after.generated == 1 &&
                            key_rows.size() == static_cast<std::size_t>(kKv) * kPrefix * kD && std::isfinite(key_rows[5]);
-    const bool ok = worst < 2e-3 && threw && extras_ok;
-    std::printf("shim %s worst=%.3e checksum=%.6f bytes=%zu q8=%.2e pos=%u\n", ok ? "ok" : "MISMATCH", worst, checksum,
-                cache.raw_tokens_bytes(kPrefix), q8_worst, after.position);
+    // the same chunk and the same decode step through the layer object (attention_layer.cpp:291-349, 587-656) on a second
+    // cache: its outputs must equal what the individual launchers gave above
+    AttentionLayerKvCacheStorage cache2(kCap, KvCacheQuantMode::kQ8Q8);
+    std::vector<float> chunk_qfull((kPrefix + kChunk) * kQ * 2 * kD, 0.0f);
+    float *dq2 = dalloc<float>(chunk_qfull.size()), *dqr2 = dalloc<float>((kPrefix + kChunk) * kQ * kD), *dg2 = dalloc<float>((kPrefix + kChunk) * kQ * kD);
+    float* dout2 = dalloc<float>((kPrefix + kChunk) * kQ * kD);
+    AttentionLayerKvPath layer(dw, dw);
+    AttentionKvPathBuffers bufs;
+    bufs.attn_qfull = dq2; bufs.attn_k = dk; bufs.attn_v = dv; bufs.attn_q_rope = dqr2; bufs.gate = dg2; bufs.attn_gated_output = dout2;
+    // prefix through forward() with zero queries (only the store matters), then one decode step with the query of above
+    cudaMemset(dq2, 0, chunk_qfull.size() * 4);
+    layer.forward(cache2.view(), bufs, kPrefix + kChunk - 1, 0);
+    DeviceDecodeState st2{}; st2.position = kPrefix + kChunk - 1;
+    cudaMemcpy(dst, &st2, sizeof st2, cudaMemcpyHostToDevice);
+    AttentionKvPathBuffers step = bufs;
+    step.attn_qfull = dqfull; step.attn_k = dk + static_cast<std::size_t>(kPrefix + kChunk - 1) * kKv * kD; step.attn_v = dv + static_cast<std::size_t>(kPrefix + kChunk - 1) * kKv * kD;
+    step.attn_q_rope = dqr; step.gate = dgate1; step.attn_gated_output = dout2;
+    layer.decode(cache2.view(), step, 0, nullptr, dst);
+    if (cudaDeviceSynchronize() != cudaSuccess) { std::printf("shim FAILED (layer): %s\n", cudaGetErrorString(cudaGetLastError())); return 1; }
+    std::vector<float> gated2(kQ * kD);
+    cudaMemcpy(gated2.data(), dout2, gated2.size() * 4, cudaMemcpyDeviceToHost);
+    double layer_worst = 0.0;
+    for (std::size_t i = 0; i < gated2.size(); ++i) layer_worst = std::fmax(layer_worst, std::fabs(static_cast<double>(gated2[i]) - gated[i]));
+    const bool ok = worst < 2e-3 && threw && extras_ok && layer_worst < 1e-5;
+    std::printf("shim %s worst=%.3e checksum=%.6f bytes=%zu q8=%.2e pos=%u layer=%.2e\n", ok ? "ok" : "MISMATCH", worst, checksum,
+                cache.raw_tokens_bytes(kPrefix), q8_worst, after.position, layer_worst);
     return ok ? 0 : 2;
 }

@@ -64,9 +64,9 @@ def test_argument_errors_are_statuses_not_aborts():
     v = View(0, 0, 16, 16, 16, 16, 8, 2, 128, 32, 3)
     assert lib.b200kv_append(C.byref(v), 16, 16, 0, None, 0, 1e6, 1e-6, 4, 6, None, None, None) == -6    # past capacity
     assert lib.b200kv_append(C.byref(v), 16, 16, 7, None, 0, 1e6, 1e-6, 1, 0, None, None, None) == -1    # dtype
-    assert lib.b200kv_decode_attn(C.byref(v), 16, 0, None, None, None, None, 8, 0.1, 4, None, None, None, 0, 0, None) == -1  # no output
-    assert lib.b200kv_decode_attn(C.byref(v), 16, 0, None, 16, None, None, 7, 0.1, 4, None, None, None, 0, 0, None) == -1   # 7 % 2
-    assert lib.b200kv_decode_attn(C.byref(v), 16, 0, None, 16, None, None, 8, 0.1, 9, None, None, None, 0, 0, None) == -6   # length > capacity
+    assert lib.b200kv_decode_attn(C.byref(v), 16, 0, None, None, None, None, 8, 0.1, 4, None, None, 0, 0, None) == -1  # no output
+    assert lib.b200kv_decode_attn(C.byref(v), 16, 0, None, 16, None, None, 7, 0.1, 4, None, None, 0, 0, None) == -1   # 7 % 2
+    assert lib.b200kv_decode_attn(C.byref(v), 16, 0, None, 16, None, None, 8, 0.1, 9, None, None, 0, 0, None) == -6   # length > capacity
     v = View(0, 0, 16, 16, 16, 24, 8, 2, 128, 32, 3)   # misaligned plane
     assert lib.b200kv_append(C.byref(v), 16, 16, 0, None, 0, 1e6, 1e-6, 1, 0, None, None, None) == -1
     assert lib.b200kv_snapshot_bytes(C.byref(View(0, 0, 16, 16, 16, 16, 8, 2, 128, 32, 3)), 5) == 2 * 5 * 2 * 136

@@ -11,7 +11,8 @@ caches resident in HBM.  With N GPUs every rank decodes its own session (weak
 scaling, no data-path collective).  Other workloads:
 `seqshard` (one 128K-token session sharded by sequence over the ranks; the per-rank
 partials are exchanged and merged inside the decode kernel, or by NCCL with --exchange nccl), `batched` (64 sessions of mixed
-length), `prefill` (512-token suffix over an 8K prefix, d=256).
+length), `prefill` (512-token suffix over an 8K prefix, d=256), `append` (the store kernel alone: 8192-token chunks at d=128,
+or with --append-shape chunk256 the 512-token d=256 chunk).
 
 The default run also measures, as sub-records of the same JSON line, the suffix-prefill
 workload (`prefill`) and -- with N > 1 GPUs -- the sharded workloads (`seqshard`, `batched`)
@@ -157,7 +158,7 @@ def run_reference_arm(args) -> None:
                 "the quantized path and its GPU code is gfx906-only HIP",
         "wall_s": time.perf_counter() - t_all,
     }
-    print(json.dumps(line))
+    emit_line(line)
 
 
 def workload_config(name: str, context: int, n_gpus: int) -> dict:
@@ -376,6 +377,25 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
     return line
 
 
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result() -> None:
+    """Everything libraries print to standard output (NCCL's version banner, for one) is sent to standard error, so
+    that standard output carries the one JSON line and nothing else."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit_line(line: dict) -> None:
+    text = (json.dumps(line) + "\n").encode()
+    sys.stdout.flush()
+    os.write(_RESULT_FD if _RESULT_FD is not None else 1, text)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -397,8 +417,11 @@ def main() -> None:
                     help="seqshard workload at N>1: cross-GPU merge inside the decode kernel (peer stores) or NCCL all-gather + merge kernel")
     ap.add_argument("--decode-kernel", default="tcgen05", choices=["tcgen05", "mma"],
                     help="which streaming decode kernel serves the int8 caches (A/B): tcgen05 (default) or warp-level mma")
+    ap.add_argument("--append-tokens", type=int, default=8192, help="append workload: rows per layer and launch")
+    ap.add_argument("--append-shape", default="fill128", choices=["fill128", "chunk256"], help="append workload: 8 kv heads d=128 or the 512-token d=256 chunk")
     ap.add_argument("--layers", type=int, default=36, help="layers per step (36 = the benchmark; fewer only for ncu captures)")
     args = ap.parse_args()
+    keep_stdout_for_the_result()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     global LAYERS
@@ -448,7 +471,7 @@ def main() -> None:
             cpu = cpu_decode_sample(args.context, 2, threads)
             cpu.pop("seconds", None)
             line["cpu_baseline"] = cpu
-        print(json.dumps(line))
+        emit_line(line)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

@@ -384,7 +384,9 @@ B200KV_API int b200kv_merge_partials_packed(const float* packed, uint32_t num_pa
  * in-kernel exchange, b200kv_decode_attn_sharded.  init takes either an existing ncclComm_t (nccl_comm != NULL; rank
  * and world are read from it) or a 128-byte NCCL unique id created by b200kv_dist_unique_id on one rank and passed
  * to the others by the host's own means.  NCCL is looked up at run time (B200KV_ERR_UNSUPPORTED if there is none).
- * These allocate and are collective: set-up calls, not for the per-token path -- except b200kv_dist_merge. */
+ * These allocate and are collective: set-up calls, not for the per-token path -- except b200kv_dist_merge.
+ * b200kv_dist_destroy of a communicator created here blocks until every CUDA graph that captured a
+ * b200kv_dist_merge has been destroyed (NCCL's rule): destroy those graphs first. */
 typedef struct b200kv_dist b200kv_dist;
 B200KV_API int b200kv_dist_unique_id(void* id128);
 B200KV_API int b200kv_dist_init(b200kv_dist** out, void* nccl_comm, const void* id128, uint32_t rank, uint32_t world,

@@ -280,9 +280,8 @@ prefill_mma_kernel(const __grid_constant__ PrefillParams p) {
 template <int D>
 int launch_prefill(const PrefillParams& p, cudaStream_t stream) {
     constexpr int kSmem = (kBM + 2 * kBN) * D * 2;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(prefill_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem); });
+    static std::atomic<uint64_t> done{0};   // one per kernel instantiation: devices that have opted in
+    const cudaError_t attr_err = opt_in_dynamic_smem(reinterpret_cast<const void*>(prefill_mma_kernel<D>), kSmem, done);
     if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err, "cudaFuncSetAttribute(prefill_mma)"); return B200KV_ERR_CUDA; }
     const uint32_t G = p.query_heads / p.view.kv_heads;
     const uint32_t row_tiles = (p.token_count * G + kBM - 1) / kBM;

@@ -554,9 +554,8 @@ bool encode_f16_plane(CUtensorMap* map, void* base, uint32_t d, uint64_t rows) {
 template <int D>
 int launch_tc5(const b200kv_view& view, Tc5Params& p, __half* k_scratch, __half* v_scratch, uint32_t rows, cudaStream_t stream) {
     using L = Layout<D>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(prefill_tc5_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc); });
+    static std::atomic<uint64_t> done{0};   // one per kernel instantiation: devices that have opted in
+    const cudaError_t attr_err = opt_in_dynamic_smem(reinterpret_cast<const void*>(prefill_tc5_kernel<D>), L::kAlloc, done);
     if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err, "cudaFuncSetAttribute(prefill_tc5)"); return B200KV_ERR_CUDA; }
     if (rows > 0) {
         DequantParams dp{};

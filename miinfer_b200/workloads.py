@@ -257,6 +257,9 @@ def run_seqshard(args, torch, dist, rank, world, local_rank):
         dist.barrier()
         exchange.destroy()
     if dm is not None:
+        # NCCL's communicator teardown waits for every CUDA graph that captured one of its collectives to be destroyed
+        graph.reset()
+        del graph
         dist.barrier()
         dm.destroy()
     bw_peak, _, kind = _peaks()
@@ -368,8 +371,57 @@ def run_batched(args, torch, dist, rank, world, local_rank):
             "check": check, "gpu_launches": args.steps * LAYERS}
 
 
+def run_append(args, torch, dist, rank, world, local_rank):
+    """The store kernel alone (K-norm, RoPE, q8_0 quantisation, cache write): `--append-tokens` fp16 rows per layer
+    into `--layers` caches.  Default 8192 tokens x 8 kv heads x d=128 with NeoX RoPE (a prefill chunk of the decode
+    benchmark's model); `--append-shape chunk256` is the 512-token chunk of the 24 Q / 4 KV d=256 model with the
+    sectioned RoPE.  Every layer has its own inputs and cache, so a step streams more than L2 holds."""
+    from miinfer_b200 import kv
+
+    if args.append_shape == "chunk256":
+        T, HKV, D, mode, LAYERS = 512, 4, 256, kv.RopeMode.SECTIONED64, max(args.layers, 36)
+    else:
+        T, HKV, D, mode, LAYERS = args.append_tokens, 8, 128, kv.RopeMode.NEOX_FULL, args.layers
+    caches = [kv.AttentionLayerKvCacheStorage(T, kv.KvCacheQuantMode.kQ8Q8, kv_heads=HKV, head_dim=D, qblock=32) for _ in range(LAYERS)]
+    g = torch.Generator(device="cuda"); g.manual_seed(5 + rank)
+    k_new = torch.randn(LAYERS, T, HKV * D, generator=g, device="cuda").half()
+    v_new = torch.randn(LAYERS, T, HKV * D, generator=g, device="cuda").half()
+    w = (1.0 + 0.1 * torch.randn(D, generator=g, device="cuda")).float()
+    views = [c.view() for c in caches]
+
+    def step():
+        for l in range(LAYERS):
+            kv.launch_kv_store_quant(views[l], k_new[l], v_new[l], w, T, 0, rope_mode=mode, theta=1.0e6)
+
+    stream = torch.cuda.Stream()
+    ms = _time(torch, dist, stream, step, args.warmup, args.steps)
+    check = None
+    if rank == 0 and not args.no_check:
+        ko = _oracle()
+        ko.set_threads(args.cpu_threads)
+        rows = min(T, 512)
+        host = ko.HostCache(rows, HKV, D, 32, 3)
+        host.append(k_new[0, :rows].float().cpu().numpy(), v_new[0, :rows].float().cpu().numpy(), w.cpu().numpy(), 0, rope_mode=int(mode), theta=1.0e6)
+        got = planes_of(torch, caches[0], rows)
+        same = all(np.array_equal(got[k], getattr(host, k)[:, :rows]) for k in ("key_q8", "value_q8", "key_scales", "value_scales"))
+        check = {"bit_exact": bool(same), "ok": bool(same), "rows": rows, "layer": 0, "against": "CPU oracle store (same quantiser, pinned trigonometry)"}
+    row_out = D + 2 * (D // 32)
+    bytes_step = LAYERS * T * HKV * 2 * (D * 2 + row_out)
+    bw_peak, _, kind = _peaks()
+    achieved = bytes_step / (ms * 1e-3) / 1e9
+    return {"metric": "kv_append_gbs", "value": achieved * world, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16 in, int8 + fp16 scales out",
+            "data": "synthetic",
+            "config": {"workload": f"append: {T} tokens x {HKV} kv heads x d={D} per layer, {LAYERS} layers, K-norm + {mode.name} RoPE + q8_0 store",
+                       "l2": f"inputs larger than L2: {bytes_step / 1e6:.0f} MB per step"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": bw_peak, "unit": "GB/s", "frac": achieved / bw_peak, "traffic": None,
+                         "peak_kind": f"{kind} (hbm_gbs)", "kernel": "append_kernel", "us_per_launch": ms * 1e3 / LAYERS,
+                         "algorithmic_bytes_per_launch": bytes_step // LAYERS},
+            "check": check, "gpu_launches": args.steps * LAYERS}
+
+
 def run(args, torch, dist, rank, world, local_rank):
-    fn = {"prefill": run_prefill, "seqshard": run_seqshard, "batched": run_batched}.get(args.workload)
+    fn = {"prefill": run_prefill, "seqshard": run_seqshard, "batched": run_batched, "append": run_append}.get(args.workload)
     if fn is None:
         raise SystemExit(f"unknown workload {args.workload}")
     line = fn(args, torch, dist, rank, world, local_rank)

@@ -20,6 +20,9 @@ CASES = [
     (128, 8, 128, 0, 1, False, np.float16),   # fp16/fp16
     (128, 2, 32, 3, 0, False, np.float32),    # no RoPE
     (128, 8, 32, 3, 1, True, np.float32),
+    (128, 12, 32, 3, 1, True, np.float16),    # more heads than one pass of the kernel takes (8 + 4)
+    (256, 6, 32, 3, 2, True, np.float16),     # the same at head_dim 256 (4 + 2)
+    (128, 3, 128, 1, 1, False, np.float32),   # a ragged pass with one scale per row and an fp16 side
 ]
 
 
@@ -105,3 +108,21 @@ def test_append_replay_is_deterministic(cuda):
         kv.launch_kv_store_quant(st.view(), k, v, None, 64, 0, rope_mode=kv.RopeMode.NEOX_FULL)
         snaps.append(torch.cat([st.key_cache_q8.flatten().view(torch.uint8), st.key_scales.flatten().view(torch.uint8)]).cpu())
     assert all(torch.equal(snaps[0], s) for s in snaps[1:])
+
+
+def test_append_unaligned_inputs_bit_exact(cuda):
+    # inputs that do not start on a 16-byte boundary take the element-wise loads: same bits
+    rng = np.random.default_rng(12)
+    T, H, d = 19, 8, 128
+    k, v = ko.normal_f16(rng, (T, H * d)), ko.normal_f16(rng, (T, H * d))
+    host = ko.HostCache(32, H, d, 32, 3)
+    host.append(k.astype(np.float32), v.astype(np.float32), None, 3, rope_mode=1)
+    st = device_storage_like(host)
+    pad_k = torch.zeros(T * H * d + 8, dtype=torch.float16, device="cuda")
+    pad_v = torch.zeros(T * H * d + 8, dtype=torch.float16, device="cuda")
+    kd, vd = pad_k[1:1 + T * H * d].view(T, H * d), pad_v[3:3 + T * H * d].view(T, H * d)
+    kd.copy_(to_dev(k)); vd.copy_(to_dev(v))
+    assert kd.data_ptr() % 16 != 0 and vd.data_ptr() % 16 != 0
+    kv.launch_kv_store_quant(st.view(), kd, vd, None, T, 3, rope_mode=kv.RopeMode.NEOX_FULL)
+    torch.cuda.synchronize()
+    assert_planes_equal(st, host, "unaligned inputs")

@@ -43,9 +43,10 @@ LAYERS, HQ, HKV, D, QB = 36, 32, 8, 128, 32
 ROW = D + 2 * (D // QB)  # 136 bytes per head-row
 THETA = 1.0e6
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch at 32K context, from an ncu capture of
-# this kernel on a 2-layer run of the same launch size (71.61 MB read + 1.74 MB written)
-NCU_TRAFFIC_BYTES_32K = 73_352_704
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch at 32K context, from ncu captures of the
+# two streaming kernels on a 2-layer run of the same launch size: the tcgen05 kernel 71.90 MB read + 1.46 MB written,
+# the warp-level mma kernel 71.61 MB + 1.74 MB
+NCU_TRAFFIC_BYTES_32K = {"tcgen05": 73_355_264, "mma": 73_352_704}
 
 
 def measured_peak_gbs() -> tuple[float, str]:
@@ -363,7 +364,7 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
         "hbm_gbs_whole_step": step_bytes / (ms_step * 1e-3) / 1e9,
         "hbm_frac_whole_step": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_BYTES_32K, "peak_kind": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs, burst copy)",
+                     "traffic": NCU_TRAFFIC_BYTES_32K[args.decode_kernel] if ctx == 32768 else None, "peak_kind": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs, burst copy)",
                      "kernel": ("decode_q8_kernel (split-K stage 1 on warp-level mma, merge fused in)" if args.decode_kernel == "mma" else
                                 "decode_tc5_kernel (split-K stage 1 on tcgen05 int8 MMA from TMA tiles, merge fused in)"), "us_per_launch": attn_us,
                      "algorithmic_bytes_per_launch": attn_bytes, "frac_of_nominal_8TBs": achieved / 8000.0},

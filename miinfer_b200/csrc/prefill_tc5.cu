@@ -7,18 +7,22 @@
 //     fp16 scratch in the caller's workspace (K and V planes, [kv_head][row][d]); with int8 -> fp16 exact up to
 //     the one rounding of q * scale.  The scratch (35.6 MB at 8704 x 4 x 256) stays in the 126 MB L2.
 //  2. The attention kernel gives each CTA 128 query ROWS of one kv head (a row is a (token, head-of-group)
-//     pair, so the G heads of a group share every K/V tile) and walks the causal range in tiles of 64 positions:
-//       - one thread feeds a 2-stage ring of K and V tiles with TMA tensor copies (64x64 boxes, 128-byte
-//         swizzle: exactly the canonical shared-memory layout of the MMA operands);
-//       - one thread issues tcgen05.mma: S = Q.K^T (M128 x N64, K = d) into one of two S buffers in TMEM,
-//         and O += P.V (M128 x N = d, K = 64; V consumed MN-major, as stored) into the O accumulator in TMEM;
-//         completion is tracked by tcgen05.commit on mbarriers;
-//       - 128 softmax threads own one row each: tcgen05.ld the S row, scale/mask (causal length per row,
-//         .hip:6829), online softmax in base 2 with LAZY rescaling (O and the running sum are only rescaled
-//         when a row's maximum grows by more than 2^8; P <= 256 fits fp16), write P as fp16 into the
-//         swizzled A-operand tile, and at the end scale O by 1/sum, apply the sigmoid gate (.hip:6714-6723)
-//         and store.
-//     TMEM: S0 | S1 | O = 64 + 64 + d columns.  Shared memory: Q (64 KB at d=256) + 2 x (K + V) + P.
+//     pair, so the G heads of a group share every K/V tile) and walks the causal range in tiles of 64 positions,
+//     two tiles at a time:
+//       - two threads feed the K ring (two stages of a PAIR of tiles each) and the V ring (two tiles) with TMA
+//         tensor copies (64x64 boxes, 128-byte swizzle: exactly the canonical shared-memory layout of the MMA
+//         operands; the two tiles of a pair lie in rows 0-63 and 64-127 of every slab, one B operand);
+//       - one thread issues S = Q.K^T for a pair of tiles at once (tcgen05.mma M128 x N128, K = d, Q read from
+//         TMEM: an MMA of this shape costs about the same at N = 64 and N = 128, so pairs halve the time the score
+//         MMAs hold the tensor pipe), another O += P.V per tile (M128 x N = d, K = 64; V consumed MN-major, as
+//         stored) into the O accumulator in TMEM; completion is tracked by tcgen05.commit on mbarriers;
+//       - two groups of 128 softmax threads, one thread per row in each, take the first and the second tile of
+//         every pair: tcgen05.ld the S row, scale/mask (causal length per row, .hip:6829), online softmax in base
+//         2 with LAZY rescaling (O and the running sums are only rescaled when a row's maximum grows by more
+//         than 2^8; P <= 256 fits fp16; the row's reference maximum is handed from tile to tile through shared
+//         memory), write P as fp16 into one of two swizzled A-operand tiles, and at the end scale O by 1/sum,
+//         apply the sigmoid gate (.hip:6714-6723) and store.
+//     TMEM: S (pair) | Q | O = 128 + d/2 + d columns.  Shared memory: 2 x 2 K tiles + 2 V tiles + 2 P tiles.
 // Every mbarrier wait is bounded; a wait that runs out poisons the output rows with NaN, and the CTA still frees
 // its TMEM and exits.
 #include "decode_common.cuh"
@@ -33,10 +37,13 @@ namespace {
 
 constexpr int kBM = 128;          // query rows per CTA
 constexpr int kBN = 64;           // positions per KV tile
-constexpr int kSoftmaxThreads = 256;              // two threads per query row: columns [0, 32) and [32, 64) of every S tile
-constexpr int kTmaWarp = kSoftmaxThreads / 32;     // TMA producer
-constexpr int kMmaWarp = kTmaWarp + 1;             // MMA issuer / TMEM owner
-constexpr int kThreads = kSoftmaxThreads + 64;
+constexpr int kSoftmaxThreads = 256;              // two groups of one thread per query row: even tiles, odd tiles
+constexpr int kTmaWarp = kSoftmaxThreads / 32;     // TMA producer of the K tiles
+constexpr int kSWarp = kTmaWarp + 1;               // S = Q.K^T issuer / TMEM owner
+constexpr int kPvWarp = kTmaWarp + 2;              // O += P.V issuer
+constexpr int kTmaVWarp = kTmaWarp + 3;            // TMA producer of the V tiles (a K load never waits for a V stage)
+constexpr int kThreads = kSoftmaxThreads + 128;
+constexpr int kKPairs = 2;                         // K ring: stages of two tiles each (one S MMA covers a pair)
 constexpr uint32_t kSpin = 1u << 20;
 constexpr float kRescaleThreshold = 8.0f;        // log2 units
 
@@ -138,21 +145,55 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+        "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32_bits(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
+        "%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+          "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]),
+          "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
+          "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+// P.V with the A operand (P, fp16, K-major: one query row per TMEM lane, two elements per 32-bit column) read from TMEM
+__device__ __forceinline__ void umma_f16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <int D>
 struct Layout {
     static constexpr int kSlabs = D / 64;                  // 128-byte (64 x fp16) slabs along d
-    static constexpr int kQBytes = kSlabs * kBM * 128;     // [slab][row][128 B]
-    static constexpr int kTileBytes = kSlabs * kBN * 128;  // one K or V tile
-    static constexpr int kOffK = kQBytes;
-    static constexpr int kOffV = kOffK + 2 * kTileBytes;
-    static constexpr int kOffP = kOffV + 2 * kTileBytes;   // [row][128 B] fp16 P tile
-    static constexpr int kOffBar = kOffP + kBM * 128;
-    static constexpr int kNumBars = 12;   // k_full[2] k_empty[2] v_full[2] v_empty[2] s_full[2] s_empty[2] -> 12, p_full, p_empty -> 14
-    static constexpr int kOffXch = kOffBar + 16 * 8 + 16;   // [2 parities][128 rows][2 halves] x {value, sequence}
-    static constexpr int kTotal = kOffXch + 2 * kBM * 2 * 8;
+    static constexpr int kTileBytes = kSlabs * kBN * 128;  // one K or V tile: [slab][row][128 B]
+    static constexpr int kPairBytes = 2 * kTileBytes;      // two K tiles as one B operand: [slab][128 rows][128 B]
+    static constexpr int kOffK = 0;
+    static constexpr int kOffV = kOffK + kKPairs * kPairBytes;
+    static constexpr int kOffP = kOffV + 2 * kTileBytes;   // 2 x [row][128 B] fp16 P tiles
+    static constexpr int kPBytes = kBM * 128;
+    static constexpr int kOffBar = kOffP + 2 * kPBytes;
+    static constexpr int kNumBars = 20;   // 16 used
+    static constexpr int kOffRef = kOffBar + kNumBars * 8 + 16;   // [128 rows] {reference maximum, sequence}: handed from tile to tile
+    static constexpr int kOffSum = kOffK;                         // [2 groups][128 rows] partial row sums: the K ring is idle in the epilogue
+    static constexpr int kTotal = kOffRef + kBM * 8;
     static constexpr int kAlloc = kTotal + 1024;
     static constexpr uint32_t kTmemCols = 512;
-    static constexpr uint32_t kColS = 0, kColO = 128;
+    static constexpr uint32_t kColS = 0, kColQ = 128, kColO = 256;   // S: 2 x 64, Q: D/2 (fp16 pairs), O: D
 };
 
 template <int D>
@@ -163,8 +204,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar0 = sbase + L::kOffBar;
     auto bar = [&](int i) { return bar0 + i * 8; };
-    enum { K_FULL = 0, K_EMPTY = 2, V_FULL = 4, V_EMPTY = 6, S_FULL = 8, S_EMPTY = 10, P_FULL = 12, P_EMPTY = 13 };
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffBar + 16 * 8);
+    enum { K_FULL = 0, K_EMPTY = 2, V_FULL = 4, V_EMPTY = 6, S_FULL = 8, S_EMPTY = 9, P_FULL = 11, P_EMPTY = 13, O_DONE = 15 };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffBar + L::kNumBars * 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t kv_head = blockIdx.y;
@@ -196,106 +237,137 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
 
     // ---- set-up: barriers, TMEM, Q tile -----------------------------------------------------------------
     if (tid == 0) {
-        for (int i = 0; i < 14; ++i) mbar_init(bar(i), (i == S_EMPTY || i == S_EMPTY + 1 || i == P_FULL) ? kSoftmaxThreads : 1);
+        for (int i = 0; i < L::kNumBars; ++i)
+            mbar_init(bar(i), (i == S_EMPTY || i == S_EMPTY + 1 || i == P_FULL || i == P_FULL + 1) ? kBM : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = tid; i < 2 * kBM * 2 * 2; i += kThreads) reinterpret_cast<uint32_t*>(smem + L::kOffXch)[i] = 0;
-    if (warp == kMmaWarp) {
+    for (int i = tid; i < kBM * 2; i += kThreads) reinterpret_cast<uint32_t*>(smem + L::kOffRef)[i] = 0;
+    if (warp == kSWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(L::kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // Q: rows of this CTA as fp16 in the canonical K-major layout [slab][row][64], 16-byte chunks XORed with row & 7
-    {
-        constexpr int CPR = D / 8;
-        for (int idx = tid; idx < kBM * CPR; idx += kThreads) {
-            const int r = idx / CPR, c = idx % CPR;
-            const uint32_t gr = row0 + r;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (gr < total_rows) {
-                const uint32_t token = gr / G, head = kv_head * G + gr % G;
-                const size_t off = (static_cast<size_t>(token) * p.query_heads + head) * D + c * 8;
-                if (p.q_is_f16) {
-                    v = *reinterpret_cast<const uint4*>(static_cast<const __half*>(p.q) + off);
-                } else {
-                    const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(p.q) + off);
-                    const float4 b = *reinterpret_cast<const float4*>(static_cast<const float*>(p.q) + off + 4);
-                    v = make_uint4(pack_half2(a.x, a.y), pack_half2(a.z, a.w), pack_half2(b.x, b.y), pack_half2(b.z, b.w));
-                }
-            }
-            const int slab = c >> 3, cc = c & 7;
-            *reinterpret_cast<uint4*>(smem + slab * (kBM * 128) + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
-        }
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // Q was written by ordinary stores, the MMA reads it through the async proxy
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Q: the CTA's rows as fp16 pairs in TMEM (row = lane, dims 2c and 2c+1 in column c), the A operand of every S MMA:
+    // read from there it costs no shared-memory bandwidth, which at N = 64 would bound the MMA.  Each of a row's two
+    // softmax threads stores half of the row.
+    if (warp < kSoftmaxThreads / 32) {
+        const int r = tid & (kBM - 1), half = tid >> 7;
+        const uint32_t gr = row0 + r;
+        const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const bool live = gr < total_rows;
+        const uint32_t token = live ? gr / G : 0, head = kv_head * G + (live ? gr % G : 0);
+        const size_t off = (static_cast<size_t>(token) * p.query_heads + head) * D + half * (D / 2);
+#pragma unroll 1
+        for (int c0 = 0; c0 < D / 4; c0 += 32) {   // 32 columns = 64 dims per store
+            uint32_t w[32];
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (live) {
+                    const size_t e = off + (c0 + i) * 2;
+                    if (p.q_is_f16) {
+                        v = *reinterpret_cast<const uint4*>(static_cast<const __half*>(p.q) + e);
+                    } else {
+                        const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(p.q) + e);
+                        const float4 b = *reinterpret_cast<const float4*>(static_cast<const float*>(p.q) + e + 4);
+                        v = make_uint4(pack_half2(a.x, a.y), pack_half2(a.z, a.w), pack_half2(b.x, b.y), pack_half2(b.z, b.w));
+                    }
+                }
+                w[i] = v.x; w[i + 1] = v.y; w[i + 2] = v.z; w[i + 3] = v.w;
+            }
+            tmem_st32_bits(tmem_base + lane_addr + L::kColQ + half * (D / 4) + c0, w);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
 
     bool failed = false;
 
     if (warp == kTmaWarp) {
-        // =============================== TMA producer ===============================
+        // =============================== TMA producer, K tiles ===============================
+        // A ring stage holds a PAIR of tiles, tile 2i in rows 0-63 and tile 2i+1 in rows 64-127 of every slab, so that
+        // one MMA instruction (N = 128) covers both.
         if (lane == 0) {
             const int row_base = static_cast<int>(kv_head * p.scratch_rows);
-            for (int j = 0; j < ntiles && !failed; ++j) {
+            for (int i = 0; 2 * i < ntiles; ++i) {
+                const int ps = i % kKPairs, n = min(2, ntiles - 2 * i);
+                if (!mbar_wait(bar(K_EMPTY + ps), static_cast<uint32_t>((i / kKPairs) & 1) ^ 1)) break;
+                mbar_expect_tx(bar(K_FULL + ps), n * L::kTileBytes);
+                for (int t = 0; t < n; ++t)
+                    for (int s = 0; s < L::kSlabs; ++s)
+                        tma_load_2d(sbase + L::kOffK + ps * L::kPairBytes + s * (2 * kBN * 128) + t * (kBN * 128), &p.kmap, s * 64,
+                                    row_base + (tile0 + 2 * i + t) * kBN, bar(K_FULL + ps));
+            }
+        }
+    } else if (warp == kTmaVWarp) {
+        // =============================== TMA producer, V tiles ===============================
+        if (lane == 0) {
+            const int row_base = static_cast<int>(kv_head * p.scratch_rows);
+            for (int j = 0; j < ntiles; ++j) {
                 const int st = j & 1;
                 const uint32_t ph = static_cast<uint32_t>((j >> 1) & 1);
-                if (!mbar_wait(bar(K_EMPTY + st), ph ^ 1)) { failed = true; break; }
-                mbar_expect_tx(bar(K_FULL + st), L::kTileBytes);
-                for (int s = 0; s < L::kSlabs; ++s)
-                    tma_load_2d(sbase + L::kOffK + st * L::kTileBytes + s * (kBN * 128), &p.kmap, s * 64, row_base + (tile0 + j) * kBN, bar(K_FULL + st));
-                if (!mbar_wait(bar(V_EMPTY + st), ph ^ 1)) { failed = true; break; }
+                if (!mbar_wait(bar(V_EMPTY + st), ph ^ 1)) break;
                 mbar_expect_tx(bar(V_FULL + st), L::kTileBytes);
                 for (int s = 0; s < L::kSlabs; ++s)
                     tma_load_2d(sbase + L::kOffV + st * L::kTileBytes + s * (kBN * 128), &p.vmap, s * 64, row_base + (tile0 + j) * kBN, bar(V_FULL + st));
             }
         }
-    } else if (warp == kMmaWarp) {
-        // =============================== MMA issuer ===============================
-        if (lane == 0 && ntiles > 0) {
-            constexpr uint32_t idesc_s = umma_idesc(kBM, kBN, 0, 0);
-            constexpr uint32_t idesc_o = umma_idesc(kBM, D, 0, 1);
-            auto issue_s = [&](int j) -> bool {
-                const int st = j & 1;
-                const uint32_t ph = static_cast<uint32_t>((j >> 1) & 1);
-                if (!mbar_wait(bar(K_FULL + st), ph)) return false;
-                if (!mbar_wait(bar(S_EMPTY + st), ph ^ 1)) return false;
+    } else if (warp == kSWarp) {
+        // =============================== S = Q.K^T issuer ===============================
+        // One chain of D/16 MMAs per PAIR of tiles (N = 128: the first tile's scores land in S columns 0-63, the second
+        // one's in 64-127).  An MMA instruction of this shape costs about 90 clocks whatever its N up to 128, so a
+        // pair costs what a single tile would.
+        if (lane == 0) {
+            constexpr uint32_t idesc_pair = umma_idesc(kBM, 2 * kBN, 0, 0), idesc_one = umma_idesc(kBM, kBN, 0, 0);
+            for (int i = 0; 2 * i < ntiles; ++i) {
+                const int ps = i % kKPairs, n = min(2, ntiles - 2 * i);
+                if (!mbar_wait(bar(K_FULL + ps), static_cast<uint32_t>((i / kKPairs) & 1))) break;
+                // both groups have read the previous pair's scores (only the last pair can be a single tile)
+                if (!mbar_wait(bar(S_EMPTY), static_cast<uint32_t>(i & 1) ^ 1) || !mbar_wait(bar(S_EMPTY + 1), static_cast<uint32_t>(i & 1) ^ 1)) break;
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t a = sbase + (kk >> 2) * (kBM * 128) + (kk & 3) * 32;
-                    const uint32_t b = sbase + L::kOffK + st * L::kTileBytes + (kk >> 2) * (kBN * 128) + (kk & 3) * 32;
-                    umma_f16(tmem_base + L::kColS + st * kBN, umma_desc(a, 16, 1024), umma_desc(b, 16, 1024), idesc_s, kk > 0);
+                    const uint32_t b = sbase + L::kOffK + ps * L::kPairBytes + (kk >> 2) * (2 * kBN * 128) + (kk & 3) * 32;
+                    umma_f16_a_tmem(tmem_base + L::kColS, tmem_base + L::kColQ + kk * 8, umma_desc(b, 16, 1024), n == 2 ? idesc_pair : idesc_one, kk > 0);
                 }
-                umma_commit(bar(S_FULL + st));    // S tile ready for the softmax rows
-                umma_commit(bar(K_EMPTY + st));   // K stage may be refilled
-                return true;
-            };
-            if (!issue_s(0)) failed = true;
-            for (int j = 0; j < ntiles && !failed; ++j) {
-                if (j + 1 < ntiles && !issue_s(j + 1)) { failed = true; break; }
+                umma_commit(bar(S_FULL));         // scores ready for both softmax groups
+                umma_commit(bar(K_EMPTY + ps));   // K stage may be refilled
+            }
+        }
+    } else if (warp == kPvWarp) {
+        // =============================== O += P.V issuer ===============================
+        if (lane == 0) {
+            constexpr uint32_t idesc_o = umma_idesc(kBM, D, 0, 1);
+            for (int j = 0; j < ntiles; ++j) {
                 const int st = j & 1;
-                if (!mbar_wait(bar(V_FULL + st), static_cast<uint32_t>((j >> 1) & 1))) { failed = true; break; }
-                if (!mbar_wait(bar(P_FULL), static_cast<uint32_t>(j & 1))) { failed = true; break; }
+                const uint32_t ph = static_cast<uint32_t>((j >> 1) & 1);
+                if (!mbar_wait(bar(V_FULL + st), ph)) break;
+                if (!mbar_wait(bar(P_FULL + st), ph)) break;
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < kBN / 16; ++kk) {
-                    const uint32_t a = sbase + L::kOffP + kk * 32;                                   // P: K-major, one 128-byte slab
                     const uint32_t b = sbase + L::kOffV + st * L::kTileBytes + kk * (16 * 128);      // V: MN-major, 16 positions per step
+                    const uint32_t a = sbase + L::kOffP + st * L::kPBytes + kk * 32;               // P: K-major, one 128-byte slab
                     umma_f16(tmem_base + L::kColO, umma_desc(a, 16, 1024), umma_desc(b, kBN * 128, 1024), idesc_o, (j > 0 || kk > 0));
                 }
-                umma_commit(bar(P_EMPTY));        // P tile free, O stable
+                umma_commit(bar(P_EMPTY + st));   // P buffer free, O holds tiles 0..j
                 umma_commit(bar(V_EMPTY + st));
+                if (j == ntiles - 1) umma_commit(bar(O_DONE));   // O complete: the epilogue's signal for both groups
             }
         }
     } else {
         // =============================== softmax rows ===============================
-        // Two threads per row: warps 0-3 take columns [0, 32) of every S tile, warps 4-7 columns [32, 64) (a warp
-        // reaches the 32 TMEM lanes of its number modulo 4).  The pair agrees on the row maximum through a small
-        // exchange area in shared memory (8-byte {value, sequence} words, polled with a bound, double-buffered by
-        // tile parity); each keeps its own partial row sum until the epilogue.
-        const int r = tid & (kBM - 1), hsel = tid >> 7;      // row of this thread == its TMEM lane; column half
+        // Two groups of 128 threads, one thread per query row in each: warps 0-3 take the even tiles, warps 4-7 the odd
+        // ones (a warp reaches the 32 TMEM lanes of its number modulo 4), so two tiles are in flight: while one group
+        // works through its exponentials the other one's S arrives and its P.V runs.  A row's reference maximum is handed
+        // from tile to tile through an 8-byte {value, sequence} word in shared memory; each thread keeps the partial row
+        // sum of its own tiles, relative to the reference it last saw.
+        const int r = tid & (kBM - 1), grp = tid >> 7;       // row of this thread == its TMEM lane; tile parity
         const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t gr = row0 + r;
         uint32_t len = 0;
@@ -304,91 +376,114 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
             const uint64_t l64 = static_cast<uint64_t>(base) + token + 1u;
             len = (token < count && l64 <= p.capacity) ? static_cast<uint32_t>(l64) : 0u;
         }
-        volatile unsigned long long* xch = reinterpret_cast<volatile unsigned long long*>(smem + L::kOffXch);
-        auto exchange = [&](int parity, uint32_t seq, float mine, float* theirs) -> bool {
-            xch[(parity * kBM + r) * 2 + hsel] = (static_cast<unsigned long long>(seq) << 32) | __float_as_uint(mine);
+        volatile unsigned long long* ref = reinterpret_cast<volatile unsigned long long*>(smem + L::kOffRef) + r;
+        auto ref_after = [&](uint32_t seq, float* value) -> bool {   // the reference as tile seq-1 left it
             for (uint32_t spin = 0; spin < kSpin; ++spin) {
-                const unsigned long long w = xch[(parity * kBM + r) * 2 + (hsel ^ 1)];
-                if (static_cast<uint32_t>(w >> 32) == seq) { *theirs = __uint_as_float(static_cast<uint32_t>(w)); return true; }
+                const unsigned long long w = *ref;
+                if (static_cast<uint32_t>(w >> 32) == seq) { *value = __uint_as_float(static_cast<uint32_t>(w)); return true; }
             }
             return false;
         };
-        constexpr int kHalf = kBN / 2;
-        float m_ref = -INFINITY, l_sum = 0.0f;
-        for (int j = 0; j < ntiles; ++j) {
-            const int st = j & 1;
-            if (!mbar_wait(bar(S_FULL + st), static_cast<uint32_t>((j >> 1) & 1))) { failed = true; break; }
+        float m_known = -INFINITY, l_sum = 0.0f;   // l_sum is relative to m_known
+        auto rebase = [&](float m_new) {
+            if (m_new != m_known) {
+                l_sum *= (m_known == -INFINITY) ? 0.0f : ex2_approx(m_known - m_new);
+                m_known = m_new;
+            }
+        };
+        const int st = grp;
+        for (int j = grp; j < ntiles; j += 2) {
+            const uint32_t ph = static_cast<uint32_t>((j >> 1) & 1);   // parity of the tile's pair
+            if (!mbar_wait(bar(S_FULL), ph)) { failed = true; break; }
             tc_fence_after();
-            float s[kHalf];
-            tmem_ld32(tmem_base + lane_addr + L::kColS + st * kBN + hsel * kHalf, s);
+            float s[kBN];
+            {
+                uint32_t lo[32], hi[32];
+                tmem_ld32_nowait(tmem_base + lane_addr + L::kColS + st * kBN, lo);
+                tmem_ld32_nowait(tmem_base + lane_addr + L::kColS + st * kBN + 32, hi);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(lo[i]); s[32 + i] = __uint_as_float(hi[i]); }
+            }
             tc_fence_before();
-            mbar_arrive(bar(S_EMPTY + st));   // this thread's part of S is in registers
-            const uint32_t pos0 = static_cast<uint32_t>(tile0 + j) * kBN + hsel * kHalf;
+            mbar_arrive(bar(S_EMPTY + st));   // this row of S is in registers
+            const uint32_t pos0 = static_cast<uint32_t>(tile0 + j) * kBN;
             // Raw scores stay unscaled; the softmax scale is folded into the exponent: p = 2^(s*c - m*c).
             // Only the tiles that straddle this row's causal length need the mask.
-            if (pos0 + kHalf > len) {
+            if (pos0 + kBN > len) {
 #pragma unroll
-                for (int i = 0; i < kHalf; ++i) s[i] = (pos0 + i < len) ? s[i] : -INFINITY;
+                for (int i = 0; i < kBN; ++i) s[i] = (pos0 + i < len) ? s[i] : -INFINITY;
             }
             float mt = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < kHalf; ++i) mt = fmaxf(mt, s[i]);
-            {
-                float other;
-                if (!exchange(j & 1, static_cast<uint32_t>(j) + 1u, mt, &other)) { failed = true; break; }
-                mt = fmaxf(mt, other);
-            }
+            for (int i = 0; i < kBN; ++i) mt = fmaxf(mt, s[i]);
             mt *= p.scale_log2;   // scale > 0: the maximum commutes with it
-            // lazy rescale: keep the old reference unless the row maximum outgrew it by more than the threshold
-            float alpha = 1.0f;
-            if (mt > m_ref + kRescaleThreshold || (m_ref == -INFINITY && mt > -INFINITY)) {
-                alpha = (m_ref == -INFINITY) ? 0.0f : exp2f(m_ref - mt);
-                m_ref = mt;
+            // the reference as the previous tile (the other group's) left it; lazy rescale: keep it unless this tile's
+            // maximum outgrew it by more than the threshold
+            float m_prev = -INFINITY;
+            if (j > 0 && !ref_after(static_cast<uint32_t>(j), &m_prev)) { failed = true; break; }
+            float alpha = 1.0f, m_new = m_prev;
+            if (mt > m_prev + kRescaleThreshold || (m_prev == -INFINITY && mt > -INFINITY)) {
+                alpha = (m_prev == -INFINITY) ? 0.0f : ex2_approx(m_prev - mt);
+                m_new = mt;
             }
-            const float neg_ref = (m_ref == -INFINITY) ? 0.0f : -m_ref;
+            // published at once (the other group's thread of this row waits for it): no later work may be scheduled before it
+            asm volatile("st.volatile.shared.u64 [%0], %1;" ::"r"(smem_u32(const_cast<unsigned long long*>(ref))),
+                         "l"((static_cast<unsigned long long>(static_cast<uint32_t>(j) + 1u) << 32) | __float_as_uint(m_new)) : "memory");
+            rebase(m_new);
+            const float neg_ref = (m_new == -INFINITY) ? 0.0f : -m_new;
             float sum = 0.0f;
-            uint32_t ph[kHalf / 2];
+            uint32_t pk[kBN / 2];
 #pragma unroll
-            for (int i = 0; i < kHalf; i += 2) {
-                const float p0 = exp2f(fmaf(s[i], p.scale_log2, neg_ref)), p1 = exp2f(fmaf(s[i + 1], p.scale_log2, neg_ref));
+            for (int i = 0; i < kBN; i += 2) {
+                const float p0 = ex2_approx(fmaf(s[i], p.scale_log2, neg_ref)), p1 = ex2_approx(fmaf(s[i + 1], p.scale_log2, neg_ref));
                 const __half2 h = __floats2half2_rn(p0, p1);
                 // the sum uses the rounded values the MMA will multiply, so numerator and denominator stay consistent
                 const float2 hf = __half22float2(h);
                 sum += hf.x + hf.y;
-                ph[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+                pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
             }
-            l_sum = fmaf(l_sum, alpha, sum);
-            // P tile and O are free once the previous P.V has completed
-            if (!mbar_wait(bar(P_EMPTY), static_cast<uint32_t>((j & 1) ^ 1))) { failed = true; break; }
+            l_sum += sum;
+            // this group's P buffer is free once the P.V of its previous tile has completed
+            if (!mbar_wait(bar(P_EMPTY + st), ph ^ 1)) { failed = true; break; }
             tc_fence_after();
             if (__any_sync(0xffffffffu, alpha != 1.0f) && j > 0) {
-                // rare: rescale this warp's 32 rows of O in TMEM, each thread of a pair its half of the columns
+                // rare: the reference moved.  O holds tiles 0..j-1 once the previous tile's P.V (the other group's) has
+                // completed; then this warp rescales its 32 rows of O in TMEM before its own P is released.
+                if (!mbar_wait(bar(P_EMPTY + (st ^ 1)), static_cast<uint32_t>(((j - 1) >> 1) & 1))) { failed = true; break; }
+                tc_fence_after();
 #pragma unroll 1
-                for (int c0 = hsel * (D / 2); c0 < (hsel + 1) * (D / 2); c0 += 32) {
+                for (int c0 = 0; c0 < D; c0 += 32) {
                     float o[32];
                     tmem_ld32(tmem_base + lane_addr + L::kColO + c0, o);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] *= alpha;
                     tmem_st32(tmem_base + lane_addr + L::kColO + c0, o);
                 }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            uint8_t* prow = smem + L::kOffP + r * 128;
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");   // the rescale's stores, if any
+            uint8_t* prow = smem + L::kOffP + st * L::kPBytes + r * 128;
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                *reinterpret_cast<uint4*>(prow + (((hsel * 4 + c) ^ (r & 7)) << 4)) = make_uint4(ph[4 * c], ph[4 * c + 1], ph[4 * c + 2], ph[4 * c + 3]);
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
-            mbar_arrive(bar(P_FULL));
+            mbar_arrive(bar(P_FULL + st));
         }
-        // ---- epilogue: O / sum, gate, store; each thread of a pair half of the columns ----
-        if (!failed && ntiles > 0 && !mbar_wait(bar(P_EMPTY), static_cast<uint32_t>((ntiles - 1) & 1))) failed = true;
+        // ---- epilogue: O / sum, gate, store; each thread of a row's pair half of the columns ----
+        if (!failed && ntiles > 0 && !mbar_wait(bar(O_DONE), 0)) failed = true;
         tc_fence_after();
         {
-            // the row sum is the two partial sums (both threads hold the same reference maximum)
-            float other = 0.0f;
-            if (!failed && !exchange(ntiles & 1, static_cast<uint32_t>(ntiles) + 1u, l_sum, &other)) failed = true;
-            l_sum += other;
+            float m_final = -INFINITY;
+            if (!failed && ntiles > 0 && !ref_after(static_cast<uint32_t>(ntiles), &m_final)) failed = true;
+            rebase(m_final);
+            float* sums = reinterpret_cast<float*>(smem + L::kOffSum);
+            sums[grp * kBM + r] = failed ? __int_as_float(0x7fc00000) : l_sum;
+            asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+            l_sum = sums[r] + sums[kBM + r];
+            if (l_sum != l_sum) failed = true;   // either thread of the row gave up
+            const float m_ref = m_final;
+            const int hsel = grp;
             // tcgen05.ld is warp-collective: every lane takes part, rows past the launch only skip the store
             const bool live = gr < total_rows;
             const uint32_t token = live ? gr / G : 0, head = kv_head * G + (live ? gr % G : 0);
@@ -434,7 +529,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
     // ---- teardown: every role arrives here, with or without a timeout; TMEM is always released ----
     tc_fence_before();
     __syncthreads();
-    if (warp == kMmaWarp) {
+    if (warp == kSWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::kTmemCols) : "memory");
     }

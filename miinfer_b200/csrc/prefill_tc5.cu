@@ -212,11 +212,15 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
     const uint32_t G = p.query_heads / p.kv_heads;
     uint32_t base = p.base_position, count = p.token_count;
     if (p.prefill_state != nullptr) {
+        pdl_wait();   // the state may be the preceding kernel's output
         base = p.prefill_state->base_position;
         count = min(count, p.prefill_state->token_count);
     }
     const uint32_t total_rows = p.token_count * G;
     const uint32_t row0 = blockIdx.x * kBM;
+    // The next kernel of the stream (the merge of the KV splits) may become resident once every CTA has got here; it
+    // orders itself against this one.  This kernel's own dependency wait comes after its set-up.
+    pdl_launch_dependents();
     if (row0 >= total_rows) return;
 
     // longest causal range among this CTA's rows (rows are token-major; see prefill_mma.cu)
@@ -250,6 +254,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();   // Q, the fp16 scratch and the device-side state come from preceding kernels
     // Q: the CTA's rows as fp16 pairs in TMEM (row = lane, dims 2c and 2c+1 in column c), the A operand of every S MMA:
     // read from there it costs no shared-memory bandwidth, which at N = 64 would bound the MMA.  Each of a row's two
     // softmax threads stores half of the row.
@@ -547,6 +552,8 @@ struct PrefillMergeParams {
 template <int D>
 __global__ void __launch_bounds__(256) prefill_merge_kernel(const __grid_constant__ PrefillMergeParams p) {
     constexpr int VPR = D / 4;   // float4 per row
+    pdl_launch_dependents();
+    pdl_wait();   // the partials are the attention kernel's output
     const uint32_t kv_head = blockIdx.y, G = p.query_heads / p.kv_heads;
     const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= static_cast<size_t>(p.total_rows) * VPR) return;
@@ -590,6 +597,8 @@ struct DequantParams {
 template <int D>
 __global__ void __launch_bounds__(256) dequant_prefix_kernel(const __grid_constant__ DequantParams p) {
     constexpr int CPR = D / 16;
+    pdl_launch_dependents();
+    pdl_wait();   // the cache rows of this chunk come from the append kernel just before
     const uint32_t head = blockIdx.y, side = blockIdx.z;   // side 0 = K, 1 = V
     const uint32_t mode = p.view.quant_mode;
     const bool q8 = side == 0 ? (mode == B200KV_Q8_F16 || mode == B200KV_Q8_Q8) : (mode == B200KV_F16_Q8 || mode == B200KV_Q8_Q8);
@@ -662,13 +671,11 @@ int launch_tc5(const b200kv_view& view, Tc5Params& p, __half* k_scratch, __half*
         const size_t units = static_cast<size_t>(p.scratch_rows) * (D / 16);
         unsigned blocks = static_cast<unsigned>((units + 255) / 256);
         if (blocks > 148u * 4u) blocks = 148u * 4u;
-        dequant_prefix_kernel<D><<<dim3(blocks, view.kv_heads, 2), 256, 0, stream>>>(dp);
-        B200KV_CUDA_TRY(cudaGetLastError());
+        B200KV_CUDA_TRY(launch_kernel(dequant_prefix_kernel<D>, dim3(blocks, view.kv_heads, 2), dim3(256), 0, stream, true, dp));
     }
     const uint32_t G = p.query_heads / p.kv_heads;
     const uint32_t row_tiles = (p.token_count * G + kBM - 1) / kBM;
-    prefill_tc5_kernel<D><<<dim3(row_tiles, p.kv_heads, p.kv_splits), kThreads, L::kAlloc, stream>>>(p);
-    B200KV_CUDA_TRY(cudaGetLastError());
+    B200KV_CUDA_TRY(launch_kernel(prefill_tc5_kernel<D>, dim3(row_tiles, p.kv_heads, p.kv_splits), dim3(kThreads), L::kAlloc, stream, true, p));
     if (p.kv_splits > 1) {
         PrefillMergeParams mp{};
         mp.part_o = p.part_o;
@@ -681,8 +688,7 @@ int launch_tc5(const b200kv_view& view, Tc5Params& p, __half* k_scratch, __half*
         mp.rows_padded = p.rows_padded;
         mp.total_rows = p.token_count * G;
         const size_t work = static_cast<size_t>(mp.total_rows) * (D / 4);
-        prefill_merge_kernel<D><<<dim3(static_cast<unsigned>((work + 255) / 256), p.kv_heads), 256, 0, stream>>>(mp);
-        B200KV_CUDA_TRY(cudaGetLastError());
+        B200KV_CUDA_TRY(launch_kernel(prefill_merge_kernel<D>, dim3(static_cast<unsigned>((work + 255) / 256), p.kv_heads), dim3(256), 0, stream, true, mp));
     }
     return B200KV_OK;
 }

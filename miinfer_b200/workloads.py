@@ -124,7 +124,9 @@ def run_prefill(args, torch, dist, rank, world, local_rank):
             kv.launch_suffix_attention_quant(views[l], q[l], gate[l], out[l], ws, T, P, query_heads=hq, scale=D ** -0.5)
 
     stream = torch.cuda.Stream()
+    kv.set_launch_overlap(0 if args.no_overlap else 1)   # every kernel of the chunk waits for its predecessor itself
     ms = _time(torch, dist, stream, step, args.warmup, args.steps)
+    kv.set_launch_overlap(0)
     check = None
     if rank == 0 and not args.no_check:
         ko = _oracle()

@@ -224,3 +224,32 @@ def test_suffix_attention_with_the_kv_range_split_over_ctas(cuda, P, T, H, Hq, d
     torch.cuda.synchronize()
     assert np.max(np.abs(split.cpu().numpy() - ref)) <= TOL
     assert float((split - plain).abs().max()) <= 1e-4     # same tiles, merged in a different order
+
+
+def test_suffix_chunks_back_to_back_with_launch_overlap(cuda):
+    """With launch overlap on, the kernels of consecutive chunks (store, fp16 pre-pass, attention, merge) become resident
+    while their predecessors still run and order themselves by their own dependency waits: the outputs of three chunks
+    launched back to back must equal those of the serialised launches bit for bit."""
+    rng = np.random.default_rng(77)
+    P, T, H, Hq, d = 1024, 128, 4, 24, 256
+    host = filled(rng, P, H, d, 32, 3, cap=P + 3 * T, std=0.5)
+    w = to_dev((1.0 + 0.1 * rng.standard_normal(d)).astype(np.float32))
+    chunks = [(to_dev(ko.normal_f16(rng, (T, H * d))), to_dev(ko.normal_f16(rng, (T, H * d))),
+               to_dev((rng.standard_normal((T, Hq, d)) * 0.5).astype(np.float32)),
+               to_dev((rng.standard_normal((T, Hq, d)) * 0.5).astype(np.float32))) for _ in range(3)]
+    outs = {}
+    for overlap in (0, 1):
+        st = upload(host)
+        ws = kv.prefill_workspace(P + 3 * T, H, d, token_count=T, query_heads=Hq)
+        out = torch.full((3, T, Hq, d), float("nan"), device="cuda")
+        kv.set_launch_overlap(overlap)
+        try:
+            for i, (k, v, q, gate) in enumerate(chunks):
+                kv.launch_kv_store_quant(st.view(), k, v, w, T, P + i * T, rope_mode=kv.RopeMode.SECTIONED64)
+                kv.launch_suffix_attention_quant(st.view(), q, gate, out[i], ws, T, P + i * T, query_heads=Hq, scale=d ** -0.5)
+            torch.cuda.synchronize()
+        finally:
+            kv.set_launch_overlap(0)
+        outs[overlap] = out.cpu()
+    assert torch.isfinite(outs[1]).all()
+    assert torch.equal(outs[0], outs[1])

@@ -11,7 +11,7 @@ caches resident in HBM.  With N GPUs every rank decodes its own session (weak
 scaling, no data-path collective).  Other workloads:
 `seqshard` (one 128K-token session sharded by sequence over the ranks; the per-rank
 partials are exchanged and merged inside the decode kernel, or by NCCL with --exchange nccl), `batched` (64 sessions of mixed
-length), `prefill` (512-token suffix over an 8K prefix, d=256), `append` (the store kernel alone: 8192-token chunks at d=128,
+length), `prefill` (512-token suffix over an 8K prefix, d=256), `decode256` (decode attention on the reference's own 24 Q / 4 KV, d=256 geometry), `append` (the store kernel alone: 8192-token chunks at d=128,
 or with --append-shape chunk256 the 512-token d=256 chunk).
 
 The default run also measures, as sub-records of the same JSON line, the suffix-prefill

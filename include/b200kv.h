@@ -327,8 +327,11 @@ B200KV_API int b200kv_exchange_close(void* peer_buffer);
 B200KV_API int b200kv_exchange_destroy(void* buffer);
 
 /* Which stage-1 kernel b200kv_decode_attn picks for this view: 1 = the streaming
- * int8 kernel (int8 K and V, head_dim 128, 1/2/4 query heads per kv head,
- * capacity a multiple of 8), 0 = the generic kernel (every other mode and shape).
+ * int8 kernels (int8 K and V, head_dim 128, 1/2/4 query heads per kv head,
+ * capacity a multiple of 8; merge, append and cross-GPU exchange fused in),
+ * 2 = the tcgen05 stage 1 for head_dim 256 (int8 K and V, 4/6/8 query heads per
+ * kv head, capacity a multiple of 8; single-session launches, the merge kernel
+ * follows), 0 = the generic kernel (every other mode and shape).
  * No counterpart in the reference. */
 B200KV_API int b200kv_decode_kernel_kind(const b200kv_view* view, uint32_t query_heads);
 

@@ -227,10 +227,13 @@ int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max
     uint32_t num_splits = num_splits_arg & ~B200KV_SPLITS_FORCE_GENERIC;
     const uint32_t cap = max_splits_per_session(p.sessions);
     bool use_fast = !force_generic && q8_fast_path_ok(geometry, p.query_heads);
+    // head_dim 256: a tcgen05 stage 1 for single-session launches (it leaves plain partials, like the generic kernel)
+    const bool use_wide = !force_generic && !use_fast && p.views == nullptr && p.lengths == nullptr && !p.causal && p.sessions == 1 &&
+                          p.new_key == nullptr && streaming_kernel_choice() != 1 && decode_tc5_wide_ok(geometry, p.query_heads);
     if (num_splits == 0) {
         uint32_t fast = use_fast ? pick_splits_q8(geometry, p.query_heads, p.sessions, max_length) : 0;
         if (fast == 0) use_fast = false;
-        num_splits = use_fast ? fast : pick_splits_generic(p.query_heads, p.sessions, max_length);
+        num_splits = use_fast ? fast : (use_wide ? pick_splits_tc5_wide(geometry, max_length) : pick_splits_generic(p.query_heads, p.sessions, max_length));
     }
     if (num_splits > cap) num_splits = cap;
     const size_t slots = static_cast<size_t>(p.sessions) * num_splits * p.query_heads;
@@ -259,6 +262,10 @@ int run_decode_stage1(DecodeParams& p, const b200kv_view& geometry, uint32_t max
         if (rc == B200KV_OK) *merged = fuse_merge;
         if (rc != B200KV_ERR_UNSUPPORTED) return rc;
         p.ws_tagged = nullptr;
+    }
+    if (use_wide) {
+        const int rc = launch_decode_tc5_wide(p, geometry, stream);
+        if (rc != B200KV_ERR_UNSUPPORTED) return rc;
     }
     dim3 grid(p.query_heads, num_splits, p.sessions);
     if (geometry.head_dim == 128) launch_generic<128>(p, geometry.quant_mode, grid, stream);
@@ -322,7 +329,8 @@ extern "C" {
 
 int b200kv_decode_kernel_kind(const b200kv_view* view, uint32_t query_heads) {
     if (validate_view(view) != B200KV_OK) return 0;
-    return q8_fast_path_ok(*view, query_heads) ? 1 : 0;
+    if (q8_fast_path_ok(*view, query_heads)) return 1;
+    return decode_tc5_wide_ok(*view, query_heads) ? 2 : 0;
 }
 
 size_t b200kv_view_table_bytes(uint32_t sessions) { return sizeof(SessionEntry) * static_cast<size_t>(sessions ? sessions : 1); }

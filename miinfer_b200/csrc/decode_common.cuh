@@ -160,6 +160,10 @@ int run_decode(DecodeParams& p, const b200kv_view& geometry, uint32_t max_length
 int launch_decode_q8(const DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, cudaStream_t stream);
 // The same launch on the tcgen05 kernel (decode_tc5.cu); B200KV_ERR_UNSUPPORTED where it does not apply.
 int launch_decode_tc5(const DecodeParams& p, const b200kv_view& geometry, uint32_t max_length, cudaStream_t stream);
+// head_dim 256 on tcgen05 (stage 1 only, plain partials, one session): decode_tc5_wide.cu
+bool decode_tc5_wide_ok(const b200kv_view& view, uint32_t query_heads);
+uint32_t pick_splits_tc5_wide(const b200kv_view& view, uint32_t max_length);
+int launch_decode_tc5_wide(const DecodeParams& p, const b200kv_view& geometry, cudaStream_t stream);
 uint32_t pick_splits_q8(const b200kv_view& geometry, uint32_t query_heads, uint32_t sessions, uint32_t max_length);
 // TMA descriptors of a view's int8 K and V planes (rows of head_dim bytes, 128-byte swizzle).
 // B200KV_ERR_UNSUPPORTED when the view cannot take the streaming kernel (then the generic kernel is used).

@@ -470,7 +470,8 @@ def set_launch_overlap(tail_positions: int) -> None:
 
 
 def decode_kernel_kind(view: View, query_heads: int) -> int:
-    """1 if decode attention on this view runs the streaming int8 kernel, 0 for the generic one."""
+    """1: decode attention on this view runs a streaming int8 kernel (head_dim 128); 2: the tcgen05 stage 1 for head_dim 256;
+    0: the generic kernel."""
     return int(lib.b200kv_decode_kernel_kind(C.byref(view), query_heads))
 
 

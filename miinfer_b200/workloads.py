@@ -430,8 +430,64 @@ def run_append(args, torch, dist, rank, world, local_rank):
             "check": check, "gpu_launches": args.steps * LAYERS}
 
 
+def run_decode256(args, torch, dist, rank, world, local_rank):
+    """Decode attention alone on the reference's own geometry: 24 query heads over 4 kv heads, head_dim 256, q8_0 K/V, one
+    session of `--context` positions per GPU, 16 attention layers (the hybrid model's count), no append.  Stage 1 on the
+    tcgen05 kernel for head_dim 256 plus the merge kernel; `--decode-kernel mma` runs the generic stage 1 instead."""
+    from miinfer_b200 import kv
+
+    L, HQ, HKV, D, LAYERS = args.context, 24, 4, 256, min(args.layers, 16)
+    cap = (L + 64 + 127) // 128 * 128
+    caches = [kv.AttentionLayerKvCacheStorage(cap, kv.KvCacheQuantMode.kQ8Q8, kv_heads=HKV, head_dim=D, qblock=32) for _ in range(LAYERS)]
+    for i, c in enumerate(caches):
+        _fill(kv, torch, c, L, 500 * rank + i)
+    g = torch.Generator(device="cuda"); g.manual_seed(3 + rank)
+    q = torch.randn(LAYERS, HQ, D, generator=g, device="cuda").half()
+    out = torch.zeros(LAYERS, HQ, D, device="cuda")
+    ws = kv.decode_workspace(HQ, D)
+    views = [c.view() for c in caches]
+    kind = kv.decode_kernel_kind(views[0], HQ)
+    kv.set_launch_overlap(0 if args.no_overlap else 1)
+
+    def step():
+        for l in range(LAYERS):
+            kv.launch_decode_attention_quant(views[l], q[l], query_heads=HQ, scale=D ** -0.5, cache_length=L, output=out[l], workspace=ws)
+
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+    torch.cuda.synchronize()
+    ms = _time(torch, dist, stream, graph.replay, args.warmup, args.steps)
+    kv.set_launch_overlap(0)
+    check = None
+    if rank == 0 and not args.no_check:
+        ko = _oracle()
+        ko.set_threads(args.cpu_threads)
+        host = host_cache_from_planes(ko, planes_of(torch, caches[0], L), L, HKV, D)
+        ref, _ = host.decode_ref(q[0].float().cpu().numpy(), D ** -0.5, L)
+        check = error_record(out[0].cpu().numpy(), ref, layer=0, context=L)
+    bytes_launch = L * HKV * (D + 2 * (D // 32)) * 2
+    bw_peak, _, kind_peak = _peaks()
+    achieved = bytes_launch * LAYERS / (ms * 1e-3) / 1e9
+    streaming = kind == 2 and args.decode_kernel != "mma"
+    return {"metric": "q8_0_kv_decode_attention_gbs_head_dim_256", "value": achieved * world, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 KV / fp32 accumulate", "data": "synthetic",
+            "config": {"workload": f"decode256: decode attention, {HQ} Q / {HKV} KV heads, d={D}, q8_0 K/V, context {L}, {LAYERS} layers, batch 1 per GPU",
+                       "l2": f"inputs larger than L2: {bytes_launch * LAYERS / 1e6:.0f} MB of KV per step"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": bw_peak, "unit": "GB/s", "frac": achieved / bw_peak, "traffic": None,
+                         "peak_kind": f"{kind_peak} (hbm_gbs)",
+                         "kernel": "decode_tc5_wide_kernel + merge_kernel" if streaming else "decode_generic_kernel + merge_kernel",
+                         "us_per_launch_pair": ms * 1e3 / LAYERS, "algorithmic_bytes_per_launch": bytes_launch},
+            "check": check, "gpu_launches": args.steps * LAYERS * 2}
+
+
 def run(args, torch, dist, rank, world, local_rank):
-    fn = {"prefill": run_prefill, "seqshard": run_seqshard, "batched": run_batched, "append": run_append}.get(args.workload)
+    fn = {"prefill": run_prefill, "seqshard": run_seqshard, "batched": run_batched, "append": run_append, "decode256": run_decode256}.get(args.workload)
     if fn is None:
         raise SystemExit(f"unknown workload {args.workload}")
     line = fn(args, torch, dist, rank, world, local_rank)

@@ -56,7 +56,8 @@ def test_decode_matches_two_pass_reference(cuda, d, H, Hq, qb, mode, L, path):
     st = upload(host)
     v = st.view()
     streaming = mode == 3 and d == 128 and Hq // H in (1, 2, 4)
-    assert kv.decode_kernel_kind(v, Hq) == (1 if streaming else 0)
+    wide = mode == 3 and d == 256 and Hq // H in (4, 6, 8)
+    assert kv.decode_kernel_kind(v, Hq) == (1 if streaming else 2 if wide else 0)
     q16 = ko.normal_f16(rng, (Hq, d))
     gate = rng.standard_normal((Hq, d)).astype(np.float32)
     ref, ref_g = host.decode_ref(q16.astype(np.float32), d ** -0.5, L, gate)
@@ -379,3 +380,38 @@ def test_fused_decode_step_long_context_many_tiles_per_pair(cuda):
     assert_planes_equal(st, host, "graph-replayed fused steps")
     ref, _ = host.decode_ref(q.float().cpu().numpy(), d ** -0.5, L0 + 3)
     assert np.max(np.abs(out.cpu().numpy() - ref)) <= TOL
+
+
+# (H, Hq, qblock, L): head_dim 256 on the tcgen05 stage-1 kernel
+WIDE = [
+    (4, 24, 32, 8200),      # the reference's geometry, q8_0 blocks, many tiles per CTA
+    (4, 24, 256, 4099),     # ... with its one-scale-per-row format
+    (2, 16, 32, 3001),      # 8 query heads per kv head
+    (4, 16, 256, 1500),     # 4 query heads per kv head
+    (4, 24, 32, 129),       # two tiles, the second one position long
+]
+
+
+@pytest.mark.parametrize("H,Hq,qb,L", WIDE)
+def test_decode_head_dim_256_tcgen05_stage1(cuda, H, Hq, qb, L):
+    d = 256
+    rng = np.random.default_rng(L + Hq)
+    host = filled(rng, L, H, d, qb, 3, cap=(L + 64 + 7) // 8 * 8)
+    st = upload(host)
+    assert kv.decode_kernel_kind(st.view(), Hq) == 2
+    q16 = ko.normal_f16(rng, (Hq, d))
+    gate = rng.standard_normal((Hq, d)).astype(np.float32)
+    ref, ref_g = host.decode_ref(q16.astype(np.float32), d ** -0.5, L, gate)
+    generic, _ = gpu_decode(st, to_dev(q16), Hq, d ** -0.5, L, gate=to_dev(gate), num_splits=kv.FORCE_GENERIC)
+    for splits in (0, 1, 3, 37):
+        for q_dev in (to_dev(q16), to_dev(q16.astype(np.float32))):
+            out, gated = gpu_decode(st, q_dev, Hq, d ** -0.5, L, gate=to_dev(gate), num_splits=splits)
+            assert_attention_close(out, ref, f"decode d=256 tcgen05 H={H}/{Hq} qb={qb} L={L} splits={splits}")
+            assert_attention_close(gated, ref_g, "decode d=256 tcgen05 gated")
+            assert np.linalg.norm(out - generic) <= 5e-4 * np.linalg.norm(generic)   # same sums, 16-bit fixed-point weights per tile
+    # the length from a device-side state, and replay determinism
+    state = kv.make_decode_state(L - 1)
+    a, _ = gpu_decode(st, to_dev(q16), Hq, d ** -0.5, 0, decode_state=state)
+    assert_attention_close(a, ref, "decode d=256 tcgen05, device-side length")
+    b, _ = gpu_decode(st, to_dev(q16), Hq, d ** -0.5, 0, decode_state=state)
+    assert np.array_equal(a, b)

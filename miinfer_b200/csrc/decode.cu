@@ -116,6 +116,9 @@ __global__ void __launch_bounds__(32) decode_generic_kernel(const __grid_constan
 // ---------------------------------------------------------------------------
 __global__ void merge_kernel(const __grid_constant__ MergeParams p) {
     extern __shared__ float sh[];   // a[num_parts], then gmax, gsum
+    // the next kernel of the stream (the next layer's stage 1) may become resident; this one waits for its partials
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t head = blockIdx.x, group = blockIdx.y, dim = threadIdx.x;
     const uint32_t H = p.query_heads, D = p.head_dim, S = p.num_parts;
     const size_t base = static_cast<size_t>(group) * S * H + head;
@@ -192,8 +195,7 @@ __global__ void merge_kernel(const __grid_constant__ MergeParams p) {
 
 int launch_merge(const MergeParams& p, uint32_t groups, cudaStream_t stream) {
     if (p.num_parts > 4096) return B200KV_ERR_UNSUPPORTED;
-    merge_kernel<<<dim3(p.query_heads, groups), p.head_dim, (2 * p.num_parts + 2) * sizeof(float), stream>>>(p);
-    B200KV_CUDA_TRY(cudaGetLastError());
+    B200KV_CUDA_TRY(launch_kernel(merge_kernel, dim3(p.query_heads, groups), dim3(p.head_dim), (2 * p.num_parts + 2) * sizeof(float), stream, true, p));
     return B200KV_OK;
 }
 

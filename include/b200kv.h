@@ -135,11 +135,12 @@ B200KV_API int b200kv_device_check(int device);
 
 /* Launch overlap (off by default; process-wide; no counterpart in the reference,
  * which replays a HIP graph of fully serialised kernels, src/prefill_v2/model.cpp:1136-1197).
- * With tail_positions > 0 the append and streaming decode kernels are launched
- * with programmatic stream serialization: a kernel may become resident and
- * start streaming OLD cache rows while the previous kernel of the stream is
- * still finishing -- this hides launch ramp and tail between the layers of a
- * decode step.  The kernels order themselves: everything a preceding kernel may
+ * With tail_positions > 0 the append, streaming decode, merge and prefill
+ * kernels are launched with programmatic stream serialization: a kernel may
+ * become resident, set itself up and (decode) start streaming OLD cache rows
+ * while the previous kernel of the stream is still finishing -- this hides
+ * launch ramp and tail between the layers of a decode step and between the
+ * kernels of a prefill chunk.  The kernels order themselves: everything a preceding kernel may
  * produce -- Q, gate, the workspace, outputs, and the last `tail_positions`
  * rows of the scanned cache range -- is only touched after that kernel has
  * completed (griddepcontrol.wait).  Set tail_positions >= the number of rows

@@ -168,8 +168,9 @@ B200KV_API int b200kv_workspace_reset(void* workspace, size_t workspace_bytes, v
  * tile seen, tile loop over, last sums folded, partial written, merge done (0 where a CTA has no such step).  Launches
  * whose grid does not fit the buffer are not traced. */
 B200KV_API int b200kv_set_timeline_buffer(uint64_t* device_words, uint32_t capacity_words);
-/* Which streaming kernel serves int8 caches (process-wide; for A/B measurement and tests): 0 = the tcgen05 kernel
- * where it applies (default), 1 = the warp-level mma kernel everywhere.  No counterpart in the reference. */
+/* Which streaming kernel serves int8 caches (process-wide; for A/B measurement and tests): 0 = the tcgen05 kernels
+ * where they apply (default), 1 = none of them: the warp-level mma kernel at head_dim 128, the generic kernel at
+ * head_dim 256.  No counterpart in the reference. */
 B200KV_API int b200kv_set_decode_kernel(int choice);
 
 /* ---- cache storage ---------------------------------------------------------

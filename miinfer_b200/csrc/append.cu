@@ -5,26 +5,24 @@
 // Behaviour follows MIInfer's store kernel
 // (gfx906/kernels/qwen3_primitives.hip:7213-7326): same operation order, same
 // quantizer, positions optionally read from device-resident state.  The mapping
-// is new: the unit of work is one PASS of one token -- 16 q8_0 blocks, K and V of two kv
-// heads at head_dim 128 or of one at 256 -- and every warp of a grid sized to the device
-// takes one contiguous run of units.  Within a row lane L holds elements L, L+32, L+64, ... so
-//   - a q8_0 block (32 consecutive dims) is one register index across the warp
-//     and its amax is one `redux.sync` on the bits of |x|;
-//   - both RoPE pairings (i, i+d/2) and (i, i+32) pair two registers of the SAME
-//     lane, so the rotation needs no exchange; the sines and cosines depend on the
-//     token only and are computed when a warp's run reaches a new token, not per head;
-//   - the reference's shared-memory binary tree for the sum of squares (stride
-//     d/2 .. 1) becomes register adds followed by a shuffle-down tree that adds
-//     exactly the same pairs in the same order (bit-identical sum);
-//   - the warp-uniform IEEE divisions (1/rms per head, amax/127 and its reciprocal
-//     per block) are spread over the lanes -- lane i does head i, then block i --
-//     and handed back through shared memory instead of being repeated by all 32 lanes.
-// Input rows are fetched with 16-byte loads, all of a pass in flight at once, and re-read
-// from a per-warp staging area in the lane-strided order; output rows are staged through
-// shared memory and written with 16-byte stores (whole 128/256-byte cache rows).
-// The row arithmetic is the same, operation for operation, as append_row.cuh's (used by the
-// decode kernel's fused single-token append and the query-side kernel): all three write
-// identical bits.
+// is new: the unit of work is one PASS of one token -- 16 K blocks and 16 V blocks of 32 dims, i.e. four kv heads
+// at head_dim 128, two at 256 -- and every warp of a grid sized to the device takes one contiguous run of units.
+//   - K rows: lane L holds elements L, L+32, L+64, ... so a q8_0 block is one register index across the warp (its
+//     maximum is one `redux.sync` on the bits of |x|), both RoPE pairings (i, i+d/2) and (i, i+32) pair two
+//     registers of the SAME lane, and the reference's shared-memory binary tree for the sum of squares (stride
+//     d/2 .. 1) becomes register adds followed by a shuffle-down tree that adds exactly the same pairs in the same
+//     order (bit-identical sum).  Elements are read and written one by one: every access of the warp is one
+//     contiguous run of 32 elements, so nothing is staged.
+//   - V rows, which are only quantised: lane L holds the 4 (8) consecutive elements 4L .. (8L ..), one vector load and
+//     one vector store per row; a block is 8 (4) neighbouring lanes and its maximum takes 3 (2) shuffles.
+//   - the sines and cosines depend on the token only and are computed when a warp's run reaches a new token;
+//   - the warp-uniform IEEE divisions are spread over the lanes: lane h takes head h's 1/rms, lanes 0-15 the K
+//     blocks' amax/127 and reciprocal, lanes 16-31 the V blocks'; the results come back by shuffle.
+// (Earlier layouts -- a warp per row pair with every division repeated by all lanes; all rows lane-strided through
+// shared-memory staging rows -- ran at 0.11 and 0.33 of the HBM rate on 8192-token chunks; this one at 0.37.  Fetching a
+// unit's rows one unit ahead of the arithmetic measured slower: 34 us against 21.5.)
+// The row arithmetic is the same, operation for operation, as append_row.cuh's (used by the decode kernel's fused
+// single-token append and the query-side kernel): all three write identical bits.
 #include "append_row.cuh"
 
 #include <algorithm>
@@ -49,6 +47,7 @@ struct AppendParams {
 };
 
 constexpr int kAppendWarps = 2;
+constexpr int kAppendCtasPerSm = 8;    // 128 registers per thread: a pass keeps 32 row values per lane (10, 12 and 16 CTAs spill and measured slower)
 
 __device__ __forceinline__ int quantize_s8(float v) {
     // round to nearest even and saturate to [-128, 127] (NaN -> 0): __float2int_rn followed by the clamp, in one step
@@ -56,25 +55,19 @@ __device__ __forceinline__ int quantize_s8(float v) {
     asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(v));
     return q;
 }
+// max over the warp of non-negative floats (NaN counts as 0, as with fmaxf): one redux on the bit patterns
+__device__ __forceinline__ float warp_amax(float a) {
+    return __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fmaxf(a, 0.0f))));
+}
 
-template <int ITEMS> struct AppendTuning;
-template <> struct AppendTuning<16> { static constexpr int kCtasPerSm = 16; };
-template <> struct AppendTuning<32> { static constexpr int kCtasPerSm = 12; };   // measured: equal on 8192-token chunks, slower on 512
-template <> struct AppendTuning<64> { static constexpr int kCtasPerSm = 8; };    // measured: 17 % slower on 8192-token chunks
-
-template <int D, bool IN_F16, int ITEMS>
-__global__ void __launch_bounds__(kAppendWarps * 32, AppendTuning<ITEMS>::kCtasPerSm)
+template <int D, bool IN_F16>
+__global__ void __launch_bounds__(kAppendWarps * 32, kAppendCtasPerSm)
 append_kernel(const __grid_constant__ AppendParams p, const bool vec) {
-    constexpr int NJ = D / 32;
-    constexpr int GH = ITEMS / (2 * NJ);        // kv heads per pass: K and V of GH heads make ITEMS q8_0 blocks
-    constexpr int kEsize = IN_F16 ? 2 : 4;
-    constexpr int kRowBytes = D * kEsize;
-    __shared__ __align__(16) uint8_t in_stage[kAppendWarps][2][GH * kRowBytes];   // [warp][K | V][head][D]
-    __shared__ __align__(16) int8_t out_stage[kAppendWarps][2][GH * D];
-    __shared__ __align__(16) float amax_s[kAppendWarps][ITEMS];
-    __shared__ __align__(16) float inv_s[kAppendWarps][ITEMS];
-    __shared__ float norm_s[kAppendWarps][GH];
+    constexpr int NJ = D / 32;                  // q8_0 blocks per row = K registers per lane
+    constexpr int HB = 16 / NJ;                 // kv heads per pass: 16 K blocks + 16 V blocks, one scale per lane
+    constexpr int GS = 32 / NJ;                 // lanes that share one V block (each holds NJ consecutive elements of it)
     __shared__ float freq_s[D / 2];
+    __shared__ float kmax_s[kAppendWarps][16];
     // Let the next kernel of the stream become resident now (it orders itself against this one), then wait
     // for everything before us: K/V inputs and the device-side position come from preceding kernels.
     pdl_launch_dependents();
@@ -111,67 +104,74 @@ append_kernel(const __grid_constant__ AppendParams p, const bool vec) {
     }
     float sn[NJ / 2], cs[NJ / 2];   // what depends on the token alone: the rotation of every pair this lane holds
 
-    // One pass: K and V of kv heads g0 .. g0 + hn - 1 of one token.  FAST: a full pass (hn == GH) of an int8/int8
-    // cache with q8_0 blocks -- every check below is decided at compile time.
+    // One pass: K and V of kv heads g0 .. g0 + hn - 1 of one token.
+    //   K rows: lane L holds elements L, L+32, ... (a block = one register index across the warp), fetched and stored
+    //           element by element -- every access of the warp is one contiguous run of 32 elements;
+    //   V rows: lane L holds the NJ consecutive elements NJ*L ..  (a block = GS neighbouring lanes), one vector load and
+    //           one vector store per row.
+    // FAST: a full pass (hn == HB) of an int8/int8 cache with q8_0 blocks -- every check below is decided at compile time.
     auto pass = [&](auto fast_c, uint32_t token, uint32_t g0, uint64_t position, int hn) {
         constexpr bool FAST = decltype(fast_c)::value;
-        if constexpr (FAST) hn = GH;
+        if constexpr (FAST) hn = HB;
         const bool kq = FAST || k_q8, vq = FAST || v_q8, rows = !FAST && row_scale;
         const uint64_t row0 = g0 * capacity + position;   // cache row of the pass's first head; the next head is `capacity` rows on
-        // ---- the pass's K and V rows (contiguous in the [token][kv_heads * D] inputs) into the staging area
-        {
-            const size_t in_off = (static_cast<size_t>(token) * H + g0) * kRowBytes;
-            const uint8_t* ksrc = static_cast<const uint8_t*>(p.key) + in_off;
-            const uint8_t* vsrc = static_cast<const uint8_t*>(p.value) + in_off;
-            const int bytes = hn * kRowBytes;
-            if (vec) {
-                constexpr int kIters = (GH * kRowBytes + 511) / 512;
-                constexpr bool kExact = kIters * 512 == GH * kRowBytes;
+        const size_t in0 = (static_cast<size_t>(token) * H + g0) * D;
+        float kx[HB][NJ], vx[HB][NJ];
 #pragma unroll
-                for (int side = 0; side < 2; ++side) {
-                    const uint8_t* src = side == 0 ? ksrc : vsrc;
-                    uint4 reg[kIters];
+        for (int h = 0; h < HB; ++h) {
+            if (!FAST && h >= hn) break;
+            const size_t in_h = in0 + static_cast<size_t>(h) * D;
+            if (IN_F16) {
+                const __half* ksrc = static_cast<const __half*>(p.key) + in_h;
+                const __half* vsrc = static_cast<const __half*>(p.value) + in_h + NJ * lane;
 #pragma unroll
-                    for (int it = 0; it < kIters; ++it) {
-                        const int off = it * 512 + lane * 16;
-                        if ((FAST && kExact) || off < bytes) reg[it] = *reinterpret_cast<const uint4*>(src + off);
+                for (int j = 0; j < NJ; ++j) kx[h][j] = __half2float(ksrc[lane + 32 * j]);
+                if (vec) {
+                    if constexpr (NJ == 4) {
+                        const uint2 raw = *reinterpret_cast<const uint2*>(vsrc);
+                        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                        vx[h][0] = a.x; vx[h][1] = a.y; vx[h][2] = b.x; vx[h][3] = b.y;
+                    } else {
+                        const uint4 raw = *reinterpret_cast<const uint4*>(vsrc);
+                        const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u[i]));
+                            vx[h][2 * i] = a.x; vx[h][2 * i + 1] = a.y;
+                        }
                     }
+                } else {
 #pragma unroll
-                    for (int it = 0; it < kIters; ++it) {
-                        const int off = it * 512 + lane * 16;
-                        if ((FAST && kExact) || off < bytes) *reinterpret_cast<uint4*>(&in_stage[warp][side][off]) = reg[it];
-                    }
+                    for (int j = 0; j < NJ; ++j) vx[h][j] = __half2float(vsrc[j]);
                 }
-            } else {   // inputs that are not 16-byte aligned: element by element
-                using elem_t = typename std::conditional<IN_F16, uint16_t, uint32_t>::type;
-                for (int i = lane; i < hn * D; i += 32) {
-                    reinterpret_cast<elem_t*>(in_stage[warp][0])[i] = reinterpret_cast<const elem_t*>(ksrc)[i];
-                    reinterpret_cast<elem_t*>(in_stage[warp][1])[i] = reinterpret_cast<const elem_t*>(vsrc)[i];
+            } else {
+                const float* ksrc = static_cast<const float*>(p.key) + in_h;
+                const float* vsrc = static_cast<const float*>(p.value) + in_h + NJ * lane;
+#pragma unroll
+                for (int j = 0; j < NJ; ++j) kx[h][j] = ksrc[lane + 32 * j];
+                if (vec) {
+#pragma unroll
+                    for (int i = 0; i < NJ / 4; ++i) {
+                        const float4 a = *reinterpret_cast<const float4*>(vsrc + 4 * i);
+                        vx[h][4 * i] = a.x; vx[h][4 * i + 1] = a.y; vx[h][4 * i + 2] = a.z; vx[h][4 * i + 3] = a.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < NJ; ++j) vx[h][j] = vsrc[j];
                 }
             }
-            __syncwarp();
-        }
-        float x[GH][2][NJ];
-#pragma unroll
-        for (int h = 0; h < GH; ++h) {
-            if (!FAST && h >= hn) break;
-#pragma unroll
-            for (int s = 0; s < 2; ++s)
-#pragma unroll
-                for (int j = 0; j < NJ; ++j) {
-                    if (IN_F16) x[h][s][j] = __half2float(reinterpret_cast<const __half*>(in_stage[warp][s])[h * D + lane + 32 * j]);
-                    else x[h][s][j] = reinterpret_cast<const float*>(in_stage[warp][s])[h * D + lane + 32 * j];
-                }
         }
 
-        // ---- K: RMSNorm * weight
+        // ---- K: RMSNorm * weight.  The reference's shared-memory tree (stride D/2 .. 1): register adds, then a shuffle-down
+        //      tree over the same pairs; lane h then takes head h's IEEE division and square root ----
         if (have_norm) {
+            float ss_mine = 0.0f;
 #pragma unroll
-            for (int h = 0; h < GH; ++h) {
+            for (int h = 0; h < HB; ++h) {
                 if (!FAST && h >= hn) break;
                 float sq[NJ];
 #pragma unroll
-                for (int j = 0; j < NJ; ++j) sq[j] = __fmul_rn(x[h][0][j], x[h][0][j]);
+                for (int j = 0; j < NJ; ++j) sq[j] = __fmul_rn(kx[h][j], kx[h][j]);
 #pragma unroll
                 for (int half = NJ / 2; half >= 1; half >>= 1)
 #pragma unroll
@@ -179,145 +179,125 @@ append_kernel(const __grid_constant__ AppendParams p, const bool vec) {
                 float ss = sq[0];
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, o));
-                if (lane == 0) norm_s[warp][h] = ss;
+                ss = __shfl_sync(0xffffffffu, ss, 0);
+                if (lane == h) ss_mine = ss;
             }
-            __syncwarp();
-            if (lane < hn)
-                norm_s[warp][lane] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(norm_s[warp][lane], static_cast<float>(D)), p.epsilon)));
-            __syncwarp();
+            const float r_mine = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss_mine, static_cast<float>(D)), p.epsilon)));
 #pragma unroll
-            for (int h = 0; h < GH; ++h) {
+            for (int h = 0; h < HB; ++h) {
                 if (!FAST && h >= hn) break;
-                const float r = norm_s[warp][h];
+                const float r = __shfl_sync(0xffffffffu, r_mine, h);
 #pragma unroll
-                for (int j = 0; j < NJ; ++j) x[h][0][j] = __fmul_rn(__fmul_rn(x[h][0][j], r), w[j]);
+                for (int j = 0; j < NJ; ++j) kx[h][j] = __fmul_rn(__fmul_rn(kx[h][j], r), w[j]);
             }
         }
         // ---- K: RoPE
         if (rope_mode == B200KV_ROPE_NEOX_FULL) {
 #pragma unroll
-            for (int h = 0; h < GH; ++h) {
+            for (int h = 0; h < HB; ++h) {
                 if (!FAST && h >= hn) break;
 #pragma unroll
                 for (int j = 0; j < NJ / 2; ++j) {
-                    const float x0 = x[h][0][j], x1 = x[h][0][j + NJ / 2];
-                    x[h][0][j] = __fsub_rn(__fmul_rn(x0, cs[j]), __fmul_rn(x1, sn[j]));
-                    x[h][0][j + NJ / 2] = __fadd_rn(__fmul_rn(x0, sn[j]), __fmul_rn(x1, cs[j]));
+                    const float x0 = kx[h][j], x1 = kx[h][j + NJ / 2];
+                    kx[h][j] = __fsub_rn(__fmul_rn(x0, cs[j]), __fmul_rn(x1, sn[j]));
+                    kx[h][j + NJ / 2] = __fadd_rn(__fmul_rn(x0, sn[j]), __fmul_rn(x1, cs[j]));
                 }
             }
         } else if (rope_mode == B200KV_ROPE_SECTIONED64) {
 #pragma unroll
-            for (int h = 0; h < GH; ++h) {
+            for (int h = 0; h < HB; ++h) {
                 if (!FAST && h >= hn) break;
-                const float x0 = x[h][0][0], x1 = x[h][0][1];
-                x[h][0][0] = __fsub_rn(__fmul_rn(x0, cs[0]), __fmul_rn(x1, sn[0]));
-                x[h][0][1] = __fadd_rn(__fmul_rn(x0, sn[0]), __fmul_rn(x1, cs[0]));
+                const float x0 = kx[h][0], x1 = kx[h][1];
+                kx[h][0] = __fsub_rn(__fmul_rn(x0, cs[0]), __fmul_rn(x1, sn[0]));
+                kx[h][1] = __fadd_rn(__fmul_rn(x0, sn[0]), __fmul_rn(x1, cs[0]));
             }
         }
 
-        // ---- block maxima (NaN counts as 0, as with fmaxf), one shared-memory word per block; every lane holds
-        //      the reduced value, so the store needs no predicate
+        // ---- block maxima.  K: one redux per block, the 16 results through shared memory to lanes 0-15 (lane = HB... NJ*h + j).
+        //      V: a block's GS lanes reduce among themselves; lane 16 + NJ*h + j fetches the result from the block's first lane.
+        //      With one scale per row (rows): lanes h and 16 + h. ----
+        float amax_mine = 0.0f;
 #pragma unroll
-        for (int h = 0; h < GH; ++h) {
+        for (int h = 0; h < HB; ++h) {
             if (!FAST && h >= hn) break;
+            if (rows) {
+                float a = 0.0f, b = 0.0f;
 #pragma unroll
-            for (int s = 0; s < 2; ++s) {
-                if (rows) {
-                    float a = 0.0f;
+                for (int j = 0; j < NJ; ++j) { a = fmaxf(a, fabsf(kx[h][j])); b = fmaxf(b, fabsf(vx[h][j])); }
+                a = warp_amax(a); b = warp_amax(b);
+                if (lane == h) amax_mine = a;
+                if (lane == 16 + h) amax_mine = b;
+            } else {
 #pragma unroll
-                    for (int j = 0; j < NJ; ++j) a = fmaxf(a, fabsf(x[h][s][j]));
-                    amax_s[warp][h * 2 + s] = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(a)));
-                } else {
+                for (int j = 0; j < NJ; ++j) kmax_s[warp][NJ * h + j] = warp_amax(fabsf(kx[h][j]));   // every lane holds the value: no predicate
+                float b = 0.0f;
 #pragma unroll
-                    for (int j = 0; j < NJ; ++j)
-                        amax_s[warp][(h * 2 + s) * NJ + j] =
-                            __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fmaxf(fabsf(x[h][s][j]), 0.0f))));
-                }
+                for (int j = 0; j < NJ; ++j) b = fmaxf(b, fabsf(vx[h][j]));
+#pragma unroll
+                for (int o = GS / 2; o > 0; o >>= 1) b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, o));
+                const float got = __shfl_sync(0xffffffffu, b, (lane & (NJ - 1)) * GS);   // block j = lane % NJ of head h
+                if ((lane >> 4) == 1 && ((lane & 15) / NJ) == h) amax_mine = got;
             }
         }
-        __syncwarp();
-        // ---- scales: lane i takes block i (and i + 32): amax / 127, its reciprocal, the fp16 scale to the cache
+        if (!rows) {
+            __syncwarp();
+            if (lane < 16) amax_mine = kmax_s[warp][lane];
+            __syncwarp();   // the next pass overwrites the words
+        }
+        // ---- scales: amax / 127, its reciprocal, the fp16 scale to the cache -- one block per lane
+        const float scale_mine = (amax_mine > 0.0f) ? __fdiv_rn(amax_mine, 127.0f) : 1.0f;
+        const float inv_mine = (scale_mine > 0.0f) ? __fdiv_rn(1.0f, scale_mine) : 1.0f;
         {
-            const int shift = rows ? 0 : (NJ == 4 ? 2 : 3);   // log2(blocks per row)
-            const int items = (hn * 2) << shift;
-#pragma unroll
-            for (int it = 0; it < (ITEMS + 31) / 32; ++it) {
-                const int item = lane + 32 * it;
-                if (item < items) {
-                    const float amax = amax_s[warp][item];
-                    const float scale = (amax > 0.0f) ? __fdiv_rn(amax, 127.0f) : 1.0f;
-                    inv_s[warp][item] = (scale > 0.0f) ? __fdiv_rn(1.0f, scale) : 1.0f;
-                    const int hs = item >> shift, j = item - (hs << shift);
-                    const int h = hs >> 1, s = hs & 1;
-                    if (s == 0 ? kq : vq) {
-                        __half* plane = static_cast<__half*>(s == 0 ? p.view.key_scales : p.view.value_scales);
-                        plane[((row0 + h * capacity) << shift) + j] = __float2half_rn(scale);
-                    }
-                }
+            const int side = lane >> 4, idx = lane & 15;
+            const int h = rows ? idx : idx / NJ, j = rows ? 0 : idx % NJ;
+            const bool mine = rows ? idx < hn : h < hn;
+            if (mine && (side == 0 ? kq : vq)) {
+                __half* plane = static_cast<__half*>(side == 0 ? p.view.key_scales : p.view.value_scales);
+                const uint64_t r = row0 + static_cast<uint64_t>(h) * capacity;
+                plane[rows ? r : r * NJ + j] = __float2half_rn(scale_mine);
             }
         }
-        __syncwarp();
-        // ---- quantise into the output staging rows
+        // ---- quantise and store
 #pragma unroll
-        for (int h = 0; h < GH; ++h) {
+        for (int h = 0; h < HB; ++h) {
             if (!FAST && h >= hn) break;
+            const uint64_t r = row0 + static_cast<uint64_t>(h) * capacity;
+            if (kq) {
+                int8_t* dst = p.view.key_q8 + r * D + lane;
 #pragma unroll
-            for (int s = 0; s < 2; ++s) {
-                if (!(s == 0 ? kq : vq)) continue;
-                float inv[NJ];
-                if (rows) {
-                    const float one = inv_s[warp][h * 2 + s];
-#pragma unroll
-                    for (int j = 0; j < NJ; ++j) inv[j] = one;
-                } else {
-#pragma unroll
-                    for (int j4 = 0; j4 < NJ / 4; ++j4) {
-                        const float4 f = *reinterpret_cast<const float4*>(&inv_s[warp][(h * 2 + s) * NJ + 4 * j4]);
-                        inv[4 * j4] = f.x; inv[4 * j4 + 1] = f.y; inv[4 * j4 + 2] = f.z; inv[4 * j4 + 3] = f.w;
-                    }
+                for (int j = 0; j < NJ; ++j) {
+                    const float inv = __shfl_sync(0xffffffffu, inv_mine, rows ? h : NJ * h + j);
+                    dst[32 * j] = static_cast<int8_t>(quantize_s8(__fmul_rn(kx[h][j], inv)));
                 }
+            } else {
+                __half* dst = static_cast<__half*>(p.view.key_f16) + r * D + lane;
 #pragma unroll
-                for (int j = 0; j < NJ; ++j)
-                    out_stage[warp][s][h * D + lane + 32 * j] = static_cast<int8_t>(quantize_s8(__fmul_rn(x[h][s][j], inv[j])));
+                for (int j = 0; j < NJ; ++j) dst[32 * j] = __float2half_rn(kx[h][j]);
+            }
+            if (vq) {
+                const float inv = __shfl_sync(0xffffffffu, inv_mine, 16 + (rows ? h : NJ * h + lane / GS));
+                uint32_t packed[NJ / 4];
+#pragma unroll
+                for (int i = 0; i < NJ / 4; ++i) {
+                    const uint32_t b0 = quantize_s8(__fmul_rn(vx[h][4 * i], inv)) & 0xff, b1 = quantize_s8(__fmul_rn(vx[h][4 * i + 1], inv)) & 0xff;
+                    const uint32_t b2 = quantize_s8(__fmul_rn(vx[h][4 * i + 2], inv)) & 0xff, b3 = quantize_s8(__fmul_rn(vx[h][4 * i + 3], inv)) & 0xff;
+                    packed[i] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+                }
+                int8_t* dst = p.view.value_q8 + r * D + NJ * lane;
+                if constexpr (NJ == 4) *reinterpret_cast<uint32_t*>(dst) = packed[0];
+                else *reinterpret_cast<uint2*>(dst) = make_uint2(packed[0], packed[1]);
+            } else {
+                __half* dst = static_cast<__half*>(p.view.value_f16) + r * D + NJ * lane;
+#pragma unroll
+                for (int j = 0; j < NJ; j += 2) *reinterpret_cast<__half2*>(dst + j) = __floats2half2_rn(vx[h][j], vx[h][j + 1]);
             }
         }
-        __syncwarp();
-        // ---- cache rows out: 16 bytes per lane, 32 / (D/16) rows per store instruction
-        {
-            constexpr int kLanesPerRow = D / 16;
-            constexpr int kRowsPerStore = 32 / kLanesPerRow;
-            const int sub = lane / kLanesPerRow, chunk = lane % kLanesPerRow;
-#pragma unroll
-            for (int r0 = 0; r0 < 2 * GH; r0 += kRowsPerStore) {
-                const int rr = r0 + sub, s = rr / GH, h = rr % GH;
-                if ((FAST || h < hn) && (s == 0 ? kq : vq)) {
-                    int8_t* plane = s == 0 ? p.view.key_q8 : p.view.value_q8;
-                    *reinterpret_cast<uint4*>(plane + (row0 + h * capacity) * D + chunk * 16) =
-                        *reinterpret_cast<const uint4*>(&out_stage[warp][s][h * D + chunk * 16]);
-                }
-            }
-        }
-        // ---- sides kept in fp16: straight from the registers
-        if (!FAST && (!k_q8 || !v_q8)) {
-#pragma unroll
-            for (int h = 0; h < GH; ++h) {
-                if (h >= hn) break;
-#pragma unroll
-                for (int s = 0; s < 2; ++s) {
-                    if (s == 0 ? k_q8 : v_q8) continue;
-                    __half* dst = static_cast<__half*>(s == 0 ? p.view.key_f16 : p.view.value_f16) + (row0 + h * capacity) * D;
-#pragma unroll
-                    for (int j = 0; j < NJ; ++j) dst[lane + 32 * j] = __float2half_rn(x[h][s][j]);
-                }
-            }
-        }
-        __syncwarp();   // the staging areas are reused by the next pass
     };
 
     // The unit of work is one pass of one token; every warp of the grid takes one contiguous run of units, so a
     // large launch spreads evenly over the resident warps (and a warp meets few tokens), while a small one
     // spreads the passes of a token over several warps.  (32-bit arithmetic: the host keeps units below 2^32.)
-    const uint32_t passes = (H + GH - 1) / GH;
+    const uint32_t passes = (H + HB - 1) / HB;
     const uint32_t total_units = token_count * passes;
     const uint32_t warps = gridDim.x * kAppendWarps;
     const uint32_t per_warp = (total_units + warps - 1) / warps;
@@ -342,9 +322,9 @@ append_kernel(const __grid_constant__ AppendParams p, const bool vec) {
                     sincos_pinned(angle, &sn[0], &cs[0]);
                 }
             }
-            const uint32_t g0 = pass_index * GH;
-            const int hn = static_cast<int>(min(static_cast<uint32_t>(GH), H - g0));
-            if (fast_cache && hn == GH) pass(std::true_type{}, token, g0, position, hn);
+            const uint32_t g0 = pass_index * HB;
+            const int hn = static_cast<int>(min(static_cast<uint32_t>(HB), H - g0));
+            if (fast_cache && hn == HB) pass(std::true_type{}, token, g0, position, hn);
             else pass(std::false_type{}, token, g0, position, hn);
         }
         if (++pass_index == passes) {
@@ -396,24 +376,23 @@ extern "C" int b200kv_append(const b200kv_view* view, const void* key, const voi
         p.sectioned_step = std::pow(theta, -2.0f / 64.0f);
     }
 
-    constexpr int kItems = 16;   // q8_0 blocks per pass: K and V of 2 kv heads at head_dim 128, of 1 at 256 (32 and 64 measured slower)
     const uint32_t d = view->head_dim;
-    const uint32_t heads_per_pass = kItems * 16 / d;
+    const uint32_t heads_per_pass = 512 / d;   // 16 K blocks and 16 V blocks of 32 dims per pass
     const uint64_t units = static_cast<uint64_t>(token_count) * ((view->kv_heads + heads_per_pass - 1) / heads_per_pass);
     if (units >= (1ull << 32)) return B200KV_ERR_RANGE;
     int device = 0, sms = 0;
     B200KV_CUDA_TRY(cudaGetDevice(&device));
     B200KV_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-    const uint64_t resident = static_cast<uint64_t>(sms) * AppendTuning<kItems>::kCtasPerSm;
+    const uint64_t resident = static_cast<uint64_t>(sms) * kAppendCtasPerSm;
     const unsigned grid = static_cast<unsigned>(std::min<uint64_t>((units + kAppendWarps - 1) / kAppendWarps, resident));
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool f16 = (dtype == B200KV_F16);
-    const bool vec = ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) & 15u) == 0;   // 16-byte loads need aligned inputs
+    const bool vec = (reinterpret_cast<uintptr_t>(value) & 15u) == 0;   // vector loads of the V rows need an aligned input
     const dim3 block(kAppendWarps * 32);
     cudaError_t err;
     auto launch = [&](auto kernel) { return launch_kernel(kernel, grid, block, 0, s, true, p, vec); };
-    if (d == 128) err = f16 ? launch(append_kernel<128, true, kItems>) : launch(append_kernel<128, false, kItems>);
-    else err = f16 ? launch(append_kernel<256, true, kItems>) : launch(append_kernel<256, false, kItems>);
+    if (d == 128) err = f16 ? launch(append_kernel<128, true>) : launch(append_kernel<128, false>);
+    else err = f16 ? launch(append_kernel<256, true>) : launch(append_kernel<256, false>);
     B200KV_CUDA_TRY(err);
     return B200KV_OK;
 }

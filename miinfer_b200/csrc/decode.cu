@@ -148,15 +148,22 @@ __global__ void merge_kernel(const __grid_constant__ MergeParams p) {
     const float gmax = sh[2 * S], gsum = sh[2 * S + 1];
     const float* accp = p.part_acc + base * D + dim;
     const size_t stride = p.part_stride ? p.part_stride : static_cast<size_t>(H) * D;
-    float t0 = 0.0f, t1 = 0.0f, t2 = 0.0f, t3 = 0.0f;
-    uint32_t s = 0;
-    for (; s + 4 <= S; s += 4) {
-        const float a0 = accp[(s + 0) * stride], a1 = accp[(s + 1) * stride];
-        const float a2 = accp[(s + 2) * stride], a3 = accp[(s + 3) * stride];
-        t0 = fmaf(a0, sa[s], t0); t1 = fmaf(a1, sa[s + 1], t1); t2 = fmaf(a2, sa[s + 2], t2); t3 = fmaf(a3, sa[s + 3], t3);
+    // four running sums (part s goes to sum s % 4, a tail of S % 4 parts to sum 0); the loads are issued sixteen at a time so
+    // that a launch with a few dozen parts needs two or three trips to L2, not one per four parts
+    float t[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const uint32_t S4 = S & ~3u;
+    for (uint32_t s0 = 0; s0 < S; s0 += 16) {
+        float a[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) a[i] = (s0 + i < S) ? accp[(s0 + i) * stride] : 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t s = s0 + i;
+            if (s < S4) t[i & 3] = fmaf(a[i], sa[s], t[i & 3]);
+            else if (s < S) t[0] = fmaf(a[i], sa[s], t[0]);
+        }
     }
-    for (; s < S; ++s) t0 = fmaf(accp[s * stride], sa[s], t0);
-    const float total = (t0 + t1) + (t2 + t3);
+    const float total = (t[0] + t[1]) + (t[2] + t[3]);
     const size_t out_idx = (static_cast<size_t>(group) * H + head) * D + dim;
     if (p.out_m != nullptr) {
         p.out_acc[out_idx] = total;

@@ -98,6 +98,7 @@ struct DecodeParams {
     float sectioned_step;
     float inv_freq[64];                      // NeoX frequencies for d = 128
     uint32_t overlap_tail;                   // launch overlap: the last n positions of the range are read only after pdl_wait
+    uint32_t head_fastest;                   // tcgen05 kernel: grid is (kv heads, splits, sessions) instead of (splits, kv heads, sessions)
     uint64_t* ws_tagged;
     uint32_t tag;                            // tag of this launch's words in ws_tagged (never 0; differs from the previous launch's)
     uint32_t* status;                        // device word that collects B200KV_STATUS_* bits of waits that ran out, or null

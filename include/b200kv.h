@@ -413,7 +413,7 @@ B200KV_API size_t b200kv_prefill_workspace_bytes(uint32_t token_count, uint32_t 
 B200KV_API size_t b200kv_prefill_scratch_bytes(uint64_t rows, uint32_t kv_heads, uint32_t head_dim);
 /* Optional extra room behind that scratch (workspace_bytes >= scratch + this): when a chunk has too few query rows
  * to give every SM a row tile (512 tokens x 6 heads per kv head = 96 tiles on 148 SMs), the tcgen05 kernel then also
- * splits the KV range of each tile over up to 4 CTAs, which leave unnormalised partials here for a merge kernel.
+ * splits the KV range of each tile over up to 8 CTAs, which leave unnormalised partials here for a merge kernel.
  * 50 MB for 512 tokens x 24 heads x d=256.  Without it the launch runs unsplit. */
 B200KV_API size_t b200kv_prefill_split_bytes(uint32_t token_count, uint32_t query_heads, uint32_t kv_heads, uint32_t head_dim);
 

@@ -35,7 +35,7 @@ size_t b200kv_prefill_scratch_bytes(uint64_t rows, uint32_t kv_heads, uint32_t h
 }
 
 size_t b200kv_prefill_split_bytes(uint32_t token_count, uint32_t query_heads, uint32_t kv_heads, uint32_t head_dim) {
-    return prefill_tc5_split_bytes(token_count, query_heads, kv_heads, head_dim, 4) + 2048;   // up to 4 splits, alignment slack
+    return prefill_tc5_split_bytes(token_count, query_heads, kv_heads, head_dim, 8) + 2048;   // up to 8 splits, alignment slack
 }
 
 int b200kv_prefill_attn(const b200kv_view* view, const void* q, int q_dtype, const float* gate,

@@ -558,7 +558,7 @@ __global__ void __launch_bounds__(256) prefill_merge_kernel(const __grid_constan
     const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= static_cast<size_t>(p.total_rows) * VPR) return;
     const uint32_t gr = static_cast<uint32_t>(idx / VPR), c = static_cast<uint32_t>(idx % VPR) * 4;
-    float m[4], l[4], M = -INFINITY;
+    float m[8], l[8], M = -INFINITY;   // kv_splits <= 8
     for (uint32_t s = 0; s < p.kv_splits; ++s) {
         const float2 ml = p.part_ml[(static_cast<size_t>(s) * p.kv_heads + kv_head) * p.rows_padded + gr];
         m[s] = ml.x; l[s] = ml.y;
@@ -700,7 +700,7 @@ size_t prefill_tc5_workspace_bytes(uint32_t rows, uint32_t kv_heads, uint32_t he
     return 2 * r * kv_heads * head_dim * sizeof(__half) + 1024;   // K and V planes, 1 KB to align the base
 }
 
-constexpr uint32_t kMaxKvSplits = 4;
+constexpr uint32_t kMaxKvSplits = 8;
 
 // Extra workspace that lets a launch split the KV range of every row tile over several CTAs (partials of `splits` splits).
 size_t prefill_tc5_split_bytes(uint32_t token_count, uint32_t query_heads, uint32_t kv_heads, uint32_t head_dim, uint32_t splits) {

@@ -204,7 +204,7 @@ def test_session_file_save_find_load_gives_identical_decode(cuda, tmp_path):
         kv.load_session(found[0], "qwen3-8b", "q4_0", too_small)
 
 
-@pytest.mark.parametrize("P,T,H,Hq,d", [(2048, 128, 4, 24, 256), (1500, 200, 8, 32, 128)])
+@pytest.mark.parametrize("P,T,H,Hq,d", [(2048, 128, 4, 24, 256), (1500, 200, 8, 32, 128), (4096, 512, 1, 6, 256)])   # the last one: 6 splits
 def test_suffix_attention_with_the_kv_range_split_over_ctas(cuda, P, T, H, Hq, d):
     """Few row tiles, long prefix: with room for partials in the workspace the tcgen05 launch splits every row
     tile's KV range over several CTAs and merges the partials; the result must match the unsplit launch and the oracle."""

@@ -3,7 +3,7 @@ decode attention at 32,768 and 131,072 positions (plain and fused with the appen
 8,192-token prefix on the tcgen05 kernel (with and without the KV split), the batched step over 64 seeded
 lengths plus 16 sessions restored from a 4,096-token clone, and sequence-sharded decode with 8 ranks of which
 7 are simulated (their partials are delivered beforehand; kernels that wait for each other are never launched
-on one device).  Every case asserts max-abs <= 2e-3 and a relative L2 gate, and prints both errors."""
+on one device), and decode attention at head_dim 256 with 24 query heads over 4 kv heads at both contexts.  Every case asserts max-abs <= 2e-3 and a relative L2 gate, and prints both errors."""
 import numpy as np
 import pytest
 import torch
@@ -153,3 +153,40 @@ def test_sequence_sharded_decode_with_8_ranks_7_of_them_simulated(cuda):
     torch.cuda.synchronize()
     assert_attention_close(out.cpu().numpy(), want, "sharded decode, 8 ranks (7 simulated), L=131072")
     assert int(own.abs().sum()) == 0      # consumed words are zero again
+
+
+@pytest.mark.parametrize("length", [32768, 131072])
+def test_decode_attention_head_dim_256_at_benchmark_context(cuda, length):
+    """The reference's own geometry (24 query heads over 4 kv heads, head_dim 256, q8_0 blocks) on the tcgen05 stage-1
+    kernel for head_dim 256, at the contexts the benchmark set names; also through the fused-step entry point, which for
+    this geometry is the store kernel followed by the attention."""
+    Hk, Hq, d = 4, 24, 256
+    rng = np.random.default_rng(length + d)
+    host = ko.HostCache(length + 64, Hk, d, 32, 3)
+    chunk = 16384
+    for base in range(0, length - 1, chunk):
+        n = min(chunk, length - 1 - base)
+        host.append(ko.normal_f16(rng, (n, Hk * d)).astype(np.float32), ko.normal_f16(rng, (n, Hk * d)).astype(np.float32), None, base, rope_mode=0)
+    st = upload(host)
+    assert kv.decode_kernel_kind(st.view(), Hq) == 2
+    ws = kv.decode_workspace(Hq, d)
+    q16 = ko.normal_f16(rng, (Hq, d))
+    gate = rng.standard_normal((Hq, d)).astype(np.float32)
+    ref, ref_g = host.decode_ref(q16.astype(np.float32), d ** -0.5, length - 1, gate)
+    out = torch.full((Hq, d), float("nan"), device="cuda"); gated = torch.full((Hq, d), float("nan"), device="cuda")
+    kv.launch_decode_attention_quant(st.view(), to_dev(q16), query_heads=Hq, scale=d ** -0.5, cache_length=length - 1,
+                                     output=out, gate=to_dev(gate), gated_output=gated, workspace=ws)
+    torch.cuda.synchronize()
+    assert_attention_close(out.cpu().numpy(), ref, f"decode_attn[d=256 tcgen05] L={length - 1}")
+    assert_attention_close(gated.cpu().numpy(), ref_g, f"decode_attn[d=256 tcgen05] gated L={length - 1}")
+    kn, vn = ko.normal_f16(rng, (1, Hk * d)), ko.normal_f16(rng, (1, Hk * d))
+    w = (1.0 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+    host.append(kn.astype(np.float32), vn.astype(np.float32), w, length - 1, rope_mode=2)
+    ref2, _ = host.decode_ref(q16.astype(np.float32), d ** -0.5, length)
+    state = kv.make_decode_state(length - 1)
+    out2 = torch.full((Hq, d), float("nan"), device="cuda")
+    kv.launch_decode_step(st.view(), to_dev(kn), to_dev(vn), to_dev(q16), query_heads=Hq, scale=d ** -0.5, decode_state=state,
+                          k_norm_weight=to_dev(w), rope_mode=kv.RopeMode.SECTIONED64, output=out2, workspace=ws)
+    torch.cuda.synchronize()
+    assert_planes_equal(st, host, "row appended by the step (head_dim 256)")
+    assert_attention_close(out2.cpu().numpy(), ref2, f"decode_step[d=256] L={length}")

@@ -57,13 +57,53 @@ def measured_peak_gbs() -> tuple[float, str]:
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi during the timed region."""
+    """Samples the SM clock and the throttle reasons of one GPU during the timed region: through NVML (read-only queries
+    from a thread, every 5 ms, so that a region of a few tens of milliseconds still gets samples), with nvidia-smi as
+    the fallback where the NVML binding is missing."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, index: int):
         self.proc = None
+        self.thread = None
+        self.sm, self.mx, self.reasons = [], 0.0, set()
+        try:
+            import threading
+
+            import pynvml
+
+            pynvml.nvmlInit()
+            handle = None
+            try:   # the CUDA ordinal is not NVML's index when CUDA_VISIBLE_DEVICES reorders: go by UUID
+                import torch
+
+                uuid = str(torch.cuda.get_device_properties(index).uuid)
+                handle = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+            except Exception:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.mx = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            self._halt = threading.Event()
+
+            def loop():
+                while not self._halt.is_set():
+                    try:
+                        self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                        bits = int(reasons_fn(handle))
+                        for bit, name in self.REASON_BITS.items():
+                            if bits & bit:
+                                self.reasons.add(name)
+                    except Exception:
+                        pass
+                    self._halt.wait(0.005)
+
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}",
                                           "--format=csv,noheader,nounits", "-lms", "25"],
@@ -72,6 +112,12 @@ class ClockSampler:
             pass
 
     def stop(self) -> dict:
+        if self.thread is not None:
+            self._halt.set()
+            self.thread.join(timeout=2)
+            sm = sorted(self.sm)
+            return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.mx or None, "reasons": sorted(self.reasons),
+                    "samples": len(sm), "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -93,7 +139,7 @@ class ClockSampler:
                     reasons.add(n)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "source": "nvidia-smi"}
 
 
 # ---------------------------------------------------------------------------------

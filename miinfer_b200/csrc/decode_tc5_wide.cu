@@ -4,12 +4,17 @@
 // widened to 8 blocks of 32 dims and up to 8 query heads per kv head.  Differences from the 128-dim kernel:
 //
 //  * a tile of 128 positions is two 128-byte-wide halves of every row (two tensor copies per operand, 64 KB per
-//    stage for K and V together), so the ring has 2 stages and one CTA (all 512 TMEM columns) lives on an SM;
+//    tile for K and V together); K tiles go through a ring of 2 stages that are free again as soon as their score MMAs
+//    have run, V tiles (with both scale tiles) through a ring of 3 that are held until the tile's P.V has run, each ring
+//    with its own producer thread; one CTA (all 512 TMEM columns) lives on an SM;
 //  * S^T = K . Q^T: 8 MMAs of N = 16 per tile (one per q8_0 block; Q's two int8 planes of up to 8 heads fill all 16
 //    rows of the operand), 128 TMEM columns per S buffer;
 //  * O^T += V^T . P per half of the dims (M = 128 each): P[position] holds, for each of the half's 4 blocks, 16 bytes
 //    (hi bytes of heads 0-7, lo bytes of heads 0-7) = two 32-byte swizzle spans = 64 B-operand columns; the thread of a
 //    dim keeps its own block's 16 columns of each half;
+//  * with one CTA on an SM nothing else hides a tile's chain S MMA -> softmax -> P -> P.V MMA -> fold, so two groups of 128
+//    softmax threads take the even and the odd tiles (S, P and O are double-buffered: a buffer per group), each with its own
+//    running maxima, sums and accumulators, which are merged once at the end;
 //  * it is stage 1 only: the partials leave as plain (m, l, acc) and the merge kernel follows, and it neither appends
 //    nor exchanges (those stay with the 128-dim kernels); a launch that asks for them is declined.
 //  * Every wait is bounded, as there.
@@ -25,10 +30,11 @@ namespace {
 
 constexpr int kD = 256;
 constexpr int kTileM = 128;            // positions per tile = rows of the S MMA = TMEM lanes
-constexpr int kStages = 2;
-constexpr int kThreads = 256;
-constexpr int kConsumers = 128;
-constexpr int kProducerWarp = 4, kMmaWarp = 5, kPvWarp = 6;
+constexpr int kKStages = 2;            // K tiles: a stage is free again as soon as its score MMAs have run
+constexpr int kVStages = 3;            // V tiles (and both scale tiles): held until the tile's P.V has run
+constexpr int kThreads = 384;
+constexpr int kConsumers = 128;        // softmax threads per group; warps 0-3 take the even tiles, warps 4-7 the odd ones
+constexpr int kProducerWarp = 8, kMmaWarp = 9, kPvWarp = 10, kVProducerWarp = 11;
 constexpr uint32_t kSpin = 1u << 20;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0;          // two S buffers of 8 blocks x 16 columns
@@ -41,16 +47,16 @@ struct Smem {
     static constexpr int kKTile = 2 * kHalfTile;                       // 32768
     static constexpr int kSTile = kTileM * NBLK * 2;                   // 2048 (q8_0) or 256 (row scale)
     static constexpr int kOffK = 0;
-    static constexpr int kOffV = kStages * kKTile;
-    static constexpr int kOffP = 2 * kStages * kKTile;                 // 2 x [half][span][128 positions][32 B]
+    static constexpr int kOffV = kKStages * kKTile;
+    static constexpr int kOffP = (kKStages + kVStages) * kKTile;       // 2 x [half][span][128 positions][32 B]
     static constexpr int kPBuf = 2 * 2 * kTileM * 32;                  // 16384
     static constexpr int kOffQ = kOffP + 2 * kPBuf;                    // [half][16 rows][128 B]
-    static constexpr int kOffS = kOffQ + 2 * 16 * 128;                 // [stage][ks | vs]
-    static constexpr int kOffXch = kOffS + kStages * 2 * kSTile;       // [2 parities][4 warps][16] words: tile maxima
-    static constexpr int kOffL = kOffXch + 2 * 4 * 16 * 4;             // [4 warps][8] row sums
-    static constexpr int kOffQmul = kOffL + 4 * 8 * 4;                 // [8]
+    static constexpr int kOffS = kOffQ + 2 * 16 * 128;                 // [V stage][ks | vs]
+    static constexpr int kOffXch = kOffS + kVStages * 2 * kSTile;      // [2 groups][2 parities][4 warps][16] words: tile maxima
+    static constexpr int kOffL = kOffXch + 2 * 2 * 4 * 16 * 4;         // [2 groups][4 warps][8] row sums
+    static constexpr int kOffQmul = kOffL + 2 * 4 * 8 * 4;             // [8]
     static constexpr int kOffBar = kOffQmul + 32;
-    static constexpr int kNumBars = 2 * kStages + 8;                   // full[2] empty[2] s_full[2] s_empty[2] p_full[2] p_empty[2]
+    static constexpr int kNumBars = 2 * kKStages + 2 * kVStages + 8;   // k_full k_empty v_full v_empty s_full[2] s_empty[2] p_full[2] p_empty[2]
     static constexpr int kOffMisc = kOffBar + kNumBars * 8;            // tmem slot, fail flag
     static constexpr int kTotal = kOffMisc + 16;
     static constexpr int kAlloc = kTotal + 1024;                       // slack to align the base to 1024
@@ -149,12 +155,15 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
     const uint32_t early_end = end > p.overlap_tail ? end - p.overlap_tail : 0;
 
     const uint32_t bar0 = sbase + L::kOffBar;
-    auto bar_full = [&](int s) { return bar0 + s * 8; };
-    auto bar_empty = [&](int s) { return bar0 + (kStages + s) * 8; };
-    auto bar_s_full = [&](int b) { return bar0 + (2 * kStages + b) * 8; };
-    auto bar_s_empty = [&](int b) { return bar0 + (2 * kStages + 2 + b) * 8; };
-    auto bar_p_full = [&](int b) { return bar0 + (2 * kStages + 4 + b) * 8; };
-    auto bar_p_empty = [&](int b) { return bar0 + (2 * kStages + 6 + b) * 8; };
+    auto bar_k_full = [&](int s) { return bar0 + s * 8; };
+    auto bar_k_empty = [&](int s) { return bar0 + (kKStages + s) * 8; };
+    auto bar_v_full = [&](int s) { return bar0 + (2 * kKStages + s) * 8; };
+    auto bar_v_empty = [&](int s) { return bar0 + (2 * kKStages + kVStages + s) * 8; };
+    constexpr int kB0 = 2 * kKStages + 2 * kVStages;
+    auto bar_s_full = [&](int b) { return bar0 + (kB0 + b) * 8; };
+    auto bar_s_empty = [&](int b) { return bar0 + (kB0 + 2 + b) * 8; };
+    auto bar_p_full = [&](int b) { return bar0 + (kB0 + 4 + b) * 8; };
+    auto bar_p_empty = [&](int b) { return bar0 + (kB0 + 6 + b) * 8; };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
     uint32_t* fail_flag = tmem_slot + 1;
 
@@ -164,28 +173,39 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
     const uint32_t capacity = static_cast<uint32_t>(view.capacity);
     const int row_base = static_cast<int>(head_row0);
 
-    // Tile i of this CTA into ring stage i % kStages (producer thread only).
-    auto issue = [&](int i) {
-        const int stage = i % kStages;
+    // Tile i of this CTA: its K halves into K stage i % kKStages, its V halves and both scale tiles into V stage i % kVStages.
+    auto issue_k = [&](int i) {
+        const int stage = i % kKStages;
+        const uint32_t pos0 = (t0 + i) * kTileM;
+        const uint32_t bar = bar_k_full(stage);
+        mbar_expect_tx(bar, L::kKTile);
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf)
+            tma_load_2d(sbase + L::kOffK + stage * L::kKTile + hf * kHalfTile, &kmap, hf * 128, row_base + static_cast<int>(pos0), bar);
+    };
+    auto issue_v = [&](int i) {
+        const int stage = i % kVStages;
         const uint32_t pos0 = (t0 + i) * kTileM;
         const uint32_t sbytes = min(static_cast<uint32_t>(kTileM), capacity - pos0) * (NBLK * 2);
-        const uint32_t bar = bar_full(stage);
-        mbar_expect_tx(bar, 2 * L::kKTile + 2 * sbytes);
+        const uint32_t bar = bar_v_full(stage);
+        mbar_expect_tx(bar, L::kKTile + 2 * sbytes);
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-            tma_load_2d(sbase + L::kOffK + stage * L::kKTile + hf * kHalfTile, &kmap, hf * 128, row_base + static_cast<int>(pos0), bar);
+        for (int hf = 0; hf < 2; ++hf)
             tma_load_2d(sbase + L::kOffV + stage * L::kKTile + hf * kHalfTile, &vmap, hf * 128, row_base + static_cast<int>(pos0), bar);
-        }
         const uint32_t sdst = sbase + L::kOffS + stage * 2 * L::kSTile;
         bulk_load(sdst, ks_plane + static_cast<size_t>(pos0) * (NBLK * 2), sbytes, bar);
         bulk_load(sdst + L::kSTile, vs_plane + static_cast<size_t>(pos0) * (NBLK * 2), sbytes, bar);
     };
 
     // ---- set-up ---------------------------------------------------------------------------------------------
-    int issued = 0;
+    // tiles whose rows are old enough to be fetched before the dependency wait
+    int early = 0;
+    while (early < ntiles && early < kVStages && (t0 + early + 1) * kTileM <= early_end) ++early;
+    const int k_early = min(early, kKStages), v_early = early;
     if (warp == kProducerWarp) {
         if (lane == 0) {
-            for (int s = 0; s < kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+            for (int s = 0; s < kKStages; ++s) { mbar_init(bar_k_full(s), 1); mbar_init(bar_k_empty(s), 1); }
+            for (int s = 0; s < kVStages; ++s) { mbar_init(bar_v_full(s), 1); mbar_init(bar_v_empty(s), 1); }
             for (int b = 0; b < 2; ++b) {
                 mbar_init(bar_s_full(b), 1); mbar_init(bar_s_empty(b), kConsumers);
                 mbar_init(bar_p_full(b), kConsumers); mbar_init(bar_p_empty(b), 1);
@@ -194,15 +214,19 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             // old cache rows do not depend on the preceding kernels: start streaming them before waiting for those
-            while (issued < kStages && issued < ntiles && (t0 + issued + 1) * kTileM <= early_end) { issue(issued); ++issued; }
+            for (int i = 0; i < v_early; ++i) { if (i < k_early) issue_k(i); issue_v(i); }
         }
     } else if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     pdl_wait();
+    // the rest of the first ring fill, by the thread that set the barriers up
     if (warp == kProducerWarp && lane == 0)
-        while (issued < kStages && issued < ntiles) { issue(issued); ++issued; }
+        for (int i = 0; i < min(kVStages, ntiles); ++i) {
+            if (i >= k_early && i < kKStages) issue_k(i);
+            if (i >= v_early) issue_v(i);
+        }
 
     // ---- Q: 15 bits per head as two int8 planes (q = 128 hi + lo).  Rows of the B operand of S^T = K . Q^T: hi planes of
     //      heads 0-7 in rows 0-7, lo planes in rows 8-15 (rows of heads past G are zero); one 16 x 128-byte tile per half
@@ -243,12 +267,14 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
             // scores are kept in base-2 units: dot * (amax/16319) * softmax_scale * log2(e)
             qm = (amax / 16319.0f) * p.scale * 1.4426950408889634f;
         }
+        if (warp < 8) {
         if (lane == 0) reinterpret_cast<float*>(smem + L::kOffQmul)[warp] = qm;
         // dims 8*lane .. 8*lane+7 of row n: half lane >> 4, 16-byte chunk ((lane & 15) >> 1) ^ (n & 7), bytes (lane & 1) * 8
         const int n_hi = warp, n_lo = 8 + warp;
         uint8_t* qt = smem + L::kOffQ + (lane >> 4) * (16 * 128);
         *reinterpret_cast<uint2*>(qt + n_hi * 128 + (((((lane & 15) >> 1) ^ (n_hi & 7))) << 4) + (lane & 1) * 8) = hi8;
         *reinterpret_cast<uint2*>(qt + n_lo * 128 + (((((lane & 15) >> 1) ^ (n_lo & 7))) << 4) + (lane & 1) * 8) = lo8;
+        }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // Q was written by ordinary stores, the MMA reads it through the async proxy
     tc_fence_before();
@@ -259,12 +285,21 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
     bool failed = false;
 
     if (warp == kProducerWarp) {
-        // =============================== TMA producer ===============================
+        // =============================== TMA producer, K tiles ===============================
         if (lane == 0) {
-            for (int i = issued; i < ntiles; ++i) {
-                // stage i % kStages is free once the P.V of tile i - kStages has completed
-                if (i >= kStages && !mbar_wait(bar_empty(i % kStages), static_cast<uint32_t>((i / kStages - 1) & 1))) { failed = true; break; }
-                issue(i);
+            for (int i = min(kKStages, ntiles); i < ntiles; ++i) {
+                // K stage i % kKStages is free once the score MMAs of tile i - kKStages have completed
+                if (!mbar_wait(bar_k_empty(i % kKStages), static_cast<uint32_t>((i / kKStages - 1) & 1))) { failed = true; break; }
+                issue_k(i);
+            }
+        }
+    } else if (warp == kVProducerWarp) {
+        // =============================== TMA producer, V and scale tiles ===============================
+        if (lane == 0) {
+            for (int i = min(kVStages, ntiles); i < ntiles; ++i) {
+                // V stage i % kVStages is free once the P.V of tile i - kVStages has completed
+                if (!mbar_wait(bar_v_empty(i % kVStages), static_cast<uint32_t>((i / kVStages - 1) & 1))) { failed = true; break; }
+                issue_v(i);
             }
         }
     } else if (warp == kMmaWarp) {
@@ -272,9 +307,9 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc_i8(kTileM, 16, 1, 1, 0);   // K (signed) x Q planes (signed), both K-major
             for (int i = 0; i < ntiles; ++i) {
-                const int stage = i % kStages, buf = i & 1;
+                const int stage = i % kKStages, buf = i & 1;
                 if (!mbar_wait(bar_s_empty(buf), static_cast<uint32_t>(((i >> 1) & 1) ^ 1))) { failed = true; break; }   // S buffer read out (tile i - 2)
-                if (!mbar_wait(bar_full(stage), static_cast<uint32_t>((i / kStages) & 1))) { failed = true; break; }     // tile landed
+                if (!mbar_wait(bar_k_full(stage), static_cast<uint32_t>((i / kKStages) & 1))) { failed = true; break; }  // K tile landed
                 tc_fence_after();
                 const uint32_t kt = sbase + L::kOffK + stage * L::kKTile;
 #pragma unroll
@@ -282,6 +317,7 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
                     umma_i8(tmem_base + kColS + buf * 128 + b * 16, umma_desc(kt + (b >> 2) * kHalfTile + 32 * (b & 3), 16, 1024, 2),
                             umma_desc(sbase + L::kOffQ + (b >> 2) * (16 * 128) + 32 * (b & 3), 16, 1024, 2), idesc_s, 0);
                 umma_commit(bar_s_full(buf));
+                umma_commit(bar_k_empty(stage));    // K stage may be refilled
             }
         }
     } else if (warp == kPvWarp) {
@@ -289,9 +325,9 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
         if (lane == 0) {
             constexpr uint32_t idesc_o = umma_idesc_i8(128, 64, 1, 0, 1, 1);    // V^T (signed, MN-major) x P planes (unsigned, MN-major)
             for (int i = 0; i < ntiles; ++i) {
-                const int stage = i % kStages, buf = i & 1;
+                const int stage = i % kVStages, buf = i & 1;
                 if (!mbar_wait(bar_p_full(buf), static_cast<uint32_t>((i >> 1) & 1))) { failed = true; break; }
-                if (!mbar_wait(bar_full(stage), static_cast<uint32_t>((i / kStages) & 1))) { failed = true; break; }   // long complete: the V tile's landing, observed by this thread
+                if (!mbar_wait(bar_v_full(stage), static_cast<uint32_t>((i / kVStages) & 1))) { failed = true; break; }   // long complete: the V tile's landing, observed by this thread
                 tc_fence_after();
                 const uint32_t vt = sbase + L::kOffV + stage * L::kKTile;
                 const uint32_t pt = sbase + L::kOffP + buf * L::kPBuf;
@@ -302,60 +338,73 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
                         umma_i8(tmem_base + kColO + buf * 128 + hf * 64, umma_desc(vt + hf * kHalfTile + j * (32 * 128), kHalfTile, 1024, 2),
                                 umma_desc(pt + hf * (2 * kTileM * 32) + j * (32 * 32), kTileM * 32, 256, 6), idesc_o, j > 0);
                 umma_commit(bar_p_empty(buf));      // P buffer free, the tile's sums complete
-                umma_commit(bar_empty(stage));      // ring stage may be refilled
+                umma_commit(bar_v_empty(stage));    // V stage (and its scale tiles) may be refilled
             }
         }
     }
 
-    if (warp < 4) {
-        // =============================== softmax threads: one per position of a tile ===============================
-        // what they hand to the epilogue: this thread's dims (tid and 128 + tid), heads 0..G-1, relative to m_run
+    if (warp < 8) {
+        // =============================== softmax threads: one per position of a tile, two groups ===============================
+        // Group g (warps 4g .. 4g+3) takes the tiles i with i % 2 == g and with them S, P and O buffer g.
+        const int grp = warp >> 2, wq = warp & 3, ltid = tid & 127;   // wq: the warp's quarter of the TMEM lanes; ltid: position in the tile / dim in a half
+        // what a group hands to the epilogue: this thread's dims (ltid and 128 + ltid), heads 0..G-1, relative to m_run
         float acc[2][G];
         float m_run[G], l_run[G];          // l_run: sums over this thread's positions only
-        float pend_a[2][G], pend_b[2][G];  // per O buffer (a = 0, b = 1) and half: fixed-point scale of the sums in flight (own block)
+        float pend[2][G];                  // per half: fixed-point scale of the sums in flight in this group's O buffer (own block)
 #pragma unroll
         for (int h = 0; h < G; ++h) {
             acc[0][h] = acc[1][h] = 0.0f; m_run[h] = -INFINITY; l_run[h] = 0.0f;
-            pend_a[0][h] = pend_a[1][h] = pend_b[0][h] = pend_b[1][h] = 0.0f;
+            pend[0][h] = pend[1][h] = 0.0f;
         }
-        const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+        const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
         float qmul[G];
 #pragma unroll
         for (int h = 0; h < G; ++h) qmul[h] = reinterpret_cast<const float*>(smem + L::kOffQmul)[h];
         // P is the MN-major B operand: per half of the dims and per 32-byte span (two blocks), this position's row of 32
         // bytes, 32-byte swizzle: 16-byte chunk c of row r sits at 32 r + ((c ^ ((r >> 2) & 1)) << 4)
-        const uint32_t p_row = static_cast<uint32_t>(tid) * 32u;
-        const uint32_t p_flip = static_cast<uint32_t>((tid >> 2) & 1) << 4;
+        const uint32_t p_row = static_cast<uint32_t>(ltid) * 32u;
+        const uint32_t p_flip = static_cast<uint32_t>((ltid >> 2) & 1) << 4;
         int* xch = reinterpret_cast<int*>(smem + L::kOffXch);
+        const int buf = grp;
         auto wait = [&](uint32_t bar, uint32_t parity) { if (!failed && !mbar_wait(bar, parity)) failed = true; };
-        auto fold_o = [&](int buf) {   // the completed sums of a tile: own block's 16 columns of each half -> fp32 accumulators
+        auto group_sync = [&]() {
+            if (grp == 0) asm volatile("bar.sync 3, 128;" ::: "memory");
+            else asm volatile("bar.sync 4, 128;" ::: "memory");
+        };
+        auto fold_o = [&]() {   // the completed sums of a tile: own block's 16 columns of each half -> fp32 accumulators
             tc_fence_after();
             int o0[16], o1[16];
-            tmem_ld16(tmem_base + lane_addr + kColO + buf * 128 + warp * 16, o0);
-            tmem_ld16(tmem_base + lane_addr + kColO + buf * 128 + 64 + warp * 16, o1);
+            tmem_ld16(tmem_base + lane_addr + kColO + buf * 128 + wq * 16, o0);
+            tmem_ld16(tmem_base + lane_addr + kColO + buf * 128 + 64 + wq * 16, o1);
             tmem_ld_wait();
             tc_fence_before();
 #pragma unroll
             for (int h = 0; h < G; ++h) {
-                acc[0][h] = fmaf(static_cast<float>(o0[h] * 256 + o0[8 + h]), buf ? pend_b[0][h] : pend_a[0][h], acc[0][h]);
-                acc[1][h] = fmaf(static_cast<float>(o1[h] * 256 + o1[8 + h]), buf ? pend_b[1][h] : pend_a[1][h], acc[1][h]);
+                acc[0][h] = fmaf(static_cast<float>(o0[h] * 256 + o0[8 + h]), pend[0][h], acc[0][h]);
+                acc[1][h] = fmaf(static_cast<float>(o1[h] * 256 + o1[8 + h]), pend[1][h], acc[1][h]);
             }
         };
 
-        for (int i = 0; i < ntiles; ++i) {
-            const int stage = i % kStages, buf = i & 1;
-            wait(bar_full(stage), static_cast<uint32_t>((i / kStages) & 1));      // the scale tiles of this stage (async-proxy writes)
+        int last_i = -1;
+        for (int i = grp; i < ntiles; i += 2) {
+            last_i = i;
+            const int stage = i % kVStages;
+            // A parity wait tells "this phase is over" only to a waiter that has seen the phase before it.  A group takes every
+            // other tile, the ring has three stages, so a group would skip phases of a stage; it therefore also waits for the
+            // tile in between (the other group's), which has normally landed long before.
+            if (i > 0) wait(bar_v_full((i - 1) % kVStages), static_cast<uint32_t>(((i - 1) / kVStages) & 1));
+            wait(bar_v_full(stage), static_cast<uint32_t>((i / kVStages) & 1));   // the scale tiles of this stage (async-proxy writes)
             wait(bar_s_full(buf), static_cast<uint32_t>((i >> 1) & 1));
             tc_fence_after();
 
-            const uint32_t pos = (t0 + i) * kTileM + tid;
+            const uint32_t pos = (t0 + i) * kTileM + ltid;
             const bool valid = pos >= begin && pos < end;
             const uint8_t* kst = smem + L::kOffS + stage * 2 * L::kSTile;
             const uint8_t* vst = kst + L::kSTile;
             float ks[8], vs[8];
             uint32_t vs_bits[8];
             if constexpr (NBLK == 8) {
-                const uint4 kr = *reinterpret_cast<const uint4*>(kst + tid * 16), vr = *reinterpret_cast<const uint4*>(vst + tid * 16);
+                const uint4 kr = *reinterpret_cast<const uint4*>(kst + ltid * 16), vr = *reinterpret_cast<const uint4*>(vst + ltid * 16);
                 const uint32_t kw[4] = {kr.x, kr.y, kr.z, kr.w}, vw[4] = {vr.x, vr.y, vr.z, vr.w};
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
@@ -364,7 +413,7 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
                     vs_bits[2 * w] = vw[w] & 0xffffu; vs_bits[2 * w + 1] = vw[w] >> 16;
                 }
             } else {
-                const uint16_t kr = *reinterpret_cast<const uint16_t*>(kst + tid * 2), vr = *reinterpret_cast<const uint16_t*>(vst + tid * 2);
+                const uint16_t kr = *reinterpret_cast<const uint16_t*>(kst + ltid * 2), vr = *reinterpret_cast<const uint16_t*>(vst + ltid * 2);
 #pragma unroll
                 for (int b = 0; b < 8; ++b) { ks[b] = __half2float(__ushort_as_half(kr)); vs[b] = __half2float(__ushort_as_half(vr)); vs_bits[b] = vr; }
             }
@@ -388,9 +437,10 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
             float s[G];
 #pragma unroll
             for (int h = 0; h < G; ++h) s[h] = valid ? a[h] * qmul[h] : -INFINITY;   // positions outside the range (or rows never written) are masked
-            // ---- tile maxima (scores per head, value scales per block): redux inside the warp, one exchange across the four ----
+            // ---- tile maxima (scores per head, value scales per block): redux inside the warp, one exchange across the group's four ----
+            const int par = (i >> 1) & 1;   // the exchange area is double-buffered by the parity of the group's tile count
             {
-                int* dst = xch + (buf * 4 + warp) * 16;
+                int* dst = xch + ((grp * 2 + par) * 4 + wq) * 16;
 #pragma unroll
                 for (int h = 0; h < G; ++h) {
                     const int mx = __reduce_max_sync(0xffffffffu, ordered(s[h]));
@@ -402,7 +452,7 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
                     if (lane == 0) dst[8 + b] = static_cast<int>(vmx);
                 }
             }
-            asm volatile("bar.sync 3, 128;" ::: "memory");
+            group_sync();
             float m_tile[G], vs_max[8];
             {
                 int mx[G];
@@ -413,7 +463,7 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
                 for (int b = 0; b < 8; ++b) vmx[b] = 0;
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
-                    const int* src = xch + (buf * 4 + w) * 16;
+                    const int* src = xch + ((grp * 2 + par) * 4 + w) * 16;
 #pragma unroll
                     for (int h = 0; h < G; ++h) mx[h] = max(mx[h], src[h]);
 #pragma unroll
@@ -429,13 +479,13 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
             float vs_own[2];
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf)
-                vs_own[hf] = warp == 0 ? vs_max[4 * hf] : warp == 1 ? vs_max[4 * hf + 1] : warp == 2 ? vs_max[4 * hf + 2] : vs_max[4 * hf + 3];
+                vs_own[hf] = wq == 0 ? vs_max[4 * hf] : wq == 1 ? vs_max[4 * hf + 1] : wq == 2 ? vs_max[4 * hf + 2] : vs_max[4 * hf + 3];
 #pragma unroll
             for (int h = 0; h < G; ++h) {
                 const float m_new = fmaxf(m_run[h], m_tile[h]);
                 const float alpha = (m_run[h] == -INFINITY) ? 0.0f : exp2f(m_run[h] - m_new);
                 acc[0][h] *= alpha; acc[1][h] *= alpha; l_run[h] *= alpha;
-                pend_a[0][h] *= alpha; pend_a[1][h] *= alpha; pend_b[0][h] *= alpha; pend_b[1][h] *= alpha;
+                pend[0][h] *= alpha; pend[1][h] *= alpha;
                 m_run[h] = m_new;
                 const float w = (s[h] == -INFINITY) ? 0.0f : exp2f(s[h] - m_new);
                 l_run[h] += w;
@@ -444,16 +494,13 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
                 nscale[0][h] = wmax * vs_own[0] * (1.0f / kPMax);
                 nscale[1][h] = wmax * vs_own[1] * (1.0f / kPMax);
             }
-            // ---- P and O buffer `buf` were last used by tile i - 2: its P.V has completed; fold its sums first ----
+            // ---- this group's P and O buffer were last used by tile i - 2: its P.V has completed; fold its sums first ----
             if (i >= 2) {
                 wait(bar_p_empty(buf), static_cast<uint32_t>(((i >> 1) - 1) & 1));
-                fold_o(buf);
+                fold_o();
             }
 #pragma unroll
-            for (int h = 0; h < G; ++h) {
-                if (buf) { pend_b[0][h] = nscale[0][h]; pend_b[1][h] = nscale[1][h]; }
-                else { pend_a[0][h] = nscale[0][h]; pend_a[1][h] = nscale[1][h]; }
-            }
+            for (int h = 0; h < G; ++h) { pend[0][h] = nscale[0][h]; pend[1][h] = nscale[1][h]; }
             // [block]: w * value_scale as 16-bit fixed point, 16 bytes per block: hi bytes of heads 0-7, lo bytes of heads 0-7
             const uint32_t pt = sbase + L::kOffP + buf * L::kPBuf + p_row;
 #pragma unroll
@@ -473,40 +520,54 @@ decode_tc5_wide_kernel(const __grid_constant__ DecodeParams p, const __grid_cons
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(bar_p_full(buf));
         }
-        // the last two tiles' sums
-        if (ntiles >= 2) {
-            const int buf = (ntiles - 2) & 1;
-            wait(bar_p_empty(buf), static_cast<uint32_t>(((ntiles - 2) >> 1) & 1));
-            fold_o(buf);
+        // the group's last tile's sums
+        if (last_i >= 0) {
+            wait(bar_p_empty(buf), static_cast<uint32_t>((last_i >> 1) & 1));
+            fold_o();
         }
-        if (ntiles >= 1) {
-            const int buf = (ntiles - 1) & 1;
-            wait(bar_p_empty(buf), static_cast<uint32_t>(((ntiles - 1) >> 1) & 1));
-            fold_o(buf);
-        }
-        // ---- row sums over the CTA, then the CTA's partial leaves: thread = dims tid and 128 + tid of every head ----
+        // ---- row sums over the group ----
 #pragma unroll
         for (int h = 0; h < G; ++h) l_run[h] = warp_sum(l_run[h]);
+        float* lsm = reinterpret_cast<float*>(smem + L::kOffL);   // [2 groups][4 warps][8]
         if (lane == 0) {
 #pragma unroll
-            for (int h = 0; h < G; ++h) reinterpret_cast<float*>(smem + L::kOffL)[warp * 8 + h] = l_run[h];
+            for (int h = 0; h < G; ++h) lsm[(grp * 4 + wq) * 8 + h] = l_run[h];
             if (failed) atomicOr(fail_flag, 1u);
         }
-        asm volatile("bar.sync 3, 128;" ::: "memory");
-        // a wait that ran out anywhere in the pipeline ends in a wait of these threads running out
-        const bool poisoned = *reinterpret_cast<volatile uint32_t*>(fail_flag) != 0;
-        if (poisoned && tid == 0 && p.status != nullptr) atomicOr(p.status, B200KV_STATUS_PIPE_TIMEOUT);
+        // ---- the odd tiles' group hands its state to the even tiles' group through its own P buffer (the P.V MMAs that read it
+        //      have completed; the other buffer may still be feeding the even group's last P.V) ----
+        float* hand = reinterpret_cast<float*>(smem + L::kOffP + L::kPBuf);   // [3 * G][128]: acc of half 0, acc of half 1, maxima
+        if (grp == 1) {
 #pragma unroll
-        for (int h = 0; h < G; ++h) {
-            float lt = 0.0f;
+            for (int h = 0; h < G; ++h) {
+                hand[(0 * G + h) * 128 + ltid] = acc[0][h];
+                hand[(1 * G + h) * 128 + ltid] = acc[1][h];
+                hand[(2 * G + h) * 128 + ltid] = m_run[h];
+            }
+        }
+        asm volatile("bar.sync 5, 256;" ::: "memory");
+        if (grp == 0) {
+            // a wait that ran out anywhere in the pipeline ends in a wait of these threads running out
+            const bool poisoned = *reinterpret_cast<volatile uint32_t*>(fail_flag) != 0;
+            if (poisoned && tid == 0 && p.status != nullptr) atomicOr(p.status, B200KV_STATUS_PIPE_TIMEOUT);
 #pragma unroll
-            for (int w = 0; w < 4; ++w) lt += reinterpret_cast<const float*>(smem + L::kOffL)[w * 8 + h];
-            float a0 = acc[0][h], a1 = acc[1][h], mh = m_run[h] * 0.6931471805599453f;   // natural-log units, as the merge expects
-            if (poisoned) { a0 = a1 = mh = lt = __int_as_float(0x7fc00000); }
-            const size_t slot = (static_cast<size_t>(session) * p.num_splits + split) * p.query_heads + kv_head * G + h;
-            p.ws_acc[slot * kD + tid] = a0;
-            p.ws_acc[slot * kD + 128 + tid] = a1;
-            if (tid == 0) { p.ws_m[slot] = mh; p.ws_l[slot] = lt; }
+            for (int h = 0; h < G; ++h) {
+                float l0 = 0.0f, l1 = 0.0f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) { l0 += lsm[w * 8 + h]; l1 += lsm[(4 + w) * 8 + h]; }
+                const float m1 = hand[(2 * G + h) * 128 + ltid];   // uniform over the group's threads
+                const float M = fmaxf(m_run[h], m1);
+                const float s0 = (m_run[h] == -INFINITY) ? 0.0f : exp2f(m_run[h] - M), s1 = (m1 == -INFINITY) ? 0.0f : exp2f(m1 - M);
+                float a0 = fmaf(acc[0][h], s0, hand[(0 * G + h) * 128 + ltid] * s1);
+                float a1 = fmaf(acc[1][h], s0, hand[(1 * G + h) * 128 + ltid] * s1);
+                float lt = fmaf(l0, s0, l1 * s1);
+                float mh = M * 0.6931471805599453f;   // natural-log units, as the merge expects
+                if (poisoned) { a0 = a1 = mh = lt = __int_as_float(0x7fc00000); }
+                const size_t slot = (static_cast<size_t>(session) * p.num_splits + split) * p.query_heads + kv_head * G + h;
+                p.ws_acc[slot * kD + ltid] = a0;
+                p.ws_acc[slot * kD + 128 + ltid] = a1;
+                if (ltid == 0) { p.ws_m[slot] = mh; p.ws_l[slot] = lt; }
+            }
         }
     }
 

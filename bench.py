@@ -15,7 +15,8 @@ length), `prefill` (512-token suffix over an 8K prefix, d=256), `decode256` (dec
 or with --append-shape chunk256 the 512-token d=256 chunk).
 
 The default run also measures, as sub-records of the same JSON line, the suffix-prefill
-workload (`prefill`) and -- with N > 1 GPUs -- the sharded workloads (`seqshard`, `batched`)
+workload (`prefill`), on one GPU the head_dim-256 decode and the append workloads (`decode256`, `append`) and -- with N > 1
+GPUs -- the sharded workloads (`seqshard`, `batched`)
 together with their own 1-GPU times; `--no-extras` leaves them out.  After the timed region the
 output of one layer is compared with the CPU oracle on the cache as it then lies (`check`),
 and the step graph is replayed for two seconds with the SM clock sampled (`sustained`).

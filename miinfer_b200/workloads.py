@@ -509,8 +509,9 @@ def _brief(line: dict, base: dict | None = None) -> dict:
 
 
 def extras(args, torch, dist, rank, world, local_rank) -> dict:
-    """Sub-records for bench.py's default line: `prefill` always; with N > 1 GPUs also `seqshard` and `batched`, each
-    next to its own 1-GPU time measured by rank 0 alone on the full problem while the other ranks wait on the host."""
+    """Sub-records for bench.py's default line: `prefill` always; on one GPU also `decode256` and `append`; with N > 1 GPUs
+    `seqshard` and `batched`, each next to its own 1-GPU time measured by rank 0 alone on the full problem while the other
+    ranks wait on the host."""
     sub = SimpleNamespace(**vars(args))
     sub.steps, sub.warmup = max(3, min(args.steps, 20)), 3
     out = {}
@@ -542,6 +543,14 @@ def extras(args, torch, dist, rank, world, local_rank) -> dict:
         base = alone(run_prefill) if world > 1 else None
         if rank == 0:
             out["prefill"] = _brief(line, base)
+    if world == 1:
+        # the reference's own decode geometry (24 Q / 4 KV, head_dim 256) at the headline context, and the store kernel alone
+        d256 = SimpleNamespace(**vars(sub))
+        d256.context = 32768
+        out["decode256"] = _brief(run_decode256(d256, torch, None, 0, 1, local_rank))
+        release()
+        out["append"] = _brief(run_append(sub, torch, None, 0, 1, local_rank))
+        release()
     if world > 1:
         for name, fn in (("seqshard", run_seqshard), ("batched", run_batched)):
             line = fn(sub, torch, dist, rank, world, local_rank)

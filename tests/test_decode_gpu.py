@@ -415,3 +415,33 @@ def test_decode_head_dim_256_tcgen05_stage1(cuda, H, Hq, qb, L):
     assert_attention_close(a, ref, "decode d=256 tcgen05, device-side length")
     b, _ = gpu_decode(st, to_dev(q16), Hq, d ** -0.5, 0, decode_state=state)
     assert np.array_equal(a, b)
+
+
+def test_decode_steps_head_dim_256_back_to_back_with_launch_overlap(cuda):
+    """At head_dim 256 a decode step is the store kernel, the tcgen05 stage 1 and the merge kernel.  With launch overlap on,
+    each becomes resident while its predecessor still runs (stage 1 even fetches the old cache rows) and orders itself by
+    its own dependency wait: eight steps launched back to back must give, bit for bit, what the serialised launches give."""
+    d, H, Hq, L0, steps = 256, 4, 24, 4000, 8
+    rng = np.random.default_rng(256)
+    host = filled(rng, L0, H, d, 32, 3, cap=L0 + 64)
+    kn = [to_dev(ko.normal_f16(rng, (1, H * d))) for _ in range(steps)]
+    vn = [to_dev(ko.normal_f16(rng, (1, H * d))) for _ in range(steps)]
+    qs = [to_dev(ko.normal_f16(rng, (Hq, d))) for _ in range(steps)]
+    w = to_dev((1.0 + 0.1 * rng.standard_normal(d)).astype(np.float32))
+    results = {}
+    for overlap in (0, 1):
+        st = upload(host)
+        ws = kv.decode_workspace(Hq, d)
+        outs = torch.full((steps, Hq, d), float("nan"), device="cuda")
+        kv.set_launch_overlap(overlap)
+        try:
+            for i in range(steps):   # host-side positions: no kernel in between that would serialise the chain
+                kv.launch_decode_step(st.view(), kn[i], vn[i], qs[i], query_heads=Hq, scale=d ** -0.5, position=L0 + i,
+                                      k_norm_weight=w, rope_mode=kv.RopeMode.SECTIONED64, output=outs[i], workspace=ws)
+            torch.cuda.synchronize()
+        finally:
+            kv.set_launch_overlap(0)
+        results[overlap] = (outs.cpu(), st.key_cache_q8[:, :L0 + steps].cpu(), st.value_cache_q8[:, :L0 + steps].cpu())
+    assert torch.isfinite(results[1][0]).all()
+    for a, b in zip(results[0], results[1]):
+        assert torch.equal(a, b)

@@ -100,26 +100,29 @@ def pick_batched_splits(lengths, kv_heads: int, cta_slots: int = 296, max_splits
     """Split count (of the longest session) for one batched decode launch over sessions of these lengths.
     A launch runs one CTA per (split, kv head, session) and `cta_slots` CTAs at a time (two per SM); the
     kernel gives a session one split per ceil(max_length / splits) positions (rounded up to 128).  The cost of
-    a choice is waves x (positions per split + the fixed cost of a CTA, about 384 positions' worth: prologue,
-    merge of its warps, tagged partial); among equally cheap choices the finer one wins (it balances better).
-    The library's own default (one split per 2048 positions) ignores the wave count."""
+    a choice, in positions streamed per CTA slot, fitted to launches timed on a B200 (1, 2, 4 and 8-GPU shares
+    of 80 sessions of 512..16384 positions):
+      * up to two waves of CTAs the waves are what counts: waves x (positions per split + 2048, the fixed
+        cost of a CTA: prologue, pipeline fill, merge of its warps, tagged partial);
+      * beyond that the slots refill as CTAs retire, so the cost is (CTAs / slots) x (positions per split +
+        3072), without rounding to whole waves.
+    Among equally cheap choices the coarser one wins (fewer partials to merge).  The library's own default
+    (one split per 2048 positions) ignores both the wave count and the fixed cost."""
     lengths = [int(x) for x in lengths if int(x) > 0]
     if not lengths:
         return 1
     longest = max(lengths)
     budget = max(1, min(max_splits, 1024 // max(1, len(lengths))))     # the library's split-slot budget
-    # with many waves the tail of the last one is small and the library's granularity measured best
-    default_splits = min(budget, max(1, -(-longest // 2048)))
-    default_per = -(-(-(-longest // default_splits)) // 128) * 128
-    if sum(-(-n // default_per) for n in lengths) * kv_heads >= 5 * cta_slots:
-        return default_splits
-    best, best_cost, best_per = 1, None, None
+    best, best_cost = 1, None
     for splits in range(1, budget + 1):
         per = max(256, -(-(-(-longest // splits)) // 128) * 128)
         if -(-longest // per) > splits:      # rounding pushed the longest session over its split count
             continue
         ctas = sum(-(-n // per) for n in lengths) * kv_heads
-        cost = -(-ctas // cta_slots) * (per + 384)
-        if best_cost is None or cost < best_cost or (cost == best_cost and per < best_per):
-            best, best_cost, best_per = splits, cost, per
+        if ctas <= 2 * cta_slots:
+            cost = -(-ctas // cta_slots) * (per + 2048)
+        else:
+            cost = ctas / cta_slots * (per + 3072)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = splits, cost
     return best

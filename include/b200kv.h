@@ -342,7 +342,10 @@ B200KV_API int b200kv_decode_kernel_kind(const b200kv_view* view, uint32_t query
  * tools/miinfer_cli.cpp:5663-5676).  views: HOST array of `sessions` views
  * (same head_dim, kv_heads, qblock, quant_mode; capacities may differ);
  * lengths: DEVICE array of `sessions` uint32 cache lengths; max_length: host
- * upper bound of those lengths (sizes the launch).  q/gate/output/gated_output:
+ * upper bound of those lengths (sizes the launch: a session gets one split
+ * per ceil(max_length / num_splits) positions, rounded up to 128, so a host
+ * that knows the lengths can choose the positions per split with the pair;
+ * num_splits 0 = one split per 2048 positions).  q/gate/output/gated_output:
  * [sessions][query_heads][head_dim].  view_table: DEVICE scratch of
  * b200kv_view_table_bytes(sessions) bytes, 128-byte aligned, that this call
  * fills with the views and their TMA descriptors (one blocking copy); pass

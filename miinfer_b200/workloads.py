@@ -286,7 +286,7 @@ def run_batched(args, torch, dist, rank, world, local_rank):
     plus 16 sessions restored from a shared 4096-token prefix snapshot kept in a snapshot pool; sessions are bin-packed
     over the ranks."""
     from miinfer_b200 import kv
-    from miinfer_b200.partition import partition_sessions, pick_batched_splits
+    from miinfer_b200.partition import partition_sessions, pick_batched_plan
 
     HQ, HKV, D, LAYERS = 32, 8, 128, min(args.layers, 4)
     rng = np.random.default_rng(42)
@@ -323,16 +323,16 @@ def run_batched(args, torch, dist, rank, world, local_rank):
                 matched = pool.restore(prefix_tokens + [1, 2, 3], [caches[l][j] for l in range(LAYERS)])
                 assert matched == 4096
     restore_ms = _time(torch, dist, stream, restore, 1, 3) if restored or dist is not None else 0.0
-    # the host knows this step's lengths: pick the split count that fills whole waves of CTAs (0 = library default)
-    splits = 0 if getattr(args, "default_splits", False) else pick_batched_splits(lengths, HKV)
+    # the host knows this step's lengths: pick the split size whose CTAs pack the device best (0 = library default)
+    splits, bound = (0, max(lengths)) if getattr(args, "default_splits", False) else pick_batched_plan(lengths, HKV)
     kv.set_launch_overlap(0 if args.no_overlap else 1)
     for l in range(LAYERS):   # fills the device view tables once
-        kv.launch_decode_attention_batched([c.view() for c in caches[l]], tables[l], lens, max(lengths), q[l], query_heads=HQ,
+        kv.launch_decode_attention_batched([c.view() for c in caches[l]], tables[l], lens, bound, q[l], query_heads=HQ,
                                            scale=D ** -0.5, output=out[l], workspace=ws, num_splits=splits)
 
     def step():
         for l in range(LAYERS):
-            kv.launch_decode_attention_batched(None, tables[l], lens, max(lengths), q[l], query_heads=HQ, scale=D ** -0.5,
+            kv.launch_decode_attention_batched(None, tables[l], lens, bound, q[l], query_heads=HQ, scale=D ** -0.5,
                                                output=out[l], workspace=ws, num_splits=splits)
 
     # the step is captured once and replayed (the launches are asynchronous: the table's geometry is remembered on the host)
@@ -369,7 +369,7 @@ def run_batched(args, torch, dist, rank, world, local_rank):
                                    f"q8_0; sessions bin-packed over {world} GPU(s)", "l2": "inputs larger than L2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": bw_peak * world, "unit": "GB/s", "frac": achieved / (bw_peak * world),
                          "traffic": None, "peak_kind": f"{kind} x {world} GPUs"},
-            "splits_of_longest_session": splits, "restore_ms_16_sessions": restore_ms, "restore_bytes": LAYERS * 16 * 4096 * HKV * 136 * 2,
+            "splits_of_longest_session": splits, "positions_per_split": (bound // splits if splits else 2048), "restore_ms_16_sessions": restore_ms, "restore_bytes": LAYERS * 16 * 4096 * HKV * 136 * 2,
             "check": check, "gpu_launches": args.steps * LAYERS}
 
 

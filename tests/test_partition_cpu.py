@@ -83,32 +83,28 @@ def test_sequence_sharded_merge_over_gloo(tmp_path, world):
         assert float((tmp_path / f"rank{r}.txt").read_text()) <= 2e-6
 
 
-def test_pick_batched_splits_fills_waves_and_respects_budgets():
-    from miinfer_b200.partition import partition_sessions, pick_batched_splits
+def test_pick_batched_plan_packs_the_slots_and_respects_budgets():
+    from miinfer_b200.partition import partition_sessions, pick_batched_plan
+
+    def per_split(splits, bound):          # what the library derives from the pair
+        return max(256, -(-(-(-bound // splits)) // 128) * 128)
 
     rng = np.random.default_rng(42)
     lengths = [int(x) for x in rng.integers(512, 16385, size=10)]
-
-    def plan(splits, lens):
-        per = max(256, -(-(-(-max(lens) // splits)) // 128) * 128)
-        return per, sum(-(-n // per) for n in lens) * 8
-
-    def cost(splits, lens):
-        per, ctas = plan(splits, lens)
-        return -(-ctas // 296) * (per + 2048) if ctas <= 592 else ctas / 296 * (per + 3072)
-
-    s = pick_batched_splits(lengths, 8)
-    per, ctas = plan(s, lengths)
-    # never worse than the library default under the picker's cost model, and the longest session fits its split count
-    assert cost(s, lengths) <= cost(-(-max(lengths) // 2048), lengths)
-    assert -(-max(lengths) // per) <= s
-    # the bench's 80 sessions: the choices that timed best on the device for a 1-, 2-, 4- and 8-GPU share
+    splits, bound = pick_batched_plan(lengths, 8)
+    per = per_split(splits, bound)
+    # the bound covers every session, the longest session fits its split count, and the launch is one wave
+    assert bound >= max(lengths) and -(-max(lengths) // per) <= splits
+    assert sum(-(-n // per) for n in lengths) * 8 <= 296
+    # the bench's 80 sessions: the split sizes that timed best (or within 2 % of it) on the device for a 1-, 2-, 4-
+    # and 8-GPU share
     all_lengths = [int(x) for x in np.random.default_rng(42).integers(512, 16385, size=64)] + [4096] * 16
-    for world, want in ((1, 2), (2, 3), (4, 6), (8, 6)):
+    for world, want in ((1, (7168,)), (2, (6144,)), (4, (2816,)), (8, (2560, 2688, 2816))):
         for share in partition_sessions(all_lengths, world):
-            assert pick_batched_splits([all_lengths[i] for i in share], 8) == want
+            s, b = pick_batched_plan([all_lengths[i] for i in share], 8)
+            assert per_split(s, b) in want
     # a single short session needs one split; many sessions are capped by the split-slot budget (1024 slots)
-    assert pick_batched_splits([100], 8) == 1
-    assert pick_batched_splits([16384] * 256, 8) <= 4
-    assert pick_batched_splits([], 8) == 1
-    assert pick_batched_splits([0, 0], 8) == 1
+    assert pick_batched_plan([100], 8)[0] == 1
+    assert pick_batched_plan([16384] * 256, 8)[0] <= 4
+    assert pick_batched_plan([], 8)[0] == 1
+    assert pick_batched_plan([0, 0], 8)[0] == 1

@@ -498,7 +498,7 @@ def _brief(line: dict, base: dict | None = None) -> dict:
     keep = {k: line[k] for k in ("metric", "value", "unit", "ms_per_step", "scaling", "n_gpus", "steps", "warmup", "roofline", "check",
                                  "gpu_launches") if k in line}
     keep["workload"] = line["config"]["workload"]
-    for k in ("restore_ms_16_sessions", "splits_of_longest_session", "output_checksum_spread_over_ranks", "status_word"):
+    for k in ("restore_ms_16_sessions", "splits_of_longest_session", "positions_per_split", "output_checksum_spread_over_ranks", "status_word"):
         if k in line:
             keep[k] = line[k]
     if base is not None:

@@ -257,8 +257,8 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
     state = kv.make_decode_state(ctx - 1, device=dev)   # position of the token being appended; length = position + 1
     scale = D ** -0.5
 
-    def layer_pass():
-        for l in range(LAYERS):
+    def layer_pass(first=0, last=LAYERS):
+        for l in range(first, last):
             if args.two_launches:   # the reference's call pair: store kernel, then decode attention
                 kv.launch_kv_store_quant(views[l], k_new[l], v_new[l], None, 1, 0, rope_mode=kv.RopeMode.NEOX_FULL,
                                          theta=THETA, decode_state=state)
@@ -330,21 +330,43 @@ def run_decode32k(args, torch, dist, rank, world, local_rank):
     attn_bytes = length_now * HKV * ROW * 2 + HQ * D * 2 + HQ * D * 4
 
     # ---- end to end through the public API with host buffers --------------------------------
-    # Every step moves all 36 layers' inputs from pinned host memory (one copy: they lie side by side) and all 36 outputs
-    # back (one copy); the two copies are nodes of the step's graph, and the host waits for the whole step before the
-    # next one.  (Splitting the copies by layer onto side streams inside the graph, so that they travel while other layers
-    # compute, measured slower: 0.84 ms against 0.69 -- 72 small copy nodes and their edges cost more than they hide.)
+    # Every step moves all 36 layers' inputs from pinned host memory (they lie side by side) and all 36 outputs back; the
+    # copies are nodes of the step's graph, and the host waits for the whole step before the next one.  The inputs travel
+    # as two copies -- the first layers' on the step's own stream, the rest on a side stream while those layers run -- and
+    # so do the outputs: all but the last layers' leave on the side stream while the last layers run.  (One copy each
+    # way, nothing overlapped: 0.69 ms.  A copy per layer and direction: 0.84 ms -- 72 small copy nodes and their
+    # edges cost more than they hide.)
     h_in = torch.randn(LAYERS, HQ * D + 2 * HKV * D).half().pin_memory()
     h_out = torch.empty(LAYERS, HQ, D).pin_memory()
     e2e_steps = max(3, min(args.steps, 50))
-    e2e_graph, e2e_mode = None, "one graph per step: copy in, 36 layers, copy out"
+    head, tail = (min(args.e2e_head, LAYERS - 1), max(LAYERS - args.e2e_tail, 1)) if LAYERS >= 3 and not args.e2e_single_copies else (LAYERS, LAYERS)
+    e2e_graph, e2e_mode = None, ("one graph per step: inputs in two copies (layers 0-%d, then the rest beside them), 36 layers, outputs in two "
+                                 "copies (layers 0-%d beside the last layers, then the rest)" % (head - 1, tail - 1))
+    if head >= LAYERS:
+        e2e_mode = "one graph per step: copy in, 36 layers, copy out"
     try:
         e2e_graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream(device=dev)
         with torch.cuda.stream(stream):
             with torch.cuda.graph(e2e_graph, stream=stream):
-                packed.copy_(h_in, non_blocking=True)
-                layer_pass()
-                h_out.copy_(out, non_blocking=True)
+                if head < LAYERS:
+                    side.wait_stream(stream)
+                    packed[:head].copy_(h_in[:head], non_blocking=True)
+                    with torch.cuda.stream(side):
+                        packed[head:].copy_(h_in[head:], non_blocking=True)
+                    layer_pass(0, head)
+                    stream.wait_stream(side)
+                    layer_pass(head, tail)
+                    side.wait_stream(stream)
+                    with torch.cuda.stream(side):
+                        h_out[:tail].copy_(out[:tail], non_blocking=True)
+                    layer_pass(tail, LAYERS)
+                    h_out[tail:].copy_(out[tail:], non_blocking=True)
+                    stream.wait_stream(side)
+                else:
+                    packed.copy_(h_in, non_blocking=True)
+                    layer_pass()
+                    h_out.copy_(out, non_blocking=True)
                 state[1] += 1
         torch.cuda.synchronize()
     except Exception as exc:   # a driver that cannot capture the copies: the plain sequence below
@@ -480,6 +502,9 @@ def main() -> None:
     ap.add_argument("--seq-context", type=int, default=131072, help="seqshard workload: context length of the one session")
     ap.add_argument("--two-launches", action="store_true", help="append and attention as two launches per layer (A/B of the fused step)")
     ap.add_argument("--prefill-kernel", default="tcgen05", choices=["tcgen05", "mma"], help="prefill workload: which attention kernel")
+    ap.add_argument("--e2e-head", type=int, default=4, help="end-to-end leg: layers whose inputs travel in the first copy")
+    ap.add_argument("--e2e-tail", type=int, default=3, help="end-to-end leg: layers whose outputs travel in the last copy")
+    ap.add_argument("--e2e-single-copies", action="store_true", help="end-to-end leg: one copy in and one copy out per step, nothing overlapped (A/B)")
     ap.add_argument("--no-overlap", action="store_true", help="launch every kernel fully serialised (A/B of launch overlap)")
     ap.add_argument("--default-splits", action="store_true", help="batched workload: leave the split count to the library (A/B of the host-side picker)")
     ap.add_argument("--exchange", default="kernel", choices=["kernel", "nccl", "nccl-c"],

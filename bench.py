@@ -505,6 +505,7 @@ def main() -> None:
     ap.add_argument("--e2e-head", type=int, default=4, help="end-to-end leg: layers whose inputs travel in the first copy")
     ap.add_argument("--e2e-tail", type=int, default=3, help="end-to-end leg: layers whose outputs travel in the last copy")
     ap.add_argument("--e2e-single-copies", action="store_true", help="end-to-end leg: one copy in and one copy out per step, nothing overlapped (A/B)")
+    ap.add_argument("--no-prepare-ahead", action="store_true", help="prefill workload: every layer converts its whole prefix itself (A/B)")
     ap.add_argument("--no-overlap", action="store_true", help="launch every kernel fully serialised (A/B of launch overlap)")
     ap.add_argument("--default-splits", action="store_true", help="batched workload: leave the split count to the library (A/B of the host-side picker)")
     ap.add_argument("--exchange", default="kernel", choices=["kernel", "nccl", "nccl-c"],

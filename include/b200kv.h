@@ -433,6 +433,22 @@ B200KV_API int b200kv_prefill_attn(const b200kv_view* view, const void* q, int q
                         uint32_t query_heads, float scale, const b200kv_prefill_state* prefill_state,
                         void* workspace, size_t workspace_bytes, void* stream);
 
+/* The tcgen05 kernel's pre-pass ahead of time: converts cache positions [0, prepared_rows) to fp16 into `workspace`,
+ * laid out for a chunk that sees `rows` positions (rows = base_position + token_count of the attention call that
+ * follows; the capacity when that call uses a device-side prefill_state).  b200kv_prefill_attn_prepared is
+ * b200kv_prefill_attn for a workspace that holds those rows already: its own pre-pass then converts only
+ * [prepared_rows, rows) -- normally the chunk just appended.  The prefix of a layer does not depend on the chunk, so
+ * a host can run the prepare call of layer l + 1 on a second stream beside the attention of layer l (two workspaces in
+ * turn; order the calls with events: the prepare call after the attention that last used its workspace, the attention
+ * after its prepare call).  Positions below prepared_rows must not change between the two calls.  No counterpart in the
+ * reference.  B200KV_ERR_WORKSPACE when the workspace is too small for `rows`. */
+B200KV_API int b200kv_prefill_prepare(const b200kv_view* view, uint32_t prepared_rows, uint64_t rows, void* workspace,
+                           size_t workspace_bytes, void* stream);
+B200KV_API int b200kv_prefill_attn_prepared(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
+                                 float* gated_output, uint32_t token_count, uint32_t base_position,
+                                 uint32_t query_heads, float scale, const b200kv_prefill_state* prefill_state,
+                                 void* workspace, size_t workspace_bytes, uint32_t prepared_rows, void* stream);
+
 /* ---- prefix snapshot / restore ---------------------------------------------
  * Raw compact layout of AttentionLayerKvCacheStorage::download_raw/upload_raw
  * (src/prefill_v2/kv_cache.cpp:214-369): K first -- per kv head the int8 slice

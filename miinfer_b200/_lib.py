@@ -91,6 +91,8 @@ SIGNATURES = {
     "b200kv_prefill_scratch_bytes": (sz, [u64, u32, u32]),
     "b200kv_prefill_split_bytes": (sz, [u32, u32, u32, u32]),
     "b200kv_prefill_attn": (i32, [VP, vp, i32, vp, vp, u32, u32, u32, fl, vp, vp, sz, vp]),
+    "b200kv_prefill_prepare": (i32, [VP, u32, u64, vp, sz, vp]),
+    "b200kv_prefill_attn_prepared": (i32, [VP, vp, i32, vp, vp, u32, u32, u32, fl, vp, vp, sz, u32, vp]),
     "b200kv_snapshot_bytes": (sz, [VP, u64]),
     "b200kv_snapshot_save": (i32, [VP, u64, vp, vp]),
     "b200kv_snapshot_restore": (i32, [VP, u64, vp, vp]),

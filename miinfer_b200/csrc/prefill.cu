@@ -18,7 +18,10 @@ size_t prefill_tc5_workspace_bytes(uint32_t rows, uint32_t kv_heads, uint32_t he
 size_t prefill_tc5_split_bytes(uint32_t token_count, uint32_t query_heads, uint32_t kv_heads, uint32_t head_dim, uint32_t splits);
 int launch_prefill_tc5(const b200kv_view& view, const void* q, int q_is_f16, const float* gate, float* out,
                        uint32_t token_count, uint32_t base_position, const b200kv_prefill_state* prefill_state,
-                       uint32_t query_heads, float scale, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+                       uint32_t query_heads, float scale, void* workspace, size_t workspace_bytes, uint32_t prepared_rows,
+                       cudaStream_t stream);
+int launch_prefill_tc5_prepare(const b200kv_view& view, uint32_t prepared_rows, uint64_t rows, void* workspace, size_t workspace_bytes,
+                               cudaStream_t stream);
 int launch_prefill_mma(const b200kv_view& view, const void* q, int q_is_f16, const float* gate, float* out,
                        uint32_t token_count, uint32_t base_position, const b200kv_prefill_state* prefill_state,
                        uint32_t query_heads, float scale, cudaStream_t stream);
@@ -38,10 +41,27 @@ size_t b200kv_prefill_split_bytes(uint32_t token_count, uint32_t query_heads, ui
     return prefill_tc5_split_bytes(token_count, query_heads, kv_heads, head_dim, 8) + 2048;   // up to 8 splits, alignment slack
 }
 
+int b200kv_prefill_prepare(const b200kv_view* view, uint32_t prepared_rows, uint64_t rows, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+    int rc = validate_view(view);
+    if (rc != B200KV_OK) return rc;
+    if (view->head_dim != 128 && view->head_dim != 256) return B200KV_ERR_UNSUPPORTED;
+    if ((rc = ensure_device()) != B200KV_OK) return rc;
+    return launch_prefill_tc5_prepare(*view, prepared_rows, rows, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
 int b200kv_prefill_attn(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
                         float* gated_output, uint32_t token_count, uint32_t base_position,
                         uint32_t query_heads, float scale, const b200kv_prefill_state* prefill_state,
                         void* workspace, size_t workspace_bytes, void* stream) {
+    return b200kv_prefill_attn_prepared(view, q, q_dtype, gate, gated_output, token_count, base_position, query_heads, scale,
+                                        prefill_state, workspace, workspace_bytes, 0, stream);
+}
+
+int b200kv_prefill_attn_prepared(const b200kv_view* view, const void* q, int q_dtype, const float* gate,
+                                 float* gated_output, uint32_t token_count, uint32_t base_position,
+                                 uint32_t query_heads, float scale, const b200kv_prefill_state* prefill_state,
+                                 void* workspace, size_t workspace_bytes, uint32_t prepared_rows, void* stream) {
     int rc = validate_view(view);
     if (rc != B200KV_OK) return rc;
     if (q == nullptr || gated_output == nullptr || token_count == 0) return B200KV_ERR_INVALID;
@@ -51,7 +71,7 @@ int b200kv_prefill_attn(const b200kv_view* view, const void* q, int q_dtype, con
     if ((rc = ensure_device()) != B200KV_OK) return rc;
     // tcgen05 path when the caller provides the fp16 scratch; otherwise the register-resident mma.sync kernel
     rc = launch_prefill_tc5(*view, q, q_dtype == B200KV_F16, gate, gated_output, token_count, base_position, prefill_state, query_heads,
-                            scale, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+                            scale, workspace, workspace_bytes, prepared_rows, static_cast<cudaStream_t>(stream));
     if (rc != B200KV_ERR_UNSUPPORTED) return rc;
     return launch_prefill_mma(*view, q, q_dtype == B200KV_F16, gate, gated_output, token_count, base_position, prefill_state,
                               query_heads, scale, static_cast<cudaStream_t>(stream));

@@ -191,7 +191,7 @@ struct Layout {
     static constexpr int kOffRef = kOffBar + kNumBars * 8 + 16;   // [128 rows] {reference maximum, sequence}: handed from tile to tile
     static constexpr int kOffSum = kOffK;                         // [2 groups][128 rows] partial row sums: the K ring is idle in the epilogue
     static constexpr int kTotal = kOffRef + kBM * 8;
-    static constexpr int kAlloc = kTotal + 1024;
+    static constexpr int kAlloc = kTotal;   // the dynamic shared memory is declared 1024-byte aligned; the kernel checks it
     static constexpr uint32_t kTmemCols = 512;
     static constexpr uint32_t kColS = 0, kColQ = 128, kColO = 256;   // S: 2 x 64, Q: D/2 (fp16 pairs), O: D
 };
@@ -199,8 +199,8 @@ struct Layout {
 template <int D>
 __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_constant__ Tc5Params p) {
     using L = Layout<D>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar0 = sbase + L::kOffBar;
     auto bar = [&](int i) { return bar0 + i * 8; };
@@ -238,6 +238,25 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc5_kernel(const __grid_c
     const int split = static_cast<int>(blockIdx.z), nsplit = static_cast<int>(p.kv_splits);
     const int tile0 = static_cast<int>(static_cast<long long>(ntiles_all) * split / nsplit);
     const int ntiles = static_cast<int>(static_cast<long long>(ntiles_all) * (split + 1) / nsplit) - tile0;   // tiles of this CTA
+
+    // The layout (swizzled TMA tiles, MMA descriptors) needs the 1024-byte alignment the declaration above asks for; the
+    // allocation has no slack for rounding up, so that a CTA of the neighbouring kernels fits beside this one on an SM.
+    // Should a driver ever hand out another base, nothing of the layout is touched: the CTA's rows come out as NaN.
+    if ((sbase & 1023u) != 0) {
+        pdl_wait();
+        const float nan = __int_as_float(0x7fc00000);
+        for (uint32_t r = tid; r < static_cast<uint32_t>(kBM); r += kThreads)
+            if (nsplit > 1 && row0 + r < total_rows)
+                p.part_ml[(static_cast<size_t>(split) * p.kv_heads + kv_head) * p.rows_padded + row0 + r] = make_float2(0.0f, nan);
+        if (nsplit == 1)
+            for (uint32_t i = tid; i < static_cast<uint32_t>(kBM) * (D / 4); i += kThreads) {
+                const uint32_t gr = row0 + i / (D / 4);
+                if (gr >= total_rows) continue;
+                const size_t off = (static_cast<size_t>(gr / G) * p.query_heads + kv_head * G + gr % G) * D + (i % (D / 4)) * 4;
+                *reinterpret_cast<float4*>(p.out + off) = make_float4(nan, nan, nan, nan);
+            }
+        return;
+    }
 
     // ---- set-up: barriers, TMEM, Q tile -----------------------------------------------------------------
     if (tid == 0) {
@@ -590,8 +609,10 @@ struct DequantParams {
     b200kv_view view;
     __half* k_out;       // [kv_heads][scratch_rows][D]
     __half* v_out;
-    uint32_t rows;       // positions to convert
+    uint32_t rows;       // positions that hold data; rows from here up to row_end are zero-filled
     uint32_t scratch_rows;
+    uint32_t row_begin;  // this launch converts positions [row_begin, row_end): the rows below were converted ahead of
+    uint32_t row_end;    // the chunk (b200kv_prefill_prepare), possibly beside the previous layer's attention
 };
 
 template <int D>
@@ -608,8 +629,9 @@ __global__ void __launch_bounds__(256) dequant_prefix_kernel(const __grid_consta
     __half* out = (side == 0 ? p.k_out : p.v_out) + static_cast<size_t>(head) * p.scratch_rows * D;
     const uint32_t nblk = D / p.view.qblock;
     const uint64_t head_row0 = static_cast<uint64_t>(head) * p.view.capacity;
-    const size_t total = static_cast<size_t>(p.scratch_rows) * CPR;   // rows past `rows` are zero-filled: the last tile reads them
-    for (size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t total = static_cast<size_t>(p.row_end) * CPR;   // rows past `rows` are zero-filled: the last tile reads them
+    for (size_t idx = static_cast<size_t>(p.row_begin) * CPR + static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+         idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const uint32_t pos = static_cast<uint32_t>(idx / CPR), c16 = static_cast<uint32_t>(idx % CPR);
         uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
         if (pos >= p.rows) {
@@ -655,23 +677,37 @@ bool encode_f16_plane(CUtensorMap* map, void* base, uint32_t d, uint64_t rows) {
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The pre-pass over positions [row_begin, row_end) of every kv head, K and V.
 template <int D>
-int launch_tc5(const b200kv_view& view, Tc5Params& p, __half* k_scratch, __half* v_scratch, uint32_t rows, cudaStream_t stream) {
+int launch_dequant(const b200kv_view& view, __half* k_scratch, __half* v_scratch, uint32_t rows, uint32_t scratch_rows,
+                   uint32_t row_begin, uint32_t row_end, cudaStream_t stream) {
+    if (row_begin >= row_end) return B200KV_OK;
+    DequantParams dp{};
+    dp.view = view;
+    dp.k_out = k_scratch;
+    dp.v_out = v_scratch;
+    dp.rows = rows;
+    dp.scratch_rows = scratch_rows;
+    dp.row_begin = row_begin;
+    dp.row_end = row_end;
+    const size_t units = static_cast<size_t>(row_end - row_begin) * (D / 16);
+    unsigned blocks = static_cast<unsigned>((units + 255) / 256);
+    if (blocks > 148u * 4u) blocks = 148u * 4u;
+    B200KV_CUDA_TRY(launch_kernel(dequant_prefix_kernel<D>, dim3(blocks, view.kv_heads, 2), dim3(256), 0, stream, true, dp));
+    return B200KV_OK;
+}
+
+template <int D>
+int launch_tc5(const b200kv_view& view, Tc5Params& p, __half* k_scratch, __half* v_scratch, uint32_t rows, uint32_t prepared_rows,
+               cudaStream_t stream) {
     using L = Layout<D>;
     static std::atomic<uint64_t> done{0};   // one per kernel instantiation: devices that have opted in
     const cudaError_t attr_err = opt_in_dynamic_smem(reinterpret_cast<const void*>(prefill_tc5_kernel<D>), L::kAlloc, done);
     if (attr_err != cudaSuccess) { set_last_cuda_error(attr_err, "cudaFuncSetAttribute(prefill_tc5)"); return B200KV_ERR_CUDA; }
     if (rows > 0) {
-        DequantParams dp{};
-        dp.view = view;
-        dp.k_out = k_scratch;
-        dp.v_out = v_scratch;
-        dp.rows = rows;
-        dp.scratch_rows = p.scratch_rows;
-        const size_t units = static_cast<size_t>(p.scratch_rows) * (D / 16);
-        unsigned blocks = static_cast<unsigned>((units + 255) / 256);
-        if (blocks > 148u * 4u) blocks = 148u * 4u;
-        B200KV_CUDA_TRY(launch_kernel(dequant_prefix_kernel<D>, dim3(blocks, view.kv_heads, 2), dim3(256), 0, stream, true, dp));
+        const int rc = launch_dequant<D>(view, k_scratch, v_scratch, rows, p.scratch_rows, prepared_rows < rows ? prepared_rows : rows,
+                                         p.scratch_rows, stream);
+        if (rc != B200KV_OK) return rc;
     }
     const uint32_t G = p.query_heads / p.kv_heads;
     const uint32_t row_tiles = (p.token_count * G + kBM - 1) / kBM;
@@ -726,7 +762,8 @@ static uint32_t pick_kv_splits(uint32_t units, uint32_t min_tiles) {
 // register-resident mma.sync kernel.
 int launch_prefill_tc5(const b200kv_view& view, const void* q, int q_is_f16, const float* gate, float* out,
                        uint32_t token_count, uint32_t base_position, const b200kv_prefill_state* prefill_state,
-                       uint32_t query_heads, float scale, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                       uint32_t query_heads, float scale, void* workspace, size_t workspace_bytes, uint32_t prepared_rows,
+                       cudaStream_t stream) {
     // rows the chunk can see: known on the host unless a device-side state overrides it (then: the whole cache)
     uint64_t rows = prefill_state ? view.capacity : static_cast<uint64_t>(base_position) + token_count;
     if (rows > view.capacity) rows = view.capacity;
@@ -771,8 +808,25 @@ int launch_prefill_tc5(const b200kv_view& view, const void* q, int q_is_f16, con
             p.part_ml = reinterpret_cast<float2*>(p.part_o + static_cast<size_t>(want) * view.kv_heads * p.rows_padded * view.head_dim);
         }
     }
-    return view.head_dim == 128 ? launch_tc5<128>(view, p, k_scratch, v_scratch, static_cast<uint32_t>(rows), stream)
-                                : launch_tc5<256>(view, p, k_scratch, v_scratch, static_cast<uint32_t>(rows), stream);
+    return view.head_dim == 128 ? launch_tc5<128>(view, p, k_scratch, v_scratch, static_cast<uint32_t>(rows), prepared_rows, stream)
+                                : launch_tc5<256>(view, p, k_scratch, v_scratch, static_cast<uint32_t>(rows), prepared_rows, stream);
+}
+
+// The pre-pass alone, for positions [0, prepared_rows), into the scratch laid out for a chunk that sees `rows` positions
+// (the same `rows` the attention call derives: base_position + token_count, or the capacity with a device-side state).
+int launch_prefill_tc5_prepare(const b200kv_view& view, uint32_t prepared_rows, uint64_t rows, void* workspace, size_t workspace_bytes,
+                               cudaStream_t stream) {
+    if (rows > view.capacity) rows = view.capacity;
+    if (prepared_rows > rows) return B200KV_ERR_RANGE;
+    const uint32_t scratch_rows = static_cast<uint32_t>((rows + kBN - 1) / kBN * kBN);
+    if (workspace == nullptr || workspace_bytes < prefill_tc5_workspace_bytes(static_cast<uint32_t>(rows), view.kv_heads, view.head_dim))
+        return B200KV_ERR_WORKSPACE;
+    if (static_cast<uint64_t>(view.kv_heads) * scratch_rows > 0x7fffffffull) return B200KV_ERR_UNSUPPORTED;
+    uint8_t* ws = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~static_cast<uintptr_t>(1023));
+    __half* k_scratch = reinterpret_cast<__half*>(ws);
+    __half* v_scratch = k_scratch + static_cast<size_t>(view.kv_heads) * scratch_rows * view.head_dim;
+    return view.head_dim == 128 ? launch_dequant<128>(view, k_scratch, v_scratch, prepared_rows, scratch_rows, 0, prepared_rows, stream)
+                                : launch_dequant<256>(view, k_scratch, v_scratch, prepared_rows, scratch_rows, 0, prepared_rows, stream);
 }
 
 }  // namespace b200kv

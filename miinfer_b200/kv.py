@@ -20,7 +20,7 @@ from ._lib import B200KvError, PoolCounters, ReuseOptions, ReuseStats, View, che
 __all__ = [
     "KvCacheQuantMode", "RopeMode", "AttentionKvCacheView", "AttentionLayerKvCacheStorage",
     "launch_kv_store_quant", "launch_decode_attention_quant", "launch_decode_attention_batched", "launch_decode_step",
-    "launch_decode_partials", "launch_merge_partials", "launch_merge_partials_packed", "packed_partial", "partial_views", "launch_suffix_attention_quant",
+    "launch_decode_partials", "launch_merge_partials", "launch_merge_partials_packed", "packed_partial", "partial_views", "launch_suffix_attention_quant", "prepare_suffix_attention",
     "Exchange", "launch_decode_attention_sharded", "decode_workspace", "prefill_workspace", "view_table", "make_decode_state", "make_prefill_state",
     "SnapshotPool", "ReusableContext", "DistMerge", "launch_q_split_norm_rope", "launch_decode_state_advance", "q8_1_blocks", "exchange_words", "set_status_word", "workspace_reset", "set_decode_kernel",
     "token_sequence_hash", "save_session", "load_session", "find_matching_session", "decode_kernel_kind", "set_launch_overlap", "B200KvError", "FORCE_GENERIC",
@@ -426,12 +426,23 @@ def launch_merge_partials_packed(packed: torch.Tensor, *, num_parts: int, query_
 
 def launch_suffix_attention_quant(view: View, q: torch.Tensor, gate: Optional[torch.Tensor], gated_output: torch.Tensor,
                                   workspace: Optional[torch.Tensor], token_count: int, base_position: int, *, query_heads: int,
-                                  scale: float, prefill_state: Optional[torch.Tensor] = None,
+                                  scale: float, prefill_state: Optional[torch.Tensor] = None, prepared_rows: int = 0,
                                   stream: Optional[torch.cuda.Stream] = None) -> None:
-    """launch_qwen35_splitk_suffix_attention_quant (qwen3_gpu_primitives.hpp:670-692)."""
-    check(lib.b200kv_prefill_attn(C.byref(view), _ptr(q), _dtype(q), _ptr(gate), _ptr(gated_output), token_count,
-                                  base_position, query_heads, scale, _ptr(prefill_state), _ptr(workspace),
-                                  0 if workspace is None else workspace.numel(), _stream(stream)), "b200kv_prefill_attn")
+    """launch_qwen35_splitk_suffix_attention_quant (qwen3_gpu_primitives.hpp:670-692).  `prepared_rows`: cache positions
+    whose fp16 copy `prepare_suffix_attention` has already put into this workspace."""
+    check(lib.b200kv_prefill_attn_prepared(C.byref(view), _ptr(q), _dtype(q), _ptr(gate), _ptr(gated_output), token_count,
+                                           base_position, query_heads, scale, _ptr(prefill_state), _ptr(workspace),
+                                           0 if workspace is None else workspace.numel(), prepared_rows, _stream(stream)),
+          "b200kv_prefill_attn_prepared")
+
+
+def prepare_suffix_attention(view: View, prepared_rows: int, rows: int, workspace: torch.Tensor,
+                             stream: Optional[torch.cuda.Stream] = None) -> None:
+    """b200kv_prefill_prepare: the tcgen05 suffix kernel's pre-pass over positions [0, prepared_rows), ahead of the
+    attention call that sees `rows` positions and is told `prepared_rows` -- on a second stream it runs beside the
+    previous layer's attention."""
+    check(lib.b200kv_prefill_prepare(C.byref(view), prepared_rows, rows, _ptr(workspace), workspace.numel(), _stream(stream)),
+          "b200kv_prefill_prepare")
 
 
 def q8_1_blocks(query_heads: int, head_dim: int, device=None) -> torch.Tensor:

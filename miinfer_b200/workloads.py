@@ -117,13 +117,38 @@ def run_prefill(args, torch, dist, rank, world, local_rank):
     # the fp16 scratch of the visible prefix selects the tcgen05 kernel; --prefill-kernel mma runs the mma.sync one
     # (with room for KV-split partials: the chunk's row tiles alone do not fill the SMs)
     ws = None if args.prefill_kernel == "mma" else kv.prefill_workspace(P + T, hkv, D, token_count=T, query_heads=hq)
+    # The fp16 copy of a layer's prefix does not depend on the chunk: with a second workspace and a second stream the
+    # pre-pass of layer l + 1 runs beside the attention of layer l; a layer's own launch then converts only its chunk.
+    ahead = ws is not None and not getattr(args, "no_prepare_ahead", False) and LAYERS >= 2
+    ws2 = kv.prefill_workspace(P + T, hkv, D, token_count=T, query_heads=hq) if ahead else None
+    stream = torch.cuda.Stream()
+    side = torch.cuda.Stream() if ahead else None
+    attended = [torch.cuda.Event() for _ in range(LAYERS)] if ahead else None
+    prepared = [torch.cuda.Event() for _ in range(LAYERS)] if ahead else None
+
+    def prepare(l):
+        side.wait_event(attended[l - 2]) if l >= 2 else side.wait_stream(stream)   # the workspace's previous user
+        kv.prepare_suffix_attention(views[l], P, P + T, ws2 if l & 1 else ws, stream=side)
+        prepared[l].record(side)
 
     def step():
+        if ahead:
+            prepare(0)
+            prepare(1)
         for l in range(LAYERS):
             kv.launch_kv_store_quant(views[l], k_new[l], v_new[l], w, T, P, rope_mode=kv.RopeMode.SECTIONED64, theta=1.0e6)
-            kv.launch_suffix_attention_quant(views[l], q[l], gate[l], out[l], ws, T, P, query_heads=hq, scale=D ** -0.5)
+            if ahead:
+                stream.wait_event(prepared[l])
+                kv.launch_suffix_attention_quant(views[l], q[l], gate[l], out[l], ws2 if l & 1 else ws, T, P, query_heads=hq,
+                                                 scale=D ** -0.5, prepared_rows=P)
+                attended[l].record(stream)
+                if l + 2 < LAYERS:
+                    prepare(l + 2)
+            else:
+                kv.launch_suffix_attention_quant(views[l], q[l], gate[l], out[l], ws, T, P, query_heads=hq, scale=D ** -0.5)
+        if ahead:
+            stream.wait_stream(side)
 
-    stream = torch.cuda.Stream()
     kv.set_launch_overlap(0 if args.no_overlap else 1)   # every kernel of the chunk waits for its predecessor itself
     ms = _time(torch, dist, stream, step, args.warmup, args.steps)
     kv.set_launch_overlap(0)
@@ -145,7 +170,8 @@ def run_prefill(args, torch, dist, rank, world, local_rank):
                                    f"kv heads split over {world} GPU(s); kernel {args.prefill_kernel}", "l2": "L2 flushed implicitly: 16 layer caches of 19 MB rotate"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf_peak * world, "unit": "TFLOP/s", "frac": achieved / (tf_peak * world),
                          "traffic": None, "peak_kind": f"{kind} (bf16_tflops_sustained) x {world} GPUs"},
-            "check": check, "gpu_launches": args.steps * LAYERS * (2 if ws is None else 4)}
+            "check": check, "gpu_launches": args.steps * LAYERS * (2 if ws is None else (5 if ahead else 4)),
+            "prefix_prepass": "beside the previous layers' attention (second stream, two workspaces)" if ahead else "inside the layer's own launch sequence"}
 
 
 def run_seqshard(args, torch, dist, rank, world, local_rank):

@@ -253,3 +253,48 @@ def test_suffix_chunks_back_to_back_with_launch_overlap(cuda):
         outs[overlap] = out.cpu()
     assert torch.isfinite(outs[1]).all()
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("P,T,H,Hq,d,prepared", [(2048, 128, 4, 24, 256, 2048), (1500, 200, 8, 32, 128, 1000), (640, 64, 4, 24, 256, 0)])
+def test_suffix_attention_over_a_prefix_converted_ahead_on_a_second_stream(cuda, P, T, H, Hq, d, prepared):
+    """b200kv_prefill_prepare converts the prefix to fp16 ahead of the chunk (here on a second stream, ordered by
+    events, with launch overlap on); the attention call that is told so converts only the rest.  Two layers in turn
+    on two workspaces, as a host pipelines them; every output must equal the plain call's bit for bit and match the oracle."""
+    rng = np.random.default_rng(P + T + prepared)
+    hosts = [filled(rng, P + T, H, d, 32, 3, cap=P + T + 64, std=0.5) for _ in range(2)]
+    sts = [upload(h) for h in hosts]
+    q = [(rng.standard_normal((T, Hq, d)) * 0.5).astype(np.float32) for _ in range(2)]
+    gate = [(rng.standard_normal((T, Hq, d)) * 0.5).astype(np.float32) for _ in range(2)]
+    plain = torch.full((2, T, Hq, d), float("nan"), device="cuda")
+    ws = [kv.prefill_workspace(P + T, H, d, token_count=T, query_heads=Hq) for _ in range(2)]
+    for l in range(2):
+        kv.launch_suffix_attention_quant(sts[l].view(), to_dev(q[l]), to_dev(gate[l]), plain[l], ws[l], T, P, query_heads=Hq, scale=d ** -0.5)
+    torch.cuda.synchronize()
+    for w in ws:
+        w.fill_(0xFF)            # nothing of the plain calls' scratch may help (0xFFFF is a NaN in fp16)
+    ahead = torch.full((2, T, Hq, d), float("nan"), device="cuda")
+    qd, gd = [to_dev(x) for x in q], [to_dev(x) for x in gate]
+    main, side = torch.cuda.Stream(), torch.cuda.Stream()
+    done = [torch.cuda.Event() for _ in range(2)]
+    kv.set_launch_overlap(1)
+    try:
+        with torch.cuda.stream(main):
+            side.wait_stream(main)
+            for l in range(2):
+                kv.prepare_suffix_attention(sts[l].view(), prepared, P + T, ws[l], stream=side)
+                done[l].record(side)
+            for l in range(2):
+                main.wait_event(done[l])
+                kv.launch_suffix_attention_quant(sts[l].view(), qd[l], gd[l], ahead[l], ws[l], T, P, query_heads=Hq, scale=d ** -0.5,
+                                                 prepared_rows=prepared)
+        torch.cuda.synchronize()
+    finally:
+        kv.set_launch_overlap(0)
+    assert torch.equal(ahead.cpu(), plain.cpu())
+    for l in range(2):
+        assert np.max(np.abs(ahead[l].cpu().numpy() - hosts[l].suffix_ref(q[l], gate[l], P, d ** -0.5))) <= TOL
+    # more rows declared than the chunk can see, or a workspace that is too small, are refused
+    with pytest.raises(kv.B200KvError):
+        kv.prepare_suffix_attention(sts[0].view(), P + T + 1, P + T, ws[0])
+    with pytest.raises(kv.B200KvError):
+        kv.prepare_suffix_attention(sts[0].view(), 16, P + T, torch.empty(1024, dtype=torch.uint8, device="cuda"))

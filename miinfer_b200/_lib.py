@@ -100,6 +100,7 @@ SIGNATURES = {
     "b200kv_download_key": (i32, [VP, u64, vp, vp]),
     "b200kv_download_value": (i32, [VP, u64, vp, vp]),
     "b200kv_token_sequence_hash": (u64, [C.POINTER(u32), sz]),
+    "b200kv_plan_batched_decode": (i32, [C.POINTER(u32), u32, u32, u32, C.POINTER(u32), C.POINTER(u32)]),
     "b200kv_prefix_match": (i32, [C.c_char_p, C.c_char_p, u32, vp, u32, C.c_char_p, C.c_char_p, vp, u32]),
     "b200kv_session_filename": (i32, [u64, u32, C.c_char_p, sz]),
     "b200kv_session_save": (i32, [C.c_char_p, C.c_char_p, C.c_char_p, vp, u32, VP, u32, vp]),

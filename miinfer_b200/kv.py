@@ -20,7 +20,7 @@ from ._lib import B200KvError, PoolCounters, ReuseOptions, ReuseStats, View, che
 __all__ = [
     "KvCacheQuantMode", "RopeMode", "AttentionKvCacheView", "AttentionLayerKvCacheStorage",
     "launch_kv_store_quant", "launch_decode_attention_quant", "launch_decode_attention_batched", "launch_decode_step",
-    "launch_decode_partials", "launch_merge_partials", "launch_merge_partials_packed", "packed_partial", "partial_views", "launch_suffix_attention_quant", "prepare_suffix_attention",
+    "launch_decode_partials", "launch_merge_partials", "launch_merge_partials_packed", "packed_partial", "partial_views", "launch_suffix_attention_quant", "prepare_suffix_attention", "plan_batched_decode",
     "Exchange", "launch_decode_attention_sharded", "decode_workspace", "prefill_workspace", "view_table", "make_decode_state", "make_prefill_state",
     "SnapshotPool", "ReusableContext", "DistMerge", "launch_q_split_norm_rope", "launch_decode_state_advance", "q8_1_blocks", "exchange_words", "set_status_word", "workspace_reset", "set_decode_kernel",
     "token_sequence_hash", "save_session", "load_session", "find_matching_session", "decode_kernel_kind", "set_launch_overlap", "B200KvError", "FORCE_GENERIC",
@@ -434,6 +434,16 @@ def launch_suffix_attention_quant(view: View, q: torch.Tensor, gate: Optional[to
                                            base_position, query_heads, scale, _ptr(prefill_state), _ptr(workspace),
                                            0 if workspace is None else workspace.numel(), prepared_rows, _stream(stream)),
           "b200kv_prefill_attn_prepared")
+
+
+def plan_batched_decode(lengths, kv_heads: int, cta_slots: int = 0):
+    """b200kv_plan_batched_decode: (num_splits, max_length) to pass to launch_decode_attention_batched for sessions of
+    these lengths (host integers).  Host arithmetic only."""
+    arr = (C.c_uint32 * max(1, len(lengths)))(*[int(x) for x in lengths])
+    splits, bound = C.c_uint32(0), C.c_uint32(0)
+    check(lib.b200kv_plan_batched_decode(arr, len(lengths), kv_heads, cta_slots, C.byref(splits), C.byref(bound)),
+          "b200kv_plan_batched_decode")
+    return int(splits.value), int(bound.value)
 
 
 def prepare_suffix_attention(view: View, prepared_rows: int, rows: int, workspace: torch.Tensor,

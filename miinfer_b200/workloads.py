@@ -312,7 +312,7 @@ def run_batched(args, torch, dist, rank, world, local_rank):
     plus 16 sessions restored from a shared 4096-token prefix snapshot kept in a snapshot pool; sessions are bin-packed
     over the ranks."""
     from miinfer_b200 import kv
-    from miinfer_b200.partition import partition_sessions, pick_batched_plan
+    from miinfer_b200.partition import partition_sessions
 
     HQ, HKV, D, LAYERS = 32, 8, 128, min(args.layers, 4)
     rng = np.random.default_rng(42)
@@ -350,7 +350,7 @@ def run_batched(args, torch, dist, rank, world, local_rank):
                 assert matched == 4096
     restore_ms = _time(torch, dist, stream, restore, 1, 3) if restored or dist is not None else 0.0
     # the host knows this step's lengths: pick the split size whose CTAs pack the device best (0 = library default)
-    splits, bound = (0, max(lengths)) if getattr(args, "default_splits", False) else pick_batched_plan(lengths, HKV)
+    splits, bound = (0, max(lengths)) if getattr(args, "default_splits", False) else kv.plan_batched_decode(lengths, HKV)
     kv.set_launch_overlap(0 if args.no_overlap else 1)
     for l in range(LAYERS):   # fills the device view tables once
         kv.launch_decode_attention_batched([c.view() for c in caches[l]], tables[l], lens, bound, q[l], query_heads=HQ,

@@ -108,3 +108,18 @@ def test_pick_batched_plan_packs_the_slots_and_respects_budgets():
     assert pick_batched_plan([16384] * 256, 8)[0] <= 4
     assert pick_batched_plan([], 8)[0] == 1
     assert pick_batched_plan([0, 0], 8)[0] == 1
+
+
+def test_native_batched_plan_equals_the_python_statement():
+    """b200kv_plan_batched_decode is host arithmetic: callable without a GPU.  Same pair as partition.pick_batched_plan
+    for mixed, uniform, tiny, empty and over-budget session sets, and for another slot count."""
+    from miinfer_b200 import kv
+    from miinfer_b200.partition import pick_batched_plan
+
+    rng = np.random.default_rng(5)
+    cases = [[int(x) for x in rng.integers(1, 20000, size=n)] for n in (1, 3, 10, 40, 80, 200)]
+    cases += [[4096] * 16, [100], [], [0, 0], [16384] * 256, [131072], [300, 0, 70000]]
+    for lengths in cases:
+        for kv_heads, slots in ((8, 296), (4, 296), (8, 264)):
+            assert kv.plan_batched_decode(lengths, kv_heads, slots) == pick_batched_plan(lengths, kv_heads, cta_slots=slots), (lengths[:4], kv_heads, slots)
+    assert kv.plan_batched_decode([5000, 9000], 8) == kv.plan_batched_decode([5000, 9000], 8, 296)     # 0 = the B200 default

@@ -368,13 +368,7 @@ extern "C" int b200kv_append(const b200kv_view* view, const void* key, const voi
     p.base_position = base_position;
     p.rope_mode = rope_mode;
     p.epsilon = epsilon;
-    if (rope_mode == B200KV_ROPE_NEOX_FULL) {
-        const uint32_t d = view->head_dim;
-        for (uint32_t i = 0; i < d / 2; ++i)
-            p.inv_freq[i] = std::pow(theta, -static_cast<float>(2 * i) / static_cast<float>(d));
-    } else if (rope_mode == B200KV_ROPE_SECTIONED64) {
-        p.sectioned_step = std::pow(theta, -2.0f / 64.0f);
-    }
+    rope_constants(rope_mode, theta, view->head_dim, p.inv_freq, &p.sectioned_step);
 
     const uint32_t d = view->head_dim;
     const uint32_t heads_per_pass = 512 / d;   // 16 K blocks and 16 V blocks of 32 dims per pass

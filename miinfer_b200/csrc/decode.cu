@@ -425,12 +425,7 @@ int b200kv_decode_step(const b200kv_view* view, const void* key, const void* val
     p.k_norm_weight = k_norm_weight;
     p.rope_mode = rope_mode;
     p.epsilon = epsilon;
-    if (rope_mode == B200KV_ROPE_NEOX_FULL) {
-        for (uint32_t i = 0; i < view->head_dim / 2; ++i)
-            p.inv_freq[i] = std::pow(theta, -static_cast<float>(2 * i) / static_cast<float>(view->head_dim));
-    } else if (rope_mode == B200KV_ROPE_SECTIONED64) {
-        p.sectioned_step = std::pow(theta, -2.0f / 64.0f);
-    }
+    rope_constants(rope_mode, theta, view->head_dim, p.inv_freq, &p.sectioned_step);
     const uint32_t max_length = decode_state ? static_cast<uint32_t>(view->capacity) : position + 1;
     MergeParams mp{};
     mp.query_heads = query_heads;

@@ -106,6 +106,20 @@ struct DecodeParams {
     MergeParams fuse;
 };
 
+// TMA descriptors are a pure function of (base address, extents, box, element type, swizzle); encoding one costs a
+// driver call.  A decode loop asks for the same few dozen descriptors on every step, so each host thread keeps the last
+// ones it encoded (256 entries, direct-mapped on the base address).
+struct TensorMapKey {
+    const void* base;
+    uint64_t rows;
+    uint32_t row_bytes, box_bytes, box_rows, kind;   // kind: element type and swizzle as the caller numbers them
+    bool operator==(const TensorMapKey& o) const {
+        return base == o.base && rows == o.rows && row_bytes == o.row_bytes && box_bytes == o.box_bytes && box_rows == o.box_rows && kind == o.kind;
+    }
+};
+bool tensor_map_lookup(const TensorMapKey& key, CUtensorMap* out);
+void tensor_map_remember(const TensorMapKey& key, const CUtensorMap& map);
+
 // Tag for the tagged words of one launch: a process-wide counter that skips 0.
 uint32_t next_launch_tag();
 // The device buffer registered with b200kv_set_timeline_buffer for the current device (null if none).

@@ -575,6 +575,9 @@ namespace {
 int encode_plane_map(int8_t* plane, const b200kv_view& view, uint32_t tile_positions, CUtensorMap* out) {
     EncodeFn fn = encoder();
     if (fn == nullptr) return B200KV_ERR_UNSUPPORTED;
+    const TensorMapKey key{plane, static_cast<uint64_t>(view.kv_heads) * view.capacity, static_cast<uint32_t>(kD), static_cast<uint32_t>(kD),
+                           tile_positions, 1u};   // kind 1: bytes, 128-byte swizzle
+    if (tensor_map_lookup(key, out)) return B200KV_OK;
     const cuuint64_t dims[2] = {kD, static_cast<cuuint64_t>(view.kv_heads) * view.capacity};
     const cuuint64_t strides[1] = {kD};
     const cuuint32_t box[2] = {kD, tile_positions};
@@ -582,7 +585,9 @@ int encode_plane_map(int8_t* plane, const b200kv_view& view, uint32_t tile_posit
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, plane, dims, strides, box, elem,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? B200KV_OK : B200KV_ERR_UNSUPPORTED;
+    if (r != CUDA_SUCCESS) return B200KV_ERR_UNSUPPORTED;
+    tensor_map_remember(key, *out);
+    return B200KV_OK;
 }
 }  // namespace
 

@@ -603,12 +603,18 @@ EncodeFn wide_encoder() {
 bool encode_wide_plane(CUtensorMap* map, int8_t* plane, const b200kv_view& view) {
     EncodeFn fn = wide_encoder();
     if (fn == nullptr) return false;
+    const TensorMapKey key{plane, static_cast<uint64_t>(view.kv_heads) * view.capacity, static_cast<uint32_t>(kD), 128u,
+                           static_cast<uint32_t>(kTileM), 1u};   // kind 1: bytes, 128-byte swizzle
+    if (tensor_map_lookup(key, map)) return true;
     const cuuint64_t dims[2] = {kD, static_cast<cuuint64_t>(view.kv_heads) * view.capacity};
     const cuuint64_t strides[1] = {kD};
     const cuuint32_t box[2] = {128, kTileM};
     const cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, plane, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    if (fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, plane, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    tensor_map_remember(key, *map);
+    return true;
 }
 
 template <int NBLK, int G, bool Q_F16>

@@ -76,6 +76,11 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// Host side: the RoPE constants of a launch -- inv_freq[i] = theta^(-2i/d) for i < d/2 (NeoX) or the step theta^(-2/64)
+// of the sectioned form -- kept per thread for the last (theta, d) asked for, so that a decode loop pays the 64-128
+// powf calls once and not per launch.
+void rope_constants(int rope_mode, float theta, uint32_t head_dim, float* inv_freq, float* sectioned_step);
+
 // sin/cos of an fp32 angle from IEEE double operations only (multiply, fma,
 // round-to-integer), so that a host evaluating the same sequence gets the same
 // floats: the RoPE trig is part of the bit-exact int8 contract of the append

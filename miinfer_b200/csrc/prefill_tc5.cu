@@ -669,12 +669,17 @@ EncodeFn tc5_encoder() {
 bool encode_f16_plane(CUtensorMap* map, void* base, uint32_t d, uint64_t rows) {
     EncodeFn fn = tc5_encoder();
     if (fn == nullptr) return false;
+    const TensorMapKey key{base, rows, d * 2u, 128u, static_cast<uint32_t>(kBN), 2u};   // kind 2: fp16, 128-byte swizzle
+    if (tensor_map_lookup(key, map)) return true;
     const cuuint64_t dims[2] = {d, rows};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(d) * 2};
     const cuuint32_t box[2] = {64, kBN};
     const cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    if (fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    tensor_map_remember(key, *map);
+    return true;
 }
 
 // The pre-pass over positions [row_begin, row_end) of every kv head, K and V.

@@ -117,12 +117,7 @@ int b200kv_q_split_norm_rope(const void* qfull, int in_dtype, const float* q_nor
     p.heads = heads;
     p.rope_mode = rope_mode;
     p.epsilon = epsilon;
-    if (rope_mode == B200KV_ROPE_NEOX_FULL) {
-        for (uint32_t i = 0; i < head_dim / 2; ++i)
-            p.inv_freq[i] = std::pow(theta, -static_cast<float>(2 * i) / static_cast<float>(head_dim));
-    } else if (rope_mode == B200KV_ROPE_SECTIONED64) {
-        p.sectioned_step = std::pow(theta, -2.0f / 64.0f);
-    }
+    rope_constants(rope_mode, theta, head_dim, p.inv_freq, &p.sectioned_step);
     const uint64_t rows = static_cast<uint64_t>(token_count) * heads;
     const unsigned grid = static_cast<unsigned>((rows + kQSideWarps - 1) / kQSideWarps);
     cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -4,6 +4,7 @@
 #include "decode_common.cuh"
 
 #include <atomic>
+#include <cmath>
 #include <mutex>
 #include <cstdio>
 #include <cstring>
@@ -25,6 +26,55 @@ uint32_t next_launch_tag() {
 
 constexpr int kMaxDevices = 64;
 static std::atomic<uint32_t*> g_status_word[kMaxDevices] = {};
+namespace {
+struct TensorMapSlot {
+    TensorMapKey key;
+    CUtensorMap map;
+    bool used;
+};
+TensorMapSlot* tensor_map_slot(const TensorMapKey& key) {
+    static thread_local TensorMapSlot slots[256] = {};
+    const uint64_t a = reinterpret_cast<uintptr_t>(key.base);
+    return &slots[((a >> 8) ^ (a >> 16) ^ (a >> 24) ^ key.box_rows ^ key.kind) & 255u];
+}
+}  // namespace
+
+bool tensor_map_lookup(const TensorMapKey& key, CUtensorMap* out) {
+    const TensorMapSlot* s = tensor_map_slot(key);
+    if (!s->used || !(s->key == key)) return false;
+    *out = s->map;
+    return true;
+}
+
+void tensor_map_remember(const TensorMapKey& key, const CUtensorMap& map) {
+    TensorMapSlot* s = tensor_map_slot(key);
+    s->key = key;
+    s->map = map;
+    s->used = true;
+}
+
+void rope_constants(int rope_mode, float theta, uint32_t head_dim, float* inv_freq, float* sectioned_step) {
+    static thread_local float cached_theta = 0.0f, cached_step = 0.0f, step_theta = 0.0f;
+    static thread_local uint32_t cached_dim = 0;
+    static thread_local float table[128];
+    if (rope_mode == B200KV_ROPE_NEOX_FULL) {
+        const uint32_t half = head_dim / 2 > 128 ? 128 : head_dim / 2;
+        if (cached_dim != head_dim || cached_theta != theta) {
+            for (uint32_t i = 0; i < half; ++i)
+                table[i] = std::pow(theta, -static_cast<float>(2 * i) / static_cast<float>(head_dim));
+            cached_dim = head_dim;
+            cached_theta = theta;
+        }
+        std::memcpy(inv_freq, table, half * sizeof(float));
+    } else if (rope_mode == B200KV_ROPE_SECTIONED64) {
+        if (step_theta != theta) {
+            cached_step = std::pow(theta, -2.0f / 64.0f);
+            step_theta = theta;
+        }
+        *sectioned_step = cached_step;
+    }
+}
+
 uint32_t* current_status_word() {
     int device = -1;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {

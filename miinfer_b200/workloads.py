@@ -119,7 +119,9 @@ def run_prefill(args, torch, dist, rank, world, local_rank):
     ws = None if args.prefill_kernel == "mma" else kv.prefill_workspace(P + T, hkv, D, token_count=T, query_heads=hq)
     # The fp16 copy of a layer's prefix does not depend on the chunk: with a second workspace and a second stream the
     # pre-pass of layer l + 1 runs beside the attention of layer l; a layer's own launch then converts only its chunk.
-    ahead = ws is not None and not getattr(args, "no_prepare_ahead", False) and LAYERS >= 2
+    # (Not with one kv head per GPU: a layer then takes about 50 us, which the extra stream and event calls of this eager
+    # loop exceed on the host -- 0.92 ms per chunk against 0.80.)
+    ahead = ws is not None and not getattr(args, "no_prepare_ahead", False) and LAYERS >= 2 and hkv >= 2
     ws2 = kv.prefill_workspace(P + T, hkv, D, token_count=T, query_heads=hq) if ahead else None
     stream = torch.cuda.Stream()
     side = torch.cuda.Stream() if ahead else None

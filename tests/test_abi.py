@@ -82,4 +82,13 @@ def test_launch_without_gpu_fails_loudly():
         pytest.skip("needs a machine without a GPU")
     v = View(0, 0, 16, 16, 16, 16, 8, 2, 128, 32, 3)
     assert lib.b200kv_append(C.byref(v), 16, 16, 0, None, 0, 1e6, 1e-6, 1, 0, None, None, None) == -4   # no device, no fallback
+    assert lib.b200kv_prefill_prepare(C.byref(v), 4, 8, 16, 1 << 20, None) == -4
+    assert lib.b200kv_prefill_attn_prepared(C.byref(v), 16, 0, None, 16, 4, 4, 8, 0.1, None, 16, 1 << 20, 4, None) == -4
     assert lib.b200kv_device_check(0) == -4
+    # the batched-launch plan is host arithmetic and works anywhere; bad arguments are refused
+    lengths = (C.c_uint32 * 3)(5000, 300, 9000)
+    splits, bound = C.c_uint32(0), C.c_uint32(0)
+    assert lib.b200kv_plan_batched_decode(lengths, 3, 8, 0, C.byref(splits), C.byref(bound)) == 0
+    assert splits.value >= 1 and bound.value >= 9000
+    assert lib.b200kv_plan_batched_decode(lengths, 3, 0, 0, C.byref(splits), C.byref(bound)) == -1
+    assert lib.b200kv_plan_batched_decode(None, 3, 8, 0, C.byref(splits), C.byref(bound)) == -1

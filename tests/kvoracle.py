@@ -261,6 +261,33 @@ def token_sequence_hash(tokens) -> int:
 
 
 # -- seeded synthetic inputs (fp16 N(0,1) activations, as the benchmark workloads use) ----------
+class StdNormalStream:
+    """std::mt19937(seed) feeding std::normal_distribution<float>(mean, stddev), drawn by the C++ standard library itself
+    (oracle/std_stream.cpp): the stream a C++ test sees."""
+
+    def __init__(self, seed: int, mean: float, stddev: float):
+        lib_path = ORACLE_DIR / "libstd_stream.so"
+        src = ORACLE_DIR / "std_stream.cpp"
+        if not lib_path.exists() or lib_path.stat().st_mtime < src.stat().st_mtime:
+            subprocess.run(["make", "-C", str(ORACLE_DIR), str(lib_path)], check=True, capture_output=True)
+        self._lib = C.CDLL(str(lib_path))
+        self._lib.std_stream_new.restype = C.c_void_p
+        self._lib.std_stream_new.argtypes = [C.c_uint, C.c_float, C.c_float]
+        self._lib.std_stream_fill.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+        self._lib.std_stream_free.argtypes = [C.c_void_p]
+        self._s = self._lib.std_stream_new(seed, mean, stddev)
+
+    def draw(self, count: int) -> np.ndarray:
+        out = np.empty(count, dtype=np.float32)
+        self._lib.std_stream_fill(self._s, _p(out), count)
+        return out
+
+    def __del__(self):
+        if getattr(self, "_s", None):
+            self._lib.std_stream_free(self._s)
+            self._s = None
+
+
 def normal_f16(rng: np.random.Generator, shape, std: float = 1.0) -> np.ndarray:
     """fp16 N(0, std) values as a float16 array (exactly representable inputs)."""
     return (rng.standard_normal(shape, dtype=np.float32) * std).astype(np.float16)

@@ -34,22 +34,31 @@ def metrics(ref: np.ndarray, test: np.ndarray) -> dict:
             "cos": float(r @ t / (np.sqrt(r @ r) * np.sqrt(t @ t) + 1e-12))}
 
 
-def run_cases(count: int):
-    """The first `count` cases in order (the stream runs on from one case into the next)."""
+def draw_cases(count: int):
+    """Inputs of the first `count` cases in order (the stream runs on from one case into the next):
+    (prefix, suffix, q [T][24][256], gate, k [P + T][4 * 256], v)."""
     stream = ko.StdNormalStream(42, 0.0, 0.5)
-    out = []
     for prefix, suffix in CASES[:count]:
-        total, capacity = prefix + suffix, prefix + suffix + 128
+        total = prefix + suffix
         q = stream.draw(suffix * HQ * D).reshape(suffix, HQ, D)
         gate = stream.draw(suffix * HQ * D).reshape(suffix, HQ, D)
         kv = stream.draw(HKV * total * 2 * D).reshape(HKV, total, 2, D)   # per head and position: K vector, then V vector
         k = np.ascontiguousarray(kv[:, :, 0, :].transpose(1, 0, 2)).reshape(total, HKV * D)
         v = np.ascontiguousarray(kv[:, :, 1, :].transpose(1, 0, 2)).reshape(total, HKV * D)
-        outputs = {}
-        for mode in (0, 1, 2, 3):   # fp16/fp16, q8 K, q8 V, q8 K and V; one scale per row
-            host = ko.HostCache(capacity, HKV, D, D, mode)
-            host.append(k, v, None, 0, rope_mode=0, quant_style=1)
-            outputs[mode] = host.suffix_splitk(q, gate, prefix, SCALE, num_splits=32)
+        yield prefix, suffix, q, gate, k, v
+
+
+def host_cache(prefix: int, suffix: int, k: np.ndarray, v: np.ndarray, mode: int):
+    """The test's cache of one mode (0 fp16/fp16, 1 q8 K, 2 q8 V, 3 q8 K and V; one scale per row, the test's quantiser)."""
+    host = ko.HostCache(prefix + suffix + 128, HKV, D, D, mode)
+    host.append(k, v, None, 0, rope_mode=0, quant_style=1)
+    return host
+
+
+def run_cases(count: int):
+    out = []
+    for prefix, suffix, q, gate, k, v in draw_cases(count):
+        outputs = {mode: host_cache(prefix, suffix, k, v, mode).suffix_splitk(q, gate, prefix, SCALE, num_splits=32) for mode in (0, 1, 2, 3)}
         out.append({"prefix": prefix, "suffix": suffix, "q8_k": metrics(outputs[0], outputs[1]),
                     "q8_v": metrics(outputs[0], outputs[2]), "q8_kv": metrics(outputs[0], outputs[3])})
     return out

@@ -298,3 +298,37 @@ def test_suffix_attention_over_a_prefix_converted_ahead_on_a_second_stream(cuda,
         kv.prepare_suffix_attention(sts[0].view(), P + T + 1, P + T, ws[0])
     with pytest.raises(kv.B200KvError):
         kv.prepare_suffix_attention(sts[0].view(), 16, P + T, torch.empty(1024, dtype=torch.uint8, device="cuda"))
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
+def test_quantized_suffix_errors_on_the_reference_recipe(cuda, kernel):
+    """The reference's quantized-attention test recipe (tests/qwen3_quant_kv_attention_test.cpp:79-154; the same
+    std::mt19937(42) stream, its host quantiser, fp16 against Q8-K+V caches) through the CUDA kernels: the error of
+    the quantised cache against the fp16 one must come out where the reference measured it on its own GPU kernels and
+    where the oracle puts it (tests/golden/quant_kv_attention_pin.json; first case: max-abs 0.001263, cosine
+    0.999973 in the reference's record)."""
+    import importlib.util
+    import json
+    from pathlib import Path
+
+    golden = Path(__file__).parent / "golden"
+    spec = importlib.util.spec_from_file_location("make_statistical_pin", golden / "make_statistical_pin.py")
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    want = json.loads((golden / "quant_kv_attention_pin.json").read_text())["cases"]
+    for case, (P, T, q, gate, k, v) in zip(want, gen.draw_cases(3)):
+        outs = {}
+        for mode in (0, 3):
+            st = upload(gen.host_cache(P, T, k, v, mode))
+            out = torch.full((T, 24, 256), float("nan"), device="cuda")
+            ws = kv.prefill_workspace(P + T, 4, 256, token_count=T, query_heads=24) if kernel == "tcgen05" else None
+            kv.launch_suffix_attention_quant(st.view(), to_dev(q), to_dev(gate), out, ws, T, P, query_heads=24, scale=1.0 / 16.0)
+            torch.cuda.synchronize()
+            outs[mode] = out.cpu().numpy()
+        got = gen.metrics(outs[0], outs[3])
+        ref = case["q8_kv"]
+        print(f"{kernel} P={P} T={T}: max-abs {got['max_abs']:.6f} (oracle {ref['max_abs']:.6f}), MAE {got['mae']:.6f} ({ref['mae']:.6f}), "
+              f"cos {got['cos']:.8f} ({ref['cos']:.8f})")
+        assert abs(got["max_abs"] - ref["max_abs"]) <= 0.05 * ref["max_abs"] + 2e-5
+        assert abs(got["mae"] - ref["mae"]) <= 0.05 * ref["mae"]
+        assert abs(got["cos"] - ref["cos"]) <= 3e-6
